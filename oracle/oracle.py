@@ -1,0 +1,281 @@
+"""CPU oracle for the fused norm / SwiGLU + FP8 e4m3 blockwise-quantisation path.
+
+TEST INFRASTRUCTURE ONLY.  This module restates, with torch CPU float32 ops, the
+PyTorch reference math that the upstream project (inclusionAI/linghe) uses as its
+own test oracle.  It is imported by the test-suite, by the smoke check and by the
+CPU-baseline leg of the benchmark -- never by the product path, which runs only
+hand-written CUDA and fails loudly when the CUDA library is missing.
+
+Parity pin: every function here is compared bit-for-bit (pure quantisers) or
+code-for-code (fused variants) against outputs of the upstream functions that were
+produced by importing the upstream Python on CPU; the vectors and the script that
+made them live in ``tests/golden/``.
+
+Each function cites the upstream file:line it follows (paths inside the upstream
+project).  Shapes / layouts returned are the *kernel* layouts (transposed row
+scales and so on), so tests compare buffers directly.
+"""
+
+from __future__ import annotations
+
+import torch
+
+E4M3_MAX = 448.0
+SCALE_FLOOR = 1e-30
+BLOCK = 128
+
+
+# --------------------------------------------------------------------------- #
+# quantisation primitives
+# --------------------------------------------------------------------------- #
+def _pow2_ceil(scale: torch.Tensor) -> torch.Tensor:
+    """exp2(ceil(log2(s))) in float32 -- linghe/tools/util.py:61-62."""
+    return torch.exp2(torch.ceil(torch.log2(scale)))
+
+
+def quant_rows_1x128(v: torch.Tensor, round_scale: bool = False):
+    """Quantise every 1x128 block along the last dim of a 2-D float matrix.
+
+    Follows ``torch_group_quant`` (linghe/tools/util.py:46-66): the last dim is
+    zero-padded to a multiple of 128, scale = max(amax/448, 1e-30) in float32,
+    optional power-of-two round-up, code = e4m3fn(v / scale) with IEEE division
+    and round-to-nearest-even.  Returns (codes [M,K] e4m3fn, scales [M, ceil(K/128)]).
+    """
+    assert v.dim() == 2
+    m, k = v.shape
+    v = v.float()
+    pad = (-k) % BLOCK
+    if pad:
+        v = torch.nn.functional.pad(v, (0, pad))
+    blocks = v.contiguous().view(m, (k + pad) // BLOCK, BLOCK)
+    scale = blocks.abs().amax(dim=2) / E4M3_MAX
+    scale = torch.clamp_min(scale, SCALE_FLOOR)
+    if round_scale:
+        scale = _pow2_ceil(scale)
+    codes = (blocks / scale.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    codes = codes.view(m, k + pad)[:, :k].contiguous()
+    return codes, scale
+
+
+def blockwise_quant(x: torch.Tensor, round_scale: bool = False):
+    """Dual-axis activation quantiser (1x128 rows + 128x1 columns).
+
+    Follows ``torch_blockwise_quant`` (linghe/tools/util.py:69-82, padding=False) and
+    the kernel layouts of ``triton_blockwise_quant`` (linghe/quant/block.py:129-170):
+    returns (q [M,N], s [N/128, M], qT [N, M], sT [ceil(M/128), N]).
+    """
+    x = x.float()
+    q, s = quant_rows_1x128(x, round_scale)
+    qt, st = quant_rows_1x128(x.t(), round_scale)
+    return q, s.t().contiguous(), qt, st.t().contiguous()
+
+
+def group_quant(x: torch.Tensor, round_scale: bool = False):
+    """Row-only 1x128 quantiser with untransposed scales [M, N/128].
+
+    linghe/tools/util.py:46-66 as used by tests/test_group_quant.py:14-32 and the
+    layout of ``triton_group_quant`` (linghe/quant/group.py:40-63).
+    """
+    return quant_rows_1x128(x.float(), round_scale)
+
+
+def block_quant(w: torch.Tensor, round_scale: bool = False):
+    """128x128 2-D block quantiser for weights; one scale per block, no floor.
+
+    Follows ``torch_block_quant`` (linghe/tools/util.py:85-98).  Returns
+    (codes [N,K], scales [N/128, K/128]).
+    """
+    n, k = w.shape
+    assert n % BLOCK == 0 and k % BLOCK == 0
+    tiles = w.view(n // BLOCK, BLOCK, k // BLOCK, BLOCK).permute(0, 2, 1, 3)
+    scale = tiles.abs().float().amax(dim=(2, 3)) / E4M3_MAX
+    if round_scale:
+        scale = _pow2_ceil(scale)
+    codes = (tiles / scale[:, :, None, None]).to(torch.float8_e4m3fn)
+    codes = codes.permute(0, 2, 1, 3).reshape(n, k).contiguous()
+    return codes, scale
+
+
+def batch_blockwise_quant(x: torch.Tensor, counts, round_scale: bool = False):
+    """Per-expert dual-axis quantiser with flat packed outputs.
+
+    Follows ``torch_batch_blockwise_quant`` (tests/test_blockwise_quant.py:17-43) and
+    the packing of ``triton_batch_blockwise_quant`` (linghe/quant/block.py:251-297):
+    for expert e (rows [S_e, S_e+c_e)) the flat outputs hold q [c_e,N], s [N/128,c_e],
+    qT [N,c_e], sT [ceil(c_e/128),N] back to back.
+    Returns flat tensors (q, s, qT, sT).
+    """
+    counts = [int(c) for c in counts]
+    qs, ss, qts, sts = [], [], [], []
+    start = 0
+    for c in counts:
+        if c == 0:
+            continue
+        q, s, qt, st = blockwise_quant(x[start:start + c], round_scale)
+        qs.append(q.reshape(-1))
+        ss.append(s.reshape(-1))
+        qts.append(qt.reshape(-1))
+        sts.append(st.reshape(-1))
+        start += c
+    if not qs:
+        e = torch.empty(0)
+        return (e.to(torch.float8_e4m3fn), e.float(), e.to(torch.float8_e4m3fn), e.float())
+    return torch.cat(qs), torch.cat(ss), torch.cat(qts), torch.cat(sts)
+
+
+# --------------------------------------------------------------------------- #
+# RMSNorm
+# --------------------------------------------------------------------------- #
+def rms_recip(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """r = rsqrt(sum(x^2)/n + eps) per row -- tests/test_norm.py:80."""
+    x = x.float()
+    return torch.rsqrt(torch.sum(x * x, dim=1) / x.shape[1] + eps)
+
+
+def _rms_norm_f32(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """float32 RMSNorm through torch.nn.functional.rms_norm, the same operator
+    ``torch.nn.RMSNorm`` dispatches to in tests/test_norm.py:22-32,70-79
+    (numerically (x * r) * gamma)."""
+    x = x.float()
+    return torch.nn.functional.rms_norm(x, (x.shape[-1],), weight.float(), eps)
+
+
+def rms_norm_forward(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6):
+    """Plain RMSNorm, output in x.dtype -- ``torch_rms_forward`` tests/test_norm.py:22-32."""
+    return _rms_norm_f32(x, weight, eps).to(x.dtype)
+
+
+def rms_norm_backward(x: torch.Tensor, weight: torch.Tensor, dy: torch.Tensor, eps: float = 1e-6):
+    """RMSNorm backward by autograd in float32 -- ``torch_rms_backward``
+    tests/test_norm.py:35-49.  Returns (dx in x.dtype, dgamma float32)."""
+    xf = x.float().clone().requires_grad_()
+    wf = weight.float().clone().requires_grad_()
+    y = torch.nn.functional.rms_norm(xf, (xf.shape[-1],), wf, eps)
+    y.backward(dy.float())
+    return xf.grad.to(x.dtype), wf.grad
+
+
+def rms_norm_and_block_quant_forward(x, weight, eps: float = 1e-6, round_scale: bool = False):
+    """RMSNorm then dual-axis quantisation of the float32 result.
+
+    Follows ``torch_rms_and_block_quant_forward`` (tests/test_norm.py:70-84) with the
+    output layouts of ``triton_rms_norm_and_block_quant_forward``
+    (linghe/utils/norm.py:343-502): (q [M,n], s [n/128,M], r [M], qT [n,M],
+    sT [ceil(M/128), n]).
+    """
+    y = _rms_norm_f32(x, weight, eps)
+    q, s, qt, st = blockwise_quant(y, round_scale)
+    return q, s, rms_recip(x, eps), qt, st
+
+
+# --------------------------------------------------------------------------- #
+# SwiGLU (dense)
+# --------------------------------------------------------------------------- #
+def _swiglu_f32(x: torch.Tensor, weight: torch.Tensor | None = None) -> torch.Tensor:
+    """y = sigmoid(x1) * x1 * x2 [* w_row], x1/x2 the left/right column halves.
+    tests/test_silu.py:29-43."""
+    x = x.float()
+    x1, x2 = x.chunk(2, dim=1)
+    y = torch.sigmoid(x1) * x1 * x2
+    if weight is not None:
+        y = y * weight.float().view(-1, 1)
+    return y
+
+
+def weighted_silu_forward(x, weight=None):
+    """bf16 SwiGLU with optional per-row weight -- ``torch_weighted_silu``
+    tests/test_silu.py:36-43."""
+    return _swiglu_f32(x, weight).to(x.dtype)
+
+
+def weighted_silu_backward(dy, x, weight=None):
+    """autograd of the above -- ``torch_weighted_silu_backward`` tests/test_silu.py:46-53.
+    Returns (dx float32, dw float32 or None); callers cast as needed."""
+    xf = x.float().clone().requires_grad_()
+    wf = None if weight is None else weight.float().clone().requires_grad_()
+    y = _swiglu_f32(xf, wf)
+    y.backward(dy.float())
+    return xf.grad, (None if wf is None else wf.grad)
+
+
+def silu_and_block_quant_forward(x, round_scale: bool = False):
+    """SwiGLU then dual-axis quantisation -- ``torch_silu_and_block_quant_forward``
+    tests/test_silu.py:75-84; layouts of ``triton_silu_and_block_quant_forward``
+    (linghe/utils/silu.py:279-335): (q [M,n], s [n/128,M], qT [n,M], sT [ceil(M/128),n])."""
+    return blockwise_quant(_swiglu_f32(x), round_scale)
+
+
+def silu_and_block_quant_backward(g, x, round_scale: bool = False):
+    """SwiGLU backward (autograd, float32) then dual-axis quantisation of dx [M,2n].
+
+    ``torch_silu_and_block_quant_backward`` tests/test_silu.py:113-123; layouts of
+    ``triton_silu_and_block_quant_backward`` (linghe/utils/silu.py:424-465).
+    Returns (dx_q [M,2n], dx_s [2n/128,M], dxT_q [2n,M], dxT_s [M/128,2n], dx float32).
+    """
+    dx, _ = weighted_silu_backward(g, x, None)
+    q, s, qt, st = blockwise_quant(dx, round_scale)
+    return q, s, qt, st, dx
+
+
+# --------------------------------------------------------------------------- #
+# SwiGLU (per-expert batched)
+# --------------------------------------------------------------------------- #
+def _pack_segments(y: torch.Tensor, counts, round_scale: bool):
+    """Quantise each expert segment separately and pack like the kernels do:
+    q row-major global; per expert s [nb,c] / qT [n,c] / sT [ceil(c/128),n] flattened
+    and concatenated (tests/test_silu.py:180-198)."""
+    qs, ss, qts, sts = [], [], [], []
+    start = 0
+    for c in counts:
+        seg = y[start:start + c]
+        q, s, qt, st = blockwise_quant(seg, round_scale)
+        qs.append(q)
+        ss.append(s.reshape(-1))
+        qts.append(qt.reshape(-1))
+        sts.append(st.reshape(-1))
+        start += c
+    return torch.cat(qs, 0), torch.cat(ss), torch.cat(qts), torch.cat(sts)
+
+
+def batch_weighted_silu_and_block_quant_forward(x, weight, counts, round_scale: bool = False):
+    """Per-expert weighted SwiGLU + dual quant --
+    ``torch_batch_weighted_silu_and_block_quant_forward`` tests/test_silu.py:163-199.
+    Returns (q [R,n], s flat, qT flat, sT flat)."""
+    counts = [int(c) for c in counts]
+    n = x.shape[1] // 2
+    if sum(counts) == 0:
+        return (torch.empty((0, n), dtype=torch.float8_e4m3fn), torch.empty(0),
+                torch.empty(0, dtype=torch.float8_e4m3fn), torch.empty(0))
+    y = _swiglu_f32(x, weight)
+    return _pack_segments(y, counts, round_scale)
+
+
+def batch_weighted_silu_and_block_quant_backward(g, x, weight, counts, round_scale: bool = False):
+    """Per-expert weighted SwiGLU backward + dual quant of dx --
+    ``torch_batch_weighted_silu_and_block_quant_backward`` tests/test_silu.py:260-296.
+    Returns (dx_q [R,2n], dx_s flat, dw [R,1] float32, dxT_q flat, dxT_s flat)."""
+    counts = [int(c) for c in counts]
+    two_n = x.shape[1]
+    if sum(counts) == 0:
+        return (torch.empty((0, two_n), dtype=torch.float8_e4m3fn), torch.empty(0),
+                torch.empty_like(weight, dtype=torch.float32),
+                torch.empty(0, dtype=torch.float8_e4m3fn), torch.empty(0))
+    dx, dw = weighted_silu_backward(g, x, weight)
+    q, s, qt, st = _pack_segments(dx, counts, round_scale)
+    return q, s, dw.view(weight.shape), qt, st
+
+
+# --------------------------------------------------------------------------- #
+# helpers for large shapes
+# --------------------------------------------------------------------------- #
+def chunked(fn, row_args, other_args=(), rows_per_chunk: int = 4096, **kw):
+    """Run a row-local oracle ``fn(*row_args_chunk, *other_args, **kw)`` over
+    128-row-aligned chunks and return the list of per-chunk results.  Exact for
+    1x128 and 128x1 blocks because chunk boundaries are multiples of 128 rows."""
+    assert rows_per_chunk % BLOCK == 0
+    m = row_args[0].shape[0]
+    out = []
+    for r0 in range(0, m, rows_per_chunk):
+        sl = [a[r0:r0 + rows_per_chunk] for a in row_args]
+        out.append(fn(*sl, *other_args, **kw))
+    return out

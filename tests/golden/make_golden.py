@@ -1,0 +1,163 @@
+"""Generate golden vectors by running the UPSTREAM PyTorch reference math on CPU.
+
+Run once, in a container that has the upstream checkout (read-only) available:
+
+    python tests/golden/make_golden.py --reference /path/to/linghe
+
+It imports the upstream oracle functions (linghe/tools/util.py and the helper
+functions inside upstream tests/test_norm.py, tests/test_silu.py,
+tests/test_blockwise_quant.py), feeds them small seeded inputs and stores inputs and
+outputs as raw integer views in ``tests/golden/*.npz``.  The repository's own oracle
+(``oracle/oracle.py``) and CUDA kernels are then checked against these files without
+needing the upstream checkout.
+"""
+
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def u16(t):  # bf16 -> raw bits
+    return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def u8(t):  # fp8 -> raw bits
+    return t.contiguous().view(torch.uint8).numpy()
+
+
+def f32(t):
+    return t.detach().contiguous().float().numpy()
+
+
+def bf16_randn(gen, shape, power=1, coef=1.0):
+    x = torch.randn(shape, generator=gen, dtype=torch.float32)
+    if power != 1:
+        x = x ** power
+    return (x * coef).to(torch.bfloat16)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+    sys.path.insert(0, os.path.join(args.reference, "tests"))
+    from linghe.tools import util as U
+    import test_norm as TN
+    import test_silu as TS
+    import test_blockwise_quant as TB
+
+    gen = torch.Generator().manual_seed(20240607)
+
+    # ---- pure quantisers --------------------------------------------------- #
+    out = {}
+    for tag, power in (("n1", 1), ("n3", 3)):
+        x = bf16_randn(gen, (144, 256), power)
+        x[5, 128:256] = 0  # an all-zero 1x128 block -> scale floor
+        x[:, 200] = 0      # an all-zero column
+        out[f"x_{tag}"] = u16(x)
+        for rs in (False, True):
+            q, s = U.torch_group_quant(x, round_scale=rs)
+            out[f"group_{tag}_r{int(rs)}_q"] = u8(q)
+            out[f"group_{tag}_r{int(rs)}_s"] = f32(s)
+            q, s, qt, st = U.torch_blockwise_quant(x, round_scale=rs, padding=False)
+            for k, v in (("q", u8(q)), ("s", f32(s)), ("qt", u8(qt)), ("st", f32(st))):
+                out[f"blockwise_{tag}_r{int(rs)}_{k}"] = v
+    xf = torch.randn((48, 256), generator=gen, dtype=torch.float32) * 7.5
+    out["x_f32"] = xf.numpy()
+    q, s, qt, st = U.torch_blockwise_quant(xf, round_scale=False, padding=False)
+    for k, v in (("q", u8(q)), ("s", f32(s)), ("qt", u8(qt)), ("st", f32(st))):
+        out[f"blockwise_f32_r0_{k}"] = v
+    w = bf16_randn(gen, (128, 256), 3)
+    out["w"] = u16(w)
+    for rs in (False, True):
+        q, s = U.torch_block_quant(w, round_scale=rs)
+        out[f"block_r{int(rs)}_q"] = u8(q)
+        out[f"block_r{int(rs)}_s"] = f32(s)
+    counts = [0, 48, 130, 7, 128, 0, 16]
+    xb = bf16_randn(gen, (sum(counts), 128))
+    out["xb"] = u16(xb)
+    out["xb_counts"] = np.asarray(counts, dtype=np.int64)
+    for rs in (False, True):
+        q, s, qt, st = TB.torch_batch_blockwise_quant(xb, counts, round_scale=rs)
+        for k, v in (("q", u8(q)), ("s", f32(s)), ("qt", u8(qt)), ("st", f32(st))):
+            out[f"batchq_r{int(rs)}_{k}"] = v
+    np.savez_compressed(os.path.join(HERE, "quant.npz"), **out)
+
+    # ---- RMSNorm ----------------------------------------------------------- #
+    out = {}
+    for tag, power in (("n1", 1), ("n2", 2)):
+        x = bf16_randn(gen, (144, 256), power)
+        g = (1 + 0.1 * torch.randn(256, generator=gen)).to(torch.bfloat16) if tag == "n1" \
+            else bf16_randn(gen, (256,))
+        out[f"x_{tag}"] = u16(x)
+        out[f"gamma_{tag}"] = u16(g)
+        for rs in (False, True):
+            q, s, r, qt, st = TN.torch_rms_and_block_quant_forward(x, g, round_scale=rs)
+            for k, v in (("q", u8(q)), ("s", f32(s)), ("r", f32(r)), ("qt", u8(qt)), ("st", f32(st))):
+                out[f"rmsq_{tag}_r{int(rs)}_{k}"] = v
+        out[f"rmsfwd_{tag}_y"] = u16(TN.torch_rms_forward(x, g))
+        dy = bf16_randn(gen, (144, 256), 1, 0.01)
+        out[f"dy_{tag}"] = u16(dy)
+        dx, dw = TN.torch_rms_backward(x, g, dy)
+        out[f"rmsbwd_{tag}_dx"] = u16(dx)
+        out[f"rmsbwd_{tag}_dw"] = u16(dw)
+    np.savez_compressed(os.path.join(HERE, "norm.npz"), **out)
+
+    # ---- SwiGLU dense ------------------------------------------------------ #
+    out = {}
+    for tag, coef, gcoef in (("c1", 1.0, 1.0), ("c100", 100.0, 100.0), ("c0", 0.0, 0.0)):
+        x = bf16_randn(gen, (128, 512), 1, coef)
+        g = bf16_randn(gen, (128, 256), 1, gcoef)
+        out[f"x_{tag}"] = u16(x)
+        out[f"g_{tag}"] = u16(g)
+        for rs in ((False, True) if tag == "c1" else (False,)):
+            q, s, qt, st = TS.torch_silu_and_block_quant_forward(x, round_scale=rs)
+            # upstream returns scales untransposed here; store kernel layout
+            for k, v in (("q", u8(q)), ("s", f32(s.t())), ("qt", u8(qt)), ("st", f32(st.t()))):
+                out[f"silufwd_{tag}_r{int(rs)}_{k}"] = v
+            q, s, qt, st = TS.torch_silu_and_block_quant_backward(g, x, round_scale=rs)
+            for k, v in (("q", u8(q)), ("s", f32(s.t())), ("qt", u8(qt)), ("st", f32(st.t()))):
+                out[f"silubwd_{tag}_r{int(rs)}_{k}"] = v
+        wrow = torch.randn((128, 1), generator=gen, dtype=torch.float32)
+        out[f"wrow_{tag}"] = wrow.numpy()
+        out[f"wsilu_{tag}_y"] = u16(TS.torch_weighted_silu(x, wrow))
+        dxw, dww = TS.torch_weighted_silu_backward(g.float(), x, wrow)
+        out[f"wsilubwd_{tag}_dx"] = u16(dxw)
+        out[f"wsilubwd_{tag}_dw"] = f32(dww)
+    np.savez_compressed(os.path.join(HERE, "silu.npz"), **out)
+
+    # ---- SwiGLU per-expert batched ---------------------------------------- #
+    out = {}
+    counts = [0, 32, 144, 16, 128, 0, 48]
+    R = sum(counts)
+    for tag, coef, gcoef in (("c1", 1.0, 1.0), ("c100", 100.0, 100.0)):
+        x = bf16_randn(gen, (R, 256), 1, coef)
+        x[:3] = 0
+        wrow = torch.randn((R, 1), generator=gen, dtype=torch.float32)
+        g = bf16_randn(gen, (R, 128), 1, gcoef)
+        out[f"x_{tag}"] = u16(x)
+        out[f"w_{tag}"] = wrow.numpy()
+        out[f"g_{tag}"] = u16(g)
+        ct = torch.tensor(counts, dtype=torch.int32)
+        q, s, qt, st = TS.torch_batch_weighted_silu_and_block_quant_forward(x, wrow, ct, round_scale=False)
+        for k, v in (("q", u8(q)), ("s", f32(s)), ("qt", u8(qt)), ("st", f32(st))):
+            out[f"bfwd_{tag}_{k}"] = v
+        q, s, dw, qt, st = TS.torch_batch_weighted_silu_and_block_quant_backward(
+            g, x, wrow, counts, round_scale=False)
+        for k, v in (("q", u8(q)), ("s", f32(s)), ("dw", f32(dw)), ("qt", u8(qt)), ("st", f32(st))):
+            out[f"bbwd_{tag}_{k}"] = v
+    out["counts"] = np.asarray(counts, dtype=np.int64)
+    np.savez_compressed(os.path.join(HERE, "batch.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch"):
+        p = os.path.join(HERE, f + ".npz")
+        print(p, os.path.getsize(p))
+
+
+if __name__ == "__main__":
+    main()
