@@ -1,0 +1,172 @@
+/*
+ * linghe_b200 -- C ABI of the sm_100a fused norm / SwiGLU + FP8 e4m3 blockwise
+ * quantisation kernels.
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no framework types.  Each
+ * entry point replaces one host wrapper of the upstream Python/Triton library
+ * (inclusionAI/linghe, paths below are inside that project) and keeps its tensor and
+ * scale layouts byte for byte.
+ *
+ * Conventions
+ *   - All pointers are device pointers on the current CUDA device unless said
+ *     otherwise; `stream` is a cudaStream_t (NULL = legacy default stream).
+ *   - Work is enqueued asynchronously; no entry point synchronises or allocates,
+ *     except where stated.  Scratch memory, when needed, is passed in by the caller.
+ *   - Return value: 0 = enqueued; LH_ERR_ARG (<0) = rejected arguments (nothing was
+ *     launched); >0 = a cudaError_t from the launch.  lh_last_error() returns a
+ *     thread-local message for the last non-zero return.
+ *   - `dtype`: element type of the floating-point inputs (LH_BF16 / LH_F16 / LH_F32).
+ *     Fused entry points accept LH_BF16 only; the pure quantisers accept all three.
+ *   - fp8 outputs are e4m3fn codes (1 byte each); scales are float32 dequantisation
+ *     multipliers: scale = max(amax/448, 1e-30), optionally rounded up to a power of 2.
+ *   - `output_mode`: 0 = row-wise (1x128) outputs only, 1 = column-wise (128x1,
+ *     transposed) outputs only, 2 = both.  Pointers of outputs a mode does not write
+ *     may be NULL.
+ *   - Layouts (nb = n/128, i row, j column, b = j/128, I = i/128):
+ *       q  [M,n]            offset i*n + j
+ *       s  [nb,M]           offset b*M + i            (row scales, transposed)
+ *       qT [n,M]            offset j*M + i
+ *       sT [ceil(M/128),n]  offset I*n + j
+ *     Per-expert (batched) entry points pack, for expert e with c_e rows starting at
+ *     row S_e and B_e = sum_{e'<e} ceil(c_e'/128):
+ *       q  offset (S_e+t)*n + j
+ *       s  offset S_e*nb + b*c_e + t
+ *       qT offset S_e*n + j*c_e + t
+ *       sT offset (B_e + t/128)*n + j
+ */
+#ifndef LINGHE_B200_H_
+#define LINGHE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LH_VERSION 100
+
+#define LH_OK 0
+#define LH_ERR_ARG (-1)
+
+enum { LH_BF16 = 0, LH_F16 = 1, LH_F32 = 2 };
+enum { LH_I32 = 0, LH_I64 = 1 };
+
+/* Library version (LH_VERSION of the build). */
+int lh_version(void);
+
+/* Message for the last non-zero return on this thread ("" if none). */
+const char* lh_last_error(void);
+
+/* 0 if `device` is an sm_100 GPU these kernels can run on, LH_ERR_ARG otherwise. */
+int lh_device_check(int device);
+
+/* Copies the device status word of the current device to *status (0 = no kernel ever
+ * gave up on a bounded wait) and clears it.  Synchronises the device. */
+int lh_device_status(int* status);
+
+/* Scratch bytes needed by the entry point named `what` ("rmsnorm_bwd",
+ * "batch_silu_bwd") for the given sizes; 0 if it needs none, <0 if unknown. */
+int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols);
+
+/* ---- pure quantisers (bit-exact against the PyTorch reference math) ------------ */
+
+/* Dual-axis activation quantiser.
+ * Replaces triton_blockwise_quant, linghe/quant/block.py:129.
+ * x [M,N] contiguous, N % 128 == 0. */
+int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, void* qt,
+                       float* st, int round_scale, int output_mode, void* stream);
+
+/* Row-only 1x128 quantiser with untransposed scales s [M, N/128].
+ * Replaces triton_group_quant, linghe/quant/group.py:40. */
+int lh_group_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
+                   void* stream);
+
+/* 128x128 2-D block quantiser for weights, s [M/128, N/128], no scale floor in the
+ * reference oracle but the kernel floors at 1e-30 like the upstream kernel.
+ * Replaces triton_block_quant, linghe/quant/block.py:32.  M,N multiples of 128. */
+int lh_block_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
+                   void* stream);
+
+/* Per-expert dual-axis quantiser with packed outputs.
+ * Replaces triton_batch_blockwise_quant, linghe/quant/block.py:251.
+ * counts: device array of E row counts (LH_I32 / LH_I64); R = total rows. */
+int lh_batch_blockwise_quant(const void* x, int dtype, const void* counts, int counts_type, int E,
+                             int64_t R, int64_t N, void* q, float* s, void* qt, float* st,
+                             int round_scale, void* stream);
+
+/* ---- RMSNorm ------------------------------------------------------------------- */
+
+/* y = (x * r) * gamma in the input dtype, r = rsqrt(mean(x^2) + eps) per row.
+ * Replaces triton_rms_norm_forward, linghe/utils/norm.py:58.
+ * reuse_rms != 0: read r from `rms` instead of computing (and do not write it). */
+int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
+                   float* rms, int reuse_rms, void* stream);
+
+/* RMSNorm + blockwise quantisation.
+ * Replaces triton_rms_norm_and_block_quant_forward, linghe/utils/norm.py:343.
+ * mode 0: writes q, s, rms.  mode 1: reads rms, writes qT, sT.  mode 2: writes all. */
+int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps,
+                              void* q, float* s, float* rms, void* qt, float* st, int round_scale,
+                              int output_mode, void* stream);
+
+/* RMSNorm backward: dx (input dtype) and dgamma (float32 [n]).
+ * Replaces triton_rms_norm_backward, linghe/utils/norm.py:144.
+ * rms may be NULL (recomputed).  scratch: lh_scratch_bytes("rmsnorm_bwd", M, n) bytes. */
+int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
+                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
+                   void* stream);
+
+/* RMSNorm backward fused with the dual-axis quantisation of dy (the copies the
+ * neighbouring linear layer's dgrad / wgrad GEMMs consume).  Upstream runs
+ * triton_rms_norm_backward (linghe/utils/norm.py:144) and triton_blockwise_quant
+ * (linghe/quant/block.py:129) as separate passes over dy. */
+int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, const float* rms, int dtype,
+                              int64_t M, int64_t n, float eps, void* dx, float* dgamma, void* dy_q,
+                              float* dy_s, void* dy_qt, float* dy_st, int round_scale, void* scratch,
+                              int64_t scratch_bytes, void* stream);
+
+/* ---- SwiGLU (dense) ------------------------------------------------------------ */
+
+/* y = x1*sigmoid(x1)*x2 [* w_row] in the input dtype; x [M,2n], x1 = x[:, :n].
+ * Replaces triton_weighted_silu_forward, linghe/utils/silu.py:98.
+ * w: optional per-row weight (NULL = none), w_dtype LH_F32 or LH_BF16. */
+int lh_weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,
+                         void* stream);
+
+/* Backward of the above: dx [M,2n] input dtype, dw [M] in w_dtype (when w != NULL).
+ * Replaces triton_weighted_silu_backward, linghe/utils/silu.py:177. */
+int lh_weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M,
+                         int64_t n, void* dx, void* dw, void* stream);
+
+/* SwiGLU + blockwise quantisation.
+ * Replaces triton_silu_and_block_quant_forward, linghe/utils/silu.py:279. */
+int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, void* qt,
+                           float* st, int round_scale, int output_mode, void* stream);
+
+/* SwiGLU backward + blockwise quantisation of dx = [dx1 | dx2]  ([M,2n]).
+ * Replaces triton_silu_and_block_quant_backward, linghe/utils/silu.py:424.
+ * dx_hp: optional [M,2n] copy of dx in the input dtype (NULL = none); upstream gets it
+ * from a separate triton_weighted_silu_backward pass (linghe/utils/silu.py:177). */
+int lh_silu_blockquant_bwd(const void* g, const void* x, int dtype, int64_t M, int64_t n, void* dx_q,
+                           float* dx_s, void* dx_qt, float* dx_st, void* dx_hp, int round_scale,
+                           void* stream);
+
+/* ---- SwiGLU (per-expert batched, routed experts) ------------------------------- */
+
+/* Replaces triton_batch_weighted_silu_and_block_quant_forward, linghe/utils/silu.py:797.
+ * x [R,2n]; w [R] per-row weight (w_dtype LH_F32 / LH_BF16); counts [E] device. */
+int lh_batch_silu_blockquant_fwd(const void* x, const void* w, int dtype, int w_dtype, const void* counts,
+                                 int counts_type, int E, int64_t R, int64_t n, void* q, float* s, void* qt,
+                                 float* st, int round_scale, int output_mode, void* stream);
+
+/* Replaces triton_batch_weighted_silu_and_block_quant_backward, linghe/utils/silu.py:1293.
+ * dw [R] in w_dtype.  scratch: lh_scratch_bytes("batch_silu_bwd", R, n) bytes. */
+int lh_batch_silu_blockquant_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype,
+                                 const void* counts, int counts_type, int E, int64_t R, int64_t n,
+                                 void* dx_q, float* dx_s, void* dw, void* dx_qt, float* dx_st,
+                                 int round_scale, void* scratch, int64_t scratch_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LINGHE_B200_H_ */

@@ -1,0 +1,146 @@
+"""ctypes binding of the C ABI declared in include/linghe_b200.h.
+
+The shared library is built in-tree by ``python -m linghe_b200.build``.  Loading fails
+loudly when it is missing: there is no CPU or PyTorch fallback behind these entry points.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("LINGHE_B200_LIB", os.path.join(_HERE, "lib", "liblinghe_b200.so"))
+
+LH_ERR_ARG = -1
+BF16, F16, F32 = 0, 1, 2
+I32, I64 = 0, 1
+
+_DTYPES = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
+_ITYPES = {torch.int32: I32, torch.int64: I64}
+
+_p = ctypes.c_void_p
+_i = ctypes.c_int
+_l = ctypes.c_int64
+_f = ctypes.c_float
+
+# name -> (restype, argtypes); mirrors include/linghe_b200.h one to one
+SIGNATURES = {
+    "lh_version": (_i, []),
+    "lh_last_error": (ctypes.c_char_p, []),
+    "lh_device_check": (_i, [_i]),
+    "lh_device_status": (_i, [ctypes.POINTER(_i)]),
+    "lh_scratch_bytes": (_l, [ctypes.c_char_p, _l, _l]),
+    "lh_blockwise_quant": (_i, [_p, _i, _l, _l, _p, _p, _p, _p, _i, _i, _p]),
+    "lh_group_quant": (_i, [_p, _i, _l, _l, _p, _p, _i, _p]),
+    "lh_block_quant": (_i, [_p, _i, _l, _l, _p, _p, _i, _p]),
+    "lh_batch_blockwise_quant": (_i, [_p, _i, _p, _i, _i, _l, _l, _p, _p, _p, _p, _i, _p]),
+    "lh_rmsnorm_fwd": (_i, [_p, _p, _i, _l, _l, _f, _p, _p, _i, _p]),
+    "lh_rmsnorm_blockquant_fwd": (_i, [_p, _p, _i, _l, _l, _f, _p, _p, _p, _p, _p, _i, _i, _p]),
+    "lh_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _l, _p]),
+    "lh_rmsnorm_bwd_blockquant": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _p, _p, _p, _i, _p, _l, _p]),
+    "lh_weighted_silu_fwd": (_i, [_p, _p, _i, _i, _l, _l, _p, _p]),
+    "lh_weighted_silu_bwd": (_i, [_p, _p, _p, _i, _i, _l, _l, _p, _p, _p]),
+    "lh_silu_blockquant_fwd": (_i, [_p, _i, _l, _l, _p, _p, _p, _p, _i, _i, _p]),
+    "lh_silu_blockquant_bwd": (_i, [_p, _p, _i, _l, _l, _p, _p, _p, _p, _p, _i, _p]),
+    "lh_batch_silu_blockquant_fwd": (_i, [_p, _p, _i, _i, _p, _i, _i, _l, _l, _p, _p, _p, _p, _i, _i, _p]),
+    "lh_batch_silu_blockquant_bwd": (_i, [_p, _p, _p, _i, _i, _p, _i, _i, _l, _l, _p, _p, _p, _p, _p, _i, _p, _l, _p]),
+}
+
+_lock = threading.Lock()
+_lib = None
+_checked_devices = set()
+
+
+def load() -> ctypes.CDLL:
+    """Load (once) and return the shared library with argument types declared."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"linghe_b200: CUDA library not found at {LIB_PATH}. Build it with "
+                "`python -m linghe_b200.build` (needs nvcc; targets sm_100a only). "
+                "There is no CPU fallback.")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the header and the build disagree
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    return load().lh_last_error().decode()
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise AssertionError(f"unsupported dtype {t.dtype}") from None
+
+
+def itype_code(t: torch.Tensor) -> int:
+    try:
+        return _ITYPES[t.dtype]
+    except KeyError:
+        raise AssertionError(f"counts must be int32 or int64, got {t.dtype}") from None
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _check_device(dev: torch.device):
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    if idx in _checked_devices:
+        return
+    rc = load().lh_device_check(idx)
+    if rc != 0:
+        raise RuntimeError(f"linghe_b200: {last_error()}")
+    _checked_devices.add(idx)
+
+
+def call(name: str, ref: torch.Tensor, *args):
+    """Invoke entry point `name` on the device and current stream of tensor `ref`.
+
+    Argument errors raise AssertionError (the upstream wrappers use bare asserts);
+    CUDA launch errors raise RuntimeError."""
+    if not ref.is_cuda:
+        raise RuntimeError("linghe_b200 runs on CUDA tensors only (no CPU fallback)")
+    lib = load()
+    _check_device(ref.device)
+    with torch.cuda.device(ref.device):
+        stream = torch.cuda.current_stream().cuda_stream
+        rc = getattr(lib, name)(*args, stream)
+    if rc == 0:
+        return
+    msg = lib.lh_last_error().decode()
+    if rc == LH_ERR_ARG:
+        raise AssertionError(msg)
+    raise RuntimeError(f"linghe_b200 {name}: CUDA error {rc}: {msg}")
+
+
+def scratch_bytes(what: str, rows: int, cols: int) -> int:
+    v = load().lh_scratch_bytes(what.encode(), rows, cols)
+    if v < 0:
+        raise RuntimeError(f"unknown scratch kind {what}")
+    return v
+
+
+def device_status(device=None) -> int:
+    """Read-and-clear the device status word (synchronises).  0 = no kernel gave up a wait."""
+    out = ctypes.c_int(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        rc = load().lh_device_status(ctypes.byref(out))
+    if rc != 0:
+        raise RuntimeError(last_error())
+    return out.value

@@ -1,0 +1,253 @@
+// C ABI of the library: argument validation, error reporting and dispatch to the kernel
+// launchers.  Nothing here allocates device memory or synchronises (lh_device_status
+// excepted, which reads a word back).
+#include "lh_common.cuh"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+namespace lh {
+
+__device__ int g_device_status = 0;
+
+static thread_local char tl_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+    va_end(ap);
+}
+
+int fail_arg(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
+    va_end(ap);
+    return LH_ERR_ARG;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return LH_OK;
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return int(e);
+}
+
+int sm_count(int* out_device) {
+    static int cached[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (out_device) *out_device = dev;
+    if (dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        cached[dev] = n > 0 ? n : 148;
+    }
+    return cached[dev];
+}
+
+// launchers implemented in the kernel translation units
+int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
+               void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
+               cudaStream_t stream);
+int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,
+                  int round_scale, cudaStream_t stream);
+int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts, int counts_type, int E,
+                  int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
+                  cudaStream_t stream);
+int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, const void* counts, int counts_type,
+                  int E, int64_t M, int64_t n, void* dx_q, float* dx_s, void* dx_qt, float* dx_st, void* hp,
+                  float* dws, int round_scale, cudaStream_t stream);
+int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* q,
+                    float* s, float* rms, int round_scale, cudaStream_t stream);
+int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
+                float* rms, int reuse_rms, cudaStream_t stream);
+int64_t rows_norm_bwd_scratch(int64_t n);
+int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
+                  int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
+                  cudaStream_t stream);
+int dw_reduce(const float* dws, int64_t R, int64_t nb, void* dw, int w_dtype, cudaStream_t stream);
+int weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,
+                      cudaStream_t stream);
+int weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n,
+                      void* dx, void* dw, cudaStream_t stream);
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_fused(const char* what, int dtype, int64_t M, int64_t n, int mode) {
+    if (dtype != LH_BF16) return fail_arg("%s: only bf16 inputs are supported", what);
+    if (M < 0 || n <= 0 || (n % 128) != 0) return fail_arg("%s: need n %% 128 == 0 (M=%lld n=%lld)", what, (long long)M, (long long)n);
+    if (mode < 0 || mode > 2) return fail_arg("%s: output_mode must be 0, 1 or 2", what);
+    return LH_OK;
+}
+
+}  // namespace lh
+
+using namespace lh;
+
+extern "C" {
+
+int lh_version(void) { return LH_VERSION; }
+
+const char* lh_last_error(void) { return tl_error; }
+
+int lh_device_check(int device) {
+    cudaDeviceProp prop;
+    const cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { set_error("cudaGetDeviceProperties(%d): %s", device, cudaGetErrorString(e)); return int(e); }
+    if (prop.major != 10) return fail_arg("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    return LH_OK;
+}
+
+int lh_device_status(int* status) {
+    if (!status) return fail_arg("status is NULL");
+    int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int));
+    if (e != cudaSuccess) { set_error("cudaMemcpyFromSymbol: %s", cudaGetErrorString(e)); return int(e); }
+    *status = v;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+        if (e != cudaSuccess) { set_error("cudaMemcpyToSymbol: %s", cudaGetErrorString(e)); return int(e); }
+    }
+    return LH_OK;
+}
+
+int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
+    if (!what) return -1;
+    if (!strcmp(what, "rmsnorm_bwd")) return rows_norm_bwd_scratch(cols);
+    if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
+    return -1;
+}
+
+int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, void* qt, float* st,
+                       int round_scale, int output_mode, void* stream) {
+    if (output_mode < 0 || output_mode > 2) return fail_arg("blockwise_quant: output_mode must be 0, 1 or 2");
+    return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, qt, st, round_scale, output_mode, 0,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int lh_group_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
+                   void* stream) {
+    return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, nullptr, nullptr, round_scale, 0, 1,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int lh_block_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
+                   void* stream) {
+    if ((M % 128) != 0) return fail_arg("block_quant: need M %% 128 == 0");
+    return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, nullptr, nullptr, round_scale, 3, 0,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int lh_batch_blockwise_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t R,
+                             int64_t N, void* q, float* s, void* qt, float* st, int round_scale, void* stream) {
+    if (!counts || E <= 0) return fail_arg("batch_blockwise_quant: counts is NULL or E <= 0");
+    return tile_quant(x, dtype, counts, counts_type, E, R, N, q, s, qt, st, round_scale, 2, 0,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
+                   float* rms, int reuse_rms, void* stream) {
+    return rows_norm_y(x, gamma, dtype, M, n, eps, y, rms, reuse_rms, static_cast<cudaStream_t>(stream));
+}
+
+int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps,
+                              void* q, float* s, float* rms, void* qt, float* st, int round_scale,
+                              int output_mode, void* stream) {
+    if (int rc = check_fused("rmsnorm_blockquant_fwd", dtype, M, n, output_mode)) return rc;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (!rms) return fail_arg("rmsnorm_blockquant_fwd: rms is NULL");
+    if (output_mode == 0 || output_mode == 2) {
+        if (int rc = rows_norm_quant(x, gamma, dtype, M, n, eps, q, s, rms, round_scale, cs)) return rc;
+    }
+    if (output_mode == 1 || output_mode == 2) {
+        if (!qt || !st || !x || !gamma) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
+        if (!aligned16(x) || !aligned16(qt) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: pointers must be 16-byte aligned");
+        if (M == 0) return LH_OK;
+        return tile_norm_col(x, gamma, rms, M, n, qt, st, round_scale, cs);
+    }
+    return LH_OK;
+}
+
+int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
+                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
+                   void* stream) {
+    return rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, const float* rms, int dtype,
+                              int64_t M, int64_t n, float eps, void* dx, float* dgamma, void* dy_q, float* dy_s,
+                              void* dy_qt, float* dy_st, int round_scale, void* scratch, int64_t scratch_bytes,
+                              void* stream) {
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (int rc = rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes, cs)) return rc;
+    return tile_quant(dy, dtype, nullptr, 0, 1, M, n, dy_q, dy_s, dy_qt, dy_st, round_scale, 2, 0, cs);
+}
+
+int lh_weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,
+                         void* stream) {
+    if (!x || !y || !aligned16(x) || !aligned16(y)) return fail_arg("weighted_silu_fwd: NULL or unaligned pointer");
+    return weighted_silu_fwd(x, w, dtype, w_dtype, M, n, y, static_cast<cudaStream_t>(stream));
+}
+
+int lh_weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n,
+                         void* dx, void* dw, void* stream) {
+    if (!g || !x || !dx || !aligned16(g) || !aligned16(x) || !aligned16(dx)) return fail_arg("weighted_silu_bwd: NULL or unaligned pointer");
+    return weighted_silu_bwd(g, x, w, dtype, w_dtype, M, n, dx, dw, static_cast<cudaStream_t>(stream));
+}
+
+int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, void* qt, float* st,
+                           int round_scale, int output_mode, void* stream) {
+    if (int rc = check_fused("silu_blockquant_fwd", dtype, M, n, output_mode)) return rc;
+    if (!x || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("silu_blockquant_fwd: NULL or unaligned pointer");
+    if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
+    if (M == 0) return LH_OK;
+    return tile_silu_fwd(x, nullptr, LH_F32, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int lh_silu_blockquant_bwd(const void* g, const void* x, int dtype, int64_t M, int64_t n, void* dx_q, float* dx_s,
+                           void* dx_qt, float* dx_st, void* dx_hp, int round_scale, void* stream) {
+    if (int rc = check_fused("silu_blockquant_bwd", dtype, M, n, 2)) return rc;
+    if (!g || !x || !dx_q || !dx_s || !dx_qt || !dx_st) return fail_arg("silu_blockquant_bwd: NULL pointer");
+    if (!aligned16(g) || !aligned16(x) || !aligned16(dx_q) || !aligned16(dx_qt) || !aligned16(dx_hp)) return fail_arg("silu_blockquant_bwd: pointers must be 16-byte aligned");
+    if (M == 0) return LH_OK;
+    return tile_silu_bwd(g, x, nullptr, LH_F32, nullptr, 0, 1, M, n, dx_q, dx_s, dx_qt, dx_st, dx_hp, nullptr,
+                         round_scale, static_cast<cudaStream_t>(stream));
+}
+
+int lh_batch_silu_blockquant_fwd(const void* x, const void* w, int dtype, int w_dtype, const void* counts,
+                                 int counts_type, int E, int64_t R, int64_t n, void* q, float* s, void* qt,
+                                 float* st, int round_scale, int output_mode, void* stream) {
+    if (int rc = check_fused("batch_silu_blockquant_fwd", dtype, R, n, output_mode)) return rc;
+    if (!counts || E <= 0) return fail_arg("batch_silu_blockquant_fwd: counts is NULL or E <= 0");
+    if (R == 0) return LH_OK;
+    if (!x || !w || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("batch_silu_blockquant_fwd: NULL or unaligned pointer");
+    if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("batch_silu_blockquant_fwd: output pointer is NULL");
+    return tile_silu_fwd(x, w, w_dtype, counts, counts_type, E, R, n, q, s, qt, st, round_scale, output_mode,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int lh_batch_silu_blockquant_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype,
+                                 const void* counts, int counts_type, int E, int64_t R, int64_t n, void* dx_q,
+                                 float* dx_s, void* dw, void* dx_qt, float* dx_st, int round_scale, void* scratch,
+                                 int64_t scratch_bytes, void* stream) {
+    if (int rc = check_fused("batch_silu_blockquant_bwd", dtype, R, n, 2)) return rc;
+    if (!counts || E <= 0) return fail_arg("batch_silu_blockquant_bwd: counts is NULL or E <= 0");
+    if (R == 0) return LH_OK;
+    if (!g || !x || !w || !dx_q || !dx_s || !dw || !dx_qt || !dx_st) return fail_arg("batch_silu_blockquant_bwd: NULL pointer");
+    if (!aligned16(g) || !aligned16(x) || !aligned16(dx_q) || !aligned16(dx_qt)) return fail_arg("batch_silu_blockquant_bwd: pointers must be 16-byte aligned");
+    const int64_t need = R * (n / 128) * 4;
+    if (!scratch || scratch_bytes < need) return fail_arg("batch_silu_blockquant_bwd: scratch too small (%lld < %lld)", (long long)scratch_bytes, (long long)need);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (int rc = tile_silu_bwd(g, x, w, w_dtype, counts, counts_type, E, R, n, dx_q, dx_s, dx_qt, dx_st, nullptr,
+                               static_cast<float*>(scratch), round_scale, cs)) return rc;
+    return dw_reduce(static_cast<const float*>(scratch), R, n / 128, dw, w_dtype, cs);
+}
+
+}  // extern "C"

@@ -1,0 +1,236 @@
+// Shared device helpers for the sm_100a fused norm / SwiGLU + FP8 e4m3 blockwise
+// quantisation kernels: quantisation arithmetic that reproduces the PyTorch reference
+// math bit for bit, mbarrier / bulk-copy (TMA) PTX wrappers with bounded waits, and
+// the host-side error plumbing of the C ABI.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/linghe_b200.h"
+
+namespace lh {
+
+// ----------------------------------------------------------------------------------
+// host-side error plumbing
+// ----------------------------------------------------------------------------------
+void set_error(const char* fmt, ...);
+int fail_arg(const char* fmt, ...);      // records message, returns LH_ERR_ARG
+int check_launch(const char* what);      // cudaGetLastError -> status code
+int sm_count(int* out_device = nullptr); // SM count of the current device (cached)
+
+// Device status word: 0 = fine; otherwise the code of the first bounded wait that
+// gave up.  Read back with lh_device_status().
+extern __device__ int g_device_status;
+
+enum : int {
+    DEVERR_FULL_WAIT = 1,   // consumer gave up waiting for a tile to land
+    DEVERR_EMPTY_WAIT = 2,  // producer gave up waiting for a free stage
+    DEVERR_DRAIN_WAIT = 3,  // exit path gave up waiting for copies in flight
+};
+
+// ----------------------------------------------------------------------------------
+// element types
+// ----------------------------------------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr int BYTES = 2;
+    // 8 consecutive elements held in a uint4 -> 8 floats
+    static __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+template <> struct Elem<__half> {
+    static constexpr int BYTES = 2;
+    static __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+    }
+};
+template <> struct Elem<float> {
+    static constexpr int BYTES = 4;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ----------------------------------------------------------------------------------
+// quantisation arithmetic
+// ----------------------------------------------------------------------------------
+constexpr float kE4M3Max = 448.0f;
+constexpr float kScaleFloor = 1e-30f;
+
+// exp2(ceil(log2(s))) as the float32 reference computes it.  Away from powers of two
+// the result is 2^(k+1) for s = 2^k * (1+f); within 64 ulps above a power of two a
+// correctly rounded float log2 rounds back to k for some f, which is reproduced by
+// rounding a double-precision log2 to float.
+__device__ __forceinline__ float pow2_ceil(float s) {
+    const uint32_t b = __float_as_uint(s);
+    const int k = int(b >> 23) - 127;
+    const uint32_t m = b & 0x7fffffu;
+    int K;
+    if (m == 0u) {
+        K = k;
+    } else if (m >= 64u) {
+        K = k + 1;
+    } else {
+        K = int(ceilf(float(log2(double(s)))));
+    }
+    return __uint_as_float(uint32_t(K + 127) << 23);
+}
+
+// scale = max(amax / 448, 1e-30) with IEEE division, optionally rounded up to 2^k.
+__device__ __forceinline__ float scale_from_amax(float amax, bool round_scale) {
+    float s = fmaxf(__fdiv_rn(amax, kE4M3Max), kScaleFloor);
+    if (round_scale) s = pow2_ceil(s);
+    return s;
+}
+
+// Per-block divisor.  `exact` quotients equal IEEE x / s bit for bit: q0 = x*y with
+// y = RN(1/s), residual r' = s*q0 - x (exact in an FMA), q = q0 - r'*y.  The form with
+// the negated residual keeps the sign of a zero quotient.  Blocks whose scale is so
+// small that the residual could underflow take IEEE division instead.
+struct Divisor {
+    float s;      // scale
+    float y;      // RN(1/s)
+    float ny;     // -y
+    bool tiny;    // residual may underflow: use __fdiv_rn
+    __device__ __forceinline__ explicit Divisor(float scale) {
+        s = scale;
+        y = __frcp_rn(scale);
+        ny = -y;
+        tiny = scale < 8.0e-28f;  // ~2^-90
+    }
+    template <bool EXACT>
+    __device__ __forceinline__ float quot(float x) const {
+        if (EXACT) {
+            if (tiny) return __fdiv_rn(x, s);
+            const float q0 = x * y;
+            const float r = fmaf(s, q0, -x);
+            return fmaf(r, ny, q0);
+        } else {
+            return x * y;
+        }
+    }
+};
+
+// two floats -> two e4m3 codes (round to nearest even, saturating); lo in bits 0..7.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return uint32_t(r);
+}
+__device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
+    return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+}
+
+__device__ __forceinline__ float amax8(const float* v) {
+    float m = fmaxf(fabsf(v[0]), fabsf(v[1]));
+#pragma unroll
+    for (int i = 2; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+    return m;
+}
+
+// sigmoid as the reference computes it: 1 / (1 + exp(-x)), full-precision expf and a
+// correctly rounded reciprocal.
+__device__ __forceinline__ float sigmoid_ref(float x) {
+    return __frcp_rn(1.0f + expf(-x));
+}
+
+// ----------------------------------------------------------------------------------
+// mbarrier + bulk copy (TMA) wrappers.  Every wait is bounded.
+// ----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait (about two seconds of SM clock).  On give-up records `code` in the
+// device status word and returns false; callers then stop issuing work.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > 4000000000LL) {
+            atomicCAS(&g_device_status, 0, code);
+            return false;
+        }
+    }
+}
+
+// global -> shared bulk copy, completion counted in bytes on `bar`.
+// src, dst 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// shared -> global bulk copy tracked by the thread's bulk async-group.
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src_smem)),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make generic-proxy shared-memory writes visible to the async proxy (bulk stores)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <int ID, int N>
+__device__ __forceinline__ void named_bar() {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(N) : "memory");
+}
+
+__device__ __forceinline__ void st_global_v2(void* p, uint32_t a, uint32_t b) {
+    *reinterpret_cast<uint2*>(p) = make_uint2(a, b);
+}
+
+}  // namespace lh

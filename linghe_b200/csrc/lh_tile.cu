@@ -1,0 +1,601 @@
+// 128x128-tile kernels: produce a tile of float32 values (identity / RMSNorm with known
+// 1/rms / SwiGLU forward / SwiGLU backward), quantise it along rows (1x128) and/or
+// columns (128x1, written transposed) to FP8 e4m3 and store codes and scales in the
+// dense or per-expert packed layouts.
+//
+// Execution model (sm_100a): persistent CTAs walk a static round-robin list of tiles.
+// One producer warp feeds a multi-stage shared-memory ring with bulk asynchronous
+// copies (TMA, one 256/512-byte row segment per copy, completion counted on an
+// mbarrier); consumer warps hold a 128x128 tile in registers (RPT rows x 8 columns per
+// thread), reduce row maxima by shuffles and column maxima through shared memory, and
+// write the transposed codes through an XOR-swizzled shared-memory tile so that every
+// global store is a full 128-byte row.  No tensor cores: the path is HBM-bound.
+#include "lh_common.cuh"
+
+#include <type_traits>
+
+namespace lh {
+
+enum : int { OP_IDENT = 0, OP_NORM = 1, OP_SILU_F = 2, OP_SILU_B = 3 };
+enum : int { MODE_ROW = 0, MODE_COL = 1, MODE_BOTH = 2, MODE_BLOCK = 3 };
+
+struct TileParams {
+    const uint8_t* in[3];  // operand base pointers, already offset to their column 0
+    int64_t ld[3];         // operand row pitch in elements
+    const void* w;         // optional per-row weight
+    int w_bf16;
+    const float* r;        // OP_NORM: 1/rms per row
+    const void* gamma;     // OP_NORM: weight per column
+    const void* counts;    // per-expert row counts (NULL = dense)
+    int counts_i64;
+    int E;
+    int64_t M;             // rows (dense) / total rows (batched)
+    int64_t n;             // output columns per half
+    uint8_t* q;
+    float* s;
+    uint8_t* qt;
+    float* st;
+    void* hp;              // OP_SILU_B: optional dx in the input dtype
+    float* dws;            // OP_SILU_B: optional per-(row, column block) partial dw
+    int round_scale;
+    int scale_rowmajor;    // MODE_ROW only: s[i*nb + b] instead of s[b*M + i]
+};
+
+template <int OP> struct OpTraits;
+template <> struct OpTraits<OP_IDENT> { static constexpr int K = 1, NHALF = 1; };
+template <> struct OpTraits<OP_NORM> { static constexpr int K = 1, NHALF = 1; };
+template <> struct OpTraits<OP_SILU_F> { static constexpr int K = 2, NHALF = 1; };
+template <> struct OpTraits<OP_SILU_B> { static constexpr int K = 3, NHALF = 2; };
+
+template <int OP, typename InT, int RPT, int STAGES>
+struct TileCfg {
+    static constexpr int K = OpTraits<OP>::K;
+    static constexpr int NHALF = OpTraits<OP>::NHALF;
+    static constexpr int EB = Elem<InT>::BYTES;
+    static constexpr int ROWB = 128 * EB;            // bytes of one tile row of one operand
+    static constexpr int TILEB = 128 * ROWB;         // one operand tile
+    static constexpr int STAGEB = K * TILEB;
+    static constexpr int NW = 128 / (2 * RPT);       // consumer warps
+    static constexpr int NCONS = NW * 32;
+    static constexpr int NTHREADS = NCONS;
+    // shared memory carve-up (bytes)
+    static constexpr int OFF_STAGES = 0;
+    static constexpr int OFF_QT = OFF_STAGES + STAGES * STAGEB;  // 128 x 128 transposed codes
+    static constexpr int OFF_PART = OFF_QT + 128 * 128;          // [NW][128] column maxima
+    static constexpr int OFF_CS = OFF_PART + NW * 128 * 4;       // [128] column scale
+    static constexpr int OFF_CY = OFF_CS + 512;                  // [128] 1/scale
+    static constexpr int OFF_BAR = OFF_CY + 512;                 // full[STAGES], empty[STAGES]
+    static constexpr int OFF_SEG = OFF_BAR + 2 * STAGES * 8;     // segS[E+1] int64, segB[E+1] int32
+    static constexpr size_t smem_bytes(int E) { return size_t(OFF_SEG) + size_t(E + 1) * 12 + 16; }
+};
+
+struct TileLoc {
+    int64_t S;   // first row of the segment
+    int64_t c;   // rows in the segment
+    int64_t B;   // 128-row blocks before the segment
+    int T;       // 128-row block index inside the segment
+    int ct;      // column tile
+    int valid;   // valid rows in this tile (1..128)
+};
+
+__device__ __forceinline__ TileLoc locate(int64_t tile, int col_tiles, const int64_t* segS, const int* segB,
+                                          int E) {
+    TileLoc t;
+    const int64_t rt = tile / col_tiles;
+    t.ct = int(tile - rt * col_tiles);
+    int lo = 0, hi = E - 1;
+    while (lo < hi) {  // smallest e with segB[e+1] > rt
+        const int mid = (lo + hi) >> 1;
+        if (int64_t(segB[mid + 1]) > rt) hi = mid; else lo = mid + 1;
+    }
+    t.S = segS[lo];
+    t.c = segS[lo + 1] - t.S;
+    t.B = segB[lo];
+    t.T = int(rt - t.B);
+    const int64_t left = t.c - int64_t(t.T) * 128;
+    t.valid = left < 128 ? int(left) : 128;
+    return t;
+}
+
+template <typename InT>
+__device__ __forceinline__ void load8(const uint8_t* row_base, int l16, float* f) {
+    if constexpr (sizeof(InT) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row_base + l16 * 16);
+        Elem<InT>::unpack8(raw, f);
+    } else {
+        const float4 a = *reinterpret_cast<const float4*>(row_base + l16 * 32);
+        const float4 b = *reinterpret_cast<const float4*>(row_base + l16 * 32 + 16);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+        f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+}
+
+template <typename InT>
+__device__ __forceinline__ void store8_hp(void* dst, const float* f) {
+    if constexpr (sizeof(InT) == 4) {
+        float4* d = reinterpret_cast<float4*>(dst);
+        d[0] = make_float4(f[0], f[1], f[2], f[3]);
+        d[1] = make_float4(f[4], f[5], f[6], f[7]);
+    } else if constexpr (sizeof(InT) == 2 && std::is_same<InT, __half>::value) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_f16x2(f[0], f[1]), pack_f16x2(f[2], f[3]),
+                                                    pack_f16x2(f[4], f[5]), pack_f16x2(f[6], f[7]));
+    } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                                    pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+    }
+}
+
+__device__ __forceinline__ float max16(float a) {
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 8));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    return a;
+}
+__device__ __forceinline__ float sum16(float a) {
+    a += __shfl_xor_sync(0xffffffffu, a, 8);
+    a += __shfl_xor_sync(0xffffffffu, a, 4);
+    a += __shfl_xor_sync(0xffffffffu, a, 2);
+    a += __shfl_xor_sync(0xffffffffu, a, 1);
+    return a;
+}
+
+template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int MINB>
+__global__ void __launch_bounds__(TileCfg<OP, InT, RPT, STAGES>::NTHREADS, MINB)
+tile_kernel(const __grid_constant__ TileParams p) {
+    using C = TileCfg<OP, InT, RPT, STAGES>;
+    constexpr int K = C::K, NHALF = C::NHALF, NW = C::NW, NCONS = C::NCONS;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stages = smem + C::OFF_STAGES;
+    uint8_t* qts = smem + C::OFF_QT;
+    float* part = reinterpret_cast<float*>(smem + C::OFF_PART);
+    float* cs = reinterpret_cast<float*>(smem + C::OFF_CS);
+    float* cy = reinterpret_cast<float*>(smem + C::OFF_CY);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+    uint64_t* empty = full + STAGES;
+    int64_t* segS = reinterpret_cast<int64_t*>(smem + ((C::OFF_SEG + 15) & ~15));
+    int* segB = reinterpret_cast<int*>(segS + (p.E + 1));
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int E = p.E;
+
+    // ---- prologue: barriers + segment table (exclusive scans of counts) ------------
+    if (tid == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], NW);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        if (p.counts == nullptr) {
+            if (lane == 0) {
+                segS[0] = 0; segS[1] = p.M;
+                segB[0] = 0; segB[1] = int((p.M + 127) >> 7);
+            }
+        } else {
+            const int per = (E + 31) / 32;
+            const int e0 = lane * per;
+            int64_t sumS = 0, sumB = 0;
+            for (int e = e0; e < e0 + per && e < E; ++e) {
+                const int64_t c = p.counts_i64 ? reinterpret_cast<const int64_t*>(p.counts)[e]
+                                               : int64_t(reinterpret_cast<const int32_t*>(p.counts)[e]);
+                sumS += c;
+                sumB += (c + 127) >> 7;
+            }
+            int64_t preS = sumS, preB = sumB;  // inclusive warp scan
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int64_t a = __shfl_up_sync(0xffffffffu, preS, d);
+                const int64_t b = __shfl_up_sync(0xffffffffu, preB, d);
+                if (lane >= d) { preS += a; preB += b; }
+            }
+            int64_t accS = preS - sumS, accB = preB - sumB;
+            for (int e = e0; e < e0 + per && e < E; ++e) {
+                const int64_t c = p.counts_i64 ? reinterpret_cast<const int64_t*>(p.counts)[e]
+                                               : int64_t(reinterpret_cast<const int32_t*>(p.counts)[e]);
+                segS[e] = accS; segB[e] = int(accB);
+                accS += c; accB += (c + 127) >> 7;
+            }
+            if (lane == 31) { segS[E] = preS; segB[E] = int(preB); }
+        }
+    }
+    __syncthreads();
+
+    const int col_tiles = int(p.n >> 7);
+    const int64_t total_tiles = int64_t(segB[E]) * col_tiles;
+    const int64_t nb = p.n >> 7;
+
+    // Warp 0 doubles as the producer: it fills the ring before the loop and, at the top
+    // of every iteration, refills the stage that all warps released one iteration ago.
+    auto issue = [&](int64_t tile, int stage) {
+        const TileLoc t = locate(tile, col_tiles, segS, segB, E);
+        uint8_t* dst = stages + size_t(stage) * C::STAGEB;
+        if (lane == 0) mbar_expect_tx(&full[stage], uint32_t(t.valid) * C::ROWB * K);
+        __syncwarp();
+        const int64_t r0 = t.S + int64_t(t.T) * 128;
+        for (int rr = lane; rr < t.valid; rr += 32) {
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+                const uint8_t* src = p.in[k] + ((r0 + rr) * p.ld[k] + int64_t(t.ct) * 128) * C::EB;
+                bulk_g2s(dst + k * C::TILEB + rr * C::ROWB, src, C::ROWB, &full[stage]);
+            }
+        }
+    };
+    if (warp == 0) {
+        int64_t tile = blockIdx.x;
+        for (int j = 0; j < STAGES && tile < total_tiles; ++j, tile += gridDim.x) issue(tile, j);
+    }
+
+    // ================================ consumers ===================================
+    const int cw = warp;                 // consumer warp index
+    const int hw = lane >> 4;            // half-warp
+    const int l16 = lane & 15;           // 8-column group inside the tile
+    const int row0 = cw * (2 * RPT) + hw * RPT;
+    const bool rs = p.round_scale != 0;
+
+    int it = 0;
+    for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const int stage = it % STAGES;
+        if (warp == 0 && it > 0) {
+            // tile (it-1) lived in stage (it-1)%STAGES; once every warp has released it,
+            // bring in tile it-1+STAGES.  Copies issued here are consumed by this CTA, so
+            // none is in flight when the loop ends.
+            const int64_t nxt = tile + int64_t(STAGES - 1) * gridDim.x;
+            if (nxt < total_tiles) {
+                const int ps = (it - 1) % STAGES;
+                if (!mbar_wait(&empty[ps], ((it - 1) / STAGES) & 1, DEVERR_EMPTY_WAIT)) return;
+                issue(nxt, ps);
+            }
+        }
+        const TileLoc t = locate(tile, col_tiles, segS, segB, E);
+        const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
+        const int64_t gcol0 = int64_t(t.ct) * 128;        // column inside a half
+        if (!mbar_wait(&full[stage], (it / STAGES) & 1, DEVERR_FULL_WAIT)) return;
+        const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
+
+        float v[NHALF][RPT][8];
+        float dwp[RPT];
+        float gam[8];
+        if constexpr (OP == OP_NORM) {
+            const uint4 graw = *reinterpret_cast<const uint4*>(
+                reinterpret_cast<const uint8_t*>(p.gamma) + (gcol0 + l16 * 8) * 2);
+            Elem<InT>::unpack8(graw, gam);
+        }
+#pragma unroll
+        for (int s = 0; s < RPT; ++s) {
+            const int rr = row0 + s;
+            const bool ok = rr < t.valid;
+            if constexpr (OP == OP_IDENT) {
+                load8<InT>(sbase + rr * C::ROWB, l16, v[0][s]);
+            } else if constexpr (OP == OP_NORM) {
+                float x[8];
+                load8<InT>(sbase + rr * C::ROWB, l16, x);
+                const float r = ok ? p.r[grow0 + rr] : 0.f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[0][s][c] = __fmul_rn(__fmul_rn(x[c], r), gam[c]);
+            } else if constexpr (OP == OP_SILU_F) {
+                float x1[8], x2[8];
+                load8<InT>(sbase + rr * C::ROWB, l16, x1);
+                load8<InT>(sbase + C::TILEB + rr * C::ROWB, l16, x2);
+                float w = 1.f;
+                const bool has_w = p.w != nullptr;
+                if (has_w && ok)
+                    w = p.w_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[grow0 + rr])
+                                 : reinterpret_cast<const float*>(p.w)[grow0 + rr];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float y = __fmul_rn(__fmul_rn(sigmoid_ref(x1[c]), x1[c]), x2[c]);
+                    if (has_w) y = __fmul_rn(y, w);
+                    v[0][s][c] = y;
+                }
+            } else {  // OP_SILU_B
+                float g[8], x1[8], x2[8];
+                load8<InT>(sbase + rr * C::ROWB, l16, g);
+                load8<InT>(sbase + C::TILEB + rr * C::ROWB, l16, x1);
+                load8<InT>(sbase + 2 * C::TILEB + rr * C::ROWB, l16, x2);
+                float w = 1.f;
+                const bool has_w = p.w != nullptr;
+                if (has_w && ok)
+                    w = p.w_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[grow0 + rr])
+                                 : reinterpret_cast<const float*>(p.w)[grow0 + rr];
+                float acc = 0.f;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const float sg = sigmoid_ref(x1[c]);
+                    const float sgg = sg * g[c];              // sigmoid * g
+                    const float d2 = sgg * x1[c];             // d/dx2 (unweighted)
+                    const float u = fmaf(x1[c], 1.f - sg, 1.f);
+                    const float d1 = sgg * x2[c] * u;         // d/dx1 (unweighted)
+                    acc = fmaf(d2, x2[c], acc);               // sigmoid*x1*x2*g
+                    v[0][s][c] = has_w ? d1 * w : d1;
+                    v[1][s][c] = has_w ? d2 * w : d2;
+                }
+                dwp[s] = acc;
+            }
+            if (!ok) {
+#pragma unroll
+                for (int h = 0; h < NHALF; ++h)
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) v[h][s][c] = 0.f;
+                if constexpr (OP == OP_SILU_B) dwp[s] = 0.f;
+            }
+        }
+        // all shared-memory reads of this stage are done: hand it back to the producer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[stage]);
+
+        if constexpr (OP == OP_SILU_B) {
+            if (p.dws != nullptr) {
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    const float tot = sum16(dwp[s]);
+                    const int rr = row0 + s;
+                    if (l16 == 0 && rr < t.valid) p.dws[(grow0 + rr) * nb + t.ct] = tot;
+                }
+            }
+            if (p.hp != nullptr) {
+#pragma unroll
+                for (int h = 0; h < NHALF; ++h)
+#pragma unroll
+                    for (int s = 0; s < RPT; ++s) {
+                        const int rr = row0 + s;
+                        if (rr < t.valid) {
+                            uint8_t* dst = reinterpret_cast<uint8_t*>(p.hp) +
+                                           ((grow0 + rr) * (2 * p.n) + h * p.n + gcol0 + l16 * 8) * C::EB;
+                            store8_hp<InT>(dst, v[h][s]);
+                        }
+                    }
+            }
+        }
+
+#pragma unroll
+        for (int h = 0; h < NHALF; ++h) {
+            // -------------------------- 128x128 single-scale blocks -----------------
+            if constexpr (MODE == MODE_BLOCK) {
+                float m = 0.f;
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) m = fmaxf(m, amax8(v[h][s]));
+                m = max16(m);
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                if (lane == 0) part[cw] = m;
+                named_bar<1, NCONS>();
+                float bm = part[0];
+#pragma unroll
+                for (int w2 = 1; w2 < NW; ++w2) bm = fmaxf(bm, part[w2]);
+                const float sc = scale_from_amax(bm, rs);
+                const Divisor d(sc);
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    const int rr = row0 + s;
+                    const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][s][0]), d.quot<EXACT>(v[h][s][1]),
+                                                   d.quot<EXACT>(v[h][s][2]), d.quot<EXACT>(v[h][s][3]));
+                    const uint32_t hi = cvt_e4m3x4(d.quot<EXACT>(v[h][s][4]), d.quot<EXACT>(v[h][s][5]),
+                                                   d.quot<EXACT>(v[h][s][6]), d.quot<EXACT>(v[h][s][7]));
+                    if (rr < t.valid) st_global_v2(p.q + (grow0 + rr) * p.n + gcol0 + l16 * 8, lo, hi);
+                }
+                if (tid == 0) p.s[(t.B + t.T) * nb + t.ct] = sc;
+                named_bar<1, NCONS>();  // part[] is rewritten by the next tile
+            }
+            // ------------------------------ row-wise 1x128 --------------------------
+            if constexpr (MODE == MODE_ROW || MODE == MODE_BOTH) {
+                float myscale = 0.f;
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    const int rr = row0 + s;
+                    const float a = max16(amax8(v[h][s]));
+                    const float sc = scale_from_amax(a, rs);
+                    const Divisor d(sc);
+                    const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][s][0]), d.quot<EXACT>(v[h][s][1]),
+                                                   d.quot<EXACT>(v[h][s][2]), d.quot<EXACT>(v[h][s][3]));
+                    const uint32_t hi = cvt_e4m3x4(d.quot<EXACT>(v[h][s][4]), d.quot<EXACT>(v[h][s][5]),
+                                                   d.quot<EXACT>(v[h][s][6]), d.quot<EXACT>(v[h][s][7]));
+                    if (rr < t.valid)
+                        st_global_v2(p.q + (grow0 + rr) * (NHALF * p.n) + h * p.n + gcol0 + l16 * 8, lo, hi);
+                    if (l16 == s) myscale = sc;
+                }
+                if (l16 < RPT && row0 + l16 < t.valid) {
+                    const int rr = row0 + l16;
+                    if (p.scale_rowmajor)
+                        p.s[(grow0 + rr) * nb + t.ct] = myscale;
+                    else
+                        p.s[t.S * (NHALF * nb) + (h * nb + t.ct) * t.c + int64_t(t.T) * 128 + rr] = myscale;
+                }
+            }
+            // ------------------------ column-wise 128x1, transposed -----------------
+            if constexpr (MODE == MODE_COL || MODE == MODE_BOTH) {
+                float cm[8];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    float m = fabsf(v[h][0][c]);
+#pragma unroll
+                    for (int s = 1; s < RPT; ++s) m = fmaxf(m, fabsf(v[h][s][c]));
+                    cm[c] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                }
+                if (hw == 0) {
+                    float4* dst = reinterpret_cast<float4*>(part + cw * 128 + l16 * 8);
+                    dst[0] = make_float4(cm[0], cm[1], cm[2], cm[3]);
+                    dst[1] = make_float4(cm[4], cm[5], cm[6], cm[7]);
+                }
+                named_bar<1, NCONS>();
+                if (tid < 128) {
+                    float m = part[tid];
+#pragma unroll
+                    for (int w2 = 1; w2 < NW; ++w2) m = fmaxf(m, part[w2 * 128 + tid]);
+                    const float sc = scale_from_amax(m, rs);
+                    cs[tid] = sc;
+                    cy[tid] = __frcp_rn(sc);
+                    p.st[(t.B + t.T) * (NHALF * p.n) + h * p.n + gcol0 + tid] = sc;
+                }
+                named_bar<1, NCONS>();
+                float sc8[8], y8[8];
+                {
+                    const float4 a = *reinterpret_cast<const float4*>(cs + l16 * 8);
+                    const float4 b = *reinterpret_cast<const float4*>(cs + l16 * 8 + 4);
+                    const float4 c = *reinterpret_cast<const float4*>(cy + l16 * 8);
+                    const float4 e = *reinterpret_cast<const float4*>(cy + l16 * 8 + 4);
+                    sc8[0] = a.x; sc8[1] = a.y; sc8[2] = a.z; sc8[3] = a.w;
+                    sc8[4] = b.x; sc8[5] = b.y; sc8[6] = b.z; sc8[7] = b.w;
+                    y8[0] = c.x; y8[1] = c.y; y8[2] = c.z; y8[3] = c.w;
+                    y8[4] = e.x; y8[5] = e.y; y8[6] = e.z; y8[7] = e.w;
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    Divisor d(1.f);
+                    d.s = sc8[c]; d.y = y8[c]; d.ny = -y8[c]; d.tiny = sc8[c] < 8.0e-28f;
+                    const int col = l16 * 8 + c;
+                    if constexpr (RPT == 8) {
+                        const int rc = cw * 2 + hw;
+                        const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][0][c]), d.quot<EXACT>(v[h][1][c]),
+                                                       d.quot<EXACT>(v[h][2][c]), d.quot<EXACT>(v[h][3][c]));
+                        const uint32_t hi = cvt_e4m3x4(d.quot<EXACT>(v[h][4][c]), d.quot<EXACT>(v[h][5][c]),
+                                                       d.quot<EXACT>(v[h][6][c]), d.quot<EXACT>(v[h][7][c]));
+                        *reinterpret_cast<uint2*>(qts + col * 128 + ((rc ^ l16) << 3)) = make_uint2(lo, hi);
+                    } else {
+                        static_assert(RPT == 8 || RPT == 4, "RPT");
+                        const int rc = cw;
+                        const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][0][c]), d.quot<EXACT>(v[h][1][c]),
+                                                       d.quot<EXACT>(v[h][2][c]), d.quot<EXACT>(v[h][3][c]));
+                        *reinterpret_cast<uint32_t*>(qts + col * 128 + ((rc ^ l16) << 3) + hw * 4) = lo;
+                    }
+                }
+                named_bar<1, NCONS>();
+                // copy-out: 128 columns x 16 chunks of 8 rows
+                uint8_t* qt_seg = p.qt + t.S * (NHALF * p.n) + (h * p.n + gcol0) * t.c + int64_t(t.T) * 128;
+                const bool fast = (t.c & 7) == 0;
+#pragma unroll
+                for (int k = 0; k < 2048 / NCONS; ++k) {
+                    const int u = tid + k * NCONS;
+                    const int col = u >> 4, rc = u & 15;
+                    const uint2 val = *reinterpret_cast<const uint2*>(qts + col * 128 + ((rc ^ ((col >> 3) & 15)) << 3));
+                    uint8_t* dst = qt_seg + int64_t(col) * t.c + rc * 8;
+                    const int nvalid = t.valid - rc * 8;
+                    if (fast && nvalid >= 8) {
+                        *reinterpret_cast<uint2*>(dst) = val;
+                    } else if (nvalid > 0) {
+                        const uint64_t bits = (uint64_t(val.y) << 32) | val.x;
+                        for (int b2 = 0; b2 < 8 && b2 < nvalid; ++b2) dst[b2] = uint8_t(bits >> (8 * b2));
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------
+template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int CTAS_PER_SM>
+static int launch_tile(const TileParams& p, cudaStream_t stream) {
+    using C = TileCfg<OP, InT, RPT, STAGES>;
+    auto kern = tile_kernel<OP, InT, MODE, EXACT, RPT, STAGES, CTAS_PER_SM>;
+    const size_t smem = C::smem_bytes(p.E);
+    if (smem > 227 * 1024) return fail_arg("too many experts for the shared-memory segment table (E=%d)", p.E);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
+    const int sms = sm_count();
+    int64_t grid = int64_t(sms) * CTAS_PER_SM;
+    if (p.counts == nullptr) {
+        const int64_t tiles = ((p.M + 127) / 128) * (p.n / 128);
+        if (tiles < grid) grid = tiles;
+    }
+    if (grid <= 0) return LH_OK;
+    kern<<<dim3(unsigned(grid)), dim3(C::NTHREADS), smem, stream>>>(p);
+    return check_launch("tile_kernel");
+}
+
+#ifndef LH_FUSED_EXACT
+#define LH_FUSED_EXACT true
+#endif
+
+template <typename InT>
+static int quant_dispatch(const TileParams& p, int mode, cudaStream_t st) {
+    constexpr int S = sizeof(InT) == 2 ? 2 : 2;
+    constexpr int CPS = sizeof(InT) == 2 ? 2 : 1;
+    switch (mode) {
+        case MODE_ROW: return launch_tile<OP_IDENT, InT, MODE_ROW, true, 8, S, CPS>(p, st);
+        case MODE_COL: return launch_tile<OP_IDENT, InT, MODE_COL, true, 8, S, CPS>(p, st);
+        case MODE_BOTH: return launch_tile<OP_IDENT, InT, MODE_BOTH, true, 8, S, CPS>(p, st);
+        case MODE_BLOCK: return launch_tile<OP_IDENT, InT, MODE_BLOCK, true, 8, S, CPS>(p, st);
+    }
+    return fail_arg("output_mode must be 0, 1 or 2");
+}
+
+static int quant_any(const TileParams& p, int dtype, int mode, cudaStream_t st) {
+    switch (dtype) {
+        case LH_BF16: return quant_dispatch<__nv_bfloat16>(p, mode, st);
+        case LH_F16: return quant_dispatch<__half>(p, mode, st);
+        case LH_F32: return quant_dispatch<float>(p, mode, st);
+    }
+    return fail_arg("unsupported dtype %d", dtype);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
+               void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
+               cudaStream_t stream) {
+    if (M < 0 || N <= 0 || (N % 128) != 0) return fail_arg("quant: need N %% 128 == 0 (M=%lld N=%lld)", (long long)M, (long long)N);
+    if (M == 0) return LH_OK;
+    if (!aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("quant: pointers must be 16-byte aligned");
+    if (!x) return fail_arg("quant: x is NULL");
+    if ((mode == MODE_ROW || mode == MODE_BOTH || mode == MODE_BLOCK) && (!q || !s)) return fail_arg("quant: q/s NULL");
+    if ((mode == MODE_COL || mode == MODE_BOTH) && (!qt || !st)) return fail_arg("quant: qt/st NULL");
+    TileParams p{};
+    p.in[0] = static_cast<const uint8_t*>(x);
+    p.ld[0] = N;
+    p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
+    p.M = M; p.n = N;
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
+    p.round_scale = round_scale; p.scale_rowmajor = scale_rowmajor;
+    return quant_any(p, dtype, mode, stream);
+}
+
+int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,
+                  int round_scale, cudaStream_t stream) {
+    TileParams p{};
+    p.in[0] = static_cast<const uint8_t*>(x);
+    p.ld[0] = n;
+    p.r = r; p.gamma = gamma; p.E = 1; p.M = M; p.n = n;
+    p.qt = static_cast<uint8_t*>(qt); p.st = st; p.round_scale = round_scale;
+    return launch_tile<OP_NORM, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 8, 2, 2>(p, stream);
+}
+
+int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts, int counts_type, int E,
+                  int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
+                  cudaStream_t stream) {
+    TileParams p{};
+    p.in[0] = static_cast<const uint8_t*>(x);
+    p.in[1] = static_cast<const uint8_t*>(x) + n * 2;
+    p.ld[0] = p.ld[1] = 2 * n;
+    p.w = w; p.w_bf16 = w_dtype == LH_BF16;
+    p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
+    p.M = M; p.n = n;
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
+    p.round_scale = round_scale;
+    switch (mode) {
+        case MODE_ROW: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_ROW, LH_FUSED_EXACT, 8, 3, 1>(p, stream);
+        case MODE_COL: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 8, 3, 1>(p, stream);
+        case MODE_BOTH: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 8, 3, 1>(p, stream);
+    }
+    return fail_arg("output_mode must be 0, 1 or 2");
+}
+
+int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, const void* counts, int counts_type,
+                  int E, int64_t M, int64_t n, void* dx_q, float* dx_s, void* dx_qt, float* dx_st, void* hp,
+                  float* dws, int round_scale, cudaStream_t stream) {
+    TileParams p{};
+    p.in[0] = static_cast<const uint8_t*>(g);
+    p.in[1] = static_cast<const uint8_t*>(x);
+    p.in[2] = static_cast<const uint8_t*>(x) + n * 2;
+    p.ld[0] = n; p.ld[1] = p.ld[2] = 2 * n;
+    p.w = w; p.w_bf16 = w_dtype == LH_BF16;
+    p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
+    p.M = M; p.n = n;
+    p.q = static_cast<uint8_t*>(dx_q); p.s = dx_s; p.qt = static_cast<uint8_t*>(dx_qt); p.st = dx_st;
+    p.hp = hp; p.dws = dws; p.round_scale = round_scale;
+    return launch_tile<OP_SILU_B, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 2, 1>(p, stream);
+}
+
+}  // namespace lh

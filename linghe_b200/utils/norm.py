@@ -1,0 +1,116 @@
+"""RMSNorm kernels -- same entry points as linghe/utils/norm.py (the block-quant and
+plain variants), running hand-written sm_100a CUDA through the C ABI."""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from linghe_b200 import _lib
+
+E4M3 = torch.float8_e4m3fn
+
+
+def _rows_cols(x):
+    shape = x.shape
+    assert len(shape) in (2, 3)
+    if len(shape) == 3:
+        return shape[0] * shape[1], shape[2]
+    return shape[0], shape[1]
+
+
+def triton_rms_norm_forward(x, weight, eps=1e-6, out=None, rms=None):
+    """RMSNorm (linghe/utils/norm.py:58).  Returns (out like x, rms float32 [M]);
+    a given `rms` (1/rms per row) is reused instead of recomputed."""
+    assert x.is_contiguous() and weight.is_contiguous()
+    M, n = _rows_cols(x)
+    assert n <= 8192
+    if out is None:
+        out = torch.empty_like(x)
+    reuse = rms is not None
+    if not reuse:
+        rms = torch.empty((M,), device=x.device, dtype=torch.float32)
+    _lib.call("lh_rmsnorm_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x), M, n, float(eps),
+              _lib.ptr(out), _lib.ptr(rms), int(reuse))
+    return out, rms
+
+
+def triton_rms_norm_backward(grad_output, x, w, eps=1e-6, rms=None):
+    """RMSNorm backward (linghe/utils/norm.py:144).  Returns (dx like x, dw float32 [n])."""
+    assert grad_output.is_contiguous() and x.is_contiguous()
+    M, n = _rows_cols(x)
+    assert n <= 8192
+    dx = torch.empty_like(x)
+    dw = torch.empty((n,), dtype=torch.float32, device=x.device)
+    nbytes = _lib.scratch_bytes("rmsnorm_bwd", M, n)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x.device)
+    _lib.call("lh_rmsnorm_bwd", x, _lib.ptr(grad_output), _lib.ptr(x), _lib.ptr(w), _lib.ptr(rms),
+              _lib.dtype_code(x), M, n, float(eps), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(scratch), nbytes)
+    return dx, dw
+
+
+def triton_rms_norm_and_block_quant_forward(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float = 1e-6,
+    out: Optional[torch.Tensor] = None,
+    scale: Optional[torch.Tensor] = None,
+    rms: Optional[torch.Tensor] = None,
+    round_scale: bool = False,
+    output_mode: int = 2,
+):
+    """Fused RMSNorm + blockwise FP8 quantisation (linghe/utils/norm.py:343).
+
+    Returns (out e4m3 [M,n], scale f32 [n/128,M], rms f32 [M], transpose_output e4m3
+    [n,M], transpose_scale f32 [ceil(M/128),n]).  output_mode 0: rows only (`rms` must be
+    None); 1: columns only (`rms` required, out/scale are returned as passed); 2: both
+    (a passed `rms` is ignored and recomputed)."""
+    assert x.is_contiguous() and weight.is_contiguous()
+    M, n = x.shape
+    assert n <= 8192
+    assert output_mode in (0, 1, 2)
+    device = x.device
+    if out is None and output_mode in (0, 2):
+        out = torch.empty((M, n), device=device, dtype=E4M3)
+    if scale is None and output_mode in (0, 2):
+        scale = torch.empty((n // 128, M), device=device, dtype=torch.float32)
+    transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
+    transpose_scale = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
+    if output_mode == 0:
+        assert rms is None
+        rms = torch.empty((M,), dtype=torch.float32, device=device)
+    elif output_mode == 1:
+        assert rms is not None
+    else:
+        rms = torch.empty((M,), dtype=torch.float32, device=device)
+    _lib.call("lh_rmsnorm_blockquant_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x), M, n,
+              float(eps), _lib.ptr(out) if output_mode != 1 else None,
+              _lib.ptr(scale) if output_mode != 1 else None, _lib.ptr(rms), _lib.ptr(transpose_output),
+              _lib.ptr(transpose_scale), int(bool(round_scale)), int(output_mode))
+    return out, scale, rms, transpose_output, transpose_scale
+
+
+def rms_norm_backward_and_block_quant(grad_output, x, w, eps=1e-6, rms=None, round_scale=False):
+    """RMSNorm backward fused with the dual-axis quantisation of `grad_output`.
+
+    Upstream has no single entry point for this: it calls triton_rms_norm_backward
+    (linghe/utils/norm.py:144) and triton_blockwise_quant (linghe/quant/block.py:129)
+    separately.  Returns (dx, dw, dy_q [M,n], dy_scale [n/128,M], dyT_q [n,M],
+    dyT_scale [ceil(M/128),n])."""
+    assert grad_output.is_contiguous() and x.is_contiguous()
+    M, n = _rows_cols(x)
+    assert n <= 8192 and M % 16 == 0
+    device = x.device
+    dx = torch.empty_like(x)
+    dw = torch.empty((n,), dtype=torch.float32, device=device)
+    dy_q = torch.empty((M, n), device=device, dtype=E4M3)
+    dy_s = torch.empty((n // 128, M), device=device, dtype=torch.float32)
+    dyt_q = torch.empty((n, M), device=device, dtype=E4M3)
+    dyt_s = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
+    nbytes = _lib.scratch_bytes("rmsnorm_bwd", M, n)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    _lib.call("lh_rmsnorm_bwd_blockquant", x, _lib.ptr(grad_output), _lib.ptr(x), _lib.ptr(w), _lib.ptr(rms),
+              _lib.dtype_code(x), M, n, float(eps), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(dy_q), _lib.ptr(dy_s),
+              _lib.ptr(dyt_q), _lib.ptr(dyt_s), int(bool(round_scale)), _lib.ptr(scratch), nbytes)
+    return dx, dw, dy_q, dy_s, dyt_q, dyt_s

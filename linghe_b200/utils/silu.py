@@ -1,0 +1,150 @@
+"""SwiGLU kernels -- same entry points as linghe/utils/silu.py (plain, block-quant and
+per-expert batched block-quant variants), running hand-written sm_100a CUDA through the
+C ABI."""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from linghe_b200 import _lib
+
+E4M3 = torch.float8_e4m3fn
+
+
+def _cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def triton_weighted_silu_forward(x, weight=None, out=None, asm=False):
+    """y = silu(x1) * x2 [* weight] in x.dtype (linghe/utils/silu.py:98).  `asm` selected an
+    approximate-exp kernel upstream; here it is accepted and ignored."""
+    assert x.is_contiguous()
+    M, N = x.shape
+    assert N % 256 == 0
+    if out is None:
+        out = torch.empty((M, N // 2), device=x.device, dtype=x.dtype)
+    if weight is not None:
+        assert weight.is_contiguous()
+    _lib.call("lh_weighted_silu_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
+              _lib.dtype_code(weight) if weight is not None else _lib.F32, M, N // 2, _lib.ptr(out))
+    return out
+
+
+def triton_weighted_silu_backward(g: torch.Tensor, x: torch.Tensor, weight: Optional[torch.Tensor] = None):
+    """Backward of triton_weighted_silu_forward (linghe/utils/silu.py:177).
+    Returns (dx [M,2n] x.dtype, dw like weight or None)."""
+    assert g.is_contiguous() and x.is_contiguous()
+    M, N = x.shape
+    assert N % 256 == 0
+    dw = None
+    if weight is not None:
+        assert weight.is_contiguous()
+        dw = torch.empty(weight.shape, device=x.device, dtype=weight.dtype)
+    dx = torch.empty((M, N), device=x.device, dtype=x.dtype)
+    _lib.call("lh_weighted_silu_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
+              _lib.dtype_code(weight) if weight is not None else _lib.F32, M, N // 2, _lib.ptr(dx), _lib.ptr(dw))
+    return dx, dw
+
+
+def triton_silu_and_block_quant_forward(x, out=None, scale=None, round_scale=False, output_mode=2):
+    """Fused SwiGLU + blockwise quantisation (linghe/utils/silu.py:279).
+    Returns (out [M,n], scale [n/128,M], transpose_output [n,M], transpose_scale
+    [ceil(M/128),n]); outputs a mode skips stay uninitialised."""
+    assert x.is_contiguous()
+    M, N = x.shape
+    n = N // 2
+    device = x.device
+    if out is None:
+        out = torch.empty((M, n), device=device, dtype=E4M3)
+    if scale is None:
+        scale = torch.empty((n // 128, M), device=device, dtype=torch.float32)
+    transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
+    transpose_scale = torch.empty((_cdiv(M, 128), n), device=device, dtype=torch.float32)
+    assert n % 128 == 0
+    _lib.call("lh_silu_blockquant_fwd", x, _lib.ptr(x), _lib.dtype_code(x), M, n, _lib.ptr(out), _lib.ptr(scale),
+              _lib.ptr(transpose_output), _lib.ptr(transpose_scale), int(bool(round_scale)), int(output_mode))
+    return out, scale, transpose_output, transpose_scale
+
+
+def triton_silu_and_block_quant_backward(g, x, round_scale=False, return_bf16=False):
+    """Backward of triton_silu_and_block_quant_forward (linghe/utils/silu.py:424).
+    Returns (dx e4m3 [M,2n], dx_scale [2n/128,M], transpose_dx [2n,M], transpose_dx_scale
+    [M/128,2n]).  With return_bf16=True a fifth element, dx in x.dtype [M,2n], is emitted
+    by the same kernel (upstream needs a separate triton_weighted_silu_backward pass)."""
+    assert g.is_contiguous() and x.is_contiguous()
+    M, N = x.shape
+    n = N // 2
+    device = x.device
+    assert M % 128 == 0 and N % 256 == 0
+    dx = torch.empty((M, N), device=device, dtype=E4M3)
+    dx_scale = torch.empty((N // 128, M), device=device, dtype=torch.float32)
+    transpose_dx = torch.empty((N, M), device=device, dtype=E4M3)
+    transpose_dx_scale = torch.empty((_cdiv(M, 128), N), device=device, dtype=torch.float32)
+    dx_hp = torch.empty((M, N), device=device, dtype=x.dtype) if return_bf16 else None
+    _lib.call("lh_silu_blockquant_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.dtype_code(x), M, n, _lib.ptr(dx),
+              _lib.ptr(dx_scale), _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale), _lib.ptr(dx_hp),
+              int(bool(round_scale)))
+    if return_bf16:
+        return dx, dx_scale, transpose_dx, transpose_dx_scale, dx_hp
+    return dx, dx_scale, transpose_dx, transpose_dx_scale
+
+
+def triton_batch_weighted_silu_and_block_quant_forward(
+    x, weight, counts, splits=None, out=None, scale=None, round_scale=False, output_mode=2
+):
+    """Per-expert weighted SwiGLU + blockwise quantisation for routed experts
+    (linghe/utils/silu.py:797).  `counts` is the device tensor of rows per expert,
+    `splits` the same as a host list (only used to size outputs).  Outputs use the
+    per-expert packed layouts documented in include/linghe_b200.h."""
+    assert splits is not None, "batch mode need splits to launch kernels"
+    assert x.is_contiguous() and weight.is_contiguous()
+    M, N = x.shape
+    n = N // 2
+    n_experts = counts.shape[0]
+    assert N <= 8192
+    device = x.device
+    if out is None:
+        out = torch.empty((M, n), device=device, dtype=E4M3)
+    if scale is None:
+        scale = torch.empty((M, n // 128), device=device, dtype=torch.float32)
+    blocks = sum(_cdiv(int(c), 128) for c in splits)
+    transpose_output = torch.empty((M, n), device=device, dtype=E4M3)
+    transpose_scale = torch.empty((blocks, n), device=device, dtype=torch.float32)
+    if M == 0:
+        return out, scale, transpose_output, transpose_scale
+    assert counts.is_cuda and counts.is_contiguous()
+    _lib.call("lh_batch_silu_blockquant_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
+              _lib.dtype_code(weight), _lib.ptr(counts), _lib.itype_code(counts), n_experts, M, n, _lib.ptr(out),
+              _lib.ptr(scale), _lib.ptr(transpose_output), _lib.ptr(transpose_scale), int(bool(round_scale)),
+              int(output_mode))
+    return out, scale, transpose_output, transpose_scale
+
+
+def triton_batch_weighted_silu_and_block_quant_backward(g, x, weight, counts, splits=None, round_scale=False):
+    """Backward of the per-expert forward (linghe/utils/silu.py:1293).  Returns
+    (dx e4m3 [R,2n], dx_scale, dw like weight, transpose_dx, transpose_dx_scale)."""
+    M, N = x.shape
+    n = N // 2
+    n_expert = counts.shape[0]
+    assert n % 128 == 0
+    assert g.is_contiguous() and x.is_contiguous() and weight.is_contiguous()
+    assert splits is not None, "batch mode need splits to launch kernels"
+    device = x.device
+    dx = torch.empty((M, N), device=device, dtype=E4M3)
+    dx_scale = torch.empty((M, N // 128), device=device, dtype=torch.float32)
+    s = sum(_cdiv(int(c), 128) for c in splits)
+    transpose_dx = torch.empty((M, N), device=device, dtype=E4M3)
+    transpose_dx_scale = torch.empty((s, N), device=device, dtype=torch.float32)
+    dw = torch.empty_like(weight)
+    if s == 0:
+        return dx, dx_scale, dw, transpose_dx, transpose_dx_scale
+    assert counts.is_cuda and counts.is_contiguous()
+    nbytes = _lib.scratch_bytes("batch_silu_bwd", M, n)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    _lib.call("lh_batch_silu_blockquant_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
+              _lib.dtype_code(weight), _lib.ptr(counts), _lib.itype_code(counts), n_expert, M, n, _lib.ptr(dx),
+              _lib.ptr(dx_scale), _lib.ptr(dw), _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale),
+              int(bool(round_scale)), _lib.ptr(scratch), nbytes)
+    return dx, dx_scale, dw, transpose_dx, transpose_dx_scale

@@ -1,0 +1,485 @@
+"""Parity of the CUDA path (called through the Python mirror of the upstream interface,
+which goes straight to the C ABI) against the CPU oracle and the golden vectors.
+
+Rules: pure quantisers are bit-exact in codes and scales; fused variants keep scales
+within 1e-6 relative and at most 0.1 % of codes one e4m3 ulp off; bf16 gradients within
+1e-2 relative."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.common import (golden, bf16, fp8, bits, assert_bits_equal, assert_f32_equal, assert_codes_close,
+                          assert_scales_close, assert_rel_close)
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _status_clean():
+    from linghe_b200 import _lib
+    yield
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0, "a kernel gave up on a bounded wait"
+
+
+def _cuda(t):
+    return t.to(DEV)
+
+
+def randn_bf16(shape, seed, power=1, coef=1.0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, generator=g, dtype=torch.float32)
+    if power != 1:
+        x = x ** power
+    return (x * coef).to(torch.bfloat16)
+
+
+def check_exact(got, ref, names):
+    for g, r, nm in zip(got, ref, names):
+        if r.dtype == torch.float8_e4m3fn:
+            assert_bits_equal(g, r, nm)
+        else:
+            assert_f32_equal(g, r, nm)
+
+
+def check_fused(got_q, ref_q, got_s, ref_s, what, round_scale=False):
+    """codes / scales of a fused variant.  With power-of-two scales a last-bit difference
+    in the block maximum can move a scale by a factor of two; such blocks (rare) are
+    counted against the scale tolerance budget instead."""
+    if not round_scale:
+        assert_scales_close(got_s, ref_s, what + " scale")
+        assert_codes_close(got_q, ref_q, what + " codes")
+    else:
+        g = got_s.detach().float().cpu().reshape(-1)
+        r = ref_s.detach().float().cpu().reshape(-1)
+        frac = (g != r).float().mean().item()
+        assert frac <= 1e-3, f"{what}: {frac:.2e} of power-of-two scales differ"
+        if frac == 0:
+            assert_codes_close(got_q, ref_q, what + " codes")
+
+
+# ------------------------------------------------------------------------------------
+# e4m3 conversion: every bf16 value with |x| <= 448 through a unit scale
+# ------------------------------------------------------------------------------------
+def test_e4m3_cast_exhaustive():
+    from linghe_b200.quant.group import triton_group_quant
+    allb = torch.arange(65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    ok = torch.isfinite(allb.float()) & (allb.float().abs() <= 448)
+    vals = allb[ok]
+    n = vals.numel()
+    rows = (n + 126) // 127
+    x = torch.zeros(rows * 127, dtype=torch.bfloat16)
+    x[:n] = vals
+    x = torch.cat([x.view(rows, 127), torch.full((rows, 1), 448.0, dtype=torch.bfloat16)], 1).contiguous()
+    q, s = triton_group_quant(_cuda(x))
+    rq, rs = O.group_quant(x)
+    assert_f32_equal(s, rs, "scale")
+    assert_bits_equal(q, rq, "codes")
+    assert float(s.min()) == 1.0 and float(s.max()) == 1.0
+
+
+# ------------------------------------------------------------------------------------
+# pure quantisers: bit-exact
+# ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["n1", "n3"])
+@pytest.mark.parametrize("rs", [0, 1])
+def test_golden_quant(tag, rs):
+    from linghe_b200.quant.block import triton_blockwise_quant
+    from linghe_b200.quant.group import triton_group_quant
+    G = golden("quant")
+    x = _cuda(bf16(G[f"x_{tag}"]))
+    q, s = triton_group_quant(x, round_scale=bool(rs))
+    assert_bits_equal(q, fp8(G[f"group_{tag}_r{rs}_q"]), "group q")
+    assert_f32_equal(s, torch.from_numpy(G[f"group_{tag}_r{rs}_s"]), "group s")
+    out = triton_blockwise_quant(x, round_scale=bool(rs))
+    p = f"blockwise_{tag}_r{rs}_"
+    check_exact(out, (fp8(G[p + "q"]), torch.from_numpy(G[p + "s"]), fp8(G[p + "qt"]), torch.from_numpy(G[p + "st"])),
+                ("q", "s", "qt", "st"))
+
+
+def test_golden_quant_f32_block_batch():
+    from linghe_b200.quant.block import triton_blockwise_quant, triton_block_quant, triton_batch_blockwise_quant
+    G = golden("quant")
+    out = triton_blockwise_quant(_cuda(torch.from_numpy(G["x_f32"])))
+    p = "blockwise_f32_r0_"
+    check_exact(out, (fp8(G[p + "q"]), torch.from_numpy(G[p + "s"]), fp8(G[p + "qt"]), torch.from_numpy(G[p + "st"])),
+                ("q", "s", "qt", "st"))
+    for rs in (0, 1):
+        q, s = triton_block_quant(_cuda(bf16(G["w"])), round_scale=bool(rs))
+        assert_bits_equal(q, fp8(G[f"block_r{rs}_q"]), "block q")
+        assert_f32_equal(s, torch.from_numpy(G[f"block_r{rs}_s"]), "block s")
+        counts = G["xb_counts"].tolist()
+        for dt in (torch.int32, torch.int64):
+            out = triton_batch_blockwise_quant(_cuda(bf16(G["xb"])), torch.tensor(counts, dtype=dt, device=DEV),
+                                               counts, round_scale=bool(rs))
+            p = f"batchq_r{rs}_"
+            check_exact(out, (fp8(G[p + "q"]), torch.from_numpy(G[p + "s"]), fp8(G[p + "qt"]),
+                              torch.from_numpy(G[p + "st"])), ("q", "s", "qt", "st"))
+
+
+@pytest.mark.parametrize("shape,power,dtype", [
+    ((256, 512), 3, torch.bfloat16), ((144, 384), 1, torch.bfloat16), ((4096, 2048), 3, torch.bfloat16),
+    ((1040, 1536), 2, torch.float16), ((528, 640), 3, torch.float32), ((16, 128), 1, torch.bfloat16),
+])
+@pytest.mark.parametrize("rs", [False, True])
+def test_blockwise_quant(shape, power, dtype, rs):
+    from linghe_b200.quant.block import triton_blockwise_quant
+    x = randn_bf16(shape, 1, power).to(dtype)
+    if dtype == torch.float32:
+        x = x * 1.2345
+    x[3, :128] = 0
+    ref = O.blockwise_quant(x, rs)
+    xd = _cuda(x)
+    out = triton_blockwise_quant(xd, round_scale=rs, output_mode=2)
+    check_exact(out, ref, ("q", "s", "qt", "st"))
+    o0 = triton_blockwise_quant(xd, round_scale=rs, output_mode=0)
+    check_exact(o0[:2], ref[:2], ("q", "s"))
+    o1 = triton_blockwise_quant(xd, round_scale=rs, output_mode=1)
+    check_exact(o1[2:], ref[2:], ("qt", "st"))
+
+
+def test_blockwise_quant_extremes():
+    """tiny, huge and signed-zero inputs: scale floor, division slow path, sign of zero"""
+    from linghe_b200.quant.block import triton_blockwise_quant
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((256, 256), generator=g)
+    x[:128, :128] *= 1e-35          # below the scale floor
+    x[:128, 128:] *= 1e30
+    x[128:, :128] *= 3e-29          # scale just above the floor
+    x[200] = 0
+    x[201] = -0.0
+    x[128:, 130] = -0.0
+    ref = O.blockwise_quant(x, False)
+    out = triton_blockwise_quant(_cuda(x))
+    check_exact(out, ref, ("q", "s", "qt", "st"))
+    xb = x.to(torch.bfloat16)
+    check_exact(triton_blockwise_quant(_cuda(xb)), O.blockwise_quant(xb, False), ("q", "s", "qt", "st"))
+
+
+@pytest.mark.parametrize("M,N", [(2049, 1024), (16, 128), (300, 2048)])
+def test_group_quant(M, N):
+    from linghe_b200.quant.group import triton_group_quant
+    x = randn_bf16((M, N), 2, 3)
+    for rs in (False, True):
+        q, s = triton_group_quant(_cuda(x), round_scale=rs)
+        rq, rsx = O.group_quant(x, rs)
+        assert_bits_equal(q, rq, "q")
+        assert_f32_equal(s, rsx, "s")
+
+
+def test_block_quant():
+    from linghe_b200.quant.block import triton_block_quant
+    x = randn_bf16((512, 768), 3, 3)
+    for rs in (False, True):
+        q, s = triton_block_quant(_cuda(x), round_scale=rs)
+        rq, rsx = O.block_quant(x, rs)
+        assert_bits_equal(q, rq, "q")
+        assert_f32_equal(s, rsx, "s")
+
+
+@pytest.mark.parametrize("counts", [[5, 0, 130, 128, 1, 257, 0, 64], [16] * 40, [0, 0, 384], [1000]])
+def test_batch_blockwise_quant(counts):
+    from linghe_b200.quant.block import triton_batch_blockwise_quant
+    R = sum(counts)
+    x = randn_bf16((R, 256), 4)
+    ref = O.batch_blockwise_quant(x, counts, True)
+    out = triton_batch_blockwise_quant(_cuda(x), torch.tensor(counts, dtype=torch.int64, device=DEV), counts,
+                                       round_scale=True)
+    check_exact(out, ref, ("q", "s", "qt", "st"))
+
+
+# ------------------------------------------------------------------------------------
+# RMSNorm
+# ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["n1", "n2"])
+@pytest.mark.parametrize("rs", [0, 1])
+def test_golden_rms_block_quant(tag, rs):
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    G = golden("norm")
+    x, g = _cuda(bf16(G[f"x_{tag}"])), _cuda(bf16(G[f"gamma_{tag}"]))
+    p = f"rmsq_{tag}_r{rs}_"
+    q, s, r, qt, st = triton_rms_norm_and_block_quant_forward(x, g, round_scale=bool(rs), output_mode=2)
+    assert_scales_close(r, torch.from_numpy(G[p + "r"]), "rms")
+    check_fused(q, fp8(G[p + "q"]), s, torch.from_numpy(G[p + "s"]), "row", bool(rs))
+    check_fused(qt, fp8(G[p + "qt"]), st, torch.from_numpy(G[p + "st"]), "col", bool(rs))
+
+
+@pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (384, 4096), (130, 8192), (64, 128), (2048, 1664)])
+def test_rms_block_quant_modes(M, n):
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    x = randn_bf16((M, n), 7, 2)
+    g = randn_bf16((n,), 8)
+    rq, rs, rr, rqt, rst = O.rms_norm_and_block_quant_forward(x, g, 1e-6, False)
+    xd, gd = _cuda(x), _cuda(g)
+    q, s, r, _, _ = triton_rms_norm_and_block_quant_forward(xd, gd, output_mode=0)
+    assert_scales_close(r, rr, "rms")
+    check_fused(q, rq, s, rs, "mode0 row")
+    o = triton_rms_norm_and_block_quant_forward(xd, gd, rms=r, output_mode=1)
+    assert o[0] is None and o[1] is None and o[2] is r
+    check_fused(o[3], rqt, o[4], rst, "mode1 col")
+    q, s, r2, qt, st = triton_rms_norm_and_block_quant_forward(xd, gd, output_mode=2)
+    check_fused(q, rq, s, rs, "mode2 row")
+    check_fused(qt, rqt, st, rst, "mode2 col")
+    assert_scales_close(r2, rr, "rms2")
+    # round_scale path
+    rq, rs, _, rqt, rst = O.rms_norm_and_block_quant_forward(x, g, 1e-6, True)
+    q, s, _, qt, st = triton_rms_norm_and_block_quant_forward(xd, gd, round_scale=True, output_mode=2)
+    check_fused(q, rq, s, rs, "pow2 row", True)
+    check_fused(qt, rqt, st, rst, "pow2 col", True)
+
+
+@pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (4096, 4096), (130, 8192), (96, 256)])
+def test_rms_fwd_bwd(M, n):
+    from linghe_b200.utils.norm import triton_rms_norm_forward, triton_rms_norm_backward
+    x = randn_bf16((M, n), 11)
+    g = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(12))).to(torch.bfloat16)
+    dy = randn_bf16((M, n), 13, 1, 0.01)
+    xd, gd, dyd = _cuda(x), _cuda(g), _cuda(dy)
+    y, r = triton_rms_norm_forward(xd, gd)
+    assert_rel_close(y, O.rms_norm_forward(x, g), "y", 1e-2)
+    assert_scales_close(r, O.rms_recip(x), "rms")
+    y2, r2 = triton_rms_norm_forward(xd, gd, rms=r)
+    assert r2 is r and torch.equal(y2, y)
+    rdx, rdw = O.rms_norm_backward(x, g, dy)
+    for rms in (None, r):
+        dx, dw = triton_rms_norm_backward(dyd, xd, gd, rms=rms)
+        assert dw.dtype == torch.float32 and tuple(dw.shape) == (n,)
+        assert_rel_close(dx, rdx, "dx", 1e-2)
+        assert_rel_close(dw, rdw, "dgamma", 1e-3, 1e-5)
+    # 3-D input as the facade passes it
+    dx3, dw3 = triton_rms_norm_backward(dyd.view(2, M // 2, n), xd.view(2, M // 2, n), gd)
+    assert dx3.shape == (2, M // 2, n) and torch.equal(dx3.view(M, n), dx)
+
+
+def test_golden_rms_fwd_bwd():
+    from linghe_b200.utils.norm import triton_rms_norm_forward, triton_rms_norm_backward
+    G = golden("norm")
+    for tag in ("n1", "n2"):
+        x, g, dy = (_cuda(bf16(G[f"{k}_{tag}"])) for k in ("x", "gamma", "dy"))
+        y, _ = triton_rms_norm_forward(x, g)
+        assert_rel_close(y, bf16(G[f"rmsfwd_{tag}_y"]), "y", 1e-2)
+        dx, dw = triton_rms_norm_backward(dy, x, g)
+        assert_rel_close(dx, bf16(G[f"rmsbwd_{tag}_dx"]), "dx", 1e-2)
+        assert_rel_close(dw.to(torch.bfloat16), bf16(G[f"rmsbwd_{tag}_dw"]), "dw", 1e-2)
+
+
+def test_rms_bwd_fused_dy_quant():
+    from linghe_b200.utils.norm import rms_norm_backward_and_block_quant
+    M, n = 1024, 2048
+    x = randn_bf16((M, n), 21)
+    g = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(22))).to(torch.bfloat16)
+    dy = randn_bf16((M, n), 23, 1, 0.01)
+    dx, dw, q, s, qt, st = rms_norm_backward_and_block_quant(_cuda(dy), _cuda(x), _cuda(g))
+    rdx, rdw = O.rms_norm_backward(x, g, dy)
+    assert_rel_close(dx, rdx, "dx", 1e-2)
+    assert_rel_close(dw, rdw, "dgamma", 1e-3, 1e-5)
+    check_exact((q, s, qt, st), O.blockwise_quant(dy, False), ("dy q", "dy s", "dy qt", "dy st"))
+
+
+# ------------------------------------------------------------------------------------
+# SwiGLU dense
+# ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag,rs", [("c1", 0), ("c1", 1), ("c100", 0), ("c0", 0)])
+def test_golden_silu(tag, rs):
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward, triton_silu_and_block_quant_backward
+    G = golden("silu")
+    x, g = _cuda(bf16(G[f"x_{tag}"])), _cuda(bf16(G[f"g_{tag}"]))
+    q, s, qt, st = triton_silu_and_block_quant_forward(x, round_scale=bool(rs))
+    p = f"silufwd_{tag}_r{rs}_"
+    check_fused(q, fp8(G[p + "q"]), s, torch.from_numpy(G[p + "s"]), "fwd row", bool(rs))
+    check_fused(qt, fp8(G[p + "qt"]), st, torch.from_numpy(G[p + "st"]), "fwd col", bool(rs))
+    q, s, qt, st = triton_silu_and_block_quant_backward(g, x, round_scale=bool(rs))
+    p = f"silubwd_{tag}_r{rs}_"
+    check_fused(q, fp8(G[p + "q"]), s, torch.from_numpy(G[p + "s"]), "bwd row", bool(rs))
+    check_fused(qt, fp8(G[p + "qt"]), st, torch.from_numpy(G[p + "st"]), "bwd col", bool(rs))
+
+
+@pytest.mark.parametrize("M,N,coef", [(1024, 1024, 1.0), (1000, 2816, 1.0), (512, 4096, 100.0), (256, 3072, 0.0),
+                                      (72, 256, 1.0)])
+def test_silu_fwd_modes(M, N, coef):
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward
+    x = randn_bf16((M, N), 31, 1, coef)
+    rq, rs, rqt, rst = O.silu_and_block_quant_forward(x, False)
+    xd = _cuda(x)
+    q, s, qt, st = triton_silu_and_block_quant_forward(xd, output_mode=2)
+    check_fused(q, rq, s, rs, "mode2 row")
+    check_fused(qt, rqt, st, rst, "mode2 col")
+    q, s, _, _ = triton_silu_and_block_quant_forward(xd, output_mode=0)
+    check_fused(q, rq, s, rs, "mode0 row")
+    _, _, qt, st = triton_silu_and_block_quant_forward(xd, output_mode=1)
+    check_fused(qt, rqt, st, rst, "mode1 col")
+
+
+@pytest.mark.parametrize("M,N,coef,gcoef", [(1024, 1024, 1.0, 1.0), (512, 2816, 1.0, 0.01), (256, 4096, 100.0, 100.0),
+                                            (128, 512, 0.0, 0.0)])
+def test_silu_bwd(M, N, coef, gcoef):
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_backward
+    x = randn_bf16((M, N), 41, 1, coef)
+    g = randn_bf16((M, N // 2), 42, 1, gcoef)
+    rq, rs, rqt, rst, rdx = O.silu_and_block_quant_backward(g, x, False)
+    q, s, qt, st, dx = triton_silu_and_block_quant_backward(_cuda(g), _cuda(x), return_bf16=True)
+    check_fused(q, rq, s, rs, "row")
+    check_fused(qt, rqt, st, rst, "col")
+    assert dx.dtype == torch.bfloat16
+    assert_rel_close(dx, rdx.to(torch.bfloat16), "dx bf16", 1e-2)
+    out4 = triton_silu_and_block_quant_backward(_cuda(g), _cuda(x))
+    assert len(out4) == 4 and torch.equal(out4[0].view(torch.uint8), q.view(torch.uint8))
+
+
+@pytest.mark.parametrize("tag", ["c1", "c100", "c0"])
+def test_golden_weighted_silu(tag):
+    from linghe_b200.utils.silu import triton_weighted_silu_forward, triton_weighted_silu_backward
+    G = golden("silu")
+    x, g = _cuda(bf16(G[f"x_{tag}"])), _cuda(bf16(G[f"g_{tag}"]))
+    w = _cuda(torch.from_numpy(G[f"wrow_{tag}"]))
+    y = triton_weighted_silu_forward(x, w)
+    assert_rel_close(y, bf16(G[f"wsilu_{tag}_y"]), "y", 1e-2)
+    dx, dw = triton_weighted_silu_backward(g, x, w)
+    assert_rel_close(dx, bf16(G[f"wsilubwd_{tag}_dx"]), "dx", 1e-2)
+    assert dw.shape == w.shape and dw.dtype == w.dtype
+    rate = 100.0 ** 1.5 if tag == "c100" else 1.0
+    assert_rel_close(dw, torch.from_numpy(G[f"wsilubwd_{tag}_dw"]), "dw", 1e-3, 1e-3 * rate)
+    y0 = triton_weighted_silu_forward(x)
+    assert_rel_close(y0, O.weighted_silu_forward(bf16(G[f"x_{tag}"])), "y unweighted", 1e-2)
+    dx0, dw0 = triton_weighted_silu_backward(g, x)
+    assert dw0 is None
+    assert_rel_close(dx0, O.weighted_silu_backward(bf16(G[f"g_{tag}"]), bf16(G[f"x_{tag}"]))[0].to(torch.bfloat16),
+                     "dx unweighted", 1e-2)
+
+
+# ------------------------------------------------------------------------------------
+# SwiGLU per-expert batched
+# ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag", ["c1", "c100"])
+def test_golden_batch_silu(tag):
+    from linghe_b200.utils.silu import (triton_batch_weighted_silu_and_block_quant_forward,
+                                        triton_batch_weighted_silu_and_block_quant_backward)
+    G = golden("batch")
+    counts = G["counts"].tolist()
+    x, g = _cuda(bf16(G[f"x_{tag}"])), _cuda(bf16(G[f"g_{tag}"]))
+    w = _cuda(torch.from_numpy(G[f"w_{tag}"]))
+    ct = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    q, s, qt, st = triton_batch_weighted_silu_and_block_quant_forward(x, w, ct, counts)
+    check_fused(q, fp8(G[f"bfwd_{tag}_q"]), s, torch.from_numpy(G[f"bfwd_{tag}_s"]), "fwd row")
+    check_fused(qt, fp8(G[f"bfwd_{tag}_qt"]), st, torch.from_numpy(G[f"bfwd_{tag}_st"]), "fwd col")
+    q, s, dw, qt, st = triton_batch_weighted_silu_and_block_quant_backward(g, x, w, ct, splits=counts)
+    check_fused(q, fp8(G[f"bbwd_{tag}_q"]), s, torch.from_numpy(G[f"bbwd_{tag}_s"]), "bwd row")
+    check_fused(qt, fp8(G[f"bbwd_{tag}_qt"]), st, torch.from_numpy(G[f"bbwd_{tag}_st"]), "bwd col")
+    rate = 100.0 ** 1.5 if tag == "c100" else 1.0
+    assert_rel_close(dw, torch.from_numpy(G[f"bbwd_{tag}_dw"]), "dw", 1e-3, 1e-3 * rate)
+
+
+@pytest.mark.parametrize("counts,N,cdt", [
+    ([48, 0, 272, 128, 16, 0, 400, 96], 1024, torch.int32),
+    ([0, 0, 0], 512, torch.int64),
+    ([16] * 33, 256, torch.int64),
+    ([1536], 2048, torch.int32),
+])
+def test_batch_silu(counts, N, cdt):
+    from linghe_b200.utils.silu import (triton_batch_weighted_silu_and_block_quant_forward,
+                                        triton_batch_weighted_silu_and_block_quant_backward)
+    R = sum(counts)
+    x = randn_bf16((R, N), 51)
+    if R > 3:
+        x[:3] = 0
+    g = randn_bf16((R, N // 2), 52, 1, 0.01)
+    w = torch.randn((R, 1), generator=torch.Generator().manual_seed(53))
+    ct = torch.tensor(counts, dtype=cdt, device=DEV)
+    rq, rs, rqt, rst = O.batch_weighted_silu_and_block_quant_forward(x, w, counts)
+    xd, wd, gd = _cuda(x), _cuda(w), _cuda(g)
+    for mode in (2, 0, 1):
+        q, s, qt, st = triton_batch_weighted_silu_and_block_quant_forward(xd, wd, ct, counts, output_mode=mode)
+        assert q.shape == (R, N // 2) and s.shape == (R, N // 256)
+        if R == 0:
+            continue
+        if mode != 1:
+            check_fused(q, rq, s, rs, f"fwd row m{mode}")
+        if mode != 0:
+            check_fused(qt, rqt, st, rst, f"fwd col m{mode}")
+    rq, rs, rdw, rqt, rst = O.batch_weighted_silu_and_block_quant_backward(g, x, w, counts)
+    q, s, dw, qt, st = triton_batch_weighted_silu_and_block_quant_backward(gd, xd, wd, ct, splits=counts)
+    assert dw.shape == w.shape and dw.dtype == w.dtype
+    if R == 0:
+        return
+    check_fused(q, rq, s, rs, "bwd row")
+    check_fused(qt, rqt, st, rst, "bwd col")
+    assert_rel_close(dw, rdw, "dw", 1e-3, 1e-3)
+
+
+# ------------------------------------------------------------------------------------
+# facade (autograd glue) with a duck-typed FP8 container
+# ------------------------------------------------------------------------------------
+class _Box:
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+class _Quantizer:
+    def __init__(self, pow2=False):
+        self.force_pow_2_scales = pow2
+        self.dtype = "e4m3"
+
+
+def test_facade_block_rms_norm():
+    from linghe_b200.facade.norm import block_rms_norm, rms_norm
+    S, B, H = 8, 16, 1024
+    x = randn_bf16((S, B, H), 61).to(DEV).requires_grad_()
+    w = randn_bf16((H,), 62).to(DEV).requires_grad_()
+    out, rms = block_rms_norm(x, w, None, _Quantizer(), _Box)
+    assert out.rowwise_data.shape == (S, B, H) and out.columnwise_data.shape == (H, S, B)
+    assert out.rowwise_scale_inv.shape == (H // 128, S * B) and out.columnwise_scale_inv.shape == (1, H)
+    assert not rms.requires_grad and out.is_2D_scaled is False
+    rq, rs, rr, rqt, rst = O.rms_norm_and_block_quant_forward(x.detach().cpu().view(S * B, H), w.detach().cpu())
+    check_fused(out.rowwise_data, rq, out.rowwise_scale_inv, rs, "row")
+    check_fused(out.columnwise_data, rqt, out.columnwise_scale_inv, rst, "col")
+    out1, _ = block_rms_norm(x, w, rms, _Quantizer(), _Box, is_recomputing=True)
+    assert out1.rowwise_data is None
+    check_fused(out1.columnwise_data, rqt, out1.columnwise_scale_inv, rst, "recompute col")
+    y = rms_norm(x, w)
+    dy = randn_bf16((S, B, H), 63, 1, 0.01).to(DEV)
+    y.backward(dy)
+    rdx, rdw = O.rms_norm_backward(x.detach().cpu().view(S * B, H), w.detach().cpu(), dy.cpu().view(S * B, H))
+    assert_rel_close(x.grad.view(S * B, H), rdx, "dx", 1e-2)
+    assert_rel_close(w.grad.float(), rdw, "dw", 1e-2, 1e-4)
+
+
+def test_facade_silu():
+    from linghe_b200.facade.silu import block_silu_impl, block_batch_weighted_silu_impl
+    S, B, H2 = 8, 16, 1024
+    x = randn_bf16((S, B, H2), 71).to(DEV)
+    out = block_silu_impl(x, _Quantizer(), _Quantizer(), _Box)
+    assert out.rowwise_data.shape == (S, B, H2 // 2) and out.columnwise_data.shape == (H2 // 2, S, B)
+    rq, rs, rqt, rst = O.silu_and_block_quant_forward(x.cpu().view(S * B, H2))
+    check_fused(out.rowwise_data, rq, out.rowwise_scale_inv, rs, "row")
+    counts = [32, 0, 160, 64]
+    R = sum(counts)
+    xb = randn_bf16((R, 512), 72).to(DEV)
+    wb = torch.randn((R, 1), generator=torch.Generator().manual_seed(73)).to(DEV)
+    ct = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    ob = block_batch_weighted_silu_impl(xb, wb, ct, counts, [_Quantizer()], [_Quantizer()], _Box)
+    rq, rs, rqt, rst = O.batch_weighted_silu_and_block_quant_forward(xb.cpu(), wb.cpu(), counts)
+    check_fused(ob.rowwise_data, rq, ob.rowwise_scale_inv, rs, "batch row")
+    check_fused(ob.columnwise_data, rqt, ob.columnwise_scale_inv, rst, "batch col")
+
+
+# ------------------------------------------------------------------------------------
+# argument errors surface as AssertionError like upstream's bare asserts
+# ------------------------------------------------------------------------------------
+def test_argument_errors():
+    from linghe_b200.quant.block import triton_blockwise_quant
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    x = torch.zeros((32, 200), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(AssertionError):
+        triton_blockwise_quant(x)
+    with pytest.raises(AssertionError):
+        triton_blockwise_quant(torch.zeros((30, 128), dtype=torch.bfloat16, device=DEV))
+    xx = torch.zeros((32, 256), dtype=torch.bfloat16, device=DEV)
+    w = torch.ones((256,), dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(AssertionError):
+        triton_rms_norm_and_block_quant_forward(xx, w, output_mode=1)  # needs rms
+    with pytest.raises(AssertionError):
+        triton_rms_norm_and_block_quant_forward(xx.t(), w)  # not contiguous
