@@ -1,0 +1,357 @@
+#!/usr/bin/env python
+"""Benchmark of the fused norm / SwiGLU + FP8 blockwise-quant hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    torchrun ... bench.py --gpus N ...           (one rank per GPU, N > 1)
+
+Workload ("scaleout-65536x8192"): per GPU, one step is
+  (1) RMSNorm + 1x128 FP8 quantisation of x bf16 [65536, 8192]   (row-wise outputs)
+  (2) SwiGLU  + 1x128 FP8 quantisation of x bf16 [65536, 16384] -> [65536, 8192]
+on seeded synthetic N(0,1) inputs; token rows are sharded across ranks with no
+data-path collective (weak scaling: every rank owns 65536 rows).  Inputs (1 GiB and
+2 GiB) are far larger than L2, so no L2 flush is needed between iterations.
+
+`value` is the aggregate algorithmic GB/s (each tensor counted once) over all ranks,
+timed on the device with CUDA events, max over ranks.  `e2e` is the same metric through
+the public Python API with HOST (pinned) inputs and outputs: host->device copies of both
+inputs and device->host copies of every output are inside the timed region.
+`--impl reference` times the CPU oracle (the reference's PyTorch math restated) on the
+host cores for a bounded row sample of the same workload.
+
+One JSON line is printed by rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+ROWS = 65536
+HIDDEN = 8192
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def norm_bytes(M, n):  # x bf16 + q fp8 + scales + rms + gamma
+    return M * n * 3 + M * (n // 128) * 4 + M * 4 + n * 2
+
+
+def silu_bytes(M, n):  # x bf16 [M,2n] + q fp8 [M,n] + scales
+    return M * 2 * n * 2 + M * n + M * (n // 128) * 4
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken during the timed region."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            f = [c.strip() for c in r.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(rank, device, rows):
+    g = torch.Generator(device=device).manual_seed(1000 + rank)
+    xn = torch.randn((rows, HIDDEN), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn((HIDDEN,), generator=g, device=device)).to(torch.bfloat16)
+    xs = torch.empty((rows, 2 * HIDDEN), device=device, dtype=torch.bfloat16)
+    half = rows // 2
+    for r0 in (0, half):  # generate in two pieces to bound the float32 temporary
+        xs[r0:r0 + half] = torch.randn((half, 2 * HIDDEN), generator=g, device=device).to(torch.bfloat16)
+    return xn, gamma, xs
+
+
+def run_ours(args, rank, world, device):
+    from linghe_b200 import _lib
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward as norm_q
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward as silu_q
+
+    _lib.load()
+    rows = args.rows
+    xn, gamma, xs = make_inputs(rank, device, rows)
+    # preallocated outputs: the timed region measures the kernels, not the allocator
+    q1 = torch.empty((rows, HIDDEN), device=device, dtype=torch.float8_e4m3fn)
+    s1 = torch.empty((HIDDEN // 128, rows), device=device, dtype=torch.float32)
+    q2 = torch.empty_like(q1)
+    s2 = torch.empty_like(s1)
+
+    def step():
+        norm_q(xn, gamma, out=q1, scale=s1, output_mode=0)
+        silu_q(xs, out=q2, scale=s2, output_mode=0)
+
+    bytes_norm, bytes_silu = norm_bytes(rows, HIDDEN), silu_bytes(rows, HIDDEN)
+    step_bytes = bytes_norm + bytes_silu
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ
+                           else int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[torch.cuda.current_device()]))
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    t_start = torch.cuda.Event(enable_timing=True)
+    t_stop = torch.cuda.Event(enable_timing=True)
+    t_start.record()
+    for i in range(K):
+        ev[i][0].record()
+        norm_q(xn, gamma, out=q1, scale=s1, output_mode=0)
+        ev[i][1].record()
+        silu_q(xs, out=q2, scale=s2, output_mode=0)
+        ev[i][2].record()
+    t_stop.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    total_ms = t_start.elapsed_time(t_stop)
+    norm_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
+    silu_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+
+    # ---- end to end through the public API with host buffers --------------------------
+    Ke = min(K, args.e2e_steps)
+    h_xn = torch.empty(xn.shape, dtype=xn.dtype, pin_memory=True).copy_(xn)
+    h_xs = torch.empty(xs.shape, dtype=xs.dtype, pin_memory=True).copy_(xs)
+    h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (q1, s1, q2, s2)]
+    h_rms = torch.empty((rows,), dtype=torch.float32, pin_memory=True)
+    h2d = h_xn.numel() * 2 + h_xs.numel() * 2
+    d2h = sum(t.numel() * t.element_size() for t in h_out) + h_rms.numel() * 4
+
+    def e2e_step():
+        dxn = h_xn.to(device, non_blocking=True)
+        dxs = h_xs.to(device, non_blocking=True)
+        a, b, r, _, _ = norm_q(dxn, gamma, output_mode=0)
+        c, d, _, _ = silu_q(dxs, output_mode=0)
+        for dst, src in zip(h_out, (a, b, c, d)):
+            dst.copy_(src, non_blocking=True)
+        h_rms.copy_(r, non_blocking=True)
+
+    del xn, xs
+    e2e_step()
+    torch.cuda.synchronize()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(Ke):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    times = torch.tensor([total_ms, e2e_ms, norm_ms, silu_ms], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    total_ms, e2e_ms, norm_ms, silu_ms = times.tolist()
+
+    if rank != 0:
+        return None
+    peak, peak_kind = measured_peak()
+    value = world * step_bytes * K / (total_ms * 1e-3) / 1e9
+    e2e_value = world * step_bytes * Ke / (e2e_ms * 1e-3) / 1e9
+    achieved = bytes_silu / (silu_ms * 1e-3) / 1e9
+    line = {
+        "metric": "achieved HBM GB/s, fused RMSNorm+FP8 quant and SwiGLU+FP8 quant (algorithmic bytes / device time)",
+        "value": round(value, 1),
+        "unit": "GB/s",
+        "n_gpus": world,
+        "steps": K,
+        "warmup": max(args.warmup, 3),
+        "ms_per_step": round(total_ms / K, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32 math, bf16 in, e4m3 out",
+        "data": "synthetic",
+        "config": {"workload": f"scaleout-{rows}x{HIDDEN}: RMSNorm+quant [{rows},{HIDDEN}] and SwiGLU+quant "
+                               f"[{rows},{2 * HIDDEN}]->[{rows},{HIDDEN}] per GPU, row-wise 1x128 outputs",
+                   "rows_per_gpu": rows, "hidden": HIDDEN, "sharding": f"rows x{world}, no collective",
+                   "l2": "inputs (1 GiB, 2 GiB) larger than L2; no flush needed",
+                   "bytes_per_step_per_gpu": step_bytes},
+        "pct_of_nominal_8TBs_per_gpu": round(100 * value / world / NOMINAL_HBM_GBS, 1),
+        "us_per_call": {"rmsnorm_quant": round(norm_ms * 1e3, 1), "swiglu_quant": round(silu_ms * 1e3, 1)},
+        "gbs_per_call": {"rmsnorm_quant": round(bytes_norm / norm_ms / 1e6, 1),
+                         "swiglu_quant": round(bytes_silu / silu_ms / 1e6, 1)},
+        "roofline": {"bound": "hbm", "kernel": "tile_kernel<SwiGLU fwd, row mode> (SwiGLU+quant)",
+                     "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
+                     "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": TRAFFIC_SWIGLU_BYTES},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": Ke},
+        "gpu_launches": 2 * K,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.cpu_rows, repeats=1)
+    return line
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the SwiGLU+quant kernel at the
+# bench size, scaled from an ncu capture of a smaller case (see profiles/); None until measured.
+TRAFFIC_SWIGLU_BYTES = None
+
+
+def cpu_baseline(rows, repeats=1):
+    """The CPU oracle (PyTorch reference math restated) on `rows` rows of the workload."""
+    from oracle import oracle as O
+    g = torch.Generator().manual_seed(7)
+    xn = torch.randn((rows, HIDDEN), generator=g).to(torch.bfloat16)
+    gamma = (1 + 0.1 * torch.randn((HIDDEN,), generator=g)).to(torch.bfloat16)
+    xs = torch.randn((rows, 2 * HIDDEN), generator=g).to(torch.bfloat16)
+    best = None
+    for _ in range(repeats + 1):  # first pass warms the allocator
+        t0 = time.perf_counter()
+        y = torch.nn.functional.rms_norm(xn.float(), (HIDDEN,), gamma.float(), 1e-6)
+        O.quant_rows_1x128(y)
+        O.rms_recip(xn)
+        O.quant_rows_1x128(O._swiglu_f32(xs))
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    nbytes = norm_bytes(rows, HIDDEN) + silu_bytes(rows, HIDDEN)
+    return {"value": round(nbytes / best / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(),
+            "kind": "port", "sample": f"{rows} of {ROWS} rows of each tensor, {best:.2f} s per pass, "
+                                      "torch CPU float32 oracle (oracle/oracle.py)"}
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's own CPU math (oracle port) on the host cores."""
+    if rank != 0:
+        return None
+    rows = args.cpu_rows
+    from oracle import oracle as O  # noqa: F401
+    res = []
+    for i in range(max(args.warmup, 1) + args.steps):
+        t0 = time.perf_counter()
+        cb = cpu_baseline(rows, repeats=0)
+        res.append((time.perf_counter() - t0, cb))
+    timed = res[max(args.warmup, 1):]
+    nbytes = norm_bytes(rows, HIDDEN) + silu_bytes(rows, HIDDEN)
+    tot = sum(float(cb["sample"].split(" rows of each tensor, ")[1].split(" s")[0]) for _, cb in timed)
+    value = nbytes * len(timed) / tot / 1e9
+    cb = dict(timed[-1][1])
+    cb["value"] = round(value, 3)
+    return {
+        "impl": "reference",
+        "metric": "achieved HBM GB/s, fused RMSNorm+FP8 quant and SwiGLU+FP8 quant (algorithmic bytes / device time)",
+        "value": round(value, 3), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 1), "ms_per_step": round(1e3 * tot / len(timed), 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 math, bf16 in, e4m3 out", "data": "synthetic",
+        "config": {"workload": f"scaleout-{ROWS}x{HIDDEN} (bounded sample: {rows} rows per step on host CPU)"},
+        "cpu_baseline": cb,
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows per GPU (default: the benchmark size)")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--cpu-rows", type=int, default=4096)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        line = run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this benchmark has no CPU path (use --impl reference)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    try:
+        line = run_ours(args, rank, world, device)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

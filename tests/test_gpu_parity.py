@@ -245,7 +245,7 @@ def test_rms_fwd_bwd(M, n):
     y2, r2 = triton_rms_norm_forward(xd, gd, rms=r)
     assert r2 is r and torch.equal(y2, y)
     rdx, rdw = O.rms_norm_backward(x, g, dy)
-    for rms in (None, r):
+    for rms in (r, None):
         dx, dw = triton_rms_norm_backward(dyd, xd, gd, rms=rms)
         assert dw.dtype == torch.float32 and tuple(dw.shape) == (n,)
         assert_rel_close(dx, rdx, "dx", 1e-2)
