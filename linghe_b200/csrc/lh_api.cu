@@ -49,6 +49,40 @@ int sm_count(int* out_device) {
     return cached[dev];
 }
 
+int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows, uint64_t cols,
+                    uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols) {
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+            set_error("cuTensorMapEncodeTiled is not available from the driver (%s)", cudaGetErrorString(e));
+            return e != cudaSuccess ? int(e) : int(cudaErrorNotSupported);
+        }
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const CUtensorMapDataType dt = dtype == LH_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : dtype == LH_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu pitch=%llu)", int(r),
+                  (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)pitch_bytes);
+        return int(cudaErrorInvalidValue);
+    }
+    return LH_OK;
+}
+
 // launchers implemented in the kernel translation units
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
@@ -63,6 +97,7 @@ int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, cons
                   float* dws, int round_scale, cudaStream_t stream);
 int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* q,
                     float* s, float* rms, int round_scale, cudaStream_t stream);
+int rows_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream);
 int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
                 float* rms, int reuse_rms, cudaStream_t stream);
 int64_t rows_norm_bwd_scratch(int64_t n);
@@ -207,6 +242,7 @@ int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void*
     if (!x || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("silu_blockquant_fwd: NULL or unaligned pointer");
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
+    if (output_mode == 0) return rows_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
     return tile_silu_fwd(x, nullptr, LH_F32, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
                          static_cast<cudaStream_t>(stream));
 }

@@ -4,6 +4,7 @@
 // the host-side error plumbing of the C ABI.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -20,6 +21,10 @@ void set_error(const char* fmt, ...);
 int fail_arg(const char* fmt, ...);      // records message, returns LH_ERR_ARG
 int check_launch(const char* what);      // cudaGetLastError -> status code
 int sm_count(int* out_device = nullptr); // SM count of the current device (cached)
+// Tiled 2-D tensor map over a row-major [rows, cols] matrix with `pitch_bytes` between
+// rows; the box is box_rows x box_cols elements, no swizzle, out-of-range reads give 0.
+int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows, uint64_t cols,
+                    uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols);
 
 // Device status word: 0 = fine; otherwise the code of the first bounded wait that
 // gave up.  Read back with lh_device_status().
@@ -155,6 +160,44 @@ __device__ __forceinline__ float sigmoid_ref(float x) {
     return __frcp_rn(1.0f + expf(-x));
 }
 
+// ---- packed float32x2 arithmetic (one FP32 pipe instruction per two lanes' worth) ----
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 splat2(float a) { return make_float2(a, a); }
+
+// two bf16 packed in a 32-bit word -> float2 (low element first)
+__device__ __forceinline__ float2 bf16x2_to_f2(uint32_t w) {
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// max(|a|, |b|, c) with the three-input max of sm_100
+__device__ __forceinline__ float max3abs(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(fabsf(a)), "f"(fabsf(b)), "f"(c));
+    return r;
+}
+
+// Fast sigmoid for a pair: 1 / (1 + 2^(-x*log2(e))) with the hardware ex2 / rcp
+// approximations (each within 2 ulp).  Relative error of the result stays below ~4e-7
+// wherever sigmoid(x) is not itself tiny, which is what bounds the error of block maxima.
+__device__ __forceinline__ float2 sigmoid_fast2(float2 x) {
+    const float2 t = mul2(x, splat2(-1.4426950408889634f));
+    const float2 e = make_float2(ex2_approx(t.x), ex2_approx(t.y));
+    const float2 d = add2(e, splat2(1.0f));
+    return make_float2(rcp_approx(d.x), rcp_approx(d.y));
+}
+
 // ----------------------------------------------------------------------------------
 // mbarrier + bulk copy (TMA) wrappers.  Every wait is bounded.
 // ----------------------------------------------------------------------------------
@@ -208,6 +251,18 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32
                      smem_u32(dst_smem)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+// 2-D tiled tensor copy global -> shared through a tensor map (one instruction per tile).
+// x = element column (x * element size must be a multiple of 16 bytes), y = row.
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst_smem)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 // shared -> global bulk copy tracked by the thread's bulk async-group.
 __device__ __forceinline__ void bulk_s2g(void* dst, const void* src_smem, uint32_t bytes) {

@@ -1,22 +1,20 @@
-// Row-slab kernels: operations that need a whole row before anything can be emitted
-// (RMSNorm forward with 1x128 quantisation or plain output, RMSNorm backward).
+// Row-slab kernels: RMSNorm forward (+1x128 FP8 quantisation, or plain), RMSNorm backward,
+// and SwiGLU forward + 1x128 quantisation -- the operations whose outputs depend on a
+// whole row or on nothing outside a 1x128 block, so they stream rows through the SM.
 //
-// Execution model (sm_100a): persistent CTAs walk slabs of RB complete rows
-// (RB * n <= 8192 elements).  A producer warp brings each slab in with ONE bulk
-// asynchronous copy per operand (rows are contiguous in memory) into a shared-memory
-// ring guarded by mbarriers; consumer threads each own EPT contiguous elements of the
-// slab, pull them into registers (releasing the ring slot at once), reduce the per-row
-// sums through shuffles + one named barrier, and stage the outputs in shared memory
-// from where one bulk copy per slab writes them back.  No tensor cores: HBM-bound.
+// Execution model (sm_100a): persistent CTAs walk slabs of at most 8192 output elements
+// (RB complete rows, or a column chunk of one long row).  Warp 0 brings each slab into a
+// shared-memory ring with bulk asynchronous copies (TMA; rows are contiguous, so one copy
+// per operand and row run) that complete on an mbarrier.  Every thread owns EPT
+// contiguous elements: it pulls them into registers (freeing the ring slot at once), does
+// the arithmetic with packed float32x2 instructions, reduces per-row sums through
+// shuffles and one named barrier, and stages the outputs in shared memory from where one
+// bulk copy per slab writes them back.  No tensor cores: the path is HBM-bound.
 #include "lh_common.cuh"
-
-#ifndef LH_ROWS_EXACT
-#define LH_ROWS_EXACT true
-#endif
 
 namespace lh {
 
-enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2 };
+enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3 };
 
 constexpr int kSlabElems = 8192;
 constexpr int kMaxRowCtas = 296;
@@ -29,10 +27,11 @@ struct RowParams {
     int reuse_rms;
     float eps;
     int64_t M;
-    int n;
+    int n;               // output columns
     int RB;              // rows per slab
-    uint8_t* q;          // ROP_NORM_Q: codes [M,n]
-    float* s;            // ROP_NORM_Q: scales [n/128, M]
+    int chunks;          // column chunks per row (1 unless n > 8192)
+    uint8_t* q;          // *_Q: codes [M,n]
+    float* s;            // *_Q: scales [n/128, M]
     uint8_t* hp;         // ROP_NORM_Y: y [M,n]; ROP_NORM_BWD: dx [M,n]
     float* partial;      // ROP_NORM_BWD: [gridDim.x, n] per-CTA dgamma partial sums
     int round_scale;
@@ -40,26 +39,53 @@ struct RowParams {
 
 template <int ROP, int EPT, int STAGES>
 struct RowCfg {
-    static constexpr int NIN = ROP == ROP_NORM_BWD ? 2 : 1;
-    static constexpr int NT = kSlabElems / EPT;       // consumer threads
+    static constexpr int NIN = (ROP == ROP_NORM_BWD || ROP == ROP_SILU_Q) ? 2 : 1;
+    static constexpr bool QUANT = ROP == ROP_NORM_Q || ROP == ROP_SILU_Q;
+    static constexpr int NT = kSlabElems / EPT;       // threads
     static constexpr int NW = NT / 32;
-    static constexpr int NTHREADS = NT;
     static constexpr int SLABB = kSlabElems * 2;      // bytes of one operand slab (16-bit inputs)
     static constexpr int STAGEB = NIN * SLABB;
-    static constexpr int OUTB = ROP == ROP_NORM_Q ? kSlabElems : kSlabElems * 2;
+    static constexpr int OUTB = QUANT ? kSlabElems : kSlabElems * 2;
     static constexpr int OFF_STAGES = 0;
-    static constexpr int OFF_OUT = STAGES * STAGEB;   // two output buffers
+    static constexpr int OFF_OUT = STAGES * STAGEB;               // two output buffers
     static constexpr int OFF_RED = OFF_OUT + 2 * OUTB;            // [2][2][64] partial sums
     static constexpr int OFF_BAR = OFF_RED + 2 * 2 * 64 * 4;
     static constexpr int SMEM = OFF_BAR + 2 * STAGES * 8;
 };
 
+struct SlabLoc {
+    int64_t row0;
+    int rows;   // valid rows
+    int c0;     // first column
+    int ncols;  // columns in this slab
+};
+
+__device__ __forceinline__ SlabLoc slab_loc(int64_t slab, const RowParams& p) {
+    SlabLoc L;
+    if (p.chunks == 1) {
+        L.row0 = slab * p.RB;
+        const int64_t left = p.M - L.row0;
+        L.rows = left < p.RB ? int(left) : p.RB;
+        L.c0 = 0;
+        L.ncols = p.n;
+    } else {
+        L.row0 = slab / p.chunks;
+        L.rows = 1;
+        L.c0 = int(slab - L.row0 * p.chunks) * kSlabElems;
+        L.ncols = p.n - L.c0 < kSlabElems ? p.n - L.c0 : kSlabElems;
+    }
+    return L;
+}
+
 template <int ROP, int EPT, int STAGES, int MINB>
-__global__ void __launch_bounds__(RowCfg<ROP, EPT, STAGES>::NTHREADS, MINB)
+__global__ void __launch_bounds__(RowCfg<ROP, EPT, STAGES>::NT, MINB)
 rows_kernel(const __grid_constant__ RowParams p) {
     using C = RowCfg<ROP, EPT, STAGES>;
-    constexpr int NT = C::NT, NW = C::NW, NCH = EPT / 8;  // 16-byte chunks per thread and operand
-    constexpr int LPB = 128 / EPT;                         // lanes per 128-element block
+    constexpr int NT = C::NT, NW = C::NW;
+    constexpr int NCH = EPT / 8;     // 16-byte chunks per thread and operand
+    constexpr int NP = EPT / 2;      // float2 pairs per thread
+    constexpr int LPB = 128 / EPT;   // lanes per 128-element block
+    constexpr bool NORM = ROP != ROP_SILU_Q;
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stages = smem + C::OFF_STAGES;
     uint8_t* outb = smem + C::OFF_OUT;
@@ -69,8 +95,8 @@ rows_kernel(const __grid_constant__ RowParams p) {
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int n = p.n, RB = p.RB;
-    const int64_t slabs = (p.M + RB - 1) / RB;
+    const int n = p.n;
+    const int64_t slabs = p.chunks == 1 ? (p.M + p.RB - 1) / p.RB : p.M * p.chunks;
 
     if (tid == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -81,55 +107,71 @@ rows_kernel(const __grid_constant__ RowParams p) {
     }
     __syncthreads();
 
-    // Thread 0 doubles as the producer: one bulk copy per operand and slab.
+    // Warp 0 doubles as the producer.
     auto issue = [&](int64_t slab, int stage) {
-        const int64_t r0 = slab * RB;
-        const int nrows = int(p.M - r0 < RB ? p.M - r0 : RB);
-        const uint32_t bytes = uint32_t(nrows) * uint32_t(n) * 2u;
+        const SlabLoc L = slab_loc(slab, p);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
-        mbar_expect_tx(&full[stage], bytes * C::NIN);
-        bulk_g2s(dst, p.x + r0 * n * 2, bytes, &full[stage]);
-        if constexpr (C::NIN == 2) bulk_g2s(dst + C::SLABB, p.dy + r0 * n * 2, bytes, &full[stage]);
+        if constexpr (ROP == ROP_SILU_Q) {
+            // x is [M, 2n]: gate half and up half of every row are separate runs
+            const uint32_t run = uint32_t(L.ncols) * 2u;
+            if (lane == 0) mbar_expect_tx(&full[stage], run * 2u * uint32_t(L.rows));
+            __syncwarp();
+            for (int r = lane; r < L.rows; r += 32) {
+                const uint8_t* src = p.x + ((L.row0 + r) * 2 * int64_t(n) + L.c0) * 2;
+                bulk_g2s(dst + size_t(r) * run, src, run, &full[stage]);
+                bulk_g2s(dst + C::SLABB + size_t(r) * run, src + size_t(n) * 2, run, &full[stage]);
+            }
+        } else {
+            if (lane == 0) {
+                const uint32_t bytes = uint32_t(L.rows) * uint32_t(n) * 2u;
+                mbar_expect_tx(&full[stage], bytes * C::NIN);
+                bulk_g2s(dst, p.x + L.row0 * n * 2, bytes, &full[stage]);
+                if constexpr (ROP == ROP_NORM_BWD) bulk_g2s(dst + C::SLABB, p.dy + L.row0 * n * 2, bytes, &full[stage]);
+            }
+        }
     };
-    if (tid == 0) {
+    if (warp == 0) {
         int64_t slab = blockIdx.x;
         for (int j = 0; j < STAGES && slab < slabs; ++j, slab += gridDim.x) issue(slab, j);
     }
 
-    // ================================ consumers ===================================
     const int t = tid;
     const int e0 = t * EPT;                        // first element of this thread inside the slab
-    const int my_row = e0 / n;                     // row inside the slab
-    const int col0 = e0 - my_row * n;              // first column
-    const bool in_slab = my_row < RB;              // threads beyond RB*n idle (n not dividing 8192)
-    const int TPR = n / EPT;                       // threads per row
-    const bool warp_rows = (TPR % 32) == 0;        // rows are made of whole warps
-    const int nb = n >> 7;
     const int sw = NCH == 4 ? ((t >> 1) & 3) : ((t >> 2) & 1);  // bank-conflict-free chunk order
     const bool rs = p.round_scale != 0;
 
-    // gamma for this thread's columns, in the (swizzled) chunk order used for x
-    float gam[EPT];
-    if (in_slab) {
+    // For the norm kernels a slab is RB full rows, so a thread's columns never change:
+    // keep gamma for them in registers, in the (swizzled) chunk order used for x.
+    float2 gam[NORM ? NP : 1];
+    int my_row = 0, col0 = 0;
+    bool in_slab = true;
+    if constexpr (NORM) {
+        my_row = e0 / n;
+        col0 = e0 - my_row * n;
+        in_slab = my_row < p.RB;
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.gamma) +
-                                                              (col0 + 8 * (k ^ sw)) * 2);
-            Elem<__nv_bfloat16>::unpack8(raw, gam + 8 * k);
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (in_slab)
+                raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.gamma) + (col0 + 8 * (k ^ sw)) * 2);
+            gam[4 * k + 0] = bf16x2_to_f2(raw.x);
+            gam[4 * k + 1] = bf16x2_to_f2(raw.y);
+            gam[4 * k + 2] = bf16x2_to_f2(raw.z);
+            gam[4 * k + 3] = bf16x2_to_f2(raw.w);
         }
-    } else {
-#pragma unroll
-        for (int i = 0; i < EPT; ++i) gam[i] = 0.f;
     }
-    float acc[ROP == ROP_NORM_BWD ? EPT : 1];
+    const int TPR = n / EPT;                       // threads per row (norm kernels)
+    const bool warp_rows = (TPR % 32) == 0;        // rows are made of whole warps
+    const int nb = n >> 7;
+    float2 acc[ROP == ROP_NORM_BWD ? NP : 1];
 #pragma unroll
-    for (int i = 0; i < (ROP == ROP_NORM_BWD ? EPT : 1); ++i) acc[i] = 0.f;
+    for (int i = 0; i < (ROP == ROP_NORM_BWD ? NP : 1); ++i) acc[i] = make_float2(0.f, 0.f);
 
     int it = 0;
     for (int64_t slab = blockIdx.x; slab < slabs; slab += gridDim.x, ++it) {
         const int stage = it % STAGES;
         const int buf = it & 1;
-        if (tid == 0 && it > 0) {
+        if (warp == 0 && it > 0) {
             // every warp released stage (it-1)%STAGES before the barriers of iteration it-1
             const int64_t nxt = slab + int64_t(STAGES - 1) * gridDim.x;
             if (nxt < slabs) {
@@ -137,142 +179,160 @@ rows_kernel(const __grid_constant__ RowParams p) {
                 if (mbar_wait(&empty[ps], ((it - 1) / STAGES) & 1, DEVERR_EMPTY_WAIT)) issue(nxt, ps);
             }
         }
-        const int64_t row0 = slab * RB;
-        const int rows = int(p.M - row0 < RB ? p.M - row0 : RB);
-        const bool active = in_slab && my_row < rows;
+        const SlabLoc L = slab_loc(slab, p);
+        if constexpr (!NORM) {
+            my_row = e0 / L.ncols;
+            col0 = L.c0 + (e0 - my_row * L.ncols);
+        }
+        const bool active = in_slab && my_row < L.rows;
         if (!mbar_wait(&full[stage], (it / STAGES) & 1, DEVERR_FULL_WAIT)) return;
         const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
 
-        float x[EPT];
-        float g[ROP == ROP_NORM_BWD ? EPT : 1];
-        {
-            uint4 raw[NCH];
+        float2 x[NP];
+        float2 g[C::NIN == 2 ? NP : 1];
 #pragma unroll
-            for (int k = 0; k < NCH; ++k) raw[k] = *reinterpret_cast<const uint4*>(sx + 16 * (k ^ sw));
-            if constexpr (ROP == ROP_NORM_BWD) {
-                uint4 rawg[NCH];
+        for (int k = 0; k < NCH; ++k) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(sx + 16 * (k ^ sw));
+            x[4 * k + 0] = bf16x2_to_f2(raw.x);
+            x[4 * k + 1] = bf16x2_to_f2(raw.y);
+            x[4 * k + 2] = bf16x2_to_f2(raw.z);
+            x[4 * k + 3] = bf16x2_to_f2(raw.w);
+        }
+        if constexpr (C::NIN == 2) {
 #pragma unroll
-                for (int k = 0; k < NCH; ++k)
-                    rawg[k] = *reinterpret_cast<const uint4*>(sx + C::SLABB + 16 * (k ^ sw));
-#pragma unroll
-                for (int k = 0; k < NCH; ++k) Elem<__nv_bfloat16>::unpack8(rawg[k], g + 8 * k);
+            for (int k = 0; k < NCH; ++k) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(sx + C::SLABB + 16 * (k ^ sw));
+                g[4 * k + 0] = bf16x2_to_f2(raw.x);
+                g[4 * k + 1] = bf16x2_to_f2(raw.y);
+                g[4 * k + 2] = bf16x2_to_f2(raw.z);
+                g[4 * k + 3] = bf16x2_to_f2(raw.w);
             }
-#pragma unroll
-            for (int k = 0; k < NCH; ++k) Elem<__nv_bfloat16>::unpack8(raw[k], x + 8 * k);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);   // data is in registers: free the slot
         if (!active) {
 #pragma unroll
-            for (int i = 0; i < EPT; ++i) x[i] = 0.f;
+            for (int i = 0; i < NP; ++i) x[i] = make_float2(0.f, 0.f);
+            if constexpr (C::NIN == 2) {
+#pragma unroll
+                for (int i = 0; i < NP; ++i) g[i] = make_float2(0.f, 0.f);
+            }
+        }
+
+        float r = 0.f, tot_sc = 0.f;
+        if constexpr (NORM) {
+            // ---- per-row sums: sum x^2 (unless 1/rms is given) and, backward, sum x*g*gamma
+            float2 ss2 = make_float2(0.f, 0.f), sc2 = make_float2(0.f, 0.f);
+            if (!p.reuse_rms) {
+#pragma unroll
+                for (int i = 0; i < NP; ++i) ss2 = fma2(x[i], x[i], ss2);
+            }
             if constexpr (ROP == ROP_NORM_BWD) {
 #pragma unroll
-                for (int i = 0; i < EPT; ++i) g[i] = 0.f;
+                for (int i = 0; i < NP; ++i) sc2 = fma2(x[i], mul2(g[i], gam[i]), sc2);
             }
+            float ss = ss2.x + ss2.y, sc = sc2.x + sc2.y;
+            float* red_ss = red + buf * 128;
+            float* red_sc = red + buf * 128 + 64;
+            if (warp_rows) {
+#pragma unroll
+                for (int d = 16; d >= 1; d >>= 1) {
+                    ss += __shfl_xor_sync(0xffffffffu, ss, d);
+                    if constexpr (ROP == ROP_NORM_BWD) sc += __shfl_xor_sync(0xffffffffu, sc, d);
+                }
+                if (lane == 0) { red_ss[warp] = ss; if constexpr (ROP == ROP_NORM_BWD) red_sc[warp] = sc; }
+            } else {
+#pragma unroll
+                for (int d = LPB / 2; d >= 1; d >>= 1) {
+                    ss += __shfl_xor_sync(0xffffffffu, ss, d);
+                    if constexpr (ROP == ROP_NORM_BWD) sc += __shfl_xor_sync(0xffffffffu, sc, d);
+                }
+                if ((t % LPB) == 0) { red_ss[t / LPB] = ss; if constexpr (ROP == ROP_NORM_BWD) red_sc[t / LPB] = sc; }
+            }
+            if (t == 0) bulk_wait_read<1>();               // output buffer `buf` is free again
+            named_bar<1, NT>();
+            float tot_ss = 0.f;
+            if (in_slab) {
+                const int cnt = warp_rows ? TPR / 32 : nb;
+                const int first = my_row * cnt;
+                for (int i = 0; i < cnt; ++i) {
+                    tot_ss += red_ss[first + i];
+                    if constexpr (ROP == ROP_NORM_BWD) tot_sc += red_sc[first + i];
+                }
+            }
+            if (p.reuse_rms) {
+                r = active ? p.rms[L.row0 + my_row] : 0.f;
+            } else {
+                r = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(tot_ss, float(n)), p.eps)));
+                if (active && col0 == 0 && p.rms != nullptr) p.rms[L.row0 + my_row] = r;
+            }
+        } else {
+            if (t == 0) bulk_wait_read<1>();
+            named_bar<1, NT>();
         }
 
-        // ---- per-row sums: sum x^2 (unless 1/rms is given) and, backward, sum x*g*gamma
-        float ss = 0.f, sc = 0.f;
-        if (!p.reuse_rms) {
+        if constexpr (C::QUANT) {
+            if constexpr (ROP == ROP_NORM_Q) {
+                const float2 r2 = splat2(r);
 #pragma unroll
-            for (int i = 0; i < EPT; ++i) ss = fmaf(x[i], x[i], ss);
-        }
-        if constexpr (ROP == ROP_NORM_BWD) {
+                for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(x[i], r2), gam[i]);
+            } else {
 #pragma unroll
-            for (int i = 0; i < EPT; ++i) sc = fmaf(x[i], g[i] * gam[i], sc);
-        }
-        float* red_ss = red + buf * 128;
-        float* red_sc = red + buf * 128 + 64;
-        if (warp_rows) {
-#pragma unroll
-            for (int d = 16; d >= 1; d >>= 1) {
-                ss += __shfl_xor_sync(0xffffffffu, ss, d);
-                if constexpr (ROP == ROP_NORM_BWD) sc += __shfl_xor_sync(0xffffffffu, sc, d);
+                for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(sigmoid_fast2(x[i]), x[i]), g[i]);
             }
-            if (lane == 0) { red_ss[warp] = ss; if constexpr (ROP == ROP_NORM_BWD) red_sc[warp] = sc; }
-        } else {
-#pragma unroll
-            for (int d = LPB / 2; d >= 1; d >>= 1) {
-                ss += __shfl_xor_sync(0xffffffffu, ss, d);
-                if constexpr (ROP == ROP_NORM_BWD) sc += __shfl_xor_sync(0xffffffffu, sc, d);
-            }
-            if ((t % LPB) == 0) { red_ss[t / LPB] = ss; if constexpr (ROP == ROP_NORM_BWD) red_sc[t / LPB] = sc; }
-        }
-        if (t == 0) bulk_wait_read<1>();               // output buffer `buf` is free again
-        named_bar<1, NT>();
-        float tot_ss = 0.f, tot_sc = 0.f;
-        if (in_slab) {
-            const int cnt = warp_rows ? TPR / 32 : nb;
-            const int first = my_row * cnt;
-            for (int i = 0; i < cnt; ++i) {
-                tot_ss += red_ss[first + i];
-                if constexpr (ROP == ROP_NORM_BWD) tot_sc += red_sc[first + i];
-            }
-        }
-        float r;
-        if (p.reuse_rms) {
-            r = active ? p.rms[row0 + my_row] : 0.f;
-        } else {
-            r = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(tot_ss, float(n)), p.eps)));
-            if (active && col0 == 0 && p.rms != nullptr) p.rms[row0 + my_row] = r;
-        }
-
-        if constexpr (ROP == ROP_NORM_Q) {
             float a = 0.f;
 #pragma unroll
-            for (int i = 0; i < EPT; ++i) {
-                x[i] = __fmul_rn(__fmul_rn(x[i], r), gam[i]);
-                a = fmaxf(a, fabsf(x[i]));
-            }
+            for (int i = 0; i < NP; ++i) a = max3abs(x[i].x, x[i].y, a);
 #pragma unroll
             for (int d = LPB / 2; d >= 1; d >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, d));
             const float scale = scale_from_amax(a, rs);
-            const Divisor dv(scale);
+            const float2 inv = splat2(__frcp_rn(scale));
             uint8_t* so = outb + buf * C::OUTB + e0;
 #pragma unroll
             for (int k = 0; k < NCH; ++k) {
-                const float* v = x + 8 * k;
-                const uint32_t lo = cvt_e4m3x4(dv.quot<LH_ROWS_EXACT>(v[0]), dv.quot<LH_ROWS_EXACT>(v[1]),
-                                               dv.quot<LH_ROWS_EXACT>(v[2]), dv.quot<LH_ROWS_EXACT>(v[3]));
-                const uint32_t hi = cvt_e4m3x4(dv.quot<LH_ROWS_EXACT>(v[4]), dv.quot<LH_ROWS_EXACT>(v[5]),
-                                               dv.quot<LH_ROWS_EXACT>(v[6]), dv.quot<LH_ROWS_EXACT>(v[7]));
+                const float2 q0 = mul2(x[4 * k + 0], inv), q1 = mul2(x[4 * k + 1], inv);
+                const float2 q2 = mul2(x[4 * k + 2], inv), q3 = mul2(x[4 * k + 3], inv);
+                const uint32_t lo = cvt_e4m3x2(q0.x, q0.y) | (cvt_e4m3x2(q1.x, q1.y) << 16);
+                const uint32_t hi = cvt_e4m3x2(q2.x, q2.y) | (cvt_e4m3x2(q3.x, q3.y) << 16);
                 *reinterpret_cast<uint2*>(so + 8 * (k ^ sw)) = make_uint2(lo, hi);
             }
-            if (active && (t % LPB) == 0) p.s[int64_t(col0 >> 7) * p.M + row0 + my_row] = scale;
+            if (active && (t % LPB) == 0) p.s[int64_t(col0 >> 7) * p.M + L.row0 + my_row] = scale;
         } else if constexpr (ROP == ROP_NORM_Y) {
+            const float2 r2 = splat2(r);
             uint8_t* so = outb + buf * C::OUTB + size_t(e0) * 2;
 #pragma unroll
             for (int k = 0; k < NCH; ++k) {
-                float y[8];
+                uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) y[c] = __fmul_rn(__fmul_rn(x[8 * k + c], r), gam[8 * k + c]);
-                *reinterpret_cast<uint4*>(so + 16 * (k ^ sw)) =
-                    make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
-                               pack_bf16x2(y[6], y[7]));
+                for (int j = 0; j < 4; ++j) {
+                    const float2 y = mul2(mul2(x[4 * k + j], r2), gam[4 * k + j]);
+                    w[j] = pack_bf16x2(y.x, y.y);
+                }
+                *reinterpret_cast<uint4*>(so + 16 * (k ^ sw)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         } else {  // ROP_NORM_BWD: dx = r*g*gamma - r^3 * x * sum(x*g*gamma)/n ; dgamma += x*g*r
-            const float coef = r * r * r * tot_sc / float(n);
+            const float2 ncoef = splat2(-(r * r * r * tot_sc / float(n)));
+            const float2 r2 = splat2(r);
             uint8_t* so = outb + buf * C::OUTB + size_t(e0) * 2;
 #pragma unroll
             for (int k = 0; k < NCH; ++k) {
-                float d[8];
+                uint32_t w[4];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int i = 8 * k + c;
-                    d[c] = fmaf(-coef, x[i], r * (g[i] * gam[i]));
-                    acc[i] = fmaf(x[i] * g[i], r, acc[i]);
+                for (int j = 0; j < 4; ++j) {
+                    const int i = 4 * k + j;
+                    const float2 d = fma2(ncoef, x[i], mul2(r2, mul2(g[i], gam[i])));
+                    acc[i] = fma2(mul2(x[i], g[i]), r2, acc[i]);
+                    w[j] = pack_bf16x2(d.x, d.y);
                 }
-                *reinterpret_cast<uint4*>(so + 16 * (k ^ sw)) =
-                    make_uint4(pack_bf16x2(d[0], d[1]), pack_bf16x2(d[2], d[3]), pack_bf16x2(d[4], d[5]),
-                               pack_bf16x2(d[6], d[7]));
+                *reinterpret_cast<uint4*>(so + 16 * (k ^ sw)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
         fence_async_smem();
         named_bar<2, NT>();
         if (t == 0) {
-            const uint32_t out_bytes = uint32_t(rows) * uint32_t(n) * (ROP == ROP_NORM_Q ? 1u : 2u);
-            uint8_t* gdst = (ROP == ROP_NORM_Q ? p.q : p.hp) + row0 * n * (ROP == ROP_NORM_Q ? 1 : 2);
-            bulk_s2g(gdst, outb + buf * C::OUTB, out_bytes);
+            constexpr int OB = C::QUANT ? 1 : 2;
+            uint8_t* gbase = C::QUANT ? p.q : p.hp;
+            bulk_s2g(gbase + (L.row0 * n + L.c0) * OB, outb + buf * C::OUTB, uint32_t(L.rows) * uint32_t(L.ncols) * OB);
             bulk_commit();
         }
     }
@@ -284,12 +344,16 @@ rows_kernel(const __grid_constant__ RowParams p) {
         float* fold = reinterpret_cast<float*>(stages);   // ring is idle: every slab was consumed
         named_bar<1, NT>();
 #pragma unroll
-        for (int i = 0; i < EPT; ++i) fold[(8 * ((i >> 3) ^ sw) + (i & 7)) * NT + t] = acc[i];
+        for (int i = 0; i < NP; ++i) {
+            const int j = 8 * ((i >> 2) ^ sw) + 2 * (i & 3);   // column offset inside this thread's span
+            fold[j * NT + t] = acc[i].x;
+            fold[(j + 1) * NT + t] = acc[i].y;
+        }
         named_bar<2, NT>();
         if (t < TPR) {
-            for (int j = 0; j < EPT; ++j) {   // j: column offset inside this thread's span
+            for (int j = 0; j < EPT; ++j) {
                 float a = 0.f;
-                for (int rr = 0; rr < RB; ++rr) a += fold[j * NT + t + rr * TPR];
+                for (int rr = 0; rr < p.RB; ++rr) a += fold[j * NT + t + rr * TPR];
                 p.partial[int64_t(blockIdx.x) * n + col0 + j] = a;
             }
         }
@@ -313,13 +377,21 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream) {
     auto kern = rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(C::SMEM));
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
-    p.RB = kSlabElems / p.n;
-    const int64_t slabs = (p.M + p.RB - 1) / p.RB;
+    int64_t slabs;
+    if (p.n <= kSlabElems) {
+        p.RB = kSlabElems / p.n;
+        p.chunks = 1;
+        slabs = (p.M + p.RB - 1) / p.RB;
+    } else {
+        p.RB = 1;
+        p.chunks = (p.n + kSlabElems - 1) / kSlabElems;
+        slabs = p.M * p.chunks;
+    }
     int64_t grid = int64_t(sm_count()) * CTAS_PER_SM;
     if (grid > kMaxRowCtas) grid = kMaxRowCtas;
     if (slabs < grid) grid = slabs;
     if (grid_out) *grid_out = int(grid);
-    kern<<<dim3(unsigned(grid)), dim3(C::NTHREADS), C::SMEM, stream>>>(p);
+    kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
     return check_launch("rows_kernel");
 }
 
@@ -342,6 +414,13 @@ int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int6
     p.x = static_cast<const uint8_t*>(x); p.gamma = gamma; p.rms = rms; p.eps = eps; p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
     return launch_rows<ROP_NORM_Q, 32, 4, 2>(p, nullptr, stream);
+}
+
+int rows_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream) {
+    RowParams p{};
+    p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
+    return launch_rows<ROP_SILU_Q, 32, 2, 2>(p, nullptr, stream);
 }
 
 int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,

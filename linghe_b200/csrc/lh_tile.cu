@@ -4,12 +4,13 @@
 // dense or per-expert packed layouts.
 //
 // Execution model (sm_100a): persistent CTAs walk a static round-robin list of tiles.
-// One producer warp feeds a multi-stage shared-memory ring with bulk asynchronous
-// copies (TMA, one 256/512-byte row segment per copy, completion counted on an
-// mbarrier); consumer warps hold a 128x128 tile in registers (RPT rows x 8 columns per
-// thread), reduce row maxima by shuffles and column maxima through shared memory, and
-// write the transposed codes through an XOR-swizzled shared-memory tile so that every
-// global store is a full 128-byte row.  No tensor cores: the path is HBM-bound.
+// Thread 0 feeds a multi-stage shared-memory ring with tensor-map TMA copies (one
+// cp.async.bulk.tensor.2d per operand tile, completion counted on an mbarrier); all
+// warps hold a 128x128 tile in registers (RPT rows x 8 columns per thread, as float2
+// pairs for the packed float32x2 pipe), reduce row maxima by shuffles and column maxima
+// through shared memory, and write the transposed codes through an XOR-swizzled
+// shared-memory tile so that every global store is a full 128-byte row.
+// No tensor cores: the path is HBM-bound.
 #include "lh_common.cuh"
 
 #include <type_traits>
@@ -20,8 +21,7 @@ enum : int { OP_IDENT = 0, OP_NORM = 1, OP_SILU_F = 2, OP_SILU_B = 3 };
 enum : int { MODE_ROW = 0, MODE_COL = 1, MODE_BOTH = 2, MODE_BLOCK = 3 };
 
 struct TileParams {
-    const uint8_t* in[3];  // operand base pointers, already offset to their column 0
-    int64_t ld[3];         // operand row pitch in elements
+    CUtensorMap tmap[2];   // [0]: x (or g for the backward), [1]: x for the backward
     const void* w;         // optional per-row weight
     int w_bf16;
     const float* r;        // OP_NORM: 1/rms per row
@@ -51,6 +51,7 @@ template <int OP, typename InT, int RPT, int STAGES>
 struct TileCfg {
     static constexpr int K = OpTraits<OP>::K;
     static constexpr int NHALF = OpTraits<OP>::NHALF;
+    static constexpr int NMAP = OP == OP_SILU_B ? 2 : 1;   // tensor maps (x1 and x2 share one)
     static constexpr int EB = Elem<InT>::BYTES;
     static constexpr int ROWB = 128 * EB;            // bytes of one tile row of one operand
     static constexpr int TILEB = 128 * ROWB;         // one operand tile
@@ -97,31 +98,39 @@ __device__ __forceinline__ TileLoc locate(int64_t tile, int col_tiles, const int
     return t;
 }
 
+// 8 consecutive elements of a tile row -> 4 float2 pairs
 template <typename InT>
-__device__ __forceinline__ void load8(const uint8_t* row_base, int l16, float* f) {
-    if constexpr (sizeof(InT) == 2) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(row_base + l16 * 16);
-        Elem<InT>::unpack8(raw, f);
-    } else {
+__device__ __forceinline__ void load8p(const uint8_t* row_base, int l16, float2* f) {
+    if constexpr (sizeof(InT) == 4) {
         const float4 a = *reinterpret_cast<const float4*>(row_base + l16 * 32);
         const float4 b = *reinterpret_cast<const float4*>(row_base + l16 * 32 + 16);
-        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
-        f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+        f[0] = make_float2(a.x, a.y); f[1] = make_float2(a.z, a.w);
+        f[2] = make_float2(b.x, b.y); f[3] = make_float2(b.z, b.w);
+    } else {
+        const uint4 raw = *reinterpret_cast<const uint4*>(row_base + l16 * 16);
+        if constexpr (std::is_same<InT, __half>::value) {
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        } else {
+            f[0] = bf16x2_to_f2(raw.x); f[1] = bf16x2_to_f2(raw.y);
+            f[2] = bf16x2_to_f2(raw.z); f[3] = bf16x2_to_f2(raw.w);
+        }
     }
 }
 
 template <typename InT>
-__device__ __forceinline__ void store8_hp(void* dst, const float* f) {
+__device__ __forceinline__ void store8_hp(void* dst, const float2* f) {
     if constexpr (sizeof(InT) == 4) {
         float4* d = reinterpret_cast<float4*>(dst);
-        d[0] = make_float4(f[0], f[1], f[2], f[3]);
-        d[1] = make_float4(f[4], f[5], f[6], f[7]);
-    } else if constexpr (sizeof(InT) == 2 && std::is_same<InT, __half>::value) {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_f16x2(f[0], f[1]), pack_f16x2(f[2], f[3]),
-                                                    pack_f16x2(f[4], f[5]), pack_f16x2(f[6], f[7]));
+        d[0] = make_float4(f[0].x, f[0].y, f[1].x, f[1].y);
+        d[1] = make_float4(f[2].x, f[2].y, f[3].x, f[3].y);
+    } else if constexpr (std::is_same<InT, __half>::value) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_f16x2(f[0].x, f[0].y), pack_f16x2(f[1].x, f[1].y),
+                                                    pack_f16x2(f[2].x, f[2].y), pack_f16x2(f[3].x, f[3].y));
     } else {
-        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
-                                                    pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(f[0].x, f[0].y), pack_bf16x2(f[1].x, f[1].y),
+                                                    pack_bf16x2(f[2].x, f[2].y), pack_bf16x2(f[3].x, f[3].y));
     }
 }
 
@@ -138,6 +147,33 @@ __device__ __forceinline__ float sum16(float a) {
     a += __shfl_xor_sync(0xffffffffu, a, 2);
     a += __shfl_xor_sync(0xffffffffu, a, 1);
     return a;
+}
+
+// exact quotient of one value (see Divisor); `tiny` blocks take IEEE division
+__device__ __forceinline__ float quot_exact(float x, float s, float y, bool tiny) {
+    const float q0 = x * y;
+    const float r = fmaf(s, q0, -x);
+    const float q = fmaf(r, -y, q0);
+    return tiny ? __fdiv_rn(x, s) : q;
+}
+
+// 8 values of one row, one scale -> 8 codes
+template <bool EXACT>
+__device__ __forceinline__ uint2 quant_row8(const float2* v, float sc) {
+    const float y = __frcp_rn(sc);
+    float2 q[4];
+    if constexpr (EXACT) {
+        const bool tiny = sc < 8.0e-28f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            q[j] = make_float2(quot_exact(v[j].x, sc, y, tiny), quot_exact(v[j].y, sc, y, tiny));
+    } else {
+        const float2 y2 = splat2(y);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q[j] = mul2(v[j], y2);
+    }
+    return make_uint2(cvt_e4m3x2(q[0].x, q[0].y) | (cvt_e4m3x2(q[1].x, q[1].y) << 16),
+                      cvt_e4m3x2(q[2].x, q[2].y) | (cvt_e4m3x2(q[3].x, q[3].y) << 16));
 }
 
 template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int MINB>
@@ -167,6 +203,8 @@ tile_kernel(const __grid_constant__ TileParams p) {
             mbar_init(&empty[i], NW);
         }
         mbar_fence_init();
+#pragma unroll
+        for (int k = 0; k < C::NMAP; ++k) tma_prefetch_desc(&p.tmap[k]);
     }
     if (warp == 0) {
         if (p.counts == nullptr) {
@@ -207,29 +245,33 @@ tile_kernel(const __grid_constant__ TileParams p) {
     const int64_t total_tiles = int64_t(segB[E]) * col_tiles;
     const int64_t nb = p.n >> 7;
 
-    // Warp 0 doubles as the producer: it fills the ring before the loop and, at the top
+    // Thread 0 doubles as the producer: it fills the ring before the loop and, at the top
     // of every iteration, refills the stage that all warps released one iteration ago.
+    // One tensor-map copy per operand brings a whole 128x128 tile; rows past the end of
+    // the matrix read as zero, rows of a following expert segment are masked by `valid`.
     auto issue = [&](int64_t tile, int stage) {
         const TileLoc t = locate(tile, col_tiles, segS, segB, E);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
-        if (lane == 0) mbar_expect_tx(&full[stage], uint32_t(t.valid) * C::ROWB * K);
-        __syncwarp();
-        const int64_t r0 = t.S + int64_t(t.T) * 128;
-        for (int rr = lane; rr < t.valid; rr += 32) {
-#pragma unroll
-            for (int k = 0; k < K; ++k) {
-                const uint8_t* src = p.in[k] + ((r0 + rr) * p.ld[k] + int64_t(t.ct) * 128) * C::EB;
-                bulk_g2s(dst + k * C::TILEB + rr * C::ROWB, src, C::ROWB, &full[stage]);
-            }
+        const int r0 = int(t.S + int64_t(t.T) * 128);
+        const int c0 = t.ct * 128;
+        mbar_expect_tx(&full[stage], uint32_t(C::STAGEB));
+        if constexpr (OP == OP_SILU_F) {
+            tma_load_2d(dst, &p.tmap[0], c0, r0, &full[stage]);
+            tma_load_2d(dst + C::TILEB, &p.tmap[0], int(p.n) + c0, r0, &full[stage]);
+        } else if constexpr (OP == OP_SILU_B) {
+            tma_load_2d(dst, &p.tmap[0], c0, r0, &full[stage]);
+            tma_load_2d(dst + C::TILEB, &p.tmap[1], c0, r0, &full[stage]);
+            tma_load_2d(dst + 2 * C::TILEB, &p.tmap[1], int(p.n) + c0, r0, &full[stage]);
+        } else {
+            tma_load_2d(dst, &p.tmap[0], c0, r0, &full[stage]);
         }
     };
-    if (warp == 0) {
+    if (tid == 0) {
         int64_t tile = blockIdx.x;
         for (int j = 0; j < STAGES && tile < total_tiles; ++j, tile += gridDim.x) issue(tile, j);
     }
 
-    // ================================ consumers ===================================
-    const int cw = warp;                 // consumer warp index
+    const int cw = warp;                 // warp index
     const int hw = lane >> 4;            // half-warp
     const int l16 = lane & 15;           // 8-column group inside the tile
     const int row0 = cw * (2 * RPT) + hw * RPT;
@@ -238,15 +280,14 @@ tile_kernel(const __grid_constant__ TileParams p) {
     int it = 0;
     for (int64_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
         const int stage = it % STAGES;
-        if (warp == 0 && it > 0) {
+        if (tid == 0 && it > 0) {
             // tile (it-1) lived in stage (it-1)%STAGES; once every warp has released it,
             // bring in tile it-1+STAGES.  Copies issued here are consumed by this CTA, so
             // none is in flight when the loop ends.
             const int64_t nxt = tile + int64_t(STAGES - 1) * gridDim.x;
             if (nxt < total_tiles) {
                 const int ps = (it - 1) % STAGES;
-                if (!mbar_wait(&empty[ps], ((it - 1) / STAGES) & 1, DEVERR_EMPTY_WAIT)) return;
-                issue(nxt, ps);
+                if (mbar_wait(&empty[ps], ((it - 1) / STAGES) & 1, DEVERR_EMPTY_WAIT)) issue(nxt, ps);
             }
         }
         const TileLoc t = locate(tile, col_tiles, segS, segB, E);
@@ -255,70 +296,73 @@ tile_kernel(const __grid_constant__ TileParams p) {
         if (!mbar_wait(&full[stage], (it / STAGES) & 1, DEVERR_FULL_WAIT)) return;
         const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
 
-        float v[NHALF][RPT][8];
-        float dwp[RPT];
-        float gam[8];
+        float2 v[NHALF][RPT][4];
+        float dwp[OP == OP_SILU_B ? RPT : 1];
+        float2 gam[OP == OP_NORM ? 4 : 1];
         if constexpr (OP == OP_NORM) {
             const uint4 graw = *reinterpret_cast<const uint4*>(
                 reinterpret_cast<const uint8_t*>(p.gamma) + (gcol0 + l16 * 8) * 2);
-            Elem<InT>::unpack8(graw, gam);
+            gam[0] = bf16x2_to_f2(graw.x); gam[1] = bf16x2_to_f2(graw.y);
+            gam[2] = bf16x2_to_f2(graw.z); gam[3] = bf16x2_to_f2(graw.w);
         }
+        const bool has_w = (OP == OP_SILU_F || OP == OP_SILU_B) && p.w != nullptr;
 #pragma unroll
         for (int s = 0; s < RPT; ++s) {
             const int rr = row0 + s;
             const bool ok = rr < t.valid;
             if constexpr (OP == OP_IDENT) {
-                load8<InT>(sbase + rr * C::ROWB, l16, v[0][s]);
+                load8p<InT>(sbase + rr * C::ROWB, l16, v[0][s]);
             } else if constexpr (OP == OP_NORM) {
-                float x[8];
-                load8<InT>(sbase + rr * C::ROWB, l16, x);
-                const float r = ok ? p.r[grow0 + rr] : 0.f;
+                float2 x[4];
+                load8p<InT>(sbase + rr * C::ROWB, l16, x);
+                const float2 r2 = splat2(ok ? p.r[grow0 + rr] : 0.f);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) v[0][s][c] = __fmul_rn(__fmul_rn(x[c], r), gam[c]);
-            } else if constexpr (OP == OP_SILU_F) {
-                float x1[8], x2[8];
-                load8<InT>(sbase + rr * C::ROWB, l16, x1);
-                load8<InT>(sbase + C::TILEB + rr * C::ROWB, l16, x2);
+                for (int j = 0; j < 4; ++j) v[0][s][j] = mul2(mul2(x[j], r2), gam[j]);
+            } else {
                 float w = 1.f;
-                const bool has_w = p.w != nullptr;
                 if (has_w && ok)
                     w = p.w_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[grow0 + rr])
                                  : reinterpret_cast<const float*>(p.w)[grow0 + rr];
+                const float2 w2 = splat2(w);
+                if constexpr (OP == OP_SILU_F) {
+                    float2 x1[4], x2[4];
+                    load8p<InT>(sbase + rr * C::ROWB, l16, x1);
+                    load8p<InT>(sbase + C::TILEB + rr * C::ROWB, l16, x2);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float y = __fmul_rn(__fmul_rn(sigmoid_ref(x1[c]), x1[c]), x2[c]);
-                    if (has_w) y = __fmul_rn(y, w);
-                    v[0][s][c] = y;
-                }
-            } else {  // OP_SILU_B
-                float g[8], x1[8], x2[8];
-                load8<InT>(sbase + rr * C::ROWB, l16, g);
-                load8<InT>(sbase + C::TILEB + rr * C::ROWB, l16, x1);
-                load8<InT>(sbase + 2 * C::TILEB + rr * C::ROWB, l16, x2);
-                float w = 1.f;
-                const bool has_w = p.w != nullptr;
-                if (has_w && ok)
-                    w = p.w_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[grow0 + rr])
-                                 : reinterpret_cast<const float*>(p.w)[grow0 + rr];
-                float acc = 0.f;
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 sg = EXACT ? make_float2(sigmoid_ref(x1[j].x), sigmoid_ref(x1[j].y))
+                                                : sigmoid_fast2(x1[j]);
+                        float2 y = mul2(mul2(sg, x1[j]), x2[j]);
+                        if (has_w) y = mul2(y, w2);
+                        v[0][s][j] = y;
+                    }
+                } else {  // OP_SILU_B
+                    float2 g[4], x1[4], x2[4];
+                    load8p<InT>(sbase + rr * C::ROWB, l16, g);
+                    load8p<InT>(sbase + C::TILEB + rr * C::ROWB, l16, x1);
+                    load8p<InT>(sbase + 2 * C::TILEB + rr * C::ROWB, l16, x2);
+                    float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const float sg = sigmoid_ref(x1[c]);
-                    const float sgg = sg * g[c];              // sigmoid * g
-                    const float d2 = sgg * x1[c];             // d/dx2 (unweighted)
-                    const float u = fmaf(x1[c], 1.f - sg, 1.f);
-                    const float d1 = sgg * x2[c] * u;         // d/dx1 (unweighted)
-                    acc = fmaf(d2, x2[c], acc);               // sigmoid*x1*x2*g
-                    v[0][s][c] = has_w ? d1 * w : d1;
-                    v[1][s][c] = has_w ? d2 * w : d2;
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 sg = EXACT ? make_float2(sigmoid_ref(x1[j].x), sigmoid_ref(x1[j].y))
+                                                : sigmoid_fast2(x1[j]);
+                        const float2 sgg = mul2(sg, g[j]);                                // sigmoid * g
+                        const float2 d2 = mul2(sgg, x1[j]);                               // d/dx2 (unweighted)
+                        const float2 oms = fma2(sg, splat2(-1.f), splat2(1.f));           // 1 - sigmoid
+                        const float2 u = fma2(x1[j], oms, splat2(1.f));
+                        const float2 d1 = mul2(mul2(sgg, x2[j]), u);                      // d/dx1 (unweighted)
+                        acc = fma2(d2, x2[j], acc);                                       // sigmoid*x1*x2*g
+                        v[0][s][j] = has_w ? mul2(d1, w2) : d1;
+                        v[1][s][j] = has_w ? mul2(d2, w2) : d2;
+                    }
+                    dwp[s] = acc.x + acc.y;
                 }
-                dwp[s] = acc;
             }
             if (!ok) {
 #pragma unroll
                 for (int h = 0; h < NHALF; ++h)
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) v[h][s][c] = 0.f;
+                    for (int j = 0; j < 4; ++j) v[h][s][j] = make_float2(0.f, 0.f);
                 if constexpr (OP == OP_SILU_B) dwp[s] = 0.f;
             }
         }
@@ -356,7 +400,9 @@ tile_kernel(const __grid_constant__ TileParams p) {
             if constexpr (MODE == MODE_BLOCK) {
                 float m = 0.f;
 #pragma unroll
-                for (int s = 0; s < RPT; ++s) m = fmaxf(m, amax8(v[h][s]));
+                for (int s = 0; s < RPT; ++s)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) m = max3abs(v[h][s][j].x, v[h][s][j].y, m);
                 m = max16(m);
                 m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
                 if (lane == 0) part[cw] = m;
@@ -365,15 +411,11 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
                 for (int w2 = 1; w2 < NW; ++w2) bm = fmaxf(bm, part[w2]);
                 const float sc = scale_from_amax(bm, rs);
-                const Divisor d(sc);
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     const int rr = row0 + s;
-                    const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][s][0]), d.quot<EXACT>(v[h][s][1]),
-                                                   d.quot<EXACT>(v[h][s][2]), d.quot<EXACT>(v[h][s][3]));
-                    const uint32_t hi = cvt_e4m3x4(d.quot<EXACT>(v[h][s][4]), d.quot<EXACT>(v[h][s][5]),
-                                                   d.quot<EXACT>(v[h][s][6]), d.quot<EXACT>(v[h][s][7]));
-                    if (rr < t.valid) st_global_v2(p.q + (grow0 + rr) * p.n + gcol0 + l16 * 8, lo, hi);
+                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc);
+                    if (rr < t.valid) st_global_v2(p.q + (grow0 + rr) * p.n + gcol0 + l16 * 8, codes.x, codes.y);
                 }
                 if (tid == 0) p.s[(t.B + t.T) * nb + t.ct] = sc;
                 named_bar<1, NCONS>();  // part[] is rewritten by the next tile
@@ -384,15 +426,14 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     const int rr = row0 + s;
-                    const float a = max16(amax8(v[h][s]));
+                    float a = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) a = max3abs(v[h][s][j].x, v[h][s][j].y, a);
+                    a = max16(a);
                     const float sc = scale_from_amax(a, rs);
-                    const Divisor d(sc);
-                    const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][s][0]), d.quot<EXACT>(v[h][s][1]),
-                                                   d.quot<EXACT>(v[h][s][2]), d.quot<EXACT>(v[h][s][3]));
-                    const uint32_t hi = cvt_e4m3x4(d.quot<EXACT>(v[h][s][4]), d.quot<EXACT>(v[h][s][5]),
-                                                   d.quot<EXACT>(v[h][s][6]), d.quot<EXACT>(v[h][s][7]));
+                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc);
                     if (rr < t.valid)
-                        st_global_v2(p.q + (grow0 + rr) * (NHALF * p.n) + h * p.n + gcol0 + l16 * 8, lo, hi);
+                        st_global_v2(p.q + (grow0 + rr) * (NHALF * p.n) + h * p.n + gcol0 + l16 * 8, codes.x, codes.y);
                     if (l16 == s) myscale = sc;
                 }
                 if (l16 < RPT && row0 + l16 < t.valid) {
@@ -405,18 +446,22 @@ tile_kernel(const __grid_constant__ TileParams p) {
             }
             // ------------------------ column-wise 128x1, transposed -----------------
             if constexpr (MODE == MODE_COL || MODE == MODE_BOTH) {
-                float cm[8];
+                float2 cm[4];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    float m = fabsf(v[h][0][c]);
+                for (int j = 0; j < 4; ++j) {
+                    float mx = 0.f, my = 0.f;
 #pragma unroll
-                    for (int s = 1; s < RPT; ++s) m = fmaxf(m, fabsf(v[h][s][c]));
-                    cm[c] = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+                    for (int s = 0; s < RPT; s += 2) {
+                        mx = max3abs(v[h][s][j].x, v[h][s + 1][j].x, mx);
+                        my = max3abs(v[h][s][j].y, v[h][s + 1][j].y, my);
+                    }
+                    cm[j].x = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                    cm[j].y = fmaxf(my, __shfl_xor_sync(0xffffffffu, my, 16));
                 }
                 if (hw == 0) {
                     float4* dst = reinterpret_cast<float4*>(part + cw * 128 + l16 * 8);
-                    dst[0] = make_float4(cm[0], cm[1], cm[2], cm[3]);
-                    dst[1] = make_float4(cm[4], cm[5], cm[6], cm[7]);
+                    dst[0] = make_float4(cm[0].x, cm[0].y, cm[1].x, cm[1].y);
+                    dst[1] = make_float4(cm[2].x, cm[2].y, cm[3].x, cm[3].y);
                 }
                 named_bar<1, NCONS>();
                 if (tid < 128) {
@@ -429,35 +474,47 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     p.st[(t.B + t.T) * (NHALF * p.n) + h * p.n + gcol0 + tid] = sc;
                 }
                 named_bar<1, NCONS>();
-                float sc8[8], y8[8];
+                float2 sc2[4], y2[4];
                 {
                     const float4 a = *reinterpret_cast<const float4*>(cs + l16 * 8);
                     const float4 b = *reinterpret_cast<const float4*>(cs + l16 * 8 + 4);
                     const float4 c = *reinterpret_cast<const float4*>(cy + l16 * 8);
                     const float4 e = *reinterpret_cast<const float4*>(cy + l16 * 8 + 4);
-                    sc8[0] = a.x; sc8[1] = a.y; sc8[2] = a.z; sc8[3] = a.w;
-                    sc8[4] = b.x; sc8[5] = b.y; sc8[6] = b.z; sc8[7] = b.w;
-                    y8[0] = c.x; y8[1] = c.y; y8[2] = c.z; y8[3] = c.w;
-                    y8[4] = e.x; y8[5] = e.y; y8[6] = e.z; y8[7] = e.w;
+                    sc2[0] = make_float2(a.x, a.y); sc2[1] = make_float2(a.z, a.w);
+                    sc2[2] = make_float2(b.x, b.y); sc2[3] = make_float2(b.z, b.w);
+                    y2[0] = make_float2(c.x, c.y); y2[1] = make_float2(c.z, c.w);
+                    y2[2] = make_float2(e.x, e.y); y2[3] = make_float2(e.z, e.w);
                 }
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    Divisor d(1.f);
-                    d.s = sc8[c]; d.y = y8[c]; d.ny = -y8[c]; d.tiny = sc8[c] < 8.0e-28f;
-                    const int col = l16 * 8 + c;
+                for (int j = 0; j < 4; ++j) {
+                    float2 q[RPT];
+                    if constexpr (EXACT) {
+                        const bool tx = sc2[j].x < 8.0e-28f, ty = sc2[j].y < 8.0e-28f;
+#pragma unroll
+                        for (int s = 0; s < RPT; ++s)
+                            q[s] = make_float2(quot_exact(v[h][s][j].x, sc2[j].x, y2[j].x, tx),
+                                               quot_exact(v[h][s][j].y, sc2[j].y, y2[j].y, ty));
+                    } else {
+#pragma unroll
+                        for (int s = 0; s < RPT; ++s) q[s] = mul2(v[h][s][j], y2[j]);
+                    }
+                    const int colx = l16 * 8 + 2 * j;
                     if constexpr (RPT == 8) {
                         const int rc = cw * 2 + hw;
-                        const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][0][c]), d.quot<EXACT>(v[h][1][c]),
-                                                       d.quot<EXACT>(v[h][2][c]), d.quot<EXACT>(v[h][3][c]));
-                        const uint32_t hi = cvt_e4m3x4(d.quot<EXACT>(v[h][4][c]), d.quot<EXACT>(v[h][5][c]),
-                                                       d.quot<EXACT>(v[h][6][c]), d.quot<EXACT>(v[h][7][c]));
-                        *reinterpret_cast<uint2*>(qts + col * 128 + ((rc ^ l16) << 3)) = make_uint2(lo, hi);
+                        const uint32_t off = uint32_t((rc ^ l16) << 3);
+                        *reinterpret_cast<uint2*>(qts + colx * 128 + off) = make_uint2(
+                            cvt_e4m3x2(q[0].x, q[1].x) | (cvt_e4m3x2(q[2].x, q[3].x) << 16),
+                            cvt_e4m3x2(q[4].x, q[5].x) | (cvt_e4m3x2(q[6].x, q[7].x) << 16));
+                        *reinterpret_cast<uint2*>(qts + (colx + 1) * 128 + off) = make_uint2(
+                            cvt_e4m3x2(q[0].y, q[1].y) | (cvt_e4m3x2(q[2].y, q[3].y) << 16),
+                            cvt_e4m3x2(q[4].y, q[5].y) | (cvt_e4m3x2(q[6].y, q[7].y) << 16));
                     } else {
                         static_assert(RPT == 8 || RPT == 4, "RPT");
-                        const int rc = cw;
-                        const uint32_t lo = cvt_e4m3x4(d.quot<EXACT>(v[h][0][c]), d.quot<EXACT>(v[h][1][c]),
-                                                       d.quot<EXACT>(v[h][2][c]), d.quot<EXACT>(v[h][3][c]));
-                        *reinterpret_cast<uint32_t*>(qts + col * 128 + ((rc ^ l16) << 3) + hw * 4) = lo;
+                        const uint32_t off = uint32_t(((cw ^ l16) << 3) + hw * 4);
+                        *reinterpret_cast<uint32_t*>(qts + colx * 128 + off) =
+                            cvt_e4m3x2(q[0].x, q[1].x) | (cvt_e4m3x2(q[2].x, q[3].x) << 16);
+                        *reinterpret_cast<uint32_t*>(qts + (colx + 1) * 128 + off) =
+                            cvt_e4m3x2(q[0].y, q[1].y) | (cvt_e4m3x2(q[2].y, q[3].y) << 16);
                     }
                 }
                 named_bar<1, NCONS>();
@@ -505,8 +562,10 @@ static int launch_tile(const TileParams& p, cudaStream_t stream) {
     return check_launch("tile_kernel");
 }
 
+// Fused variants (norm / SwiGLU producers) use the reciprocal-multiply quotient and the
+// hardware ex2 / rcp approximations; the pure quantisers always use exact quotients.
 #ifndef LH_FUSED_EXACT
-#define LH_FUSED_EXACT true
+#define LH_FUSED_EXACT false
 #endif
 
 template <typename InT>
@@ -543,8 +602,8 @@ int tile_quant(const void* x, int dtype, const void* counts, int counts_type, in
     if ((mode == MODE_ROW || mode == MODE_BOTH || mode == MODE_BLOCK) && (!q || !s)) return fail_arg("quant: q/s NULL");
     if ((mode == MODE_COL || mode == MODE_BOTH) && (!qt || !st)) return fail_arg("quant: qt/st NULL");
     TileParams p{};
-    p.in[0] = static_cast<const uint8_t*>(x);
-    p.ld[0] = N;
+    if (int rc = make_tensor_map(&p.tmap[0], x, dtype, uint64_t(M), uint64_t(N),
+                                 uint64_t(N) * (dtype == LH_F32 ? 4 : 2), 128, 128)) return rc;
     p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
     p.M = M; p.n = N;
     p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
@@ -555,8 +614,7 @@ int tile_quant(const void* x, int dtype, const void* counts, int counts_type, in
 int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,
                   int round_scale, cudaStream_t stream) {
     TileParams p{};
-    p.in[0] = static_cast<const uint8_t*>(x);
-    p.ld[0] = n;
+    if (int rc = make_tensor_map(&p.tmap[0], x, LH_BF16, uint64_t(M), uint64_t(n), uint64_t(n) * 2, 128, 128)) return rc;
     p.r = r; p.gamma = gamma; p.E = 1; p.M = M; p.n = n;
     p.qt = static_cast<uint8_t*>(qt); p.st = st; p.round_scale = round_scale;
     return launch_tile<OP_NORM, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 8, 2, 2>(p, stream);
@@ -566,9 +624,7 @@ int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts,
                   int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
                   cudaStream_t stream) {
     TileParams p{};
-    p.in[0] = static_cast<const uint8_t*>(x);
-    p.in[1] = static_cast<const uint8_t*>(x) + n * 2;
-    p.ld[0] = p.ld[1] = 2 * n;
+    if (int rc = make_tensor_map(&p.tmap[0], x, LH_BF16, uint64_t(M), uint64_t(2 * n), uint64_t(2 * n) * 2, 128, 128)) return rc;
     p.w = w; p.w_bf16 = w_dtype == LH_BF16;
     p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
     p.M = M; p.n = n;
@@ -586,10 +642,8 @@ int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, cons
                   int E, int64_t M, int64_t n, void* dx_q, float* dx_s, void* dx_qt, float* dx_st, void* hp,
                   float* dws, int round_scale, cudaStream_t stream) {
     TileParams p{};
-    p.in[0] = static_cast<const uint8_t*>(g);
-    p.in[1] = static_cast<const uint8_t*>(x);
-    p.in[2] = static_cast<const uint8_t*>(x) + n * 2;
-    p.ld[0] = n; p.ld[1] = p.ld[2] = 2 * n;
+    if (int rc = make_tensor_map(&p.tmap[0], g, LH_BF16, uint64_t(M), uint64_t(n), uint64_t(n) * 2, 128, 128)) return rc;
+    if (int rc = make_tensor_map(&p.tmap[1], x, LH_BF16, uint64_t(M), uint64_t(2 * n), uint64_t(2 * n) * 2, 128, 128)) return rc;
     p.w = w; p.w_bf16 = w_dtype == LH_BF16;
     p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
     p.M = M; p.n = n;
