@@ -11,6 +11,19 @@ namespace lh {
 
 __device__ int g_device_status = 0;
 
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
+    const long long t0 = clock64();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > 4000000000LL) {
+            atomicCAS(&g_device_status, 0, code);
+            return false;
+        }
+    }
+}
+
 static thread_local char tl_error[512] = "";
 
 void set_error(const char* fmt, ...) {

@@ -102,11 +102,32 @@ __device__ __forceinline__ float pow2_ceil(float s) {
     return __uint_as_float(uint32_t(K + 127) << 23);
 }
 
-// scale = max(amax / 448, 1e-30) with IEEE division, optionally rounded up to 2^k.
+// RN(a / 448) in three instructions: q = a*c with c = RN(1/448), residual r = a - 448*q
+// (exact in an FMA), result q + r*c.  Correctly rounded (Markstein) whenever the residual
+// cannot underflow, which holds for every a whose quotient is above the 1e-30 scale
+// floor; below it the floor wins anyway.
+__device__ __forceinline__ float div448(float a) {
+    constexpr float c = 1.0f / 448.0f;
+    const float q = a * c;
+    const float r = fmaf(-448.0f, q, a);
+    return fmaf(r, c, q);
+}
+
+// scale = max(amax / 448, 1e-30) (bit-identical to IEEE division), optionally rounded
+// up to a power of two.
 __device__ __forceinline__ float scale_from_amax(float amax, bool round_scale) {
-    float s = fmaxf(__fdiv_rn(amax, kE4M3Max), kScaleFloor);
+    float s = fmaxf(div448(amax), kScaleFloor);
     if (round_scale) s = pow2_ceil(s);
     return s;
+}
+
+// 1/sqrt(a) to about 1 ulp: hardware approximation plus one Newton step.
+__device__ __forceinline__ float rsqrt_nr(float a) {
+    float y;
+    asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(a));
+    const float t = a * y;
+    const float e = fmaf(-t, y, 1.0f);
+    return fmaf(0.5f * y, e, y);
 }
 
 // Per-block divisor.  `exact` quotients equal IEEE x / s bit for bit: q0 = x*y with
@@ -143,8 +164,16 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
     return uint32_t(r);
 }
+// four floats -> four e4m3 codes packed in a word (a in bits 0..7)
 __device__ __forceinline__ uint32_t cvt_e4m3x4(float a, float b, float c, float d) {
-    return cvt_e4m3x2(a, b) | (cvt_e4m3x2(c, d) << 16);
+    uint32_t r;
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+        "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+        "mov.b32 %0, {lo, hi};\n\t}"
+        : "=r"(r)
+        : "f"(a), "f"(b), "f"(c), "f"(d));
+    return r;
 }
 
 __device__ __forceinline__ float amax8(const float* v) {
@@ -181,10 +210,11 @@ __device__ __forceinline__ float rcp_approx(float x) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// max(|a|, |b|, c) with the three-input max of sm_100
+// max(|a|, |b|, |c|) with the three-input max of sm_100 (absolute values are operand
+// modifiers of the instruction, not separate operations)
 __device__ __forceinline__ float max3abs(float a, float b, float c) {
     float r;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(fabsf(a)), "f"(fabsf(b)), "f"(c));
+    asm("max.abs.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
     return r;
 }
 
@@ -229,19 +259,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait (about two seconds of SM clock).  On give-up records `code` in the
-// device status word and returns false; callers then stop issuing work.
+// device status word and returns false; callers then stop issuing work.  The spin lives
+// out of line so that the common case (data already there) costs two instructions.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code);
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (true) {
-#pragma unroll 1
-        for (int i = 0; i < 256; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > 4000000000LL) {
-            atomicCAS(&g_device_status, 0, code);
-            return false;
-        }
-    }
+    return mbar_wait_slow(bar, parity, code);
 }
 
 // global -> shared bulk copy, completion counted in bytes on `bar`.

@@ -26,6 +26,7 @@ struct RowParams {
     float* rms;          // [M] 1/rms (written unless reuse_rms)
     int reuse_rms;
     float eps;
+    float inv_n;         // 1 / n
     int64_t M;
     int n;               // output columns
     int RB;              // rows per slab
@@ -60,24 +61,7 @@ struct SlabLoc {
     int ncols;  // columns in this slab
 };
 
-__device__ __forceinline__ SlabLoc slab_loc(int64_t slab, const RowParams& p) {
-    SlabLoc L;
-    if (p.chunks == 1) {
-        L.row0 = slab * p.RB;
-        const int64_t left = p.M - L.row0;
-        L.rows = left < p.RB ? int(left) : p.RB;
-        L.c0 = 0;
-        L.ncols = p.n;
-    } else {
-        L.row0 = slab / p.chunks;
-        L.rows = 1;
-        L.c0 = int(slab - L.row0 * p.chunks) * kSlabElems;
-        L.ncols = p.n - L.c0 < kSlabElems ? p.n - L.c0 : kSlabElems;
-    }
-    return L;
-}
-
-template <int ROP, int EPT, int STAGES, int MINB>
+template <int ROP, int EPT, int STAGES, int MINB, bool CHUNKED>
 __global__ void __launch_bounds__(RowCfg<ROP, EPT, STAGES>::NT, MINB)
 rows_kernel(const __grid_constant__ RowParams p) {
     using C = RowCfg<ROP, EPT, STAGES>;
@@ -86,6 +70,8 @@ rows_kernel(const __grid_constant__ RowParams p) {
     constexpr int NP = EPT / 2;      // float2 pairs per thread
     constexpr int LPB = 128 / EPT;   // lanes per 128-element block
     constexpr bool NORM = ROP != ROP_SILU_Q;
+    constexpr int OB = C::QUANT ? 1 : 2;          // bytes per output element
+    constexpr int WSPAN = 32 * EPT;               // elements owned by one warp in a slab
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stages = smem + C::OFF_STAGES;
     uint8_t* outb = smem + C::OFF_OUT;
@@ -93,12 +79,13 @@ rows_kernel(const __grid_constant__ RowParams p) {
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
     uint64_t* empty = full + STAGES;
 
-    const int tid = threadIdx.x;
-    const int warp = tid >> 5, lane = tid & 31;
+    const int t = threadIdx.x;
+    const int warp = t >> 5, lane = t & 31;
     const int n = p.n;
-    const int64_t slabs = p.chunks == 1 ? (p.M + p.RB - 1) / p.RB : p.M * p.chunks;
+    const int RB = CHUNKED ? 1 : p.RB;
+    const int64_t slabs = CHUNKED ? p.M * p.chunks : (p.M + RB - 1) / RB;
 
-    if (tid == 0) {
+    if (t == 0) {
         for (int i = 0; i < STAGES; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], NW);
@@ -107,9 +94,26 @@ rows_kernel(const __grid_constant__ RowParams p) {
     }
     __syncthreads();
 
+    auto locate = [&](int64_t slab) {
+        SlabLoc L;
+        if constexpr (CHUNKED) {
+            L.row0 = slab / p.chunks;
+            L.rows = 1;
+            L.c0 = int(slab - L.row0 * p.chunks) * kSlabElems;
+            L.ncols = n - L.c0 < kSlabElems ? n - L.c0 : kSlabElems;
+        } else {
+            L.row0 = slab * RB;
+            const int64_t left = p.M - L.row0;
+            L.rows = left < RB ? int(left) : RB;
+            L.c0 = 0;
+            L.ncols = n;
+        }
+        return L;
+    };
+
     // Warp 0 doubles as the producer.
     auto issue = [&](int64_t slab, int stage) {
-        const SlabLoc L = slab_loc(slab, p);
+        const SlabLoc L = locate(slab);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
         if constexpr (ROP == ROP_SILU_Q) {
             // x is [M, 2n]: gate half and up half of every row are separate runs
@@ -135,10 +139,10 @@ rows_kernel(const __grid_constant__ RowParams p) {
         for (int j = 0; j < STAGES && slab < slabs; ++j, slab += gridDim.x) issue(slab, j);
     }
 
-    const int t = tid;
     const int e0 = t * EPT;                        // first element of this thread inside the slab
     const int sw = NCH == 4 ? ((t >> 1) & 3) : ((t >> 2) & 1);  // bank-conflict-free chunk order
     const bool rs = p.round_scale != 0;
+    const bool reuse = ROP != ROP_NORM_Q && p.reuse_rms != 0;
 
     // For the norm kernels a slab is RB full rows, so a thread's columns never change:
     // keep gamma for them in registers, in the (swizzled) chunk order used for x.
@@ -148,7 +152,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
     if constexpr (NORM) {
         my_row = e0 / n;
         col0 = e0 - my_row * n;
-        in_slab = my_row < p.RB;
+        in_slab = my_row < RB;
 #pragma unroll
         for (int k = 0; k < NCH; ++k) {
             uint4 raw = make_uint4(0, 0, 0, 0);
@@ -162,30 +166,29 @@ rows_kernel(const __grid_constant__ RowParams p) {
     }
     const int TPR = n / EPT;                       // threads per row (norm kernels)
     const bool warp_rows = (TPR % 32) == 0;        // rows are made of whole warps
-    const int nb = n >> 7;
+    const int red_cnt = warp_rows ? TPR / 32 : (n >> 7);
+    const int red_first = my_row * red_cnt;
     float2 acc[ROP == ROP_NORM_BWD ? NP : 1];
 #pragma unroll
     for (int i = 0; i < (ROP == ROP_NORM_BWD ? NP : 1); ++i) acc[i] = make_float2(0.f, 0.f);
 
-    int it = 0;
-    for (int64_t slab = blockIdx.x; slab < slabs; slab += gridDim.x, ++it) {
-        const int stage = it % STAGES;
-        const int buf = it & 1;
-        if (warp == 0 && it > 0) {
-            // every warp released stage (it-1)%STAGES before the barriers of iteration it-1
+    int stage = 0, prev_stage = 0;
+    uint32_t phase = 0, prev_phase = 0;
+    int buf = 0;
+    bool first_it = true;
+    for (int64_t slab = blockIdx.x; slab < slabs; slab += gridDim.x) {
+        if (warp == 0 && !first_it) {
+            // every warp released the previous stage early in the previous iteration
             const int64_t nxt = slab + int64_t(STAGES - 1) * gridDim.x;
-            if (nxt < slabs) {
-                const int ps = (it - 1) % STAGES;
-                if (mbar_wait(&empty[ps], ((it - 1) / STAGES) & 1, DEVERR_EMPTY_WAIT)) issue(nxt, ps);
-            }
+            if (nxt < slabs && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
         }
-        const SlabLoc L = slab_loc(slab, p);
+        const SlabLoc L = locate(slab);
         if constexpr (!NORM) {
-            my_row = e0 / L.ncols;
+            my_row = CHUNKED ? 0 : e0 / L.ncols;
             col0 = L.c0 + (e0 - my_row * L.ncols);
         }
-        const bool active = in_slab && my_row < L.rows;
-        if (!mbar_wait(&full[stage], (it / STAGES) & 1, DEVERR_FULL_WAIT)) return;
+        const bool active = in_slab && my_row < L.rows && (!CHUNKED || e0 < L.ncols);
+        if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
         const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
 
         float2 x[NP];
@@ -210,27 +213,40 @@ rows_kernel(const __grid_constant__ RowParams p) {
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);   // data is in registers: free the slot
-        if (!active) {
+        if (__any_sync(0xffffffffu, !active)) {      // only ragged slabs get here
+            if (!active) {
 #pragma unroll
-            for (int i = 0; i < NP; ++i) x[i] = make_float2(0.f, 0.f);
-            if constexpr (C::NIN == 2) {
+                for (int i = 0; i < NP; ++i) x[i] = make_float2(0.f, 0.f);
+                if constexpr (C::NIN == 2) {
 #pragma unroll
-                for (int i = 0; i < NP; ++i) g[i] = make_float2(0.f, 0.f);
+                    for (int i = 0; i < NP; ++i) g[i] = make_float2(0.f, 0.f);
+                }
             }
         }
+        // this warp's output span of the previous use of `buf` must have been read out
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
 
         float r = 0.f, tot_sc = 0.f;
         if constexpr (NORM) {
             // ---- per-row sums: sum x^2 (unless 1/rms is given) and, backward, sum x*g*gamma
-            float2 ss2 = make_float2(0.f, 0.f), sc2 = make_float2(0.f, 0.f);
-            if (!p.reuse_rms) {
+            float2 ss2 = make_float2(0.f, 0.f), ss3 = ss2, sc2 = ss2, sc3 = ss2;
+            if (!reuse) {
 #pragma unroll
-                for (int i = 0; i < NP; ++i) ss2 = fma2(x[i], x[i], ss2);
+                for (int i = 0; i < NP; i += 2) {
+                    ss2 = fma2(x[i], x[i], ss2);
+                    ss3 = fma2(x[i + 1], x[i + 1], ss3);
+                }
             }
             if constexpr (ROP == ROP_NORM_BWD) {
 #pragma unroll
-                for (int i = 0; i < NP; ++i) sc2 = fma2(x[i], mul2(g[i], gam[i]), sc2);
+                for (int i = 0; i < NP; i += 2) {
+                    sc2 = fma2(x[i], mul2(g[i], gam[i]), sc2);
+                    sc3 = fma2(x[i + 1], mul2(g[i + 1], gam[i + 1]), sc3);
+                }
             }
+            ss2 = add2(ss2, ss3);
+            sc2 = add2(sc2, sc3);
             float ss = ss2.x + ss2.y, sc = sc2.x + sc2.y;
             float* red_ss = red + buf * 128;
             float* red_sc = red + buf * 128 + 64;
@@ -249,28 +265,33 @@ rows_kernel(const __grid_constant__ RowParams p) {
                 }
                 if ((t % LPB) == 0) { red_ss[t / LPB] = ss; if constexpr (ROP == ROP_NORM_BWD) red_sc[t / LPB] = sc; }
             }
-            if (t == 0) bulk_wait_read<1>();               // output buffer `buf` is free again
             named_bar<1, NT>();
             float tot_ss = 0.f;
-            if (in_slab) {
-                const int cnt = warp_rows ? TPR / 32 : nb;
-                const int first = my_row * cnt;
-                for (int i = 0; i < cnt; ++i) {
-                    tot_ss += red_ss[first + i];
-                    if constexpr (ROP == ROP_NORM_BWD) tot_sc += red_sc[first + i];
+            if (red_cnt == 8) {   // one row per slab: two vector loads
+                const float4 a = *reinterpret_cast<const float4*>(red_ss + red_first);
+                const float4 b = *reinterpret_cast<const float4*>(red_ss + red_first + 4);
+                tot_ss = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+                if constexpr (ROP == ROP_NORM_BWD) {
+                    const float4 c = *reinterpret_cast<const float4*>(red_sc + red_first);
+                    const float4 d = *reinterpret_cast<const float4*>(red_sc + red_first + 4);
+                    tot_sc = ((c.x + c.y) + (c.z + c.w)) + ((d.x + d.y) + (d.z + d.w));
+                }
+            } else if (in_slab) {
+#pragma unroll 4
+                for (int i = 0; i < red_cnt; ++i) {
+                    tot_ss += red_ss[red_first + i];
+                    if constexpr (ROP == ROP_NORM_BWD) tot_sc += red_sc[red_first + i];
                 }
             }
-            if (p.reuse_rms) {
+            if (reuse) {
                 r = active ? p.rms[L.row0 + my_row] : 0.f;
             } else {
-                r = __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(tot_ss, float(n)), p.eps)));
+                r = rsqrt_nr(fmaf(tot_ss, p.inv_n, p.eps));
                 if (active && col0 == 0 && p.rms != nullptr) p.rms[L.row0 + my_row] = r;
             }
-        } else {
-            if (t == 0) bulk_wait_read<1>();
-            named_bar<1, NT>();
         }
 
+        uint8_t* so = outb + buf * C::OUTB + size_t(e0) * OB;
         if constexpr (C::QUANT) {
             if constexpr (ROP == ROP_NORM_Q) {
                 const float2 r2 = splat2(r);
@@ -280,26 +301,28 @@ rows_kernel(const __grid_constant__ RowParams p) {
 #pragma unroll
                 for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(sigmoid_fast2(x[i]), x[i]), g[i]);
             }
-            float a = 0.f;
+            float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-            for (int i = 0; i < NP; ++i) a = max3abs(x[i].x, x[i].y, a);
+            for (int i = 0; i < NP; i += 2) {
+                a0 = max3abs(x[i].x, x[i].y, a0);
+                a1 = max3abs(x[i + 1].x, x[i + 1].y, a1);
+            }
+            float a = fmaxf(a0, a1);
 #pragma unroll
             for (int d = LPB / 2; d >= 1; d >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, d));
             const float scale = scale_from_amax(a, rs);
-            const float2 inv = splat2(__frcp_rn(scale));
-            uint8_t* so = outb + buf * C::OUTB + e0;
+            const float2 inv = splat2(rcp_approx(scale));
 #pragma unroll
             for (int k = 0; k < NCH; ++k) {
                 const float2 q0 = mul2(x[4 * k + 0], inv), q1 = mul2(x[4 * k + 1], inv);
                 const float2 q2 = mul2(x[4 * k + 2], inv), q3 = mul2(x[4 * k + 3], inv);
-                const uint32_t lo = cvt_e4m3x2(q0.x, q0.y) | (cvt_e4m3x2(q1.x, q1.y) << 16);
-                const uint32_t hi = cvt_e4m3x2(q2.x, q2.y) | (cvt_e4m3x2(q3.x, q3.y) << 16);
+                const uint32_t lo = cvt_e4m3x4(q0.x, q0.y, q1.x, q1.y);
+                const uint32_t hi = cvt_e4m3x4(q2.x, q2.y, q3.x, q3.y);
                 *reinterpret_cast<uint2*>(so + 8 * (k ^ sw)) = make_uint2(lo, hi);
             }
             if (active && (t % LPB) == 0) p.s[int64_t(col0 >> 7) * p.M + L.row0 + my_row] = scale;
         } else if constexpr (ROP == ROP_NORM_Y) {
             const float2 r2 = splat2(r);
-            uint8_t* so = outb + buf * C::OUTB + size_t(e0) * 2;
 #pragma unroll
             for (int k = 0; k < NCH; ++k) {
                 uint32_t w[4];
@@ -311,9 +334,8 @@ rows_kernel(const __grid_constant__ RowParams p) {
                 *reinterpret_cast<uint4*>(so + 16 * (k ^ sw)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         } else {  // ROP_NORM_BWD: dx = r*g*gamma - r^3 * x * sum(x*g*gamma)/n ; dgamma += x*g*r
-            const float2 ncoef = splat2(-(r * r * r * tot_sc / float(n)));
+            const float2 ncoef = splat2(-(r * r * r * tot_sc * p.inv_n));
             const float2 r2 = splat2(r);
-            uint8_t* so = outb + buf * C::OUTB + size_t(e0) * 2;
 #pragma unroll
             for (int k = 0; k < NCH; ++k) {
                 uint32_t w[4];
@@ -327,16 +349,26 @@ rows_kernel(const __grid_constant__ RowParams p) {
                 *reinterpret_cast<uint4*>(so + 16 * (k ^ sw)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
+        // Each warp writes back its own contiguous span of the slab with one bulk copy.
         fence_async_smem();
-        named_bar<2, NT>();
-        if (t == 0) {
-            constexpr int OB = C::QUANT ? 1 : 2;
-            uint8_t* gbase = C::QUANT ? p.q : p.hp;
-            bulk_s2g(gbase + (L.row0 * n + L.c0) * OB, outb + buf * C::OUTB, uint32_t(L.rows) * uint32_t(L.ncols) * OB);
+        __syncwarp();
+        if (lane == 0) {
+            const int total = L.rows * L.ncols;                 // valid elements in the slab
+            int cnt = total - warp * WSPAN;
+            cnt = cnt > WSPAN ? WSPAN : cnt;
+            if (cnt > 0) {
+                uint8_t* gbase = C::QUANT ? p.q : p.hp;
+                bulk_s2g(gbase + (L.row0 * n + L.c0 + warp * WSPAN) * OB,
+                         outb + buf * C::OUTB + size_t(warp) * WSPAN * OB, uint32_t(cnt) * OB);
+            }
             bulk_commit();
         }
+        first_it = false;
+        prev_stage = stage; prev_phase = phase;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        buf ^= 1;
     }
-    if (t == 0) bulk_wait_all();
+    if (lane == 0) bulk_wait_all();
 
     if constexpr (ROP == ROP_NORM_BWD) {
         // Fold the per-thread dgamma sums of the RB rows of a slab into one row and
@@ -353,7 +385,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
         if (t < TPR) {
             for (int j = 0; j < EPT; ++j) {
                 float a = 0.f;
-                for (int rr = 0; rr < p.RB; ++rr) a += fold[j * NT + t + rr * TPR];
+                for (int rr = 0; rr < RB; ++rr) a += fold[j * NT + t + rr * TPR];
                 p.partial[int64_t(blockIdx.x) * n + col0 + j] = a;
             }
         }
@@ -374,11 +406,10 @@ __global__ void dgamma_reduce_kernel(const float* __restrict__ partial, int part
 template <int ROP, int EPT, int STAGES, int CTAS_PER_SM>
 static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream) {
     using C = RowCfg<ROP, EPT, STAGES>;
-    auto kern = rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(C::SMEM));
-    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
     int64_t slabs;
-    if (p.n <= kSlabElems) {
+    p.inv_n = 1.0f / float(p.n);
+    const bool chunked = p.n > kSlabElems;
+    if (!chunked) {
         p.RB = kSlabElems / p.n;
         p.chunks = 1;
         slabs = (p.M + p.RB - 1) / p.RB;
@@ -391,8 +422,16 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream) {
     if (grid > kMaxRowCtas) grid = kMaxRowCtas;
     if (slabs < grid) grid = slabs;
     if (grid_out) *grid_out = int(grid);
-    kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
-    return check_launch("rows_kernel");
+    auto go = [&](auto kern) -> int {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(C::SMEM));
+        if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
+        kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
+        return check_launch("rows_kernel");
+    };
+    if constexpr (ROP == ROP_SILU_Q) {
+        if (chunked) return go(rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM, true>);
+    }
+    return go(rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM, false>);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }

@@ -149,31 +149,73 @@ __device__ __forceinline__ float sum16(float a) {
     return a;
 }
 
-// exact quotient of one value (see Divisor); `tiny` blocks take IEEE division
-__device__ __forceinline__ float quot_exact(float x, float s, float y, bool tiny) {
+// exact quotient of one value: q0 = x*y with y = RN(1/s), residual r' = s*q0 - x (exact in
+// an FMA), q = q0 - r'*y.  Equals IEEE x / s bit for bit (Markstein) unless the residual
+// underflows, which needs a scale below ~2^-90; the negated-residual form keeps the sign
+// of a zero quotient.
+__device__ __forceinline__ float quot_exact(float x, float s, float y) {
     const float q0 = x * y;
     const float r = fmaf(s, q0, -x);
-    const float q = fmaf(r, -y, q0);
-    return tiny ? __fdiv_rn(x, s) : q;
+    return fmaf(r, -y, q0);
 }
+constexpr float kTinyScale = 8.0e-28f;   // ~2^-90: below this take IEEE division
 
-// 8 values of one row, one scale -> 8 codes
+// 8 values of one row, one scale (and its reciprocal) -> 8 codes
 template <bool EXACT>
-__device__ __forceinline__ uint2 quant_row8(const float2* v, float sc) {
-    const float y = __frcp_rn(sc);
+__device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) {
     float2 q[4];
     if constexpr (EXACT) {
-        const bool tiny = sc < 8.0e-28f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            q[j] = make_float2(quot_exact(v[j].x, sc, y, tiny), quot_exact(v[j].y, sc, y, tiny));
+        for (int j = 0; j < 4; ++j) q[j] = make_float2(quot_exact(v[j].x, sc, y), quot_exact(v[j].y, sc, y));
+        if (sc < kTinyScale) {   // rare: all-zero or denormal-range blocks
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(v[j].x, sc), __fdiv_rn(v[j].y, sc));
+        }
     } else {
         const float2 y2 = splat2(y);
 #pragma unroll
         for (int j = 0; j < 4; ++j) q[j] = mul2(v[j], y2);
     }
-    return make_uint2(cvt_e4m3x2(q[0].x, q[0].y) | (cvt_e4m3x2(q[1].x, q[1].y) << 16),
-                      cvt_e4m3x2(q[2].x, q[2].y) | (cvt_e4m3x2(q[3].x, q[3].y) << 16));
+    return make_uint2(cvt_e4m3x4(q[0].x, q[0].y, q[1].x, q[1].y), cvt_e4m3x4(q[2].x, q[2].y, q[3].x, q[3].y));
+}
+
+// reciprocal of a scale: correctly rounded where exact quotients are required
+template <bool EXACT>
+__device__ __forceinline__ float scale_rcp(float sc) {
+    return EXACT ? __frcp_rn(sc) : rcp_approx(sc);
+}
+
+// Row maxima across the 16 lanes that share a tile row, for RPT rows at once: a
+// transposing butterfly halves the number of live values at each step, so RPT rows cost
+// RPT + log2(16/RPT) shuffles instead of 4*RPT.  On return a[0] holds the maximum of row
+// (l16 * RPT / 16), replicated over 16/RPT neighbouring lanes.
+template <int RPT>
+__device__ __forceinline__ float row_max_transposed(float* a, int l16) {
+    static_assert(RPT == 8 || RPT == 4, "RPT");
+    if constexpr (RPT == 8) {
+        const bool up = (l16 & 8) != 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float recv = __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 4], 8);
+            a[i] = fmaxf(up ? a[i + 4] : a[i], recv);
+        }
+    }
+    {
+        const bool up = (l16 & (RPT == 8 ? 4 : 8)) != 0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float recv = __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 2], RPT == 8 ? 4 : 8);
+            a[i] = fmaxf(up ? a[i + 2] : a[i], recv);
+        }
+    }
+    {
+        const bool up = (l16 & (RPT == 8 ? 2 : 4)) != 0;
+        const float recv = __shfl_xor_sync(0xffffffffu, up ? a[0] : a[1], RPT == 8 ? 2 : 4);
+        a[0] = fmaxf(up ? a[1] : a[0], recv);
+    }
+    if constexpr (RPT == 4) a[0] = fmaxf(a[0], __shfl_xor_sync(0xffffffffu, a[0], 2));
+    a[0] = fmaxf(a[0], __shfl_xor_sync(0xffffffffu, a[0], 1));
+    return a[0];
 }
 
 template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int MINB>
@@ -381,16 +423,15 @@ tile_kernel(const __grid_constant__ TileParams p) {
             }
             if (p.hp != nullptr) {
 #pragma unroll
-                for (int h = 0; h < NHALF; ++h)
+                for (int h = 0; h < NHALF; ++h) {
+                    uint8_t* dst = reinterpret_cast<uint8_t*>(p.hp) +
+                                   ((grow0 + row0) * (2 * p.n) + h * p.n + gcol0 + l16 * 8) * C::EB;
 #pragma unroll
                     for (int s = 0; s < RPT; ++s) {
-                        const int rr = row0 + s;
-                        if (rr < t.valid) {
-                            uint8_t* dst = reinterpret_cast<uint8_t*>(p.hp) +
-                                           ((grow0 + rr) * (2 * p.n) + h * p.n + gcol0 + l16 * 8) * C::EB;
-                            store8_hp<InT>(dst, v[h][s]);
-                        }
+                        if (row0 + s < t.valid) store8_hp<InT>(dst, v[h][s]);
+                        dst += 2 * p.n * C::EB;
                     }
+                }
             }
         }
 
@@ -411,10 +452,11 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
                 for (int w2 = 1; w2 < NW; ++w2) bm = fmaxf(bm, part[w2]);
                 const float sc = scale_from_amax(bm, rs);
+                const float y = scale_rcp<EXACT>(sc);
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     const int rr = row0 + s;
-                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc);
+                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc, y);
                     if (rr < t.valid) st_global_v2(p.q + (grow0 + rr) * p.n + gcol0 + l16 * 8, codes.x, codes.y);
                 }
                 if (tid == 0) p.s[(t.B + t.T) * nb + t.ct] = sc;
@@ -422,26 +464,36 @@ tile_kernel(const __grid_constant__ TileParams p) {
             }
             // ------------------------------ row-wise 1x128 --------------------------
             if constexpr (MODE == MODE_ROW || MODE == MODE_BOTH) {
-                float myscale = 0.f;
+                constexpr int G = 16 / RPT;   // lanes that end up holding the same row maximum
+                float a[RPT];
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
-                    const int rr = row0 + s;
-                    float a = 0.f;
+                    float m = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) a = max3abs(v[h][s][j].x, v[h][s][j].y, a);
-                    a = max16(a);
-                    const float sc = scale_from_amax(a, rs);
-                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc);
-                    if (rr < t.valid)
-                        st_global_v2(p.q + (grow0 + rr) * (NHALF * p.n) + h * p.n + gcol0 + l16 * 8, codes.x, codes.y);
-                    if (l16 == s) myscale = sc;
+                    for (int j = 0; j < 4; ++j) m = max3abs(v[h][s][j].x, v[h][s][j].y, m);
+                    a[s] = m;
                 }
-                if (l16 < RPT && row0 + l16 < t.valid) {
-                    const int rr = row0 + l16;
-                    if (p.scale_rowmajor)
-                        p.s[(grow0 + rr) * nb + t.ct] = myscale;
-                    else
-                        p.s[t.S * (NHALF * nb) + (h * nb + t.ct) * t.c + int64_t(t.T) * 128 + rr] = myscale;
+                const float mysc = scale_from_amax(row_max_transposed<RPT>(a, l16), rs);
+                const float myy = scale_rcp<EXACT>(mysc);
+                {
+                    const int rr = row0 + l16 / G;   // the row this lane holds the scale of
+                    if ((l16 % G) == 0 && rr < t.valid) {
+                        if (p.scale_rowmajor)
+                            p.s[(grow0 + rr) * nb + t.ct] = mysc;
+                        else
+                            p.s[t.S * (NHALF * nb) + (h * nb + t.ct) * t.c + int64_t(t.T) * 128 + rr] = mysc;
+                    }
+                }
+                const int64_t ldq = NHALF * p.n;
+                uint8_t* qrow = p.q + (grow0 + row0) * ldq + h * p.n + gcol0 + l16 * 8;
+                const int nrows = t.valid - row0;   // rows of this thread that exist (may exceed RPT)
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    const float sc = __shfl_sync(0xffffffffu, mysc, s * G, 16);
+                    const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
+                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc, y);
+                    if (s < nrows) st_global_v2(qrow, codes.x, codes.y);
+                    qrow += ldq;
                 }
             }
             // ------------------------ column-wise 128x1, transposed -----------------
@@ -470,7 +522,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     for (int w2 = 1; w2 < NW; ++w2) m = fmaxf(m, part[w2 * 128 + tid]);
                     const float sc = scale_from_amax(m, rs);
                     cs[tid] = sc;
-                    cy[tid] = __frcp_rn(sc);
+                    cy[tid] = scale_rcp<EXACT>(sc);
                     p.st[(t.B + t.T) * (NHALF * p.n) + h * p.n + gcol0 + tid] = sc;
                 }
                 named_bar<1, NCONS>();
@@ -489,11 +541,15 @@ tile_kernel(const __grid_constant__ TileParams p) {
                 for (int j = 0; j < 4; ++j) {
                     float2 q[RPT];
                     if constexpr (EXACT) {
-                        const bool tx = sc2[j].x < 8.0e-28f, ty = sc2[j].y < 8.0e-28f;
 #pragma unroll
                         for (int s = 0; s < RPT; ++s)
-                            q[s] = make_float2(quot_exact(v[h][s][j].x, sc2[j].x, y2[j].x, tx),
-                                               quot_exact(v[h][s][j].y, sc2[j].y, y2[j].y, ty));
+                            q[s] = make_float2(quot_exact(v[h][s][j].x, sc2[j].x, y2[j].x),
+                                               quot_exact(v[h][s][j].y, sc2[j].y, y2[j].y));
+                        if (sc2[j].x < kTinyScale || sc2[j].y < kTinyScale) {   // rare slow path
+#pragma unroll
+                            for (int s = 0; s < RPT; ++s)
+                                q[s] = make_float2(__fdiv_rn(v[h][s][j].x, sc2[j].x), __fdiv_rn(v[h][s][j].y, sc2[j].y));
+                        }
                     } else {
 #pragma unroll
                         for (int s = 0; s < RPT; ++s) q[s] = mul2(v[h][s][j], y2[j]);
@@ -503,36 +559,49 @@ tile_kernel(const __grid_constant__ TileParams p) {
                         const int rc = cw * 2 + hw;
                         const uint32_t off = uint32_t((rc ^ l16) << 3);
                         *reinterpret_cast<uint2*>(qts + colx * 128 + off) = make_uint2(
-                            cvt_e4m3x2(q[0].x, q[1].x) | (cvt_e4m3x2(q[2].x, q[3].x) << 16),
-                            cvt_e4m3x2(q[4].x, q[5].x) | (cvt_e4m3x2(q[6].x, q[7].x) << 16));
+                            cvt_e4m3x4(q[0].x, q[1].x, q[2].x, q[3].x), cvt_e4m3x4(q[4].x, q[5].x, q[6].x, q[7].x));
                         *reinterpret_cast<uint2*>(qts + (colx + 1) * 128 + off) = make_uint2(
-                            cvt_e4m3x2(q[0].y, q[1].y) | (cvt_e4m3x2(q[2].y, q[3].y) << 16),
-                            cvt_e4m3x2(q[4].y, q[5].y) | (cvt_e4m3x2(q[6].y, q[7].y) << 16));
+                            cvt_e4m3x4(q[0].y, q[1].y, q[2].y, q[3].y), cvt_e4m3x4(q[4].y, q[5].y, q[6].y, q[7].y));
                     } else {
                         static_assert(RPT == 8 || RPT == 4, "RPT");
                         const uint32_t off = uint32_t(((cw ^ l16) << 3) + hw * 4);
                         *reinterpret_cast<uint32_t*>(qts + colx * 128 + off) =
-                            cvt_e4m3x2(q[0].x, q[1].x) | (cvt_e4m3x2(q[2].x, q[3].x) << 16);
+                            cvt_e4m3x4(q[0].x, q[1].x, q[2].x, q[3].x);
                         *reinterpret_cast<uint32_t*>(qts + (colx + 1) * 128 + off) =
-                            cvt_e4m3x2(q[0].y, q[1].y) | (cvt_e4m3x2(q[2].y, q[3].y) << 16);
+                            cvt_e4m3x4(q[0].y, q[1].y, q[2].y, q[3].y);
                     }
                 }
                 named_bar<1, NCONS>();
-                // copy-out: 128 columns x 16 chunks of 8 rows
-                uint8_t* qt_seg = p.qt + t.S * (NHALF * p.n) + (h * p.n + gcol0) * t.c + int64_t(t.T) * 128;
-                const bool fast = (t.c & 7) == 0;
-#pragma unroll
-                for (int k = 0; k < 2048 / NCONS; ++k) {
-                    const int u = tid + k * NCONS;
-                    const int col = u >> 4, rc = u & 15;
-                    const uint2 val = *reinterpret_cast<const uint2*>(qts + col * 128 + ((rc ^ ((col >> 3) & 15)) << 3));
-                    uint8_t* dst = qt_seg + int64_t(col) * t.c + rc * 8;
+                // copy-out: 128 columns x 16 chunks of 8 rows; thread u handles chunk (u & 15)
+                // of columns (u >> 4) + k * NCONS / 16
+                {
+                    const int rc = tid & 15, colb = tid >> 4;
+                    uint8_t* dst = p.qt + t.S * (NHALF * p.n) + (h * p.n + gcol0 + colb) * t.c + int64_t(t.T) * 128 + rc * 8;
+                    const int64_t dstep = int64_t(NCONS / 16) * t.c;
+                    const uint8_t* src = qts + colb * 128;
                     const int nvalid = t.valid - rc * 8;
-                    if (fast && nvalid >= 8) {
-                        *reinterpret_cast<uint2*>(dst) = val;
-                    } else if (nvalid > 0) {
-                        const uint64_t bits = (uint64_t(val.y) << 32) | val.x;
-                        for (int b2 = 0; b2 < 8 && b2 < nvalid; ++b2) dst[b2] = uint8_t(bits >> (8 * b2));
+                    if ((t.c & 7) == 0 && t.valid == 128) {
+#pragma unroll
+                        for (int k = 0; k < 2048 / NCONS; ++k) {
+                            const int col = colb + k * (NCONS / 16);
+                            *reinterpret_cast<uint2*>(dst) =
+                                *reinterpret_cast<const uint2*>(src + k * (NCONS / 16) * 128 + ((rc ^ ((col >> 3) & 15)) << 3));
+                            dst += dstep;
+                        }
+                    } else {
+                        const bool vec = (t.c & 7) == 0 && nvalid >= 8;
+                        for (int k = 0; k < 2048 / NCONS; ++k) {
+                            const int col = colb + k * (NCONS / 16);
+                            const uint2 val =
+                                *reinterpret_cast<const uint2*>(src + k * (NCONS / 16) * 128 + ((rc ^ ((col >> 3) & 15)) << 3));
+                            if (vec) {
+                                *reinterpret_cast<uint2*>(dst) = val;
+                            } else if (nvalid > 0) {
+                                const uint64_t bits = (uint64_t(val.y) << 32) | val.x;
+                                for (int b2 = 0; b2 < 8 && b2 < nvalid; ++b2) dst[b2] = uint8_t(bits >> (8 * b2));
+                            }
+                            dst += dstep;
+                        }
                     }
                 }
             }
@@ -631,9 +700,9 @@ int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts,
     p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
     p.round_scale = round_scale;
     switch (mode) {
-        case MODE_ROW: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_ROW, LH_FUSED_EXACT, 8, 3, 1>(p, stream);
-        case MODE_COL: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 8, 3, 1>(p, stream);
-        case MODE_BOTH: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 8, 3, 1>(p, stream);
+        case MODE_ROW: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_ROW, LH_FUSED_EXACT, 4, 3, 1>(p, stream);
+        case MODE_COL: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 4, 3, 1>(p, stream);
+        case MODE_BOTH: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 3, 1>(p, stream);
     }
     return fail_arg("output_mode must be 0, 1 or 2");
 }
