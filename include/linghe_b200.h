@@ -116,6 +116,32 @@ int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float
                    int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
                    void* stream);
 
+/* RMSNorm backward for callers that must not allocate device memory.
+ * No counterpart in the reference (its wrapper always allocates a partial buffer with
+ * torch.empty): this is lh_rmsnorm_bwd with the dgamma scratch built into the library.
+ *
+ * Who needs it: host code that sits outside the framework's caching allocator -- a plain
+ * C/C++ integration of this ABI, or a training job that has already handed all free
+ * device memory to its pool -- cannot get scratch for lh_rmsnorm_bwd: a raw cudaMalloc
+ * may fail for lack of memory, and cudaMalloc / cudaFree stall the device besides.
+ * Here the per-CTA partial sums go to a fixed device array of 148 x 8192 floats
+ * (4 849 664 bytes) that every GPU holds from the moment it loads the library until the
+ * process exits.  The call performs no cudaMalloc, cudaFree or any other allocation.
+ *
+ * Limits and rules:
+ *   - n <= 8192 (and n % 128 == 0); larger n is rejected with LH_ERR_ARG.  M is unbounded.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress) and caches it; make that first call with the device current
+ *     and before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the last call left
+ *     in it.  Nothing needs clearing (each call overwrites every partial row it later
+ *     reads), but two calls whose kernels overlap on the GPU -- different streams, or
+ *     different host threads on different streams -- race on it: serialise them.
+ * Arguments as lh_rmsnorm_bwd without the scratch pair; results match it (bit for bit on
+ * a 148-SM B200, where both run the same grid). */
+int lh_rmsnorm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype,
+                          int64_t M, int64_t n, float eps, void* dx, float* dgamma, void* stream);
+
 /* RMSNorm backward fused with the dual-axis quantisation of dy (the copies the
  * neighbouring linear layer's dgrad / wgrad GEMMs consume).  Upstream runs
  * triton_rms_norm_backward (linghe/utils/norm.py:144) and triton_blockwise_quant

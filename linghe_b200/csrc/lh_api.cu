@@ -117,6 +117,9 @@ int64_t rows_norm_bwd_scratch(int64_t n);
 int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
                   cudaStream_t stream);
+int64_t rows_norm_bwd_static_bytes();
+int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
+                         int64_t n, float eps, void* dx, float* dgamma, cudaStream_t stream);
 int dw_reduce(const float* dws, int64_t R, int64_t nb, void* dw, int w_dtype, cudaStream_t stream);
 int weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,
                       cudaStream_t stream);
@@ -168,6 +171,7 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!what) return -1;
     if (!strcmp(what, "rmsnorm_bwd")) return rows_norm_bwd_scratch(cols);
     if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
+    if (!strcmp(what, "rmsnorm_bwd_static")) return 0;  // it carries its own
     return -1;
 }
 
@@ -226,6 +230,11 @@ int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float
                    void* stream) {
     return rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes,
                          static_cast<cudaStream_t>(stream));
+}
+
+int lh_rmsnorm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
+                          int64_t n, float eps, void* dx, float* dgamma, void* stream) {
+    return rows_norm_bwd_static(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, static_cast<cudaStream_t>(stream));
 }
 
 int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, const float* rms, int dtype,

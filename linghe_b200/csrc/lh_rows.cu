@@ -404,7 +404,7 @@ __global__ void dgamma_reduce_kernel(const float* __restrict__ partial, int part
 // host side
 // ------------------------------------------------------------------------------------
 template <int ROP, int EPT, int STAGES, int CTAS_PER_SM>
-static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream) {
+static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid_cap = kMaxRowCtas) {
     using C = RowCfg<ROP, EPT, STAGES>;
     int64_t slabs;
     p.inv_n = 1.0f / float(p.n);
@@ -419,7 +419,7 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream) {
         slabs = p.M * p.chunks;
     }
     int64_t grid = int64_t(sm_count()) * CTAS_PER_SM;
-    if (grid > kMaxRowCtas) grid = kMaxRowCtas;
+    if (grid > grid_cap) grid = grid_cap;
     if (slabs < grid) grid = slabs;
     if (grid_out) *grid_out = int(grid);
     auto go = [&](auto kern) -> int {
@@ -494,6 +494,62 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     int grid = 0;
     if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream)) return rc;
     dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(128), 0, stream>>>(p.partial, grid, int(n), dgamma);
+    return check_launch("dgamma_reduce_kernel");
+}
+
+// ------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation: the per-CTA dgamma partials live in a
+// file-scope device array instead of caller-provided scratch.
+// ------------------------------------------------------------------------------------
+constexpr int kStaticCtas = 148;                       // partial rows held by the array
+constexpr int kStaticMaxCols = kSlabElems;             // widest row supported (8192)
+static __device__ __align__(256) float g_static_dgamma_partials[kStaticCtas * kStaticMaxCols];
+
+int64_t rows_norm_bwd_static_bytes() { return int64_t(sizeof(float)) * kStaticCtas * kStaticMaxCols; }
+
+// Device address of the array for the current device.  The symbol name is only a host-side
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, once per device.
+static int static_partials_ptr(float** out) {
+    static float* cached[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_error("cudaGetDevice: %s", cudaGetErrorString(e)); return int(e); }
+    if (dev < 0 || dev >= 64) return fail_arg("rmsnorm_bwd_static: device index %d out of range", dev);
+    if (cached[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_dgamma_partials);
+        if (e != cudaSuccess || ptr == nullptr) {
+            set_error("cudaGetSymbolAddress(static dgamma partials): %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? int(e) : int(cudaErrorInvalidSymbol);
+        }
+        cached[dev] = ptr;
+    }
+    *out = cached[dev];
+    return LH_OK;
+}
+
+int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
+                         int64_t n, float eps, void* dx, float* dgamma, cudaStream_t stream) {
+    if (int rc = check_rows("rmsnorm_bwd_static", dtype, M, n)) return rc;
+    if (n > kStaticMaxCols)
+        return fail_arg("rmsnorm_bwd_static: n=%lld exceeds the built-in scratch (at most %d columns)", (long long)n, kStaticMaxCols);
+    if (!x || !dy || !gamma || !dx || !dgamma) return fail_arg("rmsnorm_bwd_static: NULL pointer");
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(gamma)) return fail_arg("rmsnorm_bwd_static: pointers must be 16-byte aligned");
+    float* partial = nullptr;
+    if (int rc = static_partials_ptr(&partial)) return rc;
+    if (M == 0) {
+        cudaError_t e = cudaMemsetAsync(dgamma, 0, size_t(n) * 4, stream);
+        return e == cudaSuccess ? LH_OK : int(e);
+    }
+    RowParams p{};
+    p.x = static_cast<const uint8_t*>(x); p.dy = static_cast<const uint8_t*>(dy); p.gamma = gamma;
+    p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr; p.eps = eps; p.M = M; p.n = int(n);
+    p.hp = static_cast<uint8_t*>(dx); p.partial = partial;
+    int grid = 0;
+    // Every launched CTA overwrites its whole partial row [0, n) and the reduction reads only
+    // the `grid` rows written by this call, so nothing in the array has to start at zero.
+    if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream, kStaticCtas)) return rc;
+    dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(128), 0, stream>>>(partial, grid, int(n), dgamma);
     return check_launch("dgamma_reduce_kernel");
 }
 
