@@ -392,6 +392,235 @@ rows_kernel(const __grid_constant__ RowParams p) {
     }
 }
 
+// ------------------------------------------------------------------------------------
+// RMSNorm + 1x128 quantisation, U slabs per iteration.
+//
+// Same data flow as rows_kernel<ROP_NORM_Q>, but one iteration covers U consecutive slabs
+// (U * RB rows): the per-iteration control work (barrier waits, the CTA barrier of the
+// row-sum reduction, address set-up, the producer's refill) is paid once per U slabs, and
+// the two independent rows give the schedulers more to overlap.  To keep the register
+// budget of one slab, each slab is read from shared memory twice: once for sum x^2, and
+// again after the barrier for normalise + quantise.
+// ------------------------------------------------------------------------------------
+template <int U, int STAGES>
+struct NormQCfg {
+    static constexpr int NT = 256, NW = 8, EPT = 32;
+    static constexpr int STAGEB = U * kSlabElems * 2;
+    static constexpr int OUTB = U * kSlabElems;
+    static constexpr int OFF_OUT = STAGES * STAGEB;
+    static constexpr int OFF_RED = OFF_OUT + 2 * OUTB;            // [2][U][64]
+    static constexpr int OFF_BAR = OFF_RED + 2 * U * 64 * 4;
+    static constexpr int SMEM = OFF_BAR + 2 * STAGES * 8;
+};
+
+template <int U, int STAGES, int MINB>
+__global__ void __launch_bounds__(256, MINB)
+normq_kernel(const __grid_constant__ RowParams p) {
+    using C = NormQCfg<U, STAGES>;
+    constexpr int NT = C::NT, NW = C::NW, EPT = C::EPT, NCH = 4, NP = 16, LPB = 4, WSPAN = 1024;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stages = smem;
+    uint8_t* outb = smem + C::OFF_OUT;
+    float* red = reinterpret_cast<float*>(smem + C::OFF_RED);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+    uint64_t* empty = full + STAGES;
+
+    const int t = threadIdx.x;
+    const int warp = t >> 5, lane = t & 31;
+    const int n = p.n;
+    const int RB = p.RB;                       // rows per slab
+    const int GR = U * RB;                     // rows per iteration
+    const int64_t groups = (p.M + GR - 1) / GR;
+
+    if (t == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], NW);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int64_t grp, int stage) {   // thread 0 only
+        const int64_t r0 = grp * GR;
+        const int64_t left = p.M - r0;
+        const uint32_t rows = uint32_t(left < GR ? left : GR);
+        const uint32_t bytes = rows * uint32_t(n) * 2u;
+        uint8_t* dst = stages + size_t(stage) * C::STAGEB;
+        mbar_expect_tx(&full[stage], bytes);
+        if (RB * n == kSlabElems) {            // slabs are dense: one copy for the whole group
+            bulk_g2s(dst, p.x + r0 * n * 2, bytes, &full[stage]);
+        } else {                               // n does not divide 8192: slabs have a tail gap
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int rws = int(rows) - u * RB;
+                if (rws > 0)
+                    bulk_g2s(dst + u * kSlabElems * 2, p.x + (r0 + u * RB) * n * 2,
+                             uint32_t(rws < RB ? rws : RB) * uint32_t(n) * 2u, &full[stage]);
+            }
+        }
+    };
+    if (t == 0) {
+        int64_t grp = blockIdx.x;
+        for (int j = 0; j < STAGES && grp < groups; ++j, grp += gridDim.x) issue(grp, j);
+    }
+
+    const int e0 = t * EPT;
+    const int sw = (t >> 1) & 3;
+    const bool rs = p.round_scale != 0;
+    const int my_row = e0 / n;
+    const int col0 = e0 - my_row * n;
+    const bool in_slab = my_row < RB;
+    float2 gam[NP];
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (in_slab)
+            raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.gamma) + (col0 + 8 * (k ^ sw)) * 2);
+        gam[4 * k + 0] = bf16x2_to_f2(raw.x);
+        gam[4 * k + 1] = bf16x2_to_f2(raw.y);
+        gam[4 * k + 2] = bf16x2_to_f2(raw.z);
+        gam[4 * k + 3] = bf16x2_to_f2(raw.w);
+    }
+    const int TPR = n / EPT;
+    const bool warp_rows = (TPR % 32) == 0;
+    const int red_cnt = warp_rows ? TPR / 32 : (n >> 7);
+    const int red_first = my_row * red_cnt;
+    float* const s_col = p.s + int64_t(col0 >> 7) * p.M + my_row;   // + global row of the slab
+
+    int stage = 0, prev_stage = 0, buf = 0;
+    uint32_t phase = 0, prev_phase = 0;
+    bool first_it = true;
+    for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+        if (t == 0 && !first_it) {
+            const int64_t nxt = grp + int64_t(STAGES - 1) * gridDim.x;
+            if (nxt < groups && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
+        }
+        const int64_t r0 = grp * GR;
+        const int64_t left = p.M - r0;
+        const int rows = int(left < GR ? left : GR);        // valid rows in this group
+        if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+        const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
+        float* red_b = red + buf * (U * 64);
+
+        // ---- pass 1: sum of squares of every slab -------------------------------------
+        float ss[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float2 a0 = make_float2(0.f, 0.f), a1 = a0;
+            const bool act = in_slab && (u * RB + my_row) < rows;
+#pragma unroll
+            for (int k = 0; k < NCH; ++k) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(sx + u * kSlabElems * 2 + 16 * (k ^ sw));
+                const float2 v0 = bf16x2_to_f2(raw.x), v1 = bf16x2_to_f2(raw.y);
+                const float2 v2 = bf16x2_to_f2(raw.z), v3 = bf16x2_to_f2(raw.w);
+                a0 = fma2(v0, v0, a0); a1 = fma2(v1, v1, a1);
+                a0 = fma2(v2, v2, a0); a1 = fma2(v3, v3, a1);
+            }
+            a0 = add2(a0, a1);
+            ss[u] = act ? a0.x + a0.y : 0.f;
+        }
+        if (warp_rows) {
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], d);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) red_b[u * 64 + warp] = ss[u];
+            }
+        } else {
+#pragma unroll
+            for (int d = LPB / 2; d >= 1; d >>= 1) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) ss[u] += __shfl_xor_sync(0xffffffffu, ss[u], d);
+            }
+            if ((t % LPB) == 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) red_b[u * 64 + t / LPB] = ss[u];
+            }
+        }
+        if (lane == 0) bulk_wait_read<U>();      // this warp's spans of out[buf] have been read out
+        named_bar<1, NT>();
+
+        // ---- pass 2: normalise, quantise, stage the codes ----------------------------
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            float tot = 0.f;
+            if (red_cnt == 8) {
+                const float4 a = *reinterpret_cast<const float4*>(red_b + u * 64 + red_first);
+                const float4 b = *reinterpret_cast<const float4*>(red_b + u * 64 + red_first + 4);
+                tot = ((a.x + a.y) + (a.z + a.w)) + ((b.x + b.y) + (b.z + b.w));
+            } else if (in_slab) {
+#pragma unroll 4
+                for (int i = 0; i < red_cnt; ++i) tot += red_b[u * 64 + red_first + i];
+            }
+            const float r = rsqrt_nr(fmaf(tot, p.inv_n, p.eps));
+            const bool act = in_slab && (u * RB + my_row) < rows;
+            const float2 r2 = splat2(act ? r : 0.f);
+            float2 x[NP];
+#pragma unroll
+            for (int k = 0; k < NCH; ++k) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(sx + u * kSlabElems * 2 + 16 * (k ^ sw));
+                x[4 * k + 0] = mul2(mul2(bf16x2_to_f2(raw.x), r2), gam[4 * k + 0]);
+                x[4 * k + 1] = mul2(mul2(bf16x2_to_f2(raw.y), r2), gam[4 * k + 1]);
+                x[4 * k + 2] = mul2(mul2(bf16x2_to_f2(raw.z), r2), gam[4 * k + 2]);
+                x[4 * k + 3] = mul2(mul2(bf16x2_to_f2(raw.w), r2), gam[4 * k + 3]);
+            }
+            if (u == U - 1) {                    // last read of the stage: hand it back
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[stage]);
+            }
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int i = 0; i < NP; i += 2) {
+                a0 = max3abs(x[i].x, x[i].y, a0);
+                a1 = max3abs(x[i + 1].x, x[i + 1].y, a1);
+            }
+            float a = fmaxf(a0, a1);
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            const float scale = scale_from_amax(a, rs);
+            const float2 inv = splat2(rcp_approx(scale));
+            uint8_t* so = outb + buf * C::OUTB + u * kSlabElems + e0;
+#pragma unroll
+            for (int k = 0; k < NCH; ++k) {
+                const float2 q0 = mul2(x[4 * k + 0], inv), q1 = mul2(x[4 * k + 1], inv);
+                const float2 q2 = mul2(x[4 * k + 2], inv), q3 = mul2(x[4 * k + 3], inv);
+                *reinterpret_cast<uint2*>(so + 8 * (k ^ sw)) =
+                    make_uint2(cvt_e4m3x4(q0.x, q0.y, q1.x, q1.y), cvt_e4m3x4(q2.x, q2.y, q3.x, q3.y));
+            }
+            if (act) {
+                const int64_t grow = r0 + u * RB;
+                if ((t % LPB) == 0) s_col[grow] = scale;
+                if (col0 == 0) p.rms[grow + my_row] = r;
+            }
+        }
+        // ---- each warp writes back its own contiguous span of every slab -------------
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                int rws = rows - u * RB;
+                rws = rws < RB ? rws : RB;
+                int cnt = rws * n - warp * WSPAN;                 // valid elements left for this warp
+                cnt = cnt > WSPAN ? WSPAN : cnt;
+                if (cnt > 0)
+                    bulk_s2g(p.q + (r0 + u * RB) * n + warp * WSPAN,
+                             outb + buf * C::OUTB + u * kSlabElems + warp * WSPAN, uint32_t(cnt));
+                bulk_commit();
+            }
+        }
+        first_it = false;
+        prev_stage = stage; prev_phase = phase;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        buf ^= 1;
+    }
+    if (lane == 0) bulk_wait_all();
+}
+
 __global__ void dgamma_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ out) {
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= n) return;
@@ -452,7 +681,21 @@ int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int6
     RowParams p{};
     p.x = static_cast<const uint8_t*>(x); p.gamma = gamma; p.rms = rms; p.eps = eps; p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
-    return launch_rows<ROP_NORM_Q, 32, 4, 2>(p, nullptr, stream);
+    // two slabs per iteration once there is enough work to fill the machine that way
+    constexpr int U = 2, STAGES = 2;
+    p.inv_n = 1.0f / float(p.n);
+    p.RB = kSlabElems / p.n;
+    p.chunks = 1;
+    const int64_t groups = (M + int64_t(U) * p.RB - 1) / (int64_t(U) * p.RB);
+    int64_t grid = int64_t(sm_count()) * 2;
+    if (grid > kMaxRowCtas) grid = kMaxRowCtas;
+    if (groups < 2 * grid) return launch_rows<ROP_NORM_Q, 32, 4, 2>(p, nullptr, stream);
+    using C = NormQCfg<U, STAGES>;
+    auto kern = normq_kernel<U, STAGES, 2>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(C::SMEM));
+    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
+    kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
+    return check_launch("normq_kernel");
 }
 
 int rows_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream) {
