@@ -257,7 +257,7 @@ def run_ours(args, rank, world, device):
                          "swiglu_quant": round(bytes_silu / silu_ms / 1e6, 1)},
         "roofline": {"bound": "hbm", "kernel": "rows_kernel<SILU_Q> (SwiGLU + 1x128 quant, dominant launch of the step)",
                      "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
-                     "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": TRAFFIC_SWIGLU_BYTES},
+                     "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": int(TRAFFIC_SWIGLU_BYTES * rows / ROWS)},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": Ke},
         "gpu_launches": 2 * K,
