@@ -103,8 +103,6 @@ int tile_quant(const void* x, int dtype, const void* counts, int counts_type, in
                cudaStream_t stream);
 int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,
                   int round_scale, cudaStream_t stream);
-int tile_norm_fused(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s,
-                    float* rms, void* qt, float* st, int round_scale, cudaStream_t stream);
 int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts, int counts_type, int E,
                   int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
                   cudaStream_t stream);
@@ -216,17 +214,6 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
     if (int rc = check_fused("rmsnorm_blockquant_fwd", dtype, M, n, output_mode)) return rc;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (!rms) return fail_arg("rmsnorm_blockquant_fwd: rms is NULL");
-    if (output_mode == 2 && getenv("LH_NORM_FUSED") != nullptr) {
-        // Opt-in single pass over x with a cluster per 128-row block.  It removes the second
-        // DRAM read of x but, as measured on B200, cluster co-scheduling leaves 19 % of the SMs
-        // idle and the kernel is slower than the two launches below; kept for tuning.
-        if (!x || !gamma || !q || !s || !qt || !st) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
-        if (n > 8192) return fail_arg("rmsnorm_blockquant_fwd: need n <= 8192");
-        if (!aligned16(x) || !aligned16(q) || !aligned16(qt) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: pointers must be 16-byte aligned");
-        if (M == 0) return LH_OK;
-        const int rc = tile_norm_fused(x, gamma, M, n, eps, q, s, rms, qt, st, round_scale, cs);
-        if (rc != LH_ERR_ARG + 1000) return rc;
-    }
     if (output_mode == 0 || output_mode == 2) {
         if (int rc = rows_norm_quant(x, gamma, dtype, M, n, eps, q, s, rms, round_scale, cs)) return rc;
     }

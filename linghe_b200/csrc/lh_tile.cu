@@ -19,7 +19,7 @@
 
 namespace lh {
 
-enum : int { OP_IDENT = 0, OP_NORM = 1, OP_SILU_F = 2, OP_SILU_B = 3, OP_NORM_FUSED = 4 };
+enum : int { OP_IDENT = 0, OP_NORM = 1, OP_SILU_F = 2, OP_SILU_B = 3 };
 enum : int { MODE_ROW = 0, MODE_COL = 1, MODE_BOTH = 2, MODE_BLOCK = 3 };
 
 struct TileParams {
@@ -27,10 +27,6 @@ struct TileParams {
     const void* w;         // optional per-row weight
     int w_bf16;
     const float* r;        // OP_NORM: 1/rms per row
-    float* rms_out;        // OP_NORM_FUSED: 1/rms per row (written)
-    float eps, inv_n;      // OP_NORM_FUSED
-    int cluster;           // OP_NORM_FUSED: CTAs per cluster (= column split of a 128-row block)
-    int tiles_per_cta;     // OP_NORM_FUSED: column tiles owned by one CTA of the cluster
     const void* gamma;     // OP_NORM: weight per column
     const void* counts;    // per-expert row counts (NULL = dense)
     int counts_i64;
@@ -52,7 +48,6 @@ template <> struct OpTraits<OP_IDENT> { static constexpr int K = 1, NHALF = 1; }
 template <> struct OpTraits<OP_NORM> { static constexpr int K = 1, NHALF = 1; };
 template <> struct OpTraits<OP_SILU_F> { static constexpr int K = 2, NHALF = 1; };
 template <> struct OpTraits<OP_SILU_B> { static constexpr int K = 3, NHALF = 2; };
-template <> struct OpTraits<OP_NORM_FUSED> { static constexpr int K = 1, NHALF = 1; };
 
 template <int OP, typename InT, int RPT, int STAGES>
 struct TileCfg {
@@ -73,8 +68,7 @@ struct TileCfg {
     static constexpr int OFF_CS = OFF_PART + NW * 128 * 4;       // [128] column scale
     static constexpr int OFF_CY = OFF_CS + 512;                  // [128] 1/scale
     static constexpr int OFF_BAR = OFF_CY + 512;                 // full[STAGES], empty[STAGES]
-    static constexpr int OFF_XCH = OFF_BAR + 2 * STAGES * 8;     // [2][8][128] row sums from the cluster
-    static constexpr int OFF_SEG = OFF_XCH + (OP == OP_NORM_FUSED ? 2 * 8 * 128 * 4 : 0);  // segS[E+1] int64, segB[E+1] int32
+    static constexpr int OFF_SEG = OFF_BAR + 2 * STAGES * 8;     // segS[E+1] int64, segB[E+1] int32
     static constexpr size_t smem_bytes(int E) { return size_t(OFF_SEG) + size_t(E + 1) * 12 + 16; }
 };
 
@@ -226,54 +220,7 @@ __device__ __forceinline__ float row_max_transposed(float* a, int l16) {
     return a[0];
 }
 
-// ---- thread-block-cluster helpers (distributed shared memory) ------------------------
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// store a float into the same shared-memory offset of CTA `rank` of this cluster
-__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t rank, float v) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
-
-// Row sums across the 16 lanes that share a tile row (transposing butterfly, see
-// row_max_transposed); on return a[0] is the sum of row (l16 * RPT / 16).
-template <int RPT>
-__device__ __forceinline__ float row_sum_transposed(float* a, int l16) {
-    static_assert(RPT == 8 || RPT == 4, "RPT");
-    if constexpr (RPT == 8) {
-        const bool up = (l16 & 8) != 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float recv = __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 4], 8);
-            a[i] = (up ? a[i + 4] : a[i]) + recv;
-        }
-    }
-    {
-        const bool up = (l16 & (RPT == 8 ? 4 : 8)) != 0;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const float recv = __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 2], RPT == 8 ? 4 : 8);
-            a[i] = (up ? a[i + 2] : a[i]) + recv;
-        }
-    }
-    {
-        const bool up = (l16 & (RPT == 8 ? 2 : 4)) != 0;
-        const float recv = __shfl_xor_sync(0xffffffffu, up ? a[0] : a[1], RPT == 8 ? 2 : 4);
-        a[0] = (up ? a[1] : a[0]) + recv;
-    }
-    if constexpr (RPT == 4) a[0] += __shfl_xor_sync(0xffffffffu, a[0], 2);
-    a[0] += __shfl_xor_sync(0xffffffffu, a[0], 1);
-    return a[0];
-}
-
-template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int MINB>
+template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int MINB, bool WEIGHTED>
 __global__ void __launch_bounds__(TileCfg<OP, InT, RPT, STAGES>::NTHREADS, MINB)
 tile_kernel(const __grid_constant__ TileParams p) {
     using C = TileCfg<OP, InT, RPT, STAGES>;
@@ -346,41 +293,6 @@ tile_kernel(const __grid_constant__ TileParams p) {
     // of every iteration, refills the stage that all warps released one iteration ago.
     // One tensor-map copy per operand brings a whole 128x128 tile; rows past the end of
     // the matrix read as zero, rows of a following expert segment are masked by `valid`.
-    // Work list.  Default: item `it` of this CTA is tile blockIdx.x + it * gridDim.x.
-    // OP_NORM_FUSED: a cluster of CL CTAs owns 128-row block (cluster id + k * clusters);
-    // CTA `crank` owns TPC column tiles of it and visits them twice -- first to sum x^2
-    // (phase A), then, after the cluster has exchanged its row sums, to normalise and
-    // quantise (phase B; these re-reads hit L2).
-    const int CL = OP == OP_NORM_FUSED ? p.cluster : 1;
-    const int TPC = OP == OP_NORM_FUSED ? p.tiles_per_cta : 1;
-    const int crank = OP == OP_NORM_FUSED ? int(cluster_ctarank()) : 0;
-    const int n_clusters = int(gridDim.x) / CL;
-    const int cluster_id = int(blockIdx.x) / CL;
-    const int row_blocks = segB[E];
-    const int my_blocks = (OP == OP_NORM_FUSED && row_blocks > cluster_id)
-        ? (row_blocks - cluster_id + n_clusters - 1) / n_clusters : 0;
-    // tile counts fit 32 bits (checked on the host); all per-item bookkeeping is 32-bit and
-    // incremental, without divisions
-    const int n_items = OP == OP_NORM_FUSED
-        ? my_blocks * 2 * TPC
-        : (total_tiles > blockIdx.x ? int((total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0);
-    // walker over the work list: `tile` of the current item, advanced one item at a time
-    struct Walk { int rb; int within; int tile; };
-    auto walk_init = [&]() {
-        Walk w;
-        w.rb = cluster_id; w.within = 0;
-        w.tile = OP == OP_NORM_FUSED ? cluster_id * col_tiles + crank * TPC : int(blockIdx.x);
-        return w;
-    };
-    auto walk_next = [&](Walk& w) {
-        if constexpr (OP == OP_NORM_FUSED) {
-            if (++w.within == 2 * TPC) { w.within = 0; w.rb += n_clusters; }
-            const int j = w.within >= TPC ? w.within - TPC : w.within;
-            w.tile = w.rb * col_tiles + crank * TPC + j;
-        } else {
-            w.tile += int(gridDim.x);
-        }
-    };
     auto issue = [&](int tile, int stage) {
         const TileLoc t = locate(tile, col_tiles, segS, segB, E);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
@@ -398,10 +310,10 @@ tile_kernel(const __grid_constant__ TileParams p) {
             tma_load_2d(dst, &p.tmap[0], c0, r0, &full[stage]);
         }
     };
-    Walk pw = walk_init();      // producer's position (thread 0 only): next item to load
-    int issued = 0;
+    const int n_tiles = int(total_tiles);   // fits 32 bits (checked on the host)
     if (tid == 0) {
-        for (; issued < STAGES && issued < n_items; ++issued) { issue(pw.tile, issued); walk_next(pw); }
+        int tile = int(blockIdx.x);
+        for (int j = 0; j < STAGES && tile < n_tiles; ++j, tile += int(gridDim.x)) issue(tile, j);
     }
 
     const int cw = warp;                 // warp index
@@ -410,27 +322,16 @@ tile_kernel(const __grid_constant__ TileParams p) {
     const int row0 = cw * (2 * RPT) + hw * RPT;
     const bool rs = p.round_scale != 0;
 
-    float ssq[OP == OP_NORM_FUSED ? RPT : 1];   // phase A: running sum of squares of this thread's rows
-    float rrow[OP == OP_NORM_FUSED ? RPT : 1];  // phase B: 1/rms of this thread's rows
-    float* xch = reinterpret_cast<float*>(smem + C::OFF_XCH);
-    bool failed = false;                        // a bounded wait gave up: stop waiting, keep barriers matched
-#pragma unroll
-    for (int s = 0; s < (OP == OP_NORM_FUSED ? RPT : 1); ++s) { ssq[s] = 0.f; rrow[s] = 0.f; }
-
-    Walk cw_ = walk_init();     // consumers' position
     int stage = 0, prev_stage = 0;
     uint32_t phase = 0, prev_phase = 0;
-    for (int it = 0; it < n_items; ++it) {
-        const int tile = cw_.tile;
-        if (tid == 0 && it > 0 && !failed) {
-            // the previous item's stage is free once every warp has released it: refill it
-            // with the next item not yet loaded.  Copies issued here are consumed by this
-            // CTA, so none is in flight when the loop ends.
-            if (issued < n_items && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) {
-                issue(pw.tile, prev_stage);
-                walk_next(pw);
-                ++issued;
-            }
+    bool first_it = true;
+    for (int tile = int(blockIdx.x); tile < n_tiles; tile += int(gridDim.x)) {
+        if (tid == 0 && !first_it) {
+            // the previous tile's stage is free once every warp has released it: refill it with
+            // the tile STAGES-1 steps ahead.  Copies issued here are consumed by this CTA, so
+            // none is in flight when the loop ends.
+            const int64_t nxt = int64_t(tile) + int64_t(STAGES - 1) * gridDim.x;
+            if (nxt < n_tiles && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(int(nxt), prev_stage);
         }
         const TileLoc t = locate(tile, col_tiles, segS, segB, E);
         const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
@@ -438,80 +339,34 @@ tile_kernel(const __grid_constant__ TileParams p) {
         // Per-row and per-column side inputs come straight from global memory: fetch them
         // before blocking on the tile so that their latency hides behind the TMA copy.
         const int nrows = t.valid - row0;   // rows of this thread that exist (may exceed RPT or be <= 0)
-        float aux[(OP == OP_NORM || OP == OP_SILU_F || OP == OP_SILU_B) ? RPT : 1];
+        constexpr bool HAS_AUX = OP == OP_NORM || ((OP == OP_SILU_F || OP == OP_SILU_B) && WEIGHTED);
+        float aux[HAS_AUX ? RPT : 1];
         if constexpr (OP == OP_NORM) {
 #pragma unroll
             for (int s = 0; s < RPT; ++s) aux[s] = s < nrows ? p.r[grow0 + row0 + s] : 0.f;
-        } else if constexpr (OP == OP_SILU_F || OP == OP_SILU_B) {
+        } else if constexpr (HAS_AUX) {
 #pragma unroll
-            for (int s = 0; s < RPT; ++s) aux[s] = 1.f;
-            if (p.w != nullptr) {
-#pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    if (s < nrows)
-                        aux[s] = p.w_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[grow0 + row0 + s])
-                                          : reinterpret_cast<const float*>(p.w)[grow0 + row0 + s];
-                }
+            for (int s = 0; s < RPT; ++s) {
+                aux[s] = 1.f;
+                if (s < nrows)
+                    aux[s] = p.w_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.w)[grow0 + row0 + s])
+                                      : reinterpret_cast<const float*>(p.w)[grow0 + row0 + s];
             }
         }
-        float2 gam[(OP == OP_NORM || OP == OP_NORM_FUSED) ? 4 : 1];
-        if constexpr (OP == OP_NORM || OP == OP_NORM_FUSED) {
+        float2 gam[OP == OP_NORM ? 4 : 1];
+        if constexpr (OP == OP_NORM) {
             const uint4 graw = *reinterpret_cast<const uint4*>(
                 reinterpret_cast<const uint8_t*>(p.gamma) + (gcol0 + l16 * 8) * 2);
             gam[0] = bf16x2_to_f2(graw.x); gam[1] = bf16x2_to_f2(graw.y);
             gam[2] = bf16x2_to_f2(graw.z); gam[3] = bf16x2_to_f2(graw.w);
         }
-        if (!failed && !mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) {
-            if constexpr (OP == OP_NORM_FUSED) failed = true; else return;
-        }
+        if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
         const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
 
-        // stage / phase / walker bookkeeping for the next iteration (the body may `continue`)
         const int cur_stage = stage;
-        const int within = cw_.within;
-        const int rb_parity = OP == OP_NORM_FUSED ? ((cw_.rb - cluster_id) / (n_clusters > 0 ? n_clusters : 1)) & 1 : 0;
+        first_it = false;
         prev_stage = stage; prev_phase = phase;
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        walk_next(cw_);
-
-        if constexpr (OP == OP_NORM_FUSED) {
-            if (within < TPC) {
-                // ---- phase A: sum of squares over this CTA's column tiles ------------------
-#pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    float2 x[4];
-                    load8p<InT>(sbase + (row0 + s) * C::ROWB, l16, x);
-                    float2 a = mul2(x[0], x[0]);
-                    a = fma2(x[1], x[1], a);
-                    a = fma2(x[2], x[2], a);
-                    a = fma2(x[3], x[3], a);
-                    ssq[s] += a.x + a.y;      // rows past the end of the matrix read as zero
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[cur_stage]);
-                if (within == TPC - 1) {
-                    // exchange row sums inside the cluster (double-buffered by row block)
-                    constexpr int G = 16 / RPT;
-                    float* buf = xch + rb_parity * (8 * 128);
-                    const float tot = row_sum_transposed<RPT>(ssq, l16);
-                    const int row = row0 + l16 / G;
-                    if ((l16 % G) == 0) {
-                        for (int c = 0; c < CL; ++c) st_cluster_f32(buf + crank * 128 + row, uint32_t(c), tot);
-                    }
-                    cluster_sync_all();
-                    float sum = 0.f;
-                    for (int c = 0; c < CL; ++c) sum += buf[c * 128 + row];
-                    const float myr = rsqrt_nr(fmaf(sum, p.inv_n, p.eps));
-                    if (crank == 0 && (l16 % G) == 0 && row < t.valid) p.rms_out[grow0 + row] = myr;
-#pragma unroll
-                    for (int s = 0; s < RPT; ++s) {
-                        rrow[s] = __shfl_sync(0xffffffffu, myr, s * G, 16);
-                        ssq[s] = 0.f;
-                    }
-                }
-                continue;
-            }
-        }
 
         float2 v[NHALF][RPT][4];
         float dwp[OP == OP_SILU_B ? RPT : 1];
@@ -520,14 +375,13 @@ tile_kernel(const __grid_constant__ TileParams p) {
             const uint8_t* srow = sbase + (row0 + s) * C::ROWB;
             if constexpr (OP == OP_IDENT) {
                 load8p<InT>(srow, l16, v[0][s]);
-            } else if constexpr (OP == OP_NORM || OP == OP_NORM_FUSED) {
+            } else if constexpr (OP == OP_NORM) {
                 float2 x[4];
                 load8p<InT>(srow, l16, x);
-                const float2 r2 = splat2(OP == OP_NORM ? aux[s] : rrow[s]);
+                const float2 r2 = splat2(aux[s]);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) v[0][s][j] = mul2(mul2(x[j], r2), gam[j]);
             } else if constexpr (OP == OP_SILU_F) {
-                const float2 w2 = splat2(aux[s]);   // 1.0 when there is no weight: exact
                 float2 x1[4], x2[4];
                 load8p<InT>(srow, l16, x1);
                 load8p<InT>(srow + C::TILEB, l16, x2);
@@ -535,10 +389,11 @@ tile_kernel(const __grid_constant__ TileParams p) {
                 for (int j = 0; j < 4; ++j) {
                     const float2 sg = EXACT ? make_float2(sigmoid_ref(x1[j].x), sigmoid_ref(x1[j].y))
                                             : sigmoid_fast2(x1[j]);
-                    v[0][s][j] = mul2(mul2(mul2(sg, x1[j]), x2[j]), w2);
+                    float2 y = mul2(mul2(sg, x1[j]), x2[j]);
+                    if constexpr (WEIGHTED) y = mul2(y, splat2(aux[s]));
+                    v[0][s][j] = y;
                 }
             } else {  // OP_SILU_B
-                const float2 w2 = splat2(aux[s]);
                 float2 g[4], x1[4], x2[4];
                 load8p<InT>(srow, l16, g);
                 load8p<InT>(srow + C::TILEB, l16, x1);
@@ -554,8 +409,8 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     const float2 u = fma2(x1[j], oms, splat2(1.f));
                     const float2 d1 = mul2(mul2(sgg, x2[j]), u);                      // d/dx1 (unweighted)
                     acc = fma2(d2, x2[j], acc);                                       // sigmoid*x1*x2*g
-                    v[0][s][j] = mul2(d1, w2);
-                    v[1][s][j] = mul2(d2, w2);
+                    v[0][s][j] = WEIGHTED ? mul2(d1, splat2(aux[s])) : d1;
+                    v[1][s][j] = WEIGHTED ? mul2(d2, splat2(aux[s])) : d2;
                 }
                 dwp[s] = acc.x + acc.y;
             }
@@ -775,10 +630,10 @@ tile_kernel(const __grid_constant__ TileParams p) {
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
-template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int CTAS_PER_SM>
+template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int CTAS_PER_SM, bool WEIGHTED = false>
 static int launch_tile(const TileParams& p, cudaStream_t stream) {
     using C = TileCfg<OP, InT, RPT, STAGES>;
-    auto kern = tile_kernel<OP, InT, MODE, EXACT, RPT, STAGES, CTAS_PER_SM>;
+    auto kern = tile_kernel<OP, InT, MODE, EXACT, RPT, STAGES, CTAS_PER_SM, WEIGHTED>;
     const size_t smem = C::smem_bytes(p.E);
     if (smem > 227 * 1024) return fail_arg("too many experts for the shared-memory segment table (E=%d)", p.E);
     if (((p.M + 127) / 128 + p.E) * (p.n / 128) >= (int64_t(1) << 31)) return fail_arg("tensor too large: tile count exceeds 2^31");
@@ -853,55 +708,6 @@ int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, i
     return launch_tile<OP_NORM, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 8, 2, 2>(p, stream);
 }
 
-// RMSNorm + both quantisation axes in one pass over HBM: clusters of `CL` CTAs split the
-// columns of a 128-row block, exchange their row sums through distributed shared memory and
-// revisit their tiles (from L2) to normalise and quantise.  Returns LH_ERR_ARG + 1000 when
-// the device cannot co-schedule such a cluster, so that the caller can fall back.
-int tile_norm_fused(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s,
-                    float* rms, void* qt, float* st, int round_scale, cudaStream_t stream) {
-    constexpr int RPT = 4, STAGES = 4;
-    using C = TileCfg<OP_NORM_FUSED, __nv_bfloat16, RPT, STAGES>;
-    auto kern = tile_kernel<OP_NORM_FUSED, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, RPT, STAGES, 1>;
-    TileParams p{};
-    if (int rc = make_tensor_map(&p.tmap[0], x, LH_BF16, uint64_t(M), uint64_t(n), uint64_t(n) * 2, 128, 128)) return rc;
-    p.gamma = gamma; p.E = 1; p.M = M; p.n = n;
-    p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
-    p.rms_out = rms; p.eps = eps; p.inv_n = 1.0f / float(n); p.round_scale = round_scale;
-    const int col_tiles = int(n / 128);
-    int CL = 8;
-    while (CL > 1 && (col_tiles % CL) != 0) CL >>= 1;
-    p.cluster = CL;
-    p.tiles_per_cta = col_tiles / CL;
-    const size_t smem = C::smem_bytes(1);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
-    cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = unsigned(CL);
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(C::NTHREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cfg.gridDim = dim3(unsigned(CL));
-    int max_clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
-    if (e != cudaSuccess || max_clusters < 1) {
-        (void)cudaGetLastError();
-        return LH_ERR_ARG + 1000;
-    }
-    const int64_t row_blocks = (M + 127) / 128;
-    const int64_t clusters = row_blocks < max_clusters ? row_blocks : max_clusters;
-    cfg.gridDim = dim3(unsigned(clusters * CL));
-    if (getenv("LH_DEBUG")) fprintf(stderr, "[lh] norm fused: CL=%d tiles/cta=%d max_clusters=%d grid=%u smem=%zu\n", CL, p.tiles_per_cta, max_clusters, cfg.gridDim.x, smem);
-    e = cudaLaunchKernelEx(&cfg, kern, p);
-    if (e != cudaSuccess) { set_error("tile_kernel<norm fused>: %s", cudaGetErrorString(e)); return int(e); }
-    return check_launch("tile_kernel<norm fused>");
-}
-
 int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts, int counts_type, int E,
                   int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
                   cudaStream_t stream) {
@@ -912,10 +718,18 @@ int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts,
     p.M = M; p.n = n;
     p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
     p.round_scale = round_scale;
-    switch (mode) {
-        case MODE_ROW: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_ROW, LH_FUSED_EXACT, 4, 3, 1>(p, stream);
-        case MODE_COL: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 4, 3, 1>(p, stream);
-        case MODE_BOTH: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 3, 1>(p, stream);
+    if (w != nullptr) {
+        switch (mode) {
+            case MODE_ROW: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_ROW, LH_FUSED_EXACT, 4, 3, 1, true>(p, stream);
+            case MODE_COL: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 4, 3, 1, true>(p, stream);
+            case MODE_BOTH: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 3, 1, true>(p, stream);
+        }
+    } else {
+        switch (mode) {
+            case MODE_ROW: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_ROW, LH_FUSED_EXACT, 4, 3, 1, false>(p, stream);
+            case MODE_COL: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_COL, LH_FUSED_EXACT, 4, 3, 1, false>(p, stream);
+            case MODE_BOTH: return launch_tile<OP_SILU_F, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 3, 1, false>(p, stream);
+        }
     }
     return fail_arg("output_mode must be 0, 1 or 2");
 }
@@ -931,7 +745,8 @@ int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, cons
     p.M = M; p.n = n;
     p.q = static_cast<uint8_t*>(dx_q); p.s = dx_s; p.qt = static_cast<uint8_t*>(dx_qt); p.st = dx_st;
     p.hp = hp; p.dws = dws; p.round_scale = round_scale;
-    return launch_tile<OP_SILU_B, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 2, 1>(p, stream);
+    if (w != nullptr) return launch_tile<OP_SILU_B, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 2, 1, true>(p, stream);
+    return launch_tile<OP_SILU_B, __nv_bfloat16, MODE_BOTH, LH_FUSED_EXACT, 4, 2, 1, false>(p, stream);
 }
 
 }  // namespace lh

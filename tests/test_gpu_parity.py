@@ -232,21 +232,6 @@ def test_rms_block_quant_modes(M, n):
     check_fused(qt, rqt, st, rst, "pow2 col", True)
 
 
-@pytest.mark.parametrize("M,n", [(1000, 1536), (2048, 2048), (300, 8192), (64, 128)])
-def test_rms_block_quant_single_pass_cluster_kernel(M, n, monkeypatch):
-    """the opt-in one-pass both-axes kernel (thread-block clusters + distributed shared memory)"""
-    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
-    monkeypatch.setenv("LH_NORM_FUSED", "1")
-    x = randn_bf16((M, n), 17, 2)
-    g = randn_bf16((n,), 18)
-    rq, rs, rr, rqt, rst = O.rms_norm_and_block_quant_forward(x, g, 1e-6, False)
-    q, s, r, qt, st = triton_rms_norm_and_block_quant_forward(_cuda(x), _cuda(g), output_mode=2)
-    torch.cuda.synchronize()
-    check_fused(q, rq, s, rs, "fused row")
-    check_fused(qt, rqt, st, rst, "fused col")
-    assert_scales_close(r, rr, "fused rms")
-
-
 @pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (4096, 4096), (130, 8192), (96, 256)])
 def test_rms_fwd_bwd(M, n):
     from linghe_b200.utils.norm import triton_rms_norm_forward, triton_rms_norm_backward
