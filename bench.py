@@ -195,17 +195,48 @@ def run_ours(args, rank, world, device):
     h_xs = torch.empty(xs.shape, dtype=xs.dtype, pin_memory=True).copy_(xs)
     h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (q1, s1, q2, s2)]
     h_rms = torch.empty((rows,), dtype=torch.float32, pin_memory=True)
+    NCH = 8 if rows % (8 * 128) == 0 else 1
+    h_s1 = [torch.empty((HIDDEN // 128, rows // NCH), dtype=torch.float32, pin_memory=True) for _ in range(NCH)]
+    h_s2 = [torch.empty((HIDDEN // 128, rows // NCH), dtype=torch.float32, pin_memory=True) for _ in range(NCH)]
     h2d = h_xn.numel() * 2 + h_xs.numel() * 2
     d2h = sum(t.numel() * t.element_size() for t in h_out) + h_rms.numel() * 4
 
+    # Rows are independent, so the end-to-end path pipelines row chunks over three streams:
+    # host->device copies, kernels, device->host copies (PCIe is full duplex).
+    NCHUNK = 8 if rows % (8 * 128) == 0 else 1
+    crow = rows // NCHUNK
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    s_main = torch.cuda.current_stream()
+
     def e2e_step():
-        dxn = h_xn.to(device, non_blocking=True)
-        dxs = h_xs.to(device, non_blocking=True)
-        a, b, r, _, _ = norm_q(dxn, gamma, output_mode=0)
-        c, d, _, _ = silu_q(dxs, output_mode=0)
-        for dst, src in zip(h_out, (a, b, c, d)):
-            dst.copy_(src, non_blocking=True)
-        h_rms.copy_(r, non_blocking=True)
+        s_in.wait_stream(s_main)
+        s_out.wait_stream(s_main)
+        keep = []
+        for c in range(NCHUNK):
+            r0, r1 = c * crow, (c + 1) * crow
+            with torch.cuda.stream(s_in):
+                dxn = h_xn[r0:r1].to(device, non_blocking=True)
+                dxs = h_xs[r0:r1].to(device, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            s_main.wait_event(ready)
+            a, b, r, _, _ = norm_q(dxn, gamma, output_mode=0)
+            cq, d, _, _ = silu_q(dxs, output_mode=0)
+            done = torch.cuda.Event()
+            done.record(s_main)
+            dxn.record_stream(s_main)
+            dxs.record_stream(s_main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                h_out[0][r0:r1].copy_(a, non_blocking=True)
+                h_out[2][r0:r1].copy_(cq, non_blocking=True)
+                h_s1[c].copy_(b, non_blocking=True)     # [n/128, chunk rows] column slice of the scales
+                h_s2[c].copy_(d, non_blocking=True)
+                h_rms[r0:r1].copy_(r, non_blocking=True)
+                for t_ in (a, b, cq, d, r):
+                    t_.record_stream(s_out)
+            keep.append((a, b, cq, d, r))
+        s_main.wait_stream(s_out)
 
     del xn, xs
     e2e_step()
