@@ -94,6 +94,19 @@ int lh_batch_blockwise_quant(const void* x, int dtype, const void* counts, int c
                              int64_t R, int64_t N, void* q, float* s, void* qt, float* st,
                              int round_scale, void* stream);
 
+/* Gather rows by index into per-expert segments padded to multiples of 16 rows, and
+ * quantise them on both axes (the step that feeds the routed experts).
+ * Replaces triton_batch_block_pad_permute_with_indices, linghe/utils/gather.py:1049.
+ * x [m,N]; counts [E] rows per expert (device); indices [M_out] source row of every
+ * padded output position (entries of padding positions are ignored), M_out = sum of the
+ * padded counts; probs optional [m,E] with prob_out [M_out] in probs_dtype (LH_F32 /
+ * LH_BF16; padding positions get 0).  Outputs use the per-expert packed layouts with
+ * c_e = padded count; padding rows are zero rows (scale floor 1e-30, codes 0). */
+int lh_batch_block_pad_permute(const void* x, int dtype, const void* probs, int probs_dtype,
+                               const void* indices, int indices_type, const void* counts, int counts_type,
+                               int E, int64_t m, int64_t M_out, int64_t N, void* q, float* s, void* qt,
+                               float* st, void* prob_out, int round_scale, void* stream);
+
 /* ---- RMSNorm ------------------------------------------------------------------- */
 
 /* y = (x * r) * gamma in the input dtype, r = rsqrt(mean(x^2) + eps) per row.

@@ -38,6 +38,7 @@ SIGNATURES = {
     "lh_group_quant": (_i, [_p, _i, _l, _l, _p, _p, _i, _p]),
     "lh_block_quant": (_i, [_p, _i, _l, _l, _p, _p, _i, _p]),
     "lh_batch_blockwise_quant": (_i, [_p, _i, _p, _i, _i, _l, _l, _p, _p, _p, _p, _i, _p]),
+    "lh_batch_block_pad_permute": (_i, [_p, _i, _p, _i, _p, _i, _p, _i, _i, _l, _l, _l, _p, _p, _p, _p, _p, _i, _p]),
     "lh_rmsnorm_fwd": (_i, [_p, _p, _i, _l, _l, _f, _p, _p, _i, _p]),
     "lh_rmsnorm_blockquant_fwd": (_i, [_p, _p, _i, _l, _l, _f, _p, _p, _p, _p, _p, _i, _i, _p]),
     "lh_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _l, _p]),

@@ -101,6 +101,9 @@ int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
                cudaStream_t stream);
+int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
+                      int idx_type, const void* counts, int counts_type, int E, int64_t m, int64_t Mout, int64_t N,
+                      void* q, float* s, void* qt, float* st, void* prob_out, int round_scale, cudaStream_t stream);
 int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,
                   int round_scale, cudaStream_t stream);
 int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts, int counts_type, int E,
@@ -201,6 +204,14 @@ int lh_batch_blockwise_quant(const void* x, int dtype, const void* counts, int c
     if (!counts || E <= 0) return fail_arg("batch_blockwise_quant: counts is NULL or E <= 0");
     return tile_quant(x, dtype, counts, counts_type, E, R, N, q, s, qt, st, round_scale, 2, 0,
                       static_cast<cudaStream_t>(stream));
+}
+
+int lh_batch_block_pad_permute(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
+                               int indices_type, const void* counts, int counts_type, int E, int64_t m,
+                               int64_t M_out, int64_t N, void* q, float* s, void* qt, float* st, void* prob_out,
+                               int round_scale, void* stream) {
+    return tile_gather_quant(x, dtype, probs, probs_dtype, indices, indices_type, counts, counts_type, E, m, M_out, N,
+                             q, s, qt, st, prob_out, round_scale, static_cast<cudaStream_t>(stream));
 }
 
 int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,

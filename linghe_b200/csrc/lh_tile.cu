@@ -19,7 +19,7 @@
 
 namespace lh {
 
-enum : int { OP_IDENT = 0, OP_NORM = 1, OP_SILU_F = 2, OP_SILU_B = 3 };
+enum : int { OP_IDENT = 0, OP_NORM = 1, OP_SILU_F = 2, OP_SILU_B = 3, OP_GATHER = 4 };
 enum : int { MODE_ROW = 0, MODE_COL = 1, MODE_BOTH = 2, MODE_BLOCK = 3 };
 
 struct TileParams {
@@ -29,6 +29,13 @@ struct TileParams {
     const float* r;        // OP_NORM: 1/rms per row
     const void* gamma;     // OP_NORM: weight per column
     const void* counts;    // per-expert row counts (NULL = dense)
+    int pad16;             // segments are padded to multiples of 16 rows (OP_GATHER)
+    const uint8_t* gx;     // OP_GATHER: source matrix [m, n]
+    const void* indices;   // OP_GATHER: source row of every padded output row
+    int indices_i64;
+    const void* probs;     // OP_GATHER: optional routing weights [m, E]
+    void* prob_out;        // OP_GATHER: optional [sum of padded counts]
+    int probs_dtype;
     int counts_i64;
     int E;
     int64_t M;             // rows (dense) / total rows (batched)
@@ -48,12 +55,13 @@ template <> struct OpTraits<OP_IDENT> { static constexpr int K = 1, NHALF = 1; }
 template <> struct OpTraits<OP_NORM> { static constexpr int K = 1, NHALF = 1; };
 template <> struct OpTraits<OP_SILU_F> { static constexpr int K = 2, NHALF = 1; };
 template <> struct OpTraits<OP_SILU_B> { static constexpr int K = 3, NHALF = 2; };
+template <> struct OpTraits<OP_GATHER> { static constexpr int K = 0, NHALF = 1; };
 
 template <int OP, typename InT, int RPT, int STAGES>
 struct TileCfg {
     static constexpr int K = OpTraits<OP>::K;
     static constexpr int NHALF = OpTraits<OP>::NHALF;
-    static constexpr int NMAP = OP == OP_SILU_B ? 2 : 1;   // tensor maps (x1 and x2 share one)
+    static constexpr int NMAP = OP == OP_SILU_B ? 2 : (OP == OP_GATHER ? 0 : 1);   // tensor maps (x1 and x2 share one)
     static constexpr int EB = Elem<InT>::BYTES;
     static constexpr int ROWB = 128 * EB;            // bytes of one tile row of one operand
     static constexpr int TILEB = 128 * ROWB;         // one operand tile
@@ -69,7 +77,7 @@ struct TileCfg {
     static constexpr int OFF_CY = OFF_CS + 512;                  // [128] 1/scale
     static constexpr int OFF_BAR = OFF_CY + 512;                 // full[STAGES], empty[STAGES]
     static constexpr int OFF_SEG = OFF_BAR + 2 * STAGES * 8;     // segS[E+1] int64, segB[E+1] int32
-    static constexpr size_t smem_bytes(int E) { return size_t(OFF_SEG) + size_t(E + 1) * 12 + 16; }
+    static constexpr size_t smem_bytes(int E) { return size_t(OFF_SEG) + size_t(E + 1) * 16 + 16; }
 };
 
 struct TileLoc {
@@ -79,6 +87,7 @@ struct TileLoc {
     int T;       // 128-row block index inside the segment
     int ct;      // column tile
     int valid;   // valid rows in this tile (1..128)
+    int e;       // segment (expert) index
 };
 
 __device__ __forceinline__ TileLoc locate(int tile, int col_tiles, const int64_t* segS, const int* segB,
@@ -91,6 +100,7 @@ __device__ __forceinline__ TileLoc locate(int tile, int col_tiles, const int64_t
         const int mid = (lo + hi) >> 1;
         if (segB[mid + 1] > rt) hi = mid; else lo = mid + 1;
     }
+    t.e = lo;
     t.S = segS[lo];
     t.c = segS[lo + 1] - t.S;
     t.B = segB[lo];
@@ -235,6 +245,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
     uint64_t* empty = full + STAGES;
     int64_t* segS = reinterpret_cast<int64_t*>(smem + ((C::OFF_SEG + 15) & ~15));
     int* segB = reinterpret_cast<int*>(segS + (p.E + 1));
+    int* segC = segB + (p.E + 1);   // true (unpadded) row counts
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
@@ -255,6 +266,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             if (lane == 0) {
                 segS[0] = 0; segS[1] = p.M;
                 segB[0] = 0; segB[1] = int((p.M + 127) >> 7);
+                segC[0] = int(p.M);
             }
         } else {
             const int per = (E + 31) / 32;
@@ -263,7 +275,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             for (int e = e0; e < e0 + per && e < E; ++e) {
                 const int64_t c = p.counts_i64 ? reinterpret_cast<const int64_t*>(p.counts)[e]
                                                : int64_t(reinterpret_cast<const int32_t*>(p.counts)[e]);
-                sumS += c;
+                sumS += p.pad16 ? ((c + 15) >> 4) << 4 : c;
                 sumB += (c + 127) >> 7;
             }
             int64_t preS = sumS, preB = sumB;  // inclusive warp scan
@@ -277,8 +289,8 @@ tile_kernel(const __grid_constant__ TileParams p) {
             for (int e = e0; e < e0 + per && e < E; ++e) {
                 const int64_t c = p.counts_i64 ? reinterpret_cast<const int64_t*>(p.counts)[e]
                                                : int64_t(reinterpret_cast<const int32_t*>(p.counts)[e]);
-                segS[e] = accS; segB[e] = int(accB);
-                accS += c; accB += (c + 127) >> 7;
+                segS[e] = accS; segB[e] = int(accB); segC[e] = int(c);
+                accS += p.pad16 ? ((c + 15) >> 4) << 4 : c; accB += (c + 127) >> 7;
             }
             if (lane == 31) { segS[E] = preS; segB[E] = int(preB); }
         }
@@ -294,6 +306,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
     // One tensor-map copy per operand brings a whole 128x128 tile; rows past the end of
     // the matrix read as zero, rows of a following expert segment are masked by `valid`.
     auto issue = [&](int tile, int stage) {
+        if constexpr (OP == OP_GATHER) return;   // gathered rows are loaded straight into registers
         const TileLoc t = locate(tile, col_tiles, segS, segB, E);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
         const int r0 = int(t.S + int64_t(t.T) * 128);
@@ -326,7 +339,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
     uint32_t phase = 0, prev_phase = 0;
     bool first_it = true;
     for (int tile = int(blockIdx.x); tile < n_tiles; tile += int(gridDim.x)) {
-        if (tid == 0 && !first_it) {
+        if (OP != OP_GATHER && tid == 0 && !first_it) {
             // the previous tile's stage is free once every warp has released it: refill it with
             // the tile STAGES-1 steps ahead.  Copies issued here are consumed by this CTA, so
             // none is in flight when the loop ends.
@@ -360,7 +373,9 @@ tile_kernel(const __grid_constant__ TileParams p) {
             gam[0] = bf16x2_to_f2(graw.x); gam[1] = bf16x2_to_f2(graw.y);
             gam[2] = bf16x2_to_f2(graw.z); gam[3] = bf16x2_to_f2(graw.w);
         }
-        if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+        if constexpr (OP != OP_GATHER) {
+            if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+        }
         const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
 
         const int cur_stage = stage;
@@ -370,10 +385,72 @@ tile_kernel(const __grid_constant__ TileParams p) {
 
         float2 v[NHALF][RPT][4];
         float dwp[OP == OP_SILU_B ? RPT : 1];
+        if constexpr (OP == OP_GATHER) {
+            // rows of this tile are rows indices[S + t] of the source for t < count and zero
+            // rows (padding to a multiple of 16) beyond; first all indices, then all rows
+            const int cnt = segC[t.e] - t.T * 128 - row0;      // source rows left for this thread
+            int64_t src[RPT];
+#pragma unroll
+            for (int s = 0; s < RPT; ++s) {
+                src[s] = -1;
+                if (s < cnt)
+                    src[s] = p.indices_i64 ? reinterpret_cast<const int64_t*>(p.indices)[grow0 + row0 + s]
+                                           : int64_t(reinterpret_cast<const int32_t*>(p.indices)[grow0 + row0 + s]);
+            }
+            if constexpr (sizeof(InT) == 2) {
+                uint4 raw[RPT];
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    raw[s] = make_uint4(0, 0, 0, 0);
+                    if (src[s] >= 0)
+                        raw[s] = __ldg(reinterpret_cast<const uint4*>(p.gx + (src[s] * p.n + gcol0 + l16 * 8) * 2));
+                }
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    if constexpr (std::is_same<InT, __half>::value) {
+                        const uint32_t w[4] = {raw[s].x, raw[s].y, raw[s].z, raw[s].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) v[0][s][i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                    } else {
+                        v[0][s][0] = bf16x2_to_f2(raw[s].x); v[0][s][1] = bf16x2_to_f2(raw[s].y);
+                        v[0][s][2] = bf16x2_to_f2(raw[s].z); v[0][s][3] = bf16x2_to_f2(raw[s].w);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                    if (src[s] >= 0) {
+                        const float4* g4 = reinterpret_cast<const float4*>(p.gx + (src[s] * p.n + gcol0 + l16 * 8) * 4);
+                        a = __ldg(g4); b = __ldg(g4 + 1);
+                    }
+                    v[0][s][0] = make_float2(a.x, a.y); v[0][s][1] = make_float2(a.z, a.w);
+                    v[0][s][2] = make_float2(b.x, b.y); v[0][s][3] = make_float2(b.z, b.w);
+                }
+            }
+            if (p.prob_out != nullptr && t.ct == 0 && l16 == 0) {
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    if (s < nrows) {
+                        float pv = 0.f;
+                        if (src[s] >= 0)
+                            pv = p.probs_dtype == LH_BF16
+                                     ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.probs)[src[s] * E + t.e])
+                                     : reinterpret_cast<const float*>(p.probs)[src[s] * E + t.e];
+                        if (p.probs_dtype == LH_BF16)
+                            reinterpret_cast<__nv_bfloat16*>(p.prob_out)[grow0 + row0 + s] = __float2bfloat16_rn(pv);
+                        else
+                            reinterpret_cast<float*>(p.prob_out)[grow0 + row0 + s] = pv;
+                    }
+                }
+            }
+        }
 #pragma unroll
         for (int s = 0; s < RPT; ++s) {
             const uint8_t* srow = sbase + (row0 + s) * C::ROWB;
-            if constexpr (OP == OP_IDENT) {
+            if constexpr (OP == OP_GATHER) {
+                (void)srow;
+            } else if constexpr (OP == OP_IDENT) {
                 load8p<InT>(srow, l16, v[0][s]);
             } else if constexpr (OP == OP_NORM) {
                 float2 x[4];
@@ -428,8 +505,10 @@ tile_kernel(const __grid_constant__ TileParams p) {
             }
         }
         // all shared-memory reads of this stage are done: hand it back to the producer
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[cur_stage]);
+        if constexpr (OP != OP_GATHER) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[cur_stage]);
+        }
 
         if constexpr (OP == OP_SILU_B) {
             if (p.dws != nullptr) {
@@ -697,6 +776,37 @@ int tile_quant(const void* x, int dtype, const void* counts, int counts_type, in
     p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
     p.round_scale = round_scale; p.scale_rowmajor = scale_rowmajor;
     return quant_any(p, dtype, mode, stream);
+}
+
+static bool aligned16(const void* p);
+
+template <typename InT>
+static int gather_launch(const TileParams& p, cudaStream_t st) {
+    return launch_tile<OP_GATHER, InT, MODE_BOTH, true, 8, 1, 2>(p, st);
+}
+
+int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
+                      int idx_type, const void* counts, int counts_type, int E, int64_t m, int64_t Mout, int64_t N,
+                      void* q, float* s, void* qt, float* st, void* prob_out, int round_scale, cudaStream_t stream) {
+    if (N <= 0 || (N % 128) != 0 || m < 0 || Mout < 0) return fail_arg("pad_permute: need N %% 128 == 0");
+    if (!counts || E <= 0) return fail_arg("pad_permute: counts is NULL or E <= 0");
+    if (Mout == 0 || m == 0) return LH_OK;
+    if (!x || !indices || !q || !s || !qt || !st) return fail_arg("pad_permute: NULL pointer");
+    if ((probs == nullptr) != (prob_out == nullptr)) return fail_arg("pad_permute: probs and prob_out go together");
+    if (!aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("pad_permute: pointers must be 16-byte aligned");
+    TileParams p{};
+    p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = E; p.pad16 = 1;
+    p.M = Mout; p.n = N;
+    p.gx = static_cast<const uint8_t*>(x); p.indices = indices; p.indices_i64 = idx_type == LH_I64;
+    p.probs = probs; p.prob_out = prob_out; p.probs_dtype = probs_dtype;
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
+    p.round_scale = round_scale;
+    switch (dtype) {
+        case LH_BF16: return gather_launch<__nv_bfloat16>(p, stream);
+        case LH_F16: return gather_launch<__half>(p, stream);
+        case LH_F32: return gather_launch<float>(p, stream);
+    }
+    return fail_arg("unsupported dtype %d", dtype);
 }
 
 int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,

@@ -107,7 +107,7 @@ def time_call(make_args, fn, nbytes_set, iters=50):
 
 def build_cases(mods):
     """name -> (make_args, callable, algorithmic bytes, ring bytes per set)"""
-    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd = mods
+    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute = mods
     cases = {}
 
     def add(name, make_args, fn, nbytes, set_bytes=None):
@@ -144,6 +144,25 @@ def build_cases(mods):
     add(f"cfg3 batched swiglu+quant bwd R={R}",
         lambda i: (bf16_randn((R, 512), 100 + i, 0.01), bf16_randn((R, 1024), i)),
         lambda g, x: bsilu_b(g, x, wrow, ct, splits), R * 5192)
+    # the step before cfg3: gather 8192 tokens x hidden 2048 into 256 experts (top-8), pad to 16, dual quant
+    if permute is not None:
+        rng = np.random.default_rng(0)
+        pe = rng.dirichlet(np.full(256, 0.3))
+        gum = -np.log(-np.log(rng.random((8192, 256))))
+        top = np.argsort(-(np.log(pe + 1e-30)[None, :] + gum), axis=1)[:, :8]
+        route = np.zeros((8192, 256), dtype=bool)
+        np.put_along_axis(route, top, True, axis=1)
+        pcounts = route.sum(0)
+        idx_parts = []
+        for e in range(256):
+            rows_e = np.nonzero(route[:, e])[0]
+            padn = (-len(rows_e)) % 16
+            idx_parts.append(np.concatenate([rows_e, np.zeros(padn, dtype=rows_e.dtype)]))
+        pidx = torch.tensor(np.concatenate(idx_parts), dtype=torch.int32, device="cuda")
+        pct = torch.tensor(pcounts, dtype=torch.int32, device="cuda")
+        Mp = int(pidx.numel())
+        add(f"next pad-permute+quant 8192x2048 -> {Mp} rows both", lambda i: (bf16_randn((8192, 2048), i),),
+            lambda x: permute(x, pct, pidx, pcounts.tolist()), Mp * 2048 * 4 + 2 * Mp * 2048 * 4 // 128)
     # cfg4: RMSNorm bwd + dual-axis dy quant 16384 x 4096
     M, n = 16384, 4096
     c4 = 3 * M * n * 2 + 2 * M * n + 2 * M * n * 4 // 128 + n * 2 + n * 4
@@ -180,7 +199,13 @@ def ours():
             triton_silu_and_block_quant_forward,
             lambda g, x: triton_silu_and_block_quant_backward(g, x, return_bf16=True),
             triton_weighted_silu_backward, triton_batch_weighted_silu_and_block_quant_forward,
-            triton_batch_weighted_silu_and_block_quant_backward, rms_norm_backward_and_block_quant)
+            triton_batch_weighted_silu_and_block_quant_backward, rms_norm_backward_and_block_quant,
+            _ours_permute())
+
+
+def _ours_permute():
+    from linghe_b200.utils.gather import triton_batch_block_pad_permute_with_indices
+    return triton_batch_block_pad_permute_with_indices
 
 
 def upstream(path):
@@ -201,7 +226,12 @@ def upstream(path):
     return (triton_rms_norm_and_block_quant_forward, triton_rms_norm_backward, triton_blockwise_quant,
             triton_silu_and_block_quant_forward, silu_b, triton_weighted_silu_backward,
             triton_batch_weighted_silu_and_block_quant_forward,
-            triton_batch_weighted_silu_and_block_quant_backward, fused_bwd)
+            triton_batch_weighted_silu_and_block_quant_backward, fused_bwd, _upstream_permute())
+
+
+def _upstream_permute():
+    from linghe.utils.gather import triton_batch_block_pad_permute_with_indices
+    return triton_batch_block_pad_permute_with_indices
 
 
 def main():

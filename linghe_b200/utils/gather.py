@@ -1,0 +1,47 @@
+"""Permute + pad + blockwise quantisation for routed experts -- the entry point of
+linghe/utils/gather.py that feeds the per-expert SwiGLU path, on hand-written sm_100a
+CUDA through the C ABI."""
+
+from __future__ import annotations
+
+import torch
+
+from linghe_b200 import _lib
+
+E4M3 = torch.float8_e4m3fn
+
+
+def triton_batch_block_pad_permute_with_indices(xs, token_count_per_expert, indices, splits, probs=None,
+                                                round_scale=False):
+    """Gather token rows per expert, pad every expert to a multiple of 16 rows and quantise
+    on both axes (linghe/utils/gather.py:1049).
+
+    xs [m, N]; token_count_per_expert [E] (device); indices [M] = source row of every padded
+    output position, M = sum of the counts rounded up to 16; splits = the counts as a host
+    list (sizes the outputs); probs optional [m, E].
+    Returns (x_q [M,N], x_scale buffer (M, N/128) packed per expert as [N/128, padded c],
+    xt_q buffer (M,N) packed per expert as [N, padded c], xt_scale [sum ceil(c/128), N],
+    prob_output [M] or None)."""
+    assert xs.is_contiguous()
+    m, N = xs.shape
+    assert N % 128 == 0
+    n_experts = token_count_per_expert.size(0)
+    M = indices.shape[0]
+    device = xs.device
+    x_q = torch.empty((M, N), device=device, dtype=E4M3)
+    x_scale = torch.empty((M, N // 128), device=device, dtype=torch.float32)
+    blocks = sum((int(c) + 127) // 128 for c in splits)
+    xt_q = torch.empty((M, N), device=device, dtype=E4M3)
+    xt_scale = torch.empty((blocks, N), device=device, dtype=torch.float32)
+    prob_output = torch.empty((M,), device=device, dtype=probs.dtype) if probs is not None else None
+    if m == 0:
+        return x_q, x_scale, xt_q, xt_scale, prob_output
+    assert indices.is_contiguous() and token_count_per_expert.is_contiguous()
+    if probs is not None:
+        assert probs.is_contiguous() and probs.shape == (m, n_experts)
+    _lib.call("lh_batch_block_pad_permute", xs, _lib.ptr(xs), _lib.dtype_code(xs), _lib.ptr(probs),
+              _lib.dtype_code(probs) if probs is not None else _lib.F32, _lib.ptr(indices), _lib.itype_code(indices),
+              _lib.ptr(token_count_per_expert), _lib.itype_code(token_count_per_expert), n_experts, m, M, N,
+              _lib.ptr(x_q), _lib.ptr(x_scale), _lib.ptr(xt_q), _lib.ptr(xt_scale), _lib.ptr(prob_output),
+              int(bool(round_scale)))
+    return x_q, x_scale, xt_q, xt_scale, prob_output

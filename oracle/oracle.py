@@ -279,3 +279,36 @@ def chunked(fn, row_args, other_args=(), rows_per_chunk: int = 4096, **kw):
         sl = [a[r0:r0 + rows_per_chunk] for a in row_args]
         out.append(fn(*sl, *other_args, **kw))
     return out
+
+
+# --------------------------------------------------------------------------- #
+# permute + pad + quantise (the step before the per-expert SwiGLU)
+# --------------------------------------------------------------------------- #
+def batch_block_pad_permute_with_indices(x, indices, probs, counts, round_scale: bool = False):
+    """Gather rows per expert, zero-pad every expert to a multiple of 16 rows, dual-axis
+    quantise.  Follows ``torch_batch_block_pad_permute_with_indices``
+    (tests/test_gather.py:150-197): `indices` is the UNPADDED concatenation of the source
+    rows of every expert; experts with zero rows contribute nothing.  Returns flat
+    (q, s, qT, sT, probs) with the per-expert packing of the kernel."""
+    counts = [int(c) for c in counts]
+    qs, ss, qts, sts, ps = [], [], [], [], []
+    start = 0
+    for e, c in enumerate(counts):
+        if c == 0:
+            continue
+        idx = indices[start:start + c]
+        y = x[idx].float()
+        pad = (-c) % 16
+        if pad:
+            y = torch.nn.functional.pad(y, (0, 0, 0, pad))
+        q, s, qt, st = blockwise_quant(y, round_scale)
+        qs.append(q.reshape(-1)); ss.append(s.reshape(-1)); qts.append(qt.reshape(-1)); sts.append(st.reshape(-1))
+        if probs is not None:
+            pe = probs[:, e][idx]
+            ps.append(torch.nn.functional.pad(pe, (0, pad)) if pad else pe)
+        start += c
+    if not qs:
+        z8 = torch.empty(0, dtype=torch.float8_e4m3fn)
+        return z8, torch.empty(0), z8.clone(), torch.empty(0), torch.empty(0)
+    return (torch.cat(qs), torch.cat(ss), torch.cat(qts), torch.cat(sts),
+            torch.cat(ps) if probs is not None else None)

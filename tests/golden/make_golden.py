@@ -154,7 +154,28 @@ def main():
             out[f"bbwd_{tag}_{k}"] = v
     out["counts"] = np.asarray(counts, dtype=np.int64)
     np.savez_compressed(os.path.join(HERE, "batch.npz"), **out)
-    for f in ("quant", "norm", "silu", "batch"):
+    # ---- permute + pad-to-16 + dual quant (the step before the per-expert SwiGLU) ----
+    import test_gather as TG
+    out = {}
+    m, E, N = 96, 6, 256
+    x = bf16_randn(gen, (m, N))
+    route = torch.rand((m, E), generator=gen) < 0.3
+    route[:, 1] = False          # an expert with no tokens
+    route[:5, 4] = True
+    probs = torch.rand((m, E), generator=gen) * route
+    counts = route.sum(0).tolist()
+    tok = torch.arange(m).unsqueeze(0).expand(E, -1)
+    indices = tok.masked_select(route.T.contiguous())      # unpadded, expert-major (as torch_make_indices)
+    out["x"] = u16(x)
+    out["probs"] = probs.numpy()
+    out["counts"] = np.asarray(counts, dtype=np.int64)
+    out["indices"] = indices.numpy()
+    for rs in (False, True):
+        q, s, qt, st, pr = TG.torch_batch_block_pad_permute_with_indices(x, indices, probs, counts, round_scale=rs)
+        for k, v in (("q", u8(q)), ("s", f32(s)), ("qt", u8(qt)), ("st", f32(st)), ("p", f32(pr))):
+            out[f"perm_r{int(rs)}_{k}"] = v
+    np.savez_compressed(os.path.join(HERE, "permute.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch", "permute"):
         p = os.path.join(HERE, f + ".npz")
         print(p, os.path.getsize(p))
 

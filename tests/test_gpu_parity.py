@@ -483,3 +483,59 @@ def test_argument_errors():
         triton_rms_norm_and_block_quant_forward(xx, w, output_mode=1)  # needs rms
     with pytest.raises(AssertionError):
         triton_rms_norm_and_block_quant_forward(xx.t(), w)  # not contiguous
+
+
+# ------------------------------------------------------------------------------------
+# permute + pad-to-16 + dual quant (the step before the per-expert SwiGLU)
+# ------------------------------------------------------------------------------------
+def _padded_indices(indices, counts, fill=0):
+    """expert-major source rows -> the padded layout the kernel takes (16-row multiples)"""
+    out, start = [], 0
+    for c in counts:
+        pc = (c + 15) // 16 * 16
+        out.append(indices[start:start + c])
+        out.append(torch.full((pc - c,), fill, dtype=indices.dtype))
+        start += c
+    return torch.cat(out) if out else indices[:0]
+
+
+@pytest.mark.parametrize("rs", [0, 1])
+@pytest.mark.parametrize("idt", [torch.int32, torch.int64])
+def test_golden_pad_permute(rs, idt):
+    from linghe_b200.utils.gather import triton_batch_block_pad_permute_with_indices as f
+    G = golden("permute")
+    counts = G["counts"].tolist()
+    idx = _padded_indices(torch.from_numpy(G["indices"]), counts, fill=10 ** 6).to(idt)   # pad entries are never read
+    probs = torch.from_numpy(G["probs"])
+    q, s, qt, st, p = f(_cuda(bf16(G["x"])), torch.tensor(counts, dtype=torch.int64, device=DEV), _cuda(idx), counts,
+                        probs=_cuda(probs), round_scale=bool(rs))
+    assert_bits_equal(q.view(-1), fp8(G[f"perm_r{rs}_q"]), "q")
+    assert_f32_equal(s.view(-1), torch.from_numpy(G[f"perm_r{rs}_s"]), "s")
+    assert_bits_equal(qt.view(-1), fp8(G[f"perm_r{rs}_qt"]), "qt")
+    assert_f32_equal(st.view(-1), torch.from_numpy(G[f"perm_r{rs}_st"]), "st")
+    assert_f32_equal(p, torch.from_numpy(G[f"perm_r{rs}_p"]), "probs")
+
+
+@pytest.mark.parametrize("m,E,N,topk,dtype", [(2048, 32, 1024, 2, torch.bfloat16), (777, 8, 256, 3, torch.float32),
+                                              (4096, 64, 512, 8, torch.bfloat16)])
+def test_pad_permute(m, E, N, topk, dtype):
+    from linghe_b200.utils.gather import triton_batch_block_pad_permute_with_indices as f
+    g = torch.Generator().manual_seed(81)
+    x = torch.randn((m, N), generator=g).to(dtype)
+    logits = torch.randn((m, E), generator=g)
+    logits[:, 0] -= 1000                                    # an expert nobody routes to
+    top = logits.topk(topk, dim=1).indices
+    route = torch.zeros((m, E), dtype=torch.bool).scatter_(1, top, True)
+    probs = torch.softmax(logits, 1) * route
+    counts = route.sum(0).tolist()
+    tok = torch.arange(m).unsqueeze(0).expand(E, -1)
+    indices = tok.masked_select(route.T.contiguous())
+    ref = O.batch_block_pad_permute_with_indices(x, indices, probs, counts, False)
+    idx = _padded_indices(indices, counts).to(torch.int32)
+    out = f(_cuda(x), torch.tensor(counts, dtype=torch.int32, device=DEV), _cuda(idx), counts, probs=_cuda(probs))
+    M = sum((c + 15) // 16 * 16 for c in counts)
+    assert out[0].shape == (M, N) and out[1].shape == (M, N // 128) and out[4].shape == (M,)
+    check_exact([o.view(-1) for o in out], ref, ("q", "s", "qt", "st", "probs"))
+    out2 = f(_cuda(x), torch.tensor(counts, dtype=torch.int32, device=DEV), _cuda(idx), counts)
+    assert out2[4] is None
+    check_exact([o.view(-1) for o in out2[:4]], ref[:4], ("q", "s", "qt", "st"))

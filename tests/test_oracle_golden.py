@@ -147,3 +147,16 @@ def test_bitexact_on_generating_machine():
     bad = (bits(q) != bits(fp8(G["silufwd_c1_r0_q"]))).sum().item()
     print("silu fwd code mismatches vs golden:", bad)
     assert bad <= q.numel() * 1e-3
+
+
+@pytest.mark.parametrize("rs", [0, 1])
+def test_pad_permute(rs):
+    G = golden("permute")
+    x = bf16(G["x"])
+    q, s, qt, st, p = O.batch_block_pad_permute_with_indices(
+        x, torch.from_numpy(G["indices"]), torch.from_numpy(G["probs"]), G["counts"].tolist(), bool(rs))
+    assert_bits_equal(q, fp8(G[f"perm_r{rs}_q"]), "q")
+    assert_f32_equal(s, torch.from_numpy(G[f"perm_r{rs}_s"]), "s")
+    assert_bits_equal(qt, fp8(G[f"perm_r{rs}_qt"]), "qt")
+    assert_f32_equal(st, torch.from_numpy(G[f"perm_r{rs}_st"]), "st")
+    assert_f32_equal(p, torch.from_numpy(G[f"perm_r{rs}_p"]), "probs")
