@@ -55,7 +55,7 @@ template <> struct OpTraits<OP_IDENT> { static constexpr int K = 1, NHALF = 1; }
 template <> struct OpTraits<OP_NORM> { static constexpr int K = 1, NHALF = 1; };
 template <> struct OpTraits<OP_SILU_F> { static constexpr int K = 2, NHALF = 1; };
 template <> struct OpTraits<OP_SILU_B> { static constexpr int K = 3, NHALF = 2; };
-template <> struct OpTraits<OP_GATHER> { static constexpr int K = 0, NHALF = 1; };
+template <> struct OpTraits<OP_GATHER> { static constexpr int K = 1, NHALF = 1; };
 
 template <int OP, typename InT, int RPT, int STAGES>
 struct TileCfg {
@@ -172,14 +172,16 @@ __device__ __forceinline__ float quot_exact(float x, float s, float y) {
 }
 constexpr float kTinyScale = 8.0e-28f;   // ~2^-90: below this take IEEE division
 
-// 8 values of one row, one scale (and its reciprocal) -> 8 codes
+// 8 values of one row, one scale (and its reciprocal) -> 8 codes.  A negative `y` marks a
+// block whose scale is so small that the residual of the exact quotient could underflow
+// (0 < amax < ~3.6e-25): those take IEEE division.  All-zero blocks do not need it.
 template <bool EXACT>
 __device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) {
     float2 q[4];
     if constexpr (EXACT) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) q[j] = make_float2(quot_exact(v[j].x, sc, y), quot_exact(v[j].y, sc, y));
-        if (sc < kTinyScale) {   // rare: all-zero or denormal-range blocks
+        if (y < 0.f) {   // rare
 #pragma unroll
             for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(v[j].x, sc), __fdiv_rn(v[j].y, sc));
         }
@@ -191,10 +193,12 @@ __device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) 
     return make_uint2(cvt_e4m3x4(q[0].x, q[0].y, q[1].x, q[1].y), cvt_e4m3x4(q[2].x, q[2].y, q[3].x, q[3].y));
 }
 
-// reciprocal of a scale: correctly rounded where exact quotients are required
+// reciprocal of a scale: correctly rounded where exact quotients are required, and -1 as the
+// "use IEEE division" marker for non-zero blocks with a denormal-range scale
 template <bool EXACT>
-__device__ __forceinline__ float scale_rcp(float sc) {
-    return EXACT ? __frcp_rn(sc) : rcp_approx(sc);
+__device__ __forceinline__ float scale_rcp(float sc, float amax) {
+    if constexpr (EXACT) return (sc < kTinyScale && amax > 0.f) ? -1.f : __frcp_rn(sc);
+    return rcp_approx(sc);
 }
 
 // Row maxima across the 16 lanes that share a tile row, for RPT rows at once: a
@@ -335,6 +339,47 @@ tile_kernel(const __grid_constant__ TileParams p) {
     const int row0 = cw * (2 * RPT) + hw * RPT;
     const bool rs = p.round_scale != 0;
 
+    // ---- OP_GATHER: per-thread index registers and cp.async row fetches ----------------------
+    int gidx_cur[OP == OP_GATHER ? RPT : 1], gidx_next[OP == OP_GATHER ? RPT : 1];   // source rows fit 31 bits
+    auto gather_indices = [&](int tile, int* idx) {      // source rows of this thread's rows of `tile`
+#pragma unroll
+        for (int s = 0; s < RPT; ++s) idx[s] = -1;           // -1: padding row (zeros) or no tile
+        if (tile < 0) return;
+        const TileLoc tl = locate(tile, col_tiles, segS, segB, E);
+        const int cnt = segC[tl.e] - tl.T * 128 - row0;      // real (unpadded) rows left for this thread
+        const int64_t g0 = tl.S + int64_t(tl.T) * 128 + row0;
+#pragma unroll
+        for (int s = 0; s < RPT; ++s) {
+            if (s < cnt)
+                idx[s] = p.indices_i64 ? int(reinterpret_cast<const int64_t*>(p.indices)[g0 + s])
+                                       : reinterpret_cast<const int32_t*>(p.indices)[g0 + s];
+        }
+    };
+    auto gather_issue = [&](int tile, const int* idx, int stg) {
+        if (tile >= 0) {
+            const int ct = tile % col_tiles;
+            uint8_t* dst = stages + size_t(stg) * C::STAGEB + row0 * C::ROWB + l16 * (8 * C::EB);
+#pragma unroll
+            for (int s = 0; s < RPT; ++s) {
+                const bool real = idx[s] >= 0;
+                const uint8_t* src = p.gx + (int64_t(real ? idx[s] : 0) * p.n + int64_t(ct) * 128 + l16 * 8) * C::EB;
+#pragma unroll
+                for (int b = 0; b < (8 * C::EB) / 16; ++b)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst + s * C::ROWB + 16 * b)),
+                                 "l"(src + 16 * b), "r"(real ? 16 : 0)
+                                 : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if constexpr (OP == OP_GATHER) {
+        const int t0 = int(blockIdx.x);
+        gather_indices(t0 < n_tiles ? t0 : -1, gidx_cur);
+        gather_issue(t0 < n_tiles ? t0 : -1, gidx_cur, 0);
+        const int64_t t1 = int64_t(t0) + gridDim.x;
+        gather_indices(t1 < n_tiles ? int(t1) : -1, gidx_next);
+    }
+
     int stage = 0, prev_stage = 0;
     uint32_t phase = 0, prev_phase = 0;
     bool first_it = true;
@@ -386,57 +431,19 @@ tile_kernel(const __grid_constant__ TileParams p) {
         float2 v[NHALF][RPT][4];
         float dwp[OP == OP_SILU_B ? RPT : 1];
         if constexpr (OP == OP_GATHER) {
-            // rows of this tile are rows indices[S + t] of the source for t < count and zero
-            // rows (padding to a multiple of 16) beyond; first all indices, then all rows
-            const int cnt = segC[t.e] - t.T * 128 - row0;      // source rows left for this thread
-            int64_t src[RPT];
-#pragma unroll
-            for (int s = 0; s < RPT; ++s) {
-                src[s] = -1;
-                if (s < cnt)
-                    src[s] = p.indices_i64 ? reinterpret_cast<const int64_t*>(p.indices)[grow0 + row0 + s]
-                                           : int64_t(reinterpret_cast<const int32_t*>(p.indices)[grow0 + row0 + s]);
-            }
-            if constexpr (sizeof(InT) == 2) {
-                uint4 raw[RPT];
-#pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    raw[s] = make_uint4(0, 0, 0, 0);
-                    if (src[s] >= 0)
-                        raw[s] = __ldg(reinterpret_cast<const uint4*>(p.gx + (src[s] * p.n + gcol0 + l16 * 8) * 2));
-                }
-#pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    if constexpr (std::is_same<InT, __half>::value) {
-                        const uint32_t w[4] = {raw[s].x, raw[s].y, raw[s].z, raw[s].w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) v[0][s][i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-                    } else {
-                        v[0][s][0] = bf16x2_to_f2(raw[s].x); v[0][s][1] = bf16x2_to_f2(raw[s].y);
-                        v[0][s][2] = bf16x2_to_f2(raw[s].z); v[0][s][3] = bf16x2_to_f2(raw[s].w);
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                    if (src[s] >= 0) {
-                        const float4* g4 = reinterpret_cast<const float4*>(p.gx + (src[s] * p.n + gcol0 + l16 * 8) * 4);
-                        a = __ldg(g4); b = __ldg(g4 + 1);
-                    }
-                    v[0][s][0] = make_float2(a.x, a.y); v[0][s][1] = make_float2(a.z, a.w);
-                    v[0][s][2] = make_float2(b.x, b.y); v[0][s][3] = make_float2(b.z, b.w);
-                }
-            }
+            // Software pipeline over three tiles: the rows of this tile were fetched with
+            // cp.async during the previous iteration; now fetch the next tile with the indices
+            // read one iteration ago, and read the indices of the tile after that.  Every
+            // thread copies exactly the 16-byte chunks it later reads, so no barrier is needed.
             if (p.prob_out != nullptr && t.ct == 0 && l16 == 0) {
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     if (s < nrows) {
                         float pv = 0.f;
-                        if (src[s] >= 0)
+                        if (gidx_cur[s] >= 0)
                             pv = p.probs_dtype == LH_BF16
-                                     ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.probs)[src[s] * E + t.e])
-                                     : reinterpret_cast<const float*>(p.probs)[src[s] * E + t.e];
+                                     ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.probs)[int64_t(gidx_cur[s]) * E + t.e])
+                                     : reinterpret_cast<const float*>(p.probs)[int64_t(gidx_cur[s]) * E + t.e];
                         if (p.probs_dtype == LH_BF16)
                             reinterpret_cast<__nv_bfloat16*>(p.prob_out)[grow0 + row0 + s] = __float2bfloat16_rn(pv);
                         else
@@ -444,13 +451,17 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     }
                 }
             }
+            const int64_t t1 = int64_t(tile) + gridDim.x, t2 = t1 + gridDim.x;
+            gather_issue(t1 < n_tiles ? int(t1) : -1, gidx_next, stage);            // `stage` already points at the next slot
+#pragma unroll
+            for (int s = 0; s < RPT; ++s) gidx_cur[s] = gidx_next[s];
+            gather_indices(t2 < n_tiles ? int(t2) : -1, gidx_next);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
         }
 #pragma unroll
         for (int s = 0; s < RPT; ++s) {
             const uint8_t* srow = sbase + (row0 + s) * C::ROWB;
-            if constexpr (OP == OP_GATHER) {
-                (void)srow;
-            } else if constexpr (OP == OP_IDENT) {
+            if constexpr (OP == OP_IDENT || OP == OP_GATHER) {
                 load8p<InT>(srow, l16, v[0][s]);
             } else if constexpr (OP == OP_NORM) {
                 float2 x[4];
@@ -550,7 +561,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
                 for (int w2 = 1; w2 < NW; ++w2) bm = fmaxf(bm, part[w2]);
                 const float sc = scale_from_amax(bm, rs);
-                const float y = scale_rcp<EXACT>(sc);
+                const float y = scale_rcp<EXACT>(sc, bm);
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     const int rr = row0 + s;
@@ -571,8 +582,9 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     for (int j = 0; j < 4; ++j) m = max3abs(v[h][s][j].x, v[h][s][j].y, m);
                     a[s] = m;
                 }
-                const float mysc = scale_from_amax(row_max_transposed<RPT>(a, l16), rs);
-                const float myy = scale_rcp<EXACT>(mysc);
+                const float mymax = row_max_transposed<RPT>(a, l16);
+                const float mysc = scale_from_amax(mymax, rs);
+                const float myy = scale_rcp<EXACT>(mysc, mymax);
                 {
                     const int rr = row0 + l16 / G;   // the row this lane holds the scale of
                     if ((l16 % G) == 0 && rr < t.valid) {
@@ -619,7 +631,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     for (int w2 = 1; w2 < NW; ++w2) m = fmaxf(m, part[w2 * 128 + tid]);
                     const float sc = scale_from_amax(m, rs);
                     cs[tid] = sc;
-                    cy[tid] = scale_rcp<EXACT>(sc);
+                    cy[tid] = scale_rcp<EXACT>(sc, m);
                     p.st[(t.B + t.T) * (NHALF * p.n) + h * p.n + gcol0 + tid] = sc;
                 }
                 named_bar<1, NCONS>();
@@ -642,7 +654,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
                         for (int s = 0; s < RPT; ++s)
                             q[s] = make_float2(quot_exact(v[h][s][j].x, sc2[j].x, y2[j].x),
                                                quot_exact(v[h][s][j].y, sc2[j].y, y2[j].y));
-                        if (sc2[j].x < kTinyScale || sc2[j].y < kTinyScale) {   // rare slow path
+                        if (y2[j].x < 0.f || y2[j].y < 0.f) {   // rare: denormal-range scale, IEEE division
 #pragma unroll
                             for (int s = 0; s < RPT; ++s)
                                 q[s] = make_float2(__fdiv_rn(v[h][s][j].x, sc2[j].x), __fdiv_rn(v[h][s][j].y, sc2[j].y));
@@ -782,7 +794,7 @@ static bool aligned16(const void* p);
 
 template <typename InT>
 static int gather_launch(const TileParams& p, cudaStream_t st) {
-    return launch_tile<OP_GATHER, InT, MODE_BOTH, true, 8, 1, 2>(p, st);
+    return launch_tile<OP_GATHER, InT, MODE_BOTH, true, 8, 2, (sizeof(InT) == 2 ? 2 : 1)>(p, st);
 }
 
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
@@ -791,6 +803,7 @@ int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dty
     if (N <= 0 || (N % 128) != 0 || m < 0 || Mout < 0) return fail_arg("pad_permute: need N %% 128 == 0");
     if (!counts || E <= 0) return fail_arg("pad_permute: counts is NULL or E <= 0");
     if (Mout == 0 || m == 0) return LH_OK;
+    if (m >= (int64_t(1) << 31)) return fail_arg("pad_permute: more than 2^31 source rows");
     if (!x || !indices || !q || !s || !qt || !st) return fail_arg("pad_permute: NULL pointer");
     if ((probs == nullptr) != (prob_out == nullptr)) return fail_arg("pad_permute: probs and prob_out go together");
     if (!aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("pad_permute: pointers must be 16-byte aligned");
