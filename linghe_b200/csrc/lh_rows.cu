@@ -82,8 +82,12 @@ rows_kernel(const __grid_constant__ RowParams p) {
     const int t = threadIdx.x;
     const int warp = t >> 5, lane = t & 31;
     const int n = p.n;
-    const int RB = CHUNKED ? 1 : p.RB;
-    const int64_t slabs = CHUNKED ? p.M * p.chunks : (p.M + RB - 1) / RB;
+    const int RB = p.RB;
+    const int nbk = n >> 7;                                   // 128-element blocks per row
+    // SwiGLU+quant has no row coupling: its slabs are 64 consecutive 1x128 blocks of the
+    // row-major output, whatever rows they fall in (full thread use for any n)
+    const int64_t total_blocks = p.M * int64_t(nbk);
+    const int64_t slabs = NORM ? (p.M + RB - 1) / RB : (total_blocks + 63) / 64;
 
     if (t == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -96,35 +100,51 @@ rows_kernel(const __grid_constant__ RowParams p) {
 
     auto locate = [&](int64_t slab) {
         SlabLoc L;
-        if constexpr (CHUNKED) {
-            L.row0 = slab / p.chunks;
-            L.rows = 1;
-            L.c0 = int(slab - L.row0 * p.chunks) * kSlabElems;
-            L.ncols = n - L.c0 < kSlabElems ? n - L.c0 : kSlabElems;
-        } else {
-            L.row0 = slab * RB;
-            const int64_t left = p.M - L.row0;
-            L.rows = left < RB ? int(left) : RB;
-            L.c0 = 0;
-            L.ncols = n;
-        }
+        L.row0 = slab * RB;
+        const int64_t left = p.M - L.row0;
+        L.rows = left < RB ? int(left) : RB;
+        L.c0 = 0;
+        L.ncols = n;
         return L;
     };
 
-    // Warp 0 doubles as the producer.
+    // Warp 0 doubles as the producer.  For SwiGLU+quant it walks (row, column block) of the
+    // first block of the slab it issues next, advanced by a fixed step per issue.
+    const int64_t sstep = 64 * int64_t(gridDim.x);
+    const int64_t sdq = NORM ? 0 : sstep / nbk;
+    const int sdr = NORM ? 0 : int(sstep - sdq * nbk);
+    int64_t prow = 0;
+    int pcb = 0;
+    if constexpr (!NORM) {
+        const int64_t b = int64_t(blockIdx.x) * 64;
+        prow = b / nbk;
+        pcb = int(b - prow * nbk);
+    }
     auto issue = [&](int64_t slab, int stage) {
         const SlabLoc L = locate(slab);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
         if constexpr (ROP == ROP_SILU_Q) {
-            // x is [M, 2n]: gate half and up half of every row are separate runs
-            const uint32_t run = uint32_t(L.ncols) * 2u;
-            if (lane == 0) mbar_expect_tx(&full[stage], run * 2u * uint32_t(L.rows));
+            // x is [M, 2n]: the slab's blocks cover a few (partial) rows; per row one run from
+            // the gate half and one from the up half, laid out in slab order
+            const int64_t bl = total_blocks - slab * 64;
+            const int nblk = bl < 64 ? int(bl) : 64;
+            if (lane == 0) mbar_expect_tx(&full[stage], uint32_t(nblk) * 128u * 2u * 2u);
             __syncwarp();
-            for (int r = lane; r < L.rows; r += 32) {
-                const uint8_t* src = p.x + ((L.row0 + r) * 2 * int64_t(n) + L.c0) * 2;
-                bulk_g2s(dst + size_t(r) * run, src, run, &full[stage]);
-                bulk_g2s(dst + C::SLABB + size_t(r) * run, src + size_t(n) * 2, run, &full[stage]);
+            for (int i = lane; ; i += 32) {                     // i-th row touched by the slab
+                const int first = i == 0 ? 0 : i * nbk - pcb;   // its first block, slab-relative
+                if (first >= nblk) break;
+                const int lo = i == 0 ? pcb : 0;
+                const int left = nblk - first;
+                const int cnt = left < nbk - lo ? left : nbk - lo;
+                const uint32_t run = uint32_t(cnt) * 256u;
+                const uint8_t* src = p.x + ((prow + i) * 2 * int64_t(n) + int64_t(lo) * 128) * 2;
+                const size_t off = size_t(first) * 256;
+                bulk_g2s(dst + off, src, run, &full[stage]);
+                bulk_g2s(dst + C::SLABB + off, src + size_t(n) * 2, run, &full[stage]);
             }
+            prow += sdq;
+            pcb += sdr;
+            if (pcb >= nbk) { pcb -= nbk; ++prow; }
         } else {
             if (lane == 0) {
                 const uint32_t bytes = uint32_t(L.rows) * uint32_t(n) * 2u;
@@ -172,6 +192,16 @@ rows_kernel(const __grid_constant__ RowParams p) {
 #pragma unroll
     for (int i = 0; i < (ROP == ROP_NORM_BWD ? NP : 1); ++i) acc[i] = make_float2(0.f, 0.f);
 
+    // SwiGLU+quant: row / column block of this thread's 1x128 block, advanced incrementally
+    // from slab to slab (one 64-bit division per thread for the whole kernel)
+    int64_t srow = 0;
+    int scolb = 0;
+    if constexpr (!NORM) {
+        const int64_t b = int64_t(blockIdx.x) * 64 + t / LPB;
+        srow = b / nbk;
+        scolb = int(b - srow * nbk);
+    }
+
     int stage = 0, prev_stage = 0;
     uint32_t phase = 0, prev_phase = 0;
     int buf = 0;
@@ -182,12 +212,15 @@ rows_kernel(const __grid_constant__ RowParams p) {
             const int64_t nxt = slab + int64_t(STAGES - 1) * gridDim.x;
             if (nxt < slabs && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
         }
-        const SlabLoc L = locate(slab);
+        SlabLoc L = locate(slab);
+        int slab_elems = L.rows * L.ncols;                 // valid elements in this slab
         if constexpr (!NORM) {
-            my_row = CHUNKED ? 0 : e0 / L.ncols;
-            col0 = L.c0 + (e0 - my_row * L.ncols);
+            const int64_t bl = total_blocks - slab * 64;
+            slab_elems = (bl < 64 ? int(bl) : 64) * 128;
+            L.row0 = srow;                                 // this thread's row
+            col0 = scolb * 128 + (t % LPB) * EPT;
         }
-        const bool active = in_slab && my_row < L.rows && (!CHUNKED || e0 < L.ncols);
+        const bool active = NORM ? (in_slab && my_row < L.rows) : (e0 < slab_elems);
         if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
         const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
 
@@ -353,12 +386,12 @@ rows_kernel(const __grid_constant__ RowParams p) {
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-            const int total = L.rows * L.ncols;                 // valid elements in the slab
-            int cnt = total - warp * WSPAN;
+            int cnt = slab_elems - warp * WSPAN;
             cnt = cnt > WSPAN ? WSPAN : cnt;
             if (cnt > 0) {
                 uint8_t* gbase = C::QUANT ? p.q : p.hp;
-                bulk_s2g(gbase + (L.row0 * n + L.c0 + warp * WSPAN) * OB,
+                const int64_t gofs = NORM ? L.row0 * n : slab * int64_t(kSlabElems);
+                bulk_s2g(gbase + (gofs + warp * WSPAN) * OB,
                          outb + buf * C::OUTB + size_t(warp) * WSPAN * OB, uint32_t(cnt) * OB);
             }
             bulk_commit();
@@ -367,6 +400,11 @@ rows_kernel(const __grid_constant__ RowParams p) {
         prev_stage = stage; prev_phase = phase;
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         buf ^= 1;
+        if constexpr (!NORM) {
+            srow += sdq;
+            scolb += sdr;
+            if (scolb >= nbk) { scolb -= nbk; ++srow; }
+        }
     }
     if (lane == 0) bulk_wait_all();
 
@@ -637,15 +675,14 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid
     using C = RowCfg<ROP, EPT, STAGES>;
     int64_t slabs;
     p.inv_n = 1.0f / float(p.n);
-    const bool chunked = p.n > kSlabElems;
-    if (!chunked) {
+    if (ROP == ROP_SILU_Q) {
+        p.RB = 1;
+        p.chunks = 1;
+        slabs = (p.M * (p.n / 128) + 63) / 64;      // 64 blocks of 1x128 per slab
+    } else {
         p.RB = kSlabElems / p.n;
         p.chunks = 1;
         slabs = (p.M + p.RB - 1) / p.RB;
-    } else {
-        p.RB = 1;
-        p.chunks = (p.n + kSlabElems - 1) / kSlabElems;
-        slabs = p.M * p.chunks;
     }
     int64_t grid = int64_t(sm_count()) * CTAS_PER_SM;
     if (grid > grid_cap) grid = grid_cap;
@@ -657,9 +694,6 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid
         kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
         return check_launch("rows_kernel");
     };
-    if constexpr (ROP == ROP_SILU_Q) {
-        if (chunked) return go(rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM, true>);
-    }
     return go(rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM, false>);
 }
 

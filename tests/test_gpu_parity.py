@@ -299,7 +299,7 @@ def test_golden_silu(tag, rs):
 
 
 @pytest.mark.parametrize("M,N,coef", [(1024, 1024, 1.0), (1000, 2816, 1.0), (512, 4096, 100.0), (256, 3072, 0.0),
-                                      (72, 256, 1.0)])
+                                      (72, 256, 1.0), (130, 32768, 1.0), (67, 16640, 1.0)])
 def test_silu_fwd_modes(M, N, coef):
     from linghe_b200.utils.silu import triton_silu_and_block_quant_forward
     x = randn_bf16((M, N), 31, 1, coef)
