@@ -122,6 +122,17 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
                               void* q, float* s, float* rms, void* qt, float* st, int round_scale,
                               int output_mode, void* stream);
 
+/* RMSNorm + float32 router logits + row quantisation (the step beside the norm in the MoE block).
+ * Replaces triton_rms_norm_fp32_gemm_block_quant_forward, linghe/utils/norm.py:688.
+ * x [M,K] bf16, gamma [K] bf16, route_w [N,K] bf16; M, K, N multiples of 128, K <= 8192.
+ * mode 0: writes y [M,K] bf16, rms [M], logits [M,N] f32 = y_f32 . route_w^T, q [M,K], s [K/128,M].
+ * mode 1: reads rms, writes qT [K,M], sT [M/128,K] (y, logits, q, s untouched).
+ * scratch: lh_scratch_bytes("rmsnorm_gemm", N, K) bytes (mode 0 only). */
+int lh_rmsnorm_gemm_blockquant_fwd(const void* x, const void* gamma, const void* route_w, int dtype, int64_t M,
+                                   int64_t K, int64_t N, float eps, void* y, float* rms, float* logits, void* q,
+                                   float* s, void* qt, float* st, int round_scale, int output_mode, void* scratch,
+                                   int64_t scratch_bytes, void* stream);
+
 /* RMSNorm backward: dx (input dtype) and dgamma (float32 [n]).
  * Replaces triton_rms_norm_backward, linghe/utils/norm.py:144.
  * rms may be NULL (recomputed).  scratch: lh_scratch_bytes("rmsnorm_bwd", M, n) bytes. */

@@ -64,7 +64,7 @@ int sm_count(int* out_device) {
 }
 
 int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows, uint64_t cols,
-                    uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols) {
+                    uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle128) {
     using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -87,7 +87,8 @@ int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows
     const cuuint32_t box[2] = {box_cols, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu pitch=%llu)", int(r),
@@ -98,6 +99,11 @@ int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows
 }
 
 // launchers implemented in the kernel translation units
+int rows_norm_yq(const void* x, const void* gamma, int64_t M, int n, float eps, void* y, void* q, float* s, float* rms,
+                 int round_scale, cudaStream_t stream);
+int64_t router_gemm_scratch(int64_t N, int64_t K);
+int router_gemm(const void* x, const void* gamma, const void* w, const float* rms, float* logits, int64_t M, int64_t N,
+                int64_t K, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
                cudaStream_t stream);
@@ -176,6 +182,7 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!strcmp(what, "rmsnorm_bwd")) return rows_norm_bwd_scratch(cols);
     if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
     if (!strcmp(what, "rmsnorm_bwd_static")) return 0;  // it carries its own
+    if (!strcmp(what, "rmsnorm_gemm")) return router_gemm_scratch(rows, cols);   // rows = N, cols = K
     return -1;
 }
 
@@ -235,6 +242,27 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
         return tile_norm_col(x, gamma, rms, M, n, qt, st, round_scale, cs);
     }
     return LH_OK;
+}
+
+int lh_rmsnorm_gemm_blockquant_fwd(const void* x, const void* gamma, const void* route_w, int dtype, int64_t M,
+                                   int64_t K, int64_t N, float eps, void* y, float* rms, float* logits, void* q,
+                                   float* s, void* qt, float* st, int round_scale, int output_mode, void* scratch,
+                                   int64_t scratch_bytes, void* stream) {
+    if (output_mode != 0 && output_mode != 1) return fail_arg("rmsnorm_gemm_blockquant_fwd: output_mode must be 0 or 1");
+    if (dtype != LH_BF16) return fail_arg("rmsnorm_gemm_blockquant_fwd: bf16 inputs only");
+    if (M <= 0 || (M % 128) || (K % 128) || (N % 128) || K <= 0 || N <= 0 || K > 8192)
+        return fail_arg("rmsnorm_gemm_blockquant_fwd: need M, K, N positive multiples of 128 and K <= 8192");
+    if (!x || !gamma || !rms) return fail_arg("rmsnorm_gemm_blockquant_fwd: NULL pointer");
+    if (!aligned16(x) || !aligned16(gamma)) return fail_arg("rmsnorm_gemm_blockquant_fwd: pointers must be 16-byte aligned");
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (output_mode == 1) {
+        if (!qt || !st || !aligned16(qt)) return fail_arg("rmsnorm_gemm_blockquant_fwd: NULL or unaligned transposed output");
+        return tile_norm_col(x, gamma, rms, M, K, qt, st, round_scale, cs);
+    }
+    if (!y || !q || !s || !logits || !route_w) return fail_arg("rmsnorm_gemm_blockquant_fwd: NULL pointer");
+    if (!aligned16(y) || !aligned16(q)) return fail_arg("rmsnorm_gemm_blockquant_fwd: pointers must be 16-byte aligned");
+    if (int rc = rows_norm_yq(x, gamma, M, int(K), eps, y, q, s, rms, round_scale, cs)) return rc;
+    return router_gemm(x, gamma, route_w, rms, logits, M, N, K, scratch, scratch_bytes, cs);
 }
 
 int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,

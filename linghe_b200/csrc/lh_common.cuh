@@ -22,9 +22,10 @@ int fail_arg(const char* fmt, ...);      // records message, returns LH_ERR_ARG
 int check_launch(const char* what);      // cudaGetLastError -> status code
 int sm_count(int* out_device = nullptr); // SM count of the current device (cached)
 // Tiled 2-D tensor map over a row-major [rows, cols] matrix with `pitch_bytes` between
-// rows; the box is box_rows x box_cols elements, no swizzle, out-of-range reads give 0.
+// rows; the box is box_rows x box_cols elements, out-of-range reads give 0.  swizzle128:
+// lay the box out with the 128-byte swizzle (box rows must then be 128 bytes long).
 int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows, uint64_t cols,
-                    uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols);
+                    uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, int swizzle128 = 0);
 
 // Device status word: 0 = fine; otherwise the code of the first bounded wait that
 // gave up.  Read back with lh_device_status().

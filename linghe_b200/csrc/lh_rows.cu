@@ -14,7 +14,7 @@
 
 namespace lh {
 
-enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3 };
+enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3, ROP_NORM_YQ = 4 };
 
 constexpr int kSlabElems = 8192;
 constexpr int kMaxRowCtas = 296;
@@ -33,7 +33,7 @@ struct RowParams {
     int chunks;          // column chunks per row (1 unless n > 8192)
     uint8_t* q;          // *_Q: codes [M,n]
     float* s;            // *_Q: scales [n/128, M]
-    uint8_t* hp;         // ROP_NORM_Y: y [M,n]; ROP_NORM_BWD: dx [M,n]
+    uint8_t* hp;         // ROP_NORM_Y, ROP_NORM_YQ: y [M,n]; ROP_NORM_BWD: dx [M,n]
     float* partial;      // ROP_NORM_BWD: [gridDim.x, n] per-CTA dgamma partial sums
     int round_scale;
 };
@@ -41,7 +41,7 @@ struct RowParams {
 template <int ROP, int EPT, int STAGES>
 struct RowCfg {
     static constexpr int NIN = (ROP == ROP_NORM_BWD || ROP == ROP_SILU_Q) ? 2 : 1;
-    static constexpr bool QUANT = ROP == ROP_NORM_Q || ROP == ROP_SILU_Q;
+    static constexpr bool QUANT = ROP == ROP_NORM_Q || ROP == ROP_SILU_Q || ROP == ROP_NORM_YQ;
     static constexpr int NT = kSlabElems / EPT;       // threads
     static constexpr int NW = NT / 32;
     static constexpr int SLABB = kSlabElems * 2;      // bytes of one operand slab (16-bit inputs)
@@ -162,7 +162,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
     const int e0 = t * EPT;                        // first element of this thread inside the slab
     const int sw = NCH == 4 ? ((t >> 1) & 3) : ((t >> 2) & 1);  // bank-conflict-free chunk order
     const bool rs = p.round_scale != 0;
-    const bool reuse = ROP != ROP_NORM_Q && p.reuse_rms != 0;
+    const bool reuse = ROP != ROP_NORM_Q && ROP != ROP_NORM_YQ && p.reuse_rms != 0;
 
     // For the norm kernels a slab is RB full rows, so a thread's columns never change:
     // keep gamma for them in registers, in the (swizzled) chunk order used for x.
@@ -326,10 +326,21 @@ rows_kernel(const __grid_constant__ RowParams p) {
 
         uint8_t* so = outb + buf * C::OUTB + size_t(e0) * OB;
         if constexpr (C::QUANT) {
-            if constexpr (ROP == ROP_NORM_Q) {
+            if constexpr (ROP == ROP_NORM_Q || ROP == ROP_NORM_YQ) {
                 const float2 r2 = splat2(r);
 #pragma unroll
                 for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(x[i], r2), gam[i]);
+                if constexpr (ROP == ROP_NORM_YQ) {
+                    // the 16-bit y goes straight from registers to global memory
+                    if (active) {
+                        uint8_t* yo = p.hp + ((L.row0 + my_row) * n + col0) * 2;
+#pragma unroll
+                        for (int k = 0; k < NCH; ++k)
+                            *reinterpret_cast<uint4*>(yo + 16 * (k ^ sw)) =
+                                make_uint4(pack_bf16x2(x[4 * k + 0].x, x[4 * k + 0].y), pack_bf16x2(x[4 * k + 1].x, x[4 * k + 1].y),
+                                           pack_bf16x2(x[4 * k + 2].x, x[4 * k + 2].y), pack_bf16x2(x[4 * k + 3].x, x[4 * k + 3].y));
+                    }
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(sigmoid_fast2(x[i]), x[i]), g[i]);
@@ -730,6 +741,22 @@ int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int6
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
     kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
     return check_launch("normq_kernel");
+}
+
+int rows_norm_yq(const void* x, const void* gamma, int64_t M, int n, float eps, void* y, void* q, float* s, float* rms,
+                 int round_scale, cudaStream_t stream) {
+    RowParams p{};
+    p.x = static_cast<const uint8_t*>(x);
+    p.gamma = gamma;
+    p.M = M;
+    p.n = n;
+    p.eps = eps;
+    p.hp = static_cast<uint8_t*>(y);
+    p.q = static_cast<uint8_t*>(q);
+    p.s = s;
+    p.rms = rms;
+    p.round_scale = round_scale;
+    return launch_rows<ROP_NORM_YQ, 32, 4, 2>(p, nullptr, stream);
 }
 
 int rows_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream) {

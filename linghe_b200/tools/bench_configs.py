@@ -107,7 +107,7 @@ def time_call(make_args, fn, nbytes_set, iters=50):
 
 def build_cases(mods):
     """name -> (make_args, callable, algorithmic bytes, ring bytes per set)"""
-    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute = mods
+    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute, router = mods
     cases = {}
 
     def add(name, make_args, fn, nbytes, set_bytes=None):
@@ -163,6 +163,14 @@ def build_cases(mods):
         Mp = int(pidx.numel())
         add(f"next pad-permute+quant 8192x2048 -> {Mp} rows both", lambda i: (bf16_randn((8192, 2048), i),),
             lambda x: permute(x, pct, pidx, pcounts.tolist()), Mp * 2048 * 4 + 2 * Mp * 2048 * 4 // 128)
+    # the step beside cfg1 in the MoE block: RMSNorm + float32 router logits (256 experts) + row quant
+    if router is not None:
+        M, K, N = 8192, 2048, 256
+        rw = torch.randn((N, K), device="cuda").to(torch.bfloat16)
+        add("next rmsnorm+router gemm+quant 8192x2048 N=256 rows",
+            lambda i: (bf16_randn((8192, 2048), i), gam[:2048].contiguous()),
+            lambda x, g: router(x, g, rw, output_mode=0),
+            M * K * 5 + M * (K // 128) * 4 + M * 4 + M * N * 4 + N * K * 2 + K * 2)
     # cfg4: RMSNorm bwd + dual-axis dy quant 16384 x 4096
     M, n = 16384, 4096
     c4 = 3 * M * n * 2 + 2 * M * n + 2 * M * n * 4 // 128 + n * 2 + n * 4
@@ -200,7 +208,12 @@ def ours():
             lambda g, x: triton_silu_and_block_quant_backward(g, x, return_bf16=True),
             triton_weighted_silu_backward, triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, rms_norm_backward_and_block_quant,
-            _ours_permute())
+            _ours_permute(), _ours_router())
+
+
+def _ours_router():
+    from linghe_b200.utils.norm import triton_rms_norm_fp32_gemm_block_quant_forward
+    return triton_rms_norm_fp32_gemm_block_quant_forward
 
 
 def _ours_permute():
@@ -226,7 +239,13 @@ def upstream(path):
     return (triton_rms_norm_and_block_quant_forward, triton_rms_norm_backward, triton_blockwise_quant,
             triton_silu_and_block_quant_forward, silu_b, triton_weighted_silu_backward,
             triton_batch_weighted_silu_and_block_quant_forward,
-            triton_batch_weighted_silu_and_block_quant_backward, fused_bwd, _upstream_permute())
+            triton_batch_weighted_silu_and_block_quant_backward, fused_bwd, _upstream_permute(),
+            _upstream_router())
+
+
+def _upstream_router():
+    from linghe.utils.norm import triton_rms_norm_fp32_gemm_block_quant_forward
+    return triton_rms_norm_fp32_gemm_block_quant_forward
 
 
 def _upstream_permute():

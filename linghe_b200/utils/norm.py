@@ -91,6 +91,47 @@ def triton_rms_norm_and_block_quant_forward(
     return out, scale, rms, transpose_output, transpose_scale
 
 
+def triton_rms_norm_fp32_gemm_block_quant_forward(
+    x: torch.Tensor,
+    norm_weight: torch.Tensor,
+    route_weight: torch.Tensor,
+    rms: Optional[torch.Tensor] = None,
+    eps: float = 1e-6,
+    output_mode: int = 0,
+    round_scale=False,
+):
+    """RMSNorm + float32 router logits + blockwise quantisation (linghe/utils/norm.py:688).
+
+    y = rms_norm(x); logits = y_f32 @ route_weight.T (float32); quantisation of y_f32.
+    output_mode 0 writes y, rms, logits, x_q, x_s (row-wise copy); output_mode 1 needs `rms`
+    and writes only the transposed copy xt_q, xt_s.  Returns
+    (y [M,K] x.dtype, rms [M], logits [M,N] f32, x_q [M,K], x_s [K/128,M], xt_q [K,M],
+    xt_s [M/128,K]); the tensors a mode does not write are allocated and left as they are."""
+    assert x.is_contiguous() and norm_weight.is_contiguous() and route_weight.is_contiguous()
+    assert output_mode in (0, 1)
+    M, K = x.size()
+    N, K2 = route_weight.size()
+    assert K2 == K
+    assert M % 128 == 0 and K % 128 == 0 and N % 128 == 0
+    device = x.device
+    y = torch.empty(M, K, dtype=x.dtype, device=device)
+    if rms is None:
+        assert output_mode == 0
+        rms = torch.empty(M, dtype=torch.float32, device=device)
+    logits = torch.empty(M, N, dtype=torch.float32, device=device)
+    x_q = torch.empty((M, K), device=device, dtype=E4M3)
+    x_s = torch.empty((K // 128, M), device=device, dtype=torch.float32)
+    xt_q = torch.empty((K, M), device=device, dtype=E4M3)
+    xt_s = torch.empty((M // 128, K), device=device, dtype=torch.float32)
+    nbytes = _lib.scratch_bytes("rmsnorm_gemm", N, K) if output_mode == 0 else 0
+    scratch = torch.empty((max(nbytes, 16),), dtype=torch.uint8, device=device)
+    _lib.call("lh_rmsnorm_gemm_blockquant_fwd", x, _lib.ptr(x), _lib.ptr(norm_weight), _lib.ptr(route_weight),
+              _lib.dtype_code(x), M, K, N, float(eps), _lib.ptr(y), _lib.ptr(rms), _lib.ptr(logits), _lib.ptr(x_q),
+              _lib.ptr(x_s), _lib.ptr(xt_q), _lib.ptr(xt_s), int(bool(round_scale)), int(output_mode),
+              _lib.ptr(scratch), nbytes)
+    return y, rms, logits, x_q, x_s, xt_q, xt_s
+
+
 def rms_norm_backward_and_block_quant(grad_output, x, w, eps=1e-6, rms=None, round_scale=False):
     """RMSNorm backward fused with the dual-axis quantisation of `grad_output`.
 

@@ -168,6 +168,22 @@ def rms_norm_and_block_quant_forward(x, weight, eps: float = 1e-6, round_scale: 
     return q, s, rms_recip(x, eps), qt, st
 
 
+def rms_norm_fp32_gemm_block_quant_forward(x, norm_weight, route_weight, eps: float = 1e-6,
+                                           round_scale: bool = False):
+    """RMSNorm, float32 router logits of the normalised rows and dual-axis quantisation.
+
+    Follows ``torch_rms_gemm_block_quant_forward`` (tests/test_norm.py:86-103) with the
+    output order and layouts of ``triton_rms_norm_fp32_gemm_block_quant_forward``
+    (linghe/utils/norm.py:688-784): (y [M,K] x.dtype, r [M], logits [M,N] f32,
+    q [M,K], s [K/128,M], qT [K,M], sT [M/128,K]).  The logits are the float32 matmul
+    of the unrounded float32 y with the router weight [N,K].
+    """
+    y = _rms_norm_f32(x, norm_weight, eps)
+    logits = y @ route_weight.float().t()
+    q, s, qt, st = blockwise_quant(y, round_scale)
+    return y.to(x.dtype), rms_recip(x, eps), logits, q, s, qt, st
+
+
 # --------------------------------------------------------------------------- #
 # SwiGLU (dense)
 # --------------------------------------------------------------------------- #

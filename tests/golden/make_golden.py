@@ -175,7 +175,23 @@ def main():
         for k, v in (("q", u8(q)), ("s", f32(s)), ("qt", u8(qt)), ("st", f32(st)), ("p", f32(pr))):
             out[f"perm_r{int(rs)}_{k}"] = v
     np.savez_compressed(os.path.join(HERE, "permute.npz"), **out)
-    for f in ("quant", "norm", "silu", "batch", "permute"):
+    # ---- RMSNorm + float32 router logits + quant (the step beside the norm in the MoE block) ----
+    out = {}
+    M, K, N = 128, 512, 128
+    x = bf16_randn(gen, (M, K), 2)
+    nw = bf16_randn(gen, (K,))
+    rw = bf16_randn(gen, (N, K))
+    out["x"] = u16(x)
+    out["norm_weight"] = u16(nw)
+    out["route_weight"] = u16(rw)
+    for rs in (False, True):
+        y, logits, q, s, qt, st = TN.torch_rms_gemm_block_quant_forward(x, nw, rw, round_scale=rs)
+        # upstream returns the scales untransposed here; store the kernel layouts
+        for k, v in (("y", u16(y)), ("logits", f32(logits)), ("q", u8(q)), ("s", f32(s.t())),
+                     ("qt", u8(qt)), ("st", f32(st.t()))):
+            out[f"router_r{int(rs)}_{k}"] = v
+    np.savez_compressed(os.path.join(HERE, "router.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch", "permute", "router"):
         p = os.path.join(HERE, f + ".npz")
         print(p, os.path.getsize(p))
 

@@ -539,3 +539,64 @@ def test_pad_permute(m, E, N, topk, dtype):
     out2 = f(_cuda(x), torch.tensor(counts, dtype=torch.int32, device=DEV), _cuda(idx), counts)
     assert out2[4] is None
     check_exact([o.view(-1) for o in out2[:4]], ref[:4], ("q", "s", "qt", "st"))
+
+
+# ------------------------------------------------------------------------------------
+# RMSNorm + float32 router logits + quantisation
+# ------------------------------------------------------------------------------------
+def _check_router(x, nw, rw, rs, golden_ref=None):
+    from linghe_b200.utils.norm import triton_rms_norm_fp32_gemm_block_quant_forward
+    if golden_ref is None:
+        ry, rr, rl, rq, rsc, rqt, rst = O.rms_norm_fp32_gemm_block_quant_forward(x, nw, rw, 1e-6, rs)
+    else:
+        ry, rl, rq, rsc, rqt, rst = golden_ref
+        rr = O.rms_recip(x)
+    xd, nwd, rwd = _cuda(x), _cuda(nw), _cuda(rw)
+    y, r, logits, q, s, qt, st = triton_rms_norm_fp32_gemm_block_quant_forward(
+        xd, nwd, rwd, round_scale=rs, output_mode=0)
+    assert logits.dtype == torch.float32 and tuple(logits.shape) == (x.shape[0], rw.shape[0])
+    assert y.dtype == x.dtype and tuple(s.shape) == (x.shape[1] // 128, x.shape[0])
+    assert_scales_close(r, rr, "rms")
+    assert_rel_close(y.float(), ry.float(), "y", 1e-2, 1e-6)
+    # float32 accumulation of exact products: only the summation order differs from the oracle
+    err = (logits.cpu().double() - rl.double()).abs().max().item()
+    mag = rl.double().abs().max().item()
+    assert err <= 1e-4 * mag + 1e-6, f"logits: max abs err {err:.3e} at magnitude {mag:.3e}"
+    check_fused(q, rq, s, rsc, "row", rs)
+    o = triton_rms_norm_fp32_gemm_block_quant_forward(xd, nwd, rwd, rms=r, round_scale=rs, output_mode=1)
+    assert o[1] is r
+    check_fused(o[5], rqt, o[6], rst, "col", rs)
+    return err / max(mag, 1e-30)
+
+
+@pytest.mark.parametrize("rs", [0, 1])
+def test_golden_rms_router_gemm(rs):
+    G = golden("router")
+    p = f"router_r{rs}_"
+    ref = (bf16(G[p + "y"]), torch.from_numpy(G[p + "logits"]), fp8(G[p + "q"]), torch.from_numpy(G[p + "s"]),
+           fp8(G[p + "qt"]), torch.from_numpy(G[p + "st"]))
+    _check_router(bf16(G["x"]), bf16(G["norm_weight"]), bf16(G["route_weight"]), bool(rs), ref)
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 128, 128), (256, 2048, 256), (1024, 1536, 128), (384, 8192, 384)])
+def test_rms_router_gemm(M, K, N):
+    x = randn_bf16((M, K), 41, 2)
+    nw = randn_bf16((K,), 42)
+    rw = randn_bf16((N, K), 43)
+    rel = _check_router(x, nw, rw, False)
+    print(f"router logits max error / max magnitude: {rel:.2e}")
+
+
+def test_rms_router_gemm_errors():
+    from linghe_b200.utils.norm import triton_rms_norm_fp32_gemm_block_quant_forward
+    x = _cuda(randn_bf16((128, 256), 1))
+    nw = _cuda(randn_bf16((256,), 2))
+    rw = _cuda(randn_bf16((128, 256), 3))
+    with pytest.raises(AssertionError):
+        triton_rms_norm_fp32_gemm_block_quant_forward(x, nw, rw, output_mode=2)
+    with pytest.raises(AssertionError):
+        triton_rms_norm_fp32_gemm_block_quant_forward(x, nw, rw, output_mode=1)      # needs rms
+    with pytest.raises(AssertionError):
+        triton_rms_norm_fp32_gemm_block_quant_forward(x[:100].contiguous(), nw, rw)  # M % 128
+    with pytest.raises(AssertionError):
+        triton_rms_norm_fp32_gemm_block_quant_forward(x, nw, rw[:64].contiguous())   # N % 128

@@ -160,3 +160,21 @@ def test_pad_permute(rs):
     assert_bits_equal(qt, fp8(G[f"perm_r{rs}_qt"]), "qt")
     assert_f32_equal(st, torch.from_numpy(G[f"perm_r{rs}_st"]), "st")
     assert_f32_equal(p, torch.from_numpy(G[f"perm_r{rs}_p"]), "probs")
+
+
+@pytest.mark.parametrize("rs", [0, 1])
+def test_rms_router_gemm_quant(rs):
+    G = golden("router")
+    x = bf16(G["x"])
+    y, r, logits, q, s, qt, st = O.rms_norm_fp32_gemm_block_quant_forward(
+        x, bf16(G["norm_weight"]), bf16(G["route_weight"]), 1e-6, bool(rs))
+    p = f"router_r{rs}_"
+    assert_rel_close(y.float(), bf16(G[p + "y"]).float(), "y", 1e-2, 1e-6)
+    assert_rel_close(logits, torch.from_numpy(G[p + "logits"]), "logits", 1e-5, 1e-4)
+    assert_codes_close(q, fp8(G[p + "q"]), "q")
+    assert_codes_close(qt, fp8(G[p + "qt"]), "qt")
+    if not rs:
+        assert_scales_close(s, torch.from_numpy(G[p + "s"]), "s")
+        assert_scales_close(st, torch.from_numpy(G[p + "st"]), "st")
+    assert tuple(logits.shape) == (x.shape[0], 128) and logits.dtype == torch.float32
+    assert tuple(s.shape) == (x.shape[1] // 128, x.shape[0])
