@@ -48,7 +48,7 @@ extern "C" {
 #define LH_OK 0
 #define LH_ERR_ARG (-1)
 
-enum { LH_BF16 = 0, LH_F16 = 1, LH_F32 = 2 };
+enum { LH_BF16 = 0, LH_F16 = 1, LH_F32 = 2, LH_U8 = 3 /* raw bytes: e4m3 codes */ };
 enum { LH_I32 = 0, LH_I64 = 1 };
 
 /* Library version (LH_VERSION of the build). */
@@ -215,6 +215,19 @@ int lh_batch_silu_blockquant_bwd(const void* g, const void* x, const void* w, in
                                  const void* counts, int counts_type, int E, int64_t R, int64_t n,
                                  void* dx_q, float* dx_s, void* dw, void* dx_qt, float* dx_st,
                                  int round_scale, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* ---- consumer of the wire format ------------------------------------------------- */
+
+/* Blockwise-scaled FP8 GEMM  c [M,N] = dequant(a) . dequant(b)^T.
+ * Replaces triton_tt_fp8_gemm, linghe/gemm/blockwise_fp8_gemm.py:152.
+ * a [M,K], b [N,K] e4m3 codes; one float32 scale per 1 x block_size run of k (block_size
+ * 128 or 64; K a multiple of 128, at most 128 scale blocks).  Scales as the reference
+ * stores them, a_s [M, K/block] and b_s [N, K/block], or -- *_transposed != 0 -- as the
+ * quantisers of this library write them, [K/block, M] and [K/block, N], so that
+ * (q, s) of lh_blockwise_quant / lh_rmsnorm_blockquant_fwd feed it unchanged.
+ * out_dtype: LH_BF16 / LH_F16 / LH_F32. */
+int lh_fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,
+                int64_t K, int block_size, int a_s_transposed, int b_s_transposed, int out_dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -42,6 +42,7 @@ SIGNATURES = {
     "lh_rmsnorm_fwd": (_i, [_p, _p, _i, _l, _l, _f, _p, _p, _i, _p]),
     "lh_rmsnorm_blockquant_fwd": (_i, [_p, _p, _i, _l, _l, _f, _p, _p, _p, _p, _p, _i, _i, _p]),
     "lh_rmsnorm_gemm_blockquant_fwd": (_i, [_p, _p, _p, _i, _l, _l, _l, _f, _p, _p, _p, _p, _p, _p, _p, _i, _i, _p, _l, _p]),
+    "lh_fp8_gemm": (_i, [_p, _p, _p, _p, _p, _l, _l, _l, _i, _i, _i, _i, _p]),
     "lh_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _l, _p]),
     "lh_rmsnorm_bwd_static": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p]),
     "lh_rmsnorm_bwd_blockquant": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _p, _p, _p, _i, _p, _l, _p]),

@@ -79,7 +79,8 @@ int make_tensor_map(CUtensorMap* out, const void* base, int dtype, uint64_t rows
         }
         encode = reinterpret_cast<EncodeFn>(fn);
     }
-    const CUtensorMapDataType dt = dtype == LH_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+    const CUtensorMapDataType dt = dtype == LH_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : dtype == LH_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : dtype == LH_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     const cuuint64_t dims[2] = {cols, rows};
@@ -104,6 +105,8 @@ int rows_norm_yq(const void* x, const void* gamma, int64_t M, int n, float eps, 
 int64_t router_gemm_scratch(int64_t N, int64_t K);
 int router_gemm(const void* x, const void* gamma, const void* w, const float* rms, float* logits, int64_t M, int64_t N,
                 int64_t K, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
+int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
+             int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
                cudaStream_t stream);
@@ -263,6 +266,12 @@ int lh_rmsnorm_gemm_blockquant_fwd(const void* x, const void* gamma, const void*
     if (!aligned16(y) || !aligned16(q)) return fail_arg("rmsnorm_gemm_blockquant_fwd: pointers must be 16-byte aligned");
     if (int rc = rows_norm_yq(x, gamma, M, int(K), eps, y, q, s, rms, round_scale, cs)) return rc;
     return router_gemm(x, gamma, route_w, rms, logits, M, N, K, scratch, scratch_bytes, cs);
+}
+
+int lh_fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,
+                int64_t K, int block_size, int a_s_transposed, int b_s_transposed, int out_dtype, void* stream) {
+    return fp8_gemm(a, b, a_s, b_s, c, M, N, K, block_size, a_s_transposed, b_s_transposed, out_dtype,
+                    static_cast<cudaStream_t>(stream));
 }
 
 int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,

@@ -184,6 +184,21 @@ def rms_norm_fp32_gemm_block_quant_forward(x, norm_weight, route_weight, eps: fl
     return y.to(x.dtype), rms_recip(x, eps), logits, q, s, qt, st
 
 
+def tt_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.bfloat16, block_size: int = 128):
+    """Blockwise-scaled FP8 GEMM: dequantise both operands and multiply in float32.
+
+    The reference's own check for ``triton_tt_fp8_gemm`` (tests/test_blockwise_fp8_gemm.py:56-74):
+    x_dq = x_q.float().view(M, K/B, B) * x_scales[:, :, None], same for w, y = x_dq @ w_dq.T.
+    a_s [M, K/B], b_s [N, K/B] (the reference's scale layout).
+    """
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    B = block_size
+    a_dq = (a_q.float().view(M, K // B, B) * a_s[:, :, None]).view(M, K)
+    b_dq = (b_q.float().view(N, K // B, B) * b_s[:, :, None]).view(N, K)
+    return (a_dq @ b_dq.t()).to(out_dtype)
+
+
 # --------------------------------------------------------------------------- #
 # SwiGLU (dense)
 # --------------------------------------------------------------------------- #

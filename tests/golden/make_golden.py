@@ -191,7 +191,29 @@ def main():
                      ("qt", u8(qt)), ("st", f32(st.t()))):
             out[f"router_r{int(rs)}_{k}"] = v
     np.savez_compressed(os.path.join(HERE, "router.npz"), **out)
-    for f in ("quant", "norm", "silu", "batch", "permute", "router"):
+    # ---- blockwise-scaled FP8 GEMM (consumer of the wire format) ----
+    # upstream has no oracle function for it: the expected value is computed inline in
+    # tests/test_blockwise_fp8_gemm.py:56-72 (dequantise, float32 matmul); the same lines are
+    # applied here to codes produced by upstream's torch_group_quant.
+    out = {}
+    M, N, K = 96, 160, 256
+    xa = bf16_randn(gen, (M, K))
+    wb = bf16_randn(gen, (N, K), 3)
+    a_q, a_s = U.torch_group_quant(xa, round_scale=False)      # scales [M, K/128]
+    b_q, b_s = U.torch_group_quant(wb, round_scale=False)
+    out["a_q"], out["b_q"] = u8(a_q), u8(b_q)
+    out["a_s128"], out["b_s128"] = f32(a_s), f32(b_s)
+    a_s64 = torch.rand((M, K // 64), generator=gen) * 0.1
+    b_s64 = torch.rand((N, K // 64), generator=gen) * 0.1
+    out["a_s64"], out["b_s64"] = f32(a_s64), f32(b_s64)
+    for B, sa, sb in ((128, a_s, b_s), (64, a_s64, b_s64)):
+        x_dq = (a_q.float().view(M, K // B, B) * sa[:, :, None]).view(M, K)
+        w_dq = (b_q.float().view(N, K // B, B) * sb[:, :, None]).view(N, K)
+        y = x_dq @ w_dq.t()
+        out[f"y{B}_f32"] = f32(y)
+        out[f"y{B}_bf16"] = u16(y.to(torch.bfloat16))
+    np.savez_compressed(os.path.join(HERE, "fp8gemm.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm"):
         p = os.path.join(HERE, f + ".npz")
         print(p, os.path.getsize(p))
 

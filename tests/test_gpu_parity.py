@@ -600,3 +600,78 @@ def test_rms_router_gemm_errors():
         triton_rms_norm_fp32_gemm_block_quant_forward(x[:100].contiguous(), nw, rw)  # M % 128
     with pytest.raises(AssertionError):
         triton_rms_norm_fp32_gemm_block_quant_forward(x, nw, rw[:64].contiguous())   # N % 128
+
+
+# ------------------------------------------------------------------------------------
+# blockwise-scaled FP8 GEMM (consumer of the quantisers' wire format)
+# ------------------------------------------------------------------------------------
+def _gemm_err(got, ref):
+    g, r = got.detach().float().cpu().double(), ref.double()
+    return (g - r).abs().max().item() / max(r.abs().max().item(), 1e-30)
+
+
+@pytest.mark.parametrize("block", [128, 64])
+def test_golden_fp8_gemm(block):
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    G = golden("fp8gemm")
+    a_q, b_q = _cuda(fp8(G["a_q"])), _cuda(fp8(G["b_q"]))
+    a_s, b_s = _cuda(torch.from_numpy(G[f"a_s{block}"])), _cuda(torch.from_numpy(G[f"b_s{block}"]))
+    y32 = triton_tt_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.float32, block_size=block)
+    ref = torch.from_numpy(G[f"y{block}_f32"])
+    assert _gemm_err(y32, ref) <= 1e-5            # exact products, float32 sums: summation order only
+    yb = triton_tt_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.bfloat16, block_size=block)
+    assert yb.dtype == torch.bfloat16
+    assert_rel_close(yb.float(), bf16(G[f"y{block}_bf16"]).float(), "y bf16", 1e-2)
+    # the same scales in the layout the quantisers of this package write
+    yt = triton_tt_fp8_gemm(a_q, b_q, a_s.t().contiguous(), b_s.t().contiguous(), out_dtype=torch.float32,
+                            block_size=block, scales_transposed=True)
+    assert torch.equal(yt, y32)
+
+
+@pytest.mark.parametrize("M,N,K,block,dt", [(512, 384, 1024, 128, torch.bfloat16), (1000, 264, 512, 64, torch.float16),
+                                            (130, 8, 4096, 128, torch.float32), (128, 128, 16384, 128, torch.bfloat16),
+                                            (2048, 2048, 2048, 64, torch.bfloat16)])
+def test_fp8_gemm(M, N, K, block, dt):
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    g = torch.Generator().manual_seed(51)
+    a_q = torch.randn((M, K), generator=g).to(torch.float8_e4m3fn)
+    b_q = torch.randn((N, K), generator=g).to(torch.float8_e4m3fn)
+    a_s = torch.rand((M, K // block), generator=g) + 0.01
+    b_s = torch.rand((N, K // block), generator=g) + 0.01
+    ref = O.tt_fp8_gemm(a_q, b_q, a_s, b_s, torch.float32, block)
+    y = triton_tt_fp8_gemm(_cuda(a_q), _cuda(b_q), _cuda(a_s), _cuda(b_s), out_dtype=dt, block_size=block)
+    assert y.dtype == dt and tuple(y.shape) == (M, N)
+    err = _gemm_err(y, ref)
+    print(f"fp8 gemm {M}x{N}x{K} block {block}: max err / max |y| = {err:.2e}")
+    assert err <= (1e-5 if dt == torch.float32 else 5e-3)
+
+
+def test_fp8_gemm_consumes_quantiser_outputs():
+    """x, w -> row-wise (q, s[K/128, M]) from this package's quantisers -> GEMM; against the
+    float32 product of the dequantised operands and, loosely, of the unquantised ones."""
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    from linghe_b200.quant.block import triton_blockwise_quant
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    M, N, K = 1024, 512, 2048
+    x = randn_bf16((M, K), 61)
+    gam = randn_bf16((K,), 62)
+    w = randn_bf16((N, K), 63)
+    xq, xs, _, _, _ = triton_rms_norm_and_block_quant_forward(_cuda(x), _cuda(gam), output_mode=0)
+    wq, ws, _, _ = triton_blockwise_quant(_cuda(w), output_mode=0)
+    y = triton_tt_fp8_gemm(xq, wq, xs, ws, out_dtype=torch.bfloat16, block_size=128, scales_transposed=True)
+    ref = O.tt_fp8_gemm(xq.cpu(), wq.cpu(), xs.cpu().t().contiguous(), ws.cpu().t().contiguous(), torch.float32, 128)
+    assert _gemm_err(y, ref) <= 5e-3
+    full = O.rms_norm_forward(x, gam).float() @ w.float().t()
+    assert _gemm_err(y, full) <= 5e-2           # the quantisation error itself
+
+
+def test_fp8_gemm_errors():
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    a = _cuda(torch.zeros((128, 256)).to(torch.float8_e4m3fn))
+    s = _cuda(torch.ones((128, 2)))
+    with pytest.raises(AssertionError):
+        triton_tt_fp8_gemm(a, a, s, s, block_size=32)
+    with pytest.raises(AssertionError):
+        triton_tt_fp8_gemm(a, a, s[:, :1].contiguous(), s, block_size=128)
+    with pytest.raises(AssertionError):
+        triton_tt_fp8_gemm(a.to(torch.bfloat16), a, s, s)

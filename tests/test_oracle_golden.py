@@ -178,3 +178,15 @@ def test_rms_router_gemm_quant(rs):
         assert_scales_close(st, torch.from_numpy(G[p + "st"]), "st")
     assert tuple(logits.shape) == (x.shape[0], 128) and logits.dtype == torch.float32
     assert tuple(s.shape) == (x.shape[1] // 128, x.shape[0])
+
+
+@pytest.mark.parametrize("block", [128, 64])
+def test_tt_fp8_gemm(block):
+    G = golden("fp8gemm")
+    a_q, b_q = fp8(G["a_q"]), fp8(G["b_q"])
+    y = O.tt_fp8_gemm(a_q, b_q, torch.from_numpy(G[f"a_s{block}"]), torch.from_numpy(G[f"b_s{block}"]),
+                      torch.float32, block)
+    assert_rel_close(y, torch.from_numpy(G[f"y{block}_f32"]), "y", 1e-5)
+    yb = O.tt_fp8_gemm(a_q, b_q, torch.from_numpy(G[f"a_s{block}"]), torch.from_numpy(G[f"b_s{block}"]),
+                       torch.bfloat16, block)
+    assert_rel_close(yb.float(), bf16(G[f"y{block}_bf16"]).float(), "y bf16", 1e-2)
