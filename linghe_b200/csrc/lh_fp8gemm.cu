@@ -7,8 +7,7 @@
 // Each k-block's partial product is an exact e4m3 x e4m3 contraction on the tensor cores
 // (tcgen05.mma kind::f8f6f4, float32 accumulator in tensor memory, started from zero per
 // block); the CUDA cores then fold it into float32 register accumulators with the two
-// scales.  Two partial buffers in tensor memory let block i+1 run on the tensor cores
-// while block i is folded.
+// scales.  Four partial buffers in tensor memory let the tensor cores run ahead of the fold.
 //
 // One CTA = one 128 x 128 tile of C.  warp 0: TMA producer; warp 1: MMA issuer and owner
 // of the tensor-memory allocation; warps 2-9: fold + store, thread = (row, 64-column half).
@@ -26,7 +25,8 @@ constexpr int F_BAR_OFF = FSTAGES * F_STAGE;
 constexpr int F_SB_OFF = F_BAR_OFF + 256;      // b scales of this tile, [k-block][128] float32
 constexpr int F_SB_MAX = 128;                  // scale blocks along k that fit
 constexpr int F_SMEM = 1024 + F_SB_OFF + F_SB_MAX * FN * 4;
-constexpr int F_TMEM_COLS = 2 * FN;
+constexpr int FBUFS = 4;                        // partial-product buffers in tensor memory
+constexpr int F_TMEM_COLS = FBUFS * FN;
 constexpr int F_THREADS = 64 + 256;
 
 enum : int { DEVERR_PART_WAIT = 5 };
@@ -54,7 +54,7 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -66,10 +66,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
         : "r"(taddr)
         : "memory");
 }
+// Bounded wait without a function call (a call would spill the accumulators around it).
+__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, int code) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicCAS(&g_device_status, 0, code);
+    return false;
+}
 // One lane polls; the others then observe the completed phase with one try_wait of their own.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int code, int lane) {
     bool ok = true;
-    if (lane == 0) ok = mbar_wait(bar, parity, code);
+    if (lane == 0) ok = mbar_wait_inline(bar, parity, code);
     ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
     if (ok && lane != 0) ok = mbar_try_wait(bar, parity);
     return __all_sync(0xffffffffu, ok);
@@ -97,9 +105,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint8_t* tiles = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
     uint64_t* full = reinterpret_cast<uint64_t*>(tiles + F_BAR_OFF);   // TMA landed
     uint64_t* empty = full + FSTAGES;                                   // MMAs have read the stage
-    uint64_t* part_full = empty + FSTAGES;                              // [2] partial product complete
-    uint64_t* part_empty = part_full + 2;                               // [2] partial product read out
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + 2);
+    uint64_t* part_full = empty + FSTAGES;                              // partial product complete
+    uint64_t* part_empty = part_full + FBUFS;                           // partial product read out
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + FBUFS);
     float* sb = reinterpret_cast<float*>(tiles + F_SB_OFF);
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -107,20 +115,12 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int kstages = p.K / FKB;
     const int nsb = p.nsb;
 
-    // b scales of this tile's 128 columns -> shared memory, [scale block][column]
-    for (int i = t; i < nsb * FN; i += F_THREADS) {
-        const int blk = i / FN, col = i - blk * FN;
-        const int n = n0 + col;
-        float v = 0.f;
-        if (n < p.N) v = p.b_s_transposed ? p.b_s[int64_t(blk) * p.N + n] : p.b_s[int64_t(n) * nsb + blk];
-        sb[i] = v;
-    }
     if (t == 0) {
         for (int i = 0; i < FSTAGES; ++i) {
             mbar_init(&full[i], 1);
             mbar_init(&empty[i], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < FBUFS; ++i) {
             mbar_init(&part_full[i], 1);
             mbar_init(&part_empty[i], 8);
         }
@@ -163,9 +163,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                 for (int h = 0; h < SUB; ++h) {
                     const int blk = ks * SUB + h;                  // scale block = partial product
-                    const int buf = blk & 1;
-                    if (blk >= 2) {
-                        ok = mbar_wait(&part_empty[buf], (uint32_t(blk >> 1) & 1u) ^ 1u, DEVERR_PART_WAIT);
+                    const int buf = blk % FBUFS;
+                    if (blk >= FBUFS) {
+                        ok = mbar_wait(&part_empty[buf], (uint32_t(blk / FBUFS) & 1u) ^ 1u, DEVERR_PART_WAIT);
                         if (!ok) break;
                     }
                     tc_fence_after();
@@ -182,6 +182,16 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
     } else {
         // ---- fold the partial products into register accumulators, then store
+        // b scales of this tile's 128 columns -> shared memory, [scale block][column]; only these
+        // warps need them, so the loads and the MMAs start meanwhile
+        for (int i = t - 64; i < nsb * FN; i += F_THREADS - 64) {
+            const int blk = i / FN, col = i - blk * FN;
+            const int n = n0 + col;
+            float v = 0.f;
+            if (n < p.N) v = p.b_s_transposed ? p.b_s[int64_t(blk) * p.N + n] : p.b_s[int64_t(n) * nsb + blk];
+            sb[i] = v;
+        }
+        named_bar<1, F_THREADS - 64>();
         const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int64_t row = int64_t(m0) + quarter * 32 + lane;
         const bool row_ok = row < p.M;
@@ -190,34 +200,48 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         float2 acc[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[j] = make_float2(0.f, 0.f);
+        // Software pipeline over 32-column chunks: the tensor-memory load of the next chunk
+        // is in flight while the current one is folded (tcgen05.wait::ld waits for every
+        // outstanding load, so it comes after the fold).
         bool ok = true;
+        uint32_t v0[32], v1[32];
+        const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(half * 64);
+        auto wait_block = [&](int blk) {
+            ok = mbar_wait_warp(&part_full[blk % FBUFS], uint32_t(blk / FBUFS) & 1u, DEVERR_PART_WAIT, lane);
+            tc_fence_after();
+        };
+        auto fold = [&](const uint32_t (&v)[32], int blk, int c, float sa) {
+            const float2 sa2 = splat2(sa);
+            const float2* sbp = reinterpret_cast<const float2*>(sb + blk * FN + half * 64 + 32 * c);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float2 pr = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                acc[16 * c + j] = fma2(mul2(pr, sbp[j]), sa2, acc[16 * c + j]);
+            }
+        };
         float sa_next = row_ok ? as_ptr[0] : 0.f;
+        wait_block(0);
+        if (ok) {
+            tmem_ld32(tbase, v0);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        }
         for (int blk = 0; blk < nsb && ok; ++blk) {
-            const int buf = blk & 1;
+            const int buf = blk % FBUFS;
             const float sa = sa_next;
             if (blk + 1 < nsb && row_ok) sa_next = as_ptr[int64_t(blk + 1) * as_step];
-            ok = mbar_wait_warp(&part_full[buf], uint32_t(blk >> 1) & 1u, DEVERR_PART_WAIT, lane);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(buf * FN + half * 64);
-            const float2 sa2 = splat2(sa);
-            const float2* sbp = reinterpret_cast<const float2*>(sb + blk * FN + half * 64);
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {                        // 32 columns at a time
-                uint32_t v[32];
-                tmem_ld32(taddr + 32 * c, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (c == 1) {                                    // the tensor cores may overwrite this buffer
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&part_empty[buf]);
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const float2 pr = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                    acc[16 * c + j] = fma2(mul2(pr, sbp[16 * c + j]), sa2, acc[16 * c + j]);
-                }
+            tmem_ld32(tbase + uint32_t(buf * FN + 32), v1);
+            fold(v0, blk, 0, sa);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&part_empty[buf]);        // the tensor cores may overwrite this buffer
+            if (blk + 1 < nsb) {
+                wait_block(blk + 1);
+                if (!ok) break;
+                tmem_ld32(tbase + uint32_t(((blk + 1) % FBUFS) * FN), v0);
             }
+            fold(v1, blk, 1, sa);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         }
         if (ok && row_ok) {
             const int c0 = n0 + half * 64;

@@ -105,9 +105,12 @@ def time_call(make_args, fn, nbytes_set, iters=50):
     return event_us, graph_us, nsets
 
 
+FLOPS = {}   # case name -> floating-point operations, for the GEMM rows
+
+
 def build_cases(mods):
     """name -> (make_args, callable, algorithmic bytes, ring bytes per set)"""
-    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute, router = mods
+    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute, router, gemm = mods
     cases = {}
 
     def add(name, make_args, fn, nbytes, set_bytes=None):
@@ -171,6 +174,17 @@ def build_cases(mods):
             lambda i: (bf16_randn((8192, 2048), i), gam[:2048].contiguous()),
             lambda x, g: router(x, g, rw, output_mode=0),
             M * K * 5 + M * (K // 128) * 4 + M * 4 + M * N * 4 + N * K * 2 + K * 2)
+    # consumer of the wire format: blockwise-scaled FP8 GEMM (upstream test shape 4096^3, blocks of 128)
+    if gemm is not None:
+        for (M, N, K) in ((4096, 4096, 4096), (8192, 2816, 2048)):
+            FLOPS[f"next fp8 gemm tt {M}x{N}x{K} block 128"] = 2 * M * N * K
+            add(f"next fp8 gemm tt {M}x{N}x{K} block 128",
+                lambda i, M=M, N=N, K=K: (torch.randn((M, K), device="cuda").to(torch.float8_e4m3fn),
+                                          torch.randn((N, K), device="cuda").to(torch.float8_e4m3fn),
+                                          torch.rand((M, K // 128), device="cuda") + 0.01,
+                                          torch.rand((N, K // 128), device="cuda") + 0.01),
+                lambda a, b, sa, sb: gemm(a, b, sa, sb, out_dtype=torch.bfloat16, block_size=128),
+                M * K + N * K + 2 * M * N + (M + N) * (K // 128) * 4)
     # cfg4: RMSNorm bwd + dual-axis dy quant 16384 x 4096
     M, n = 16384, 4096
     c4 = 3 * M * n * 2 + 2 * M * n + 2 * M * n * 4 // 128 + n * 2 + n * 4
@@ -208,7 +222,12 @@ def ours():
             lambda g, x: triton_silu_and_block_quant_backward(g, x, return_bf16=True),
             triton_weighted_silu_backward, triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, rms_norm_backward_and_block_quant,
-            _ours_permute(), _ours_router())
+            _ours_permute(), _ours_router(), _ours_gemm())
+
+
+def _ours_gemm():
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    return triton_tt_fp8_gemm
 
 
 def _ours_router():
@@ -240,7 +259,12 @@ def upstream(path):
             triton_silu_and_block_quant_forward, silu_b, triton_weighted_silu_backward,
             triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, fused_bwd, _upstream_permute(),
-            _upstream_router())
+            _upstream_router(), _upstream_gemm())
+
+
+def _upstream_gemm():
+    from linghe.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    return triton_tt_fp8_gemm
 
 
 def _upstream_router():
@@ -286,6 +310,9 @@ def main():
                          "ring": nsets})
             print(f"{impl_name:16} {name:52} event {ev_us:9.1f} us  graph {us:9.1f} us  {gbs:8.1f} GB/s  "
                   f"{100 * gbs / NOMINAL:5.1f}% of 8 TB/s  {100 * gbs / peak:5.1f}% of measured {peak:.0f}", flush=True)
+            if name in FLOPS:
+                rows[-1]["tflops"] = round(FLOPS[name] / us / 1e6, 1)
+                print(f"{'':16} {'':52} {FLOPS[name] / us / 1e6:9.1f} TFLOP/s", flush=True)
     if a.json:
         with open(a.json, "w") as fh:
             json.dump(rows, fh, indent=1)
