@@ -133,16 +133,19 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_const
         }
     } else if (t == 32) {
         // ---- MMA issuer
-        bool ok = true;
+        // The issue of an MMA blocks while the tensor pipe's queue is full, so after the last
+        // MMA of a stage only little work is queued: the wait for the next stage's data sits
+        // in the middle of the current stage's MMAs, not after them.
+        bool ok = mbar_wait(&full[0], 0, DEVERR_FULL_WAIT);
+        const uint64_t d0 = umma_desc(smem_u32(tiles));
         for (int kt = 0; kt < ktiles && ok; ++kt) {
             const int s = kt % GSTAGES;
-            ok = mbar_wait(&full[s], uint32_t(kt / GSTAGES) & 1u, DEVERR_FULL_WAIT);
-            if (!ok) break;
             tc_fence_after();
-            const uint32_t a = smem_u32(tiles + size_t(s) * G_STAGE);
-            const uint64_t da = umma_desc(a), dh = umma_desc(a + G_TILE), dl = umma_desc(a + 2 * G_TILE);
+            const uint64_t da = d0 + uint64_t(s) * (G_STAGE >> 4), dh = da + (G_TILE >> 4), dl = dh + (G_TILE >> 4);
 #pragma unroll
             for (int k4 = 0; k4 < GK / 16; ++k4) {          // 16 elements = 32 bytes = 2 descriptor units per step
+                if (k4 == GK / 32 && kt + 1 < ktiles)
+                    ok = mbar_wait(&full[(kt + 1) % GSTAGES], uint32_t((kt + 1) / GSTAGES) & 1u, DEVERR_FULL_WAIT);
                 umma_bf16(tmem, da + 2 * k4, dh + 2 * k4, (kt | k4) != 0);
                 umma_bf16(tmem, da + 2 * k4, dl + 2 * k4, 1u);
             }
