@@ -3,13 +3,14 @@
 // whole row or on nothing outside a 1x128 block, so they stream rows through the SM.
 //
 // Execution model (sm_100a): persistent CTAs walk slabs of at most 8192 output elements
-// (RB complete rows, or a column chunk of one long row).  Warp 0 brings each slab into a
+// (RB complete rows for the norm kernels; 64 consecutive 1x128 blocks of the row-major
+// output, whatever rows they fall in, for SwiGLU).  Warp 0 brings each slab into a
 // shared-memory ring with bulk asynchronous copies (TMA; rows are contiguous, so one copy
 // per operand and row run) that complete on an mbarrier.  Every thread owns EPT
 // contiguous elements: it pulls them into registers (freeing the ring slot at once), does
 // the arithmetic with packed float32x2 instructions, reduces per-row sums through
 // shuffles and one named barrier, and stages the outputs in shared memory from where one
-// bulk copy per slab writes them back.  No tensor cores: the path is HBM-bound.
+// bulk copy per warp writes them back.  No tensor cores: the path is HBM-bound.
 #include "lh_common.cuh"
 
 namespace lh {
@@ -30,7 +31,6 @@ struct RowParams {
     int64_t M;
     int n;               // output columns
     int RB;              // rows per slab
-    int chunks;          // column chunks per row (1 unless n > 8192)
     uint8_t* q;          // *_Q: codes [M,n]
     float* s;            // *_Q: scales [n/128, M]
     uint8_t* hp;         // ROP_NORM_Y, ROP_NORM_YQ: y [M,n]; ROP_NORM_BWD: dx [M,n]
@@ -57,11 +57,9 @@ struct RowCfg {
 struct SlabLoc {
     int64_t row0;
     int rows;   // valid rows
-    int c0;     // first column
-    int ncols;  // columns in this slab
 };
 
-template <int ROP, int EPT, int STAGES, int MINB, bool CHUNKED>
+template <int ROP, int EPT, int STAGES, int MINB>
 __global__ void __launch_bounds__(RowCfg<ROP, EPT, STAGES>::NT, MINB)
 rows_kernel(const __grid_constant__ RowParams p) {
     using C = RowCfg<ROP, EPT, STAGES>;
@@ -103,8 +101,6 @@ rows_kernel(const __grid_constant__ RowParams p) {
         L.row0 = slab * RB;
         const int64_t left = p.M - L.row0;
         L.rows = left < RB ? int(left) : RB;
-        L.c0 = 0;
-        L.ncols = n;
         return L;
     };
 
@@ -188,6 +184,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
     const bool warp_rows = (TPR % 32) == 0;        // rows are made of whole warps
     const int red_cnt = warp_rows ? TPR / 32 : (n >> 7);
     const int red_first = my_row * red_cnt;
+    const bool row_bar = NORM && warp_rows && RB <= 8 && RB * TPR == NT;   // the same for every thread
     float2 acc[ROP == ROP_NORM_BWD ? NP : 1];
 #pragma unroll
     for (int i = 0; i < (ROP == ROP_NORM_BWD ? NP : 1); ++i) acc[i] = make_float2(0.f, 0.f);
@@ -213,7 +210,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
             if (nxt < slabs && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
         }
         SlabLoc L = locate(slab);
-        int slab_elems = L.rows * L.ncols;                 // valid elements in this slab
+        int slab_elems = L.rows * n;                       // valid elements in this slab
         if constexpr (!NORM) {
             const int64_t bl = total_blocks - slab * 64;
             slab_elems = (bl < 64 ? int(bl) : 64) * 128;
@@ -298,7 +295,10 @@ rows_kernel(const __grid_constant__ RowParams p) {
                 }
                 if ((t % LPB) == 0) { red_ss[t / LPB] = ss; if constexpr (ROP == ROP_NORM_BWD) red_sc[t / LPB] = sc; }
             }
-            named_bar<1, NT>();
+            // rows are independent: when a row is made of whole warps only its own warps meet
+            // (barrier 1 + row), so the row groups of a slab drift apart and overlap their phases
+            if (row_bar) asm volatile("bar.sync %0, %1;" ::"r"(1 + my_row), "r"(TPR) : "memory");
+            else named_bar<1, NT>();
             float tot_ss = 0.f;
             if (red_cnt == 8) {   // one row per slab: two vector loads
                 const float4 a = *reinterpret_cast<const float4*>(red_ss + red_first);
@@ -423,14 +423,14 @@ rows_kernel(const __grid_constant__ RowParams p) {
         // Fold the per-thread dgamma sums of the RB rows of a slab into one row and
         // publish this CTA's partial; a second kernel adds the partials in a fixed order.
         float* fold = reinterpret_cast<float*>(stages);   // ring is idle: every slab was consumed
-        named_bar<1, NT>();
+        named_bar<10, NT>();
 #pragma unroll
         for (int i = 0; i < NP; ++i) {
             const int j = 8 * ((i >> 2) ^ sw) + 2 * (i & 3);   // column offset inside this thread's span
             fold[j * NT + t] = acc[i].x;
             fold[(j + 1) * NT + t] = acc[i].y;
         }
-        named_bar<2, NT>();
+        named_bar<11, NT>();
         if (t < TPR) {
             for (int j = 0; j < EPT; ++j) {
                 float a = 0.f;
@@ -688,11 +688,9 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid
     p.inv_n = 1.0f / float(p.n);
     if (ROP == ROP_SILU_Q) {
         p.RB = 1;
-        p.chunks = 1;
         slabs = (p.M * (p.n / 128) + 63) / 64;      // 64 blocks of 1x128 per slab
     } else {
         p.RB = kSlabElems / p.n;
-        p.chunks = 1;
         slabs = (p.M + p.RB - 1) / p.RB;
     }
     int64_t grid = int64_t(sm_count()) * CTAS_PER_SM;
@@ -705,7 +703,7 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid
         kern<<<dim3(unsigned(grid)), dim3(C::NT), C::SMEM, stream>>>(p);
         return check_launch("rows_kernel");
     };
-    return go(rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM, false>);
+    return go(rows_kernel<ROP, EPT, STAGES, CTAS_PER_SM>);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -730,7 +728,6 @@ int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int6
     constexpr int U = 2, STAGES = 2;
     p.inv_n = 1.0f / float(p.n);
     p.RB = kSlabElems / p.n;
-    p.chunks = 1;
     const int64_t groups = (M + int64_t(U) * p.RB - 1) / (int64_t(U) * p.RB);
     int64_t grid = int64_t(sm_count()) * 2;
     if (grid > kMaxRowCtas) grid = kMaxRowCtas;
