@@ -10,7 +10,7 @@
 // scales.  Four partial buffers in tensor memory let the tensor cores run ahead of the fold.
 //
 // One CTA = one 128 x 128 tile of C.  warp 0: TMA producer; warp 1: MMA issuer and owner
-// of the tensor-memory allocation; warps 2-9: fold + store, thread = (row, 64-column half).
+// of the tensor-memory allocation; warps 2-17: fold + store, thread = (row, 32-column group).
 #include "lh_common.cuh"
 
 namespace lh {
@@ -27,7 +27,8 @@ constexpr int F_SB_MAX = 128;                  // scale blocks along k that fit
 constexpr int F_SMEM = 1024 + F_SB_OFF + F_SB_MAX * FN * 4;
 constexpr int FBUFS = 4;                        // partial-product buffers in tensor memory
 constexpr int F_TMEM_COLS = FBUFS * FN;
-constexpr int F_THREADS = 64 + 256;
+constexpr int F_FOLD_WARPS = 16;                // each folds 32 accumulator rows x 32 columns
+constexpr int F_THREADS = 64 + 32 * F_FOLD_WARPS;
 
 enum : int { DEVERR_PART_WAIT = 5 };
 
@@ -122,7 +123,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         for (int i = 0; i < FBUFS; ++i) {
             mbar_init(&part_full[i], 1);
-            mbar_init(&part_empty[i], 8);
+            mbar_init(&part_empty[i], F_FOLD_WARPS);
         }
         mbar_fence_init();
         tma_prefetch_desc(&map_a);
@@ -192,63 +193,46 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             sb[i] = v;
         }
         named_bar<1, F_THREADS - 64>();
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        const int quarter = warp & 3, cgrp = (warp - 2) >> 2;       // tensor-memory lane quarter, 32-column group
         const int64_t row = int64_t(m0) + quarter * 32 + lane;
         const bool row_ok = row < p.M;
         const float* as_ptr = p.a_s + (p.a_s_transposed ? row : row * nsb);
         const int64_t as_step = p.a_s_transposed ? p.M : 1;
-        float2 acc[32];
+        float2 acc[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = make_float2(0.f, 0.f);
-        // Software pipeline over 32-column chunks: the tensor-memory load of the next chunk
-        // is in flight while the current one is folded (tcgen05.wait::ld waits for every
-        // outstanding load, so it comes after the fold).
+        for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.f, 0.f);
+        // Four fold warps per scheduler: their tensor-memory loads, shared-memory reads and FMAs
+        // overlap across warps, so each warp simply loads a block's 32 columns and folds them.
         bool ok = true;
-        uint32_t v0[32], v1[32];
-        const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(half * 64);
-        auto wait_block = [&](int blk) {
-            ok = mbar_wait_warp(&part_full[blk % FBUFS], uint32_t(blk / FBUFS) & 1u, DEVERR_PART_WAIT, lane);
-            tc_fence_after();
-        };
-        auto fold = [&](const uint32_t (&v)[32], int blk, int c, float sa) {
-            const float2 sa2 = splat2(sa);
-            const float2* sbp = reinterpret_cast<const float2*>(sb + blk * FN + half * 64 + 32 * c);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float2 pr = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                acc[16 * c + j] = fma2(mul2(pr, sbp[j]), sa2, acc[16 * c + j]);
-            }
-        };
+        const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(cgrp * 32);
         float sa_next = row_ok ? as_ptr[0] : 0.f;
-        wait_block(0);
-        if (ok) {
-            tmem_ld32(tbase, v0);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        }
         for (int blk = 0; blk < nsb && ok; ++blk) {
             const int buf = blk % FBUFS;
             const float sa = sa_next;
             if (blk + 1 < nsb && row_ok) sa_next = as_ptr[int64_t(blk + 1) * as_step];
-            tmem_ld32(tbase + uint32_t(buf * FN + 32), v1);
-            fold(v0, blk, 0, sa);
+            ok = mbar_wait_warp(&part_full[buf], uint32_t(blk / FBUFS) & 1u, DEVERR_PART_WAIT, lane);
+            if (!ok) break;
+            tc_fence_after();
+            uint32_t v[32];
+            tmem_ld32(tbase + uint32_t(buf * FN), v);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&part_empty[buf]);        // the tensor cores may overwrite this buffer
-            if (blk + 1 < nsb) {
-                wait_block(blk + 1);
-                if (!ok) break;
-                tmem_ld32(tbase + uint32_t(((blk + 1) % FBUFS) * FN), v0);
+            const float2 sa2 = splat2(sa);
+            const float2* sbp = reinterpret_cast<const float2*>(sb + blk * FN + cgrp * 32);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float2 pr = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                acc[j] = fma2(mul2(pr, sbp[j]), sa2, acc[j]);
             }
-            fold(v1, blk, 1, sa);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         }
         if (ok && row_ok) {
-            const int c0 = n0 + half * 64;
+            const int c0 = n0 + cgrp * 32;
             if (p.out_dtype == LH_F32) {
                 float* out = static_cast<float*>(p.c) + row * p.N + c0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
+                for (int j = 0; j < 16; ++j) {
                     if (c0 + 2 * j < p.N) out[2 * j] = acc[j].x;
                     if (c0 + 2 * j + 1 < p.N) out[2 * j + 1] = acc[j].y;
                 }
@@ -256,7 +240,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 uint16_t* out = static_cast<uint16_t*>(p.c) + row * p.N + c0;
                 const bool vec = (p.N % 8) == 0;
 #pragma unroll
-                for (int j8 = 0; j8 < 8; ++j8) {                 // 8 columns per step
+                for (int j8 = 0; j8 < 4; ++j8) {                 // 8 columns per step
                     uint32_t w[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
