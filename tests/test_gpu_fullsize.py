@@ -242,3 +242,34 @@ def test_cfg5_scaleout_shard_65536x8192():
         rq, rs, _, _ = O.silu_and_block_quant_forward(rows, False)
         assert_scales_close(s[:, blk * 128:(blk + 1) * 128], rs, "row scale")
         assert_codes_close(q[blk * 128:(blk + 1) * 128], rq, "row codes")
+
+
+# ------------------------------------------------------------------------------------
+# blockwise-scaled FP8 GEMM at the upstream test's size: an input family whose result is exact
+# ------------------------------------------------------------------------------------
+def test_fp8_gemm_exact_integers_4096():
+    """Codes drawn from small integers and power-of-two scales: every product, every partial sum
+    and every scaled accumulation is exactly representable in float32, so the kernel must match
+    an integer computation bit for bit whatever the summation order."""
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    M = N = K = 4096
+    g = torch.Generator().manual_seed(77)
+    a = torch.randint(-2, 3, (M, K), generator=g, dtype=torch.int32)
+    b = torch.randint(-2, 3, (N, K), generator=g, dtype=torch.int32)
+    ea = torch.randint(-1, 2, (M, K // 128), generator=g)
+    eb = torch.randint(-1, 2, (N, K // 128), generator=g)
+    a_s, b_s = torch.exp2(ea.float()), torch.exp2(eb.float())
+    dev = "cuda:0"
+    y = triton_tt_fp8_gemm(a.float().to(torch.float8_e4m3fn).to(dev), b.float().to(torch.float8_e4m3fn).to(dev),
+                           a_s.to(dev), b_s.to(dev), out_dtype=torch.float32, block_size=128)
+    # exact reference on the same device in float64 (|partial| <= 512, scale products 2^-2..2^2, 32 blocks:
+    # every value is a multiple of 1/4 below 2^16, far inside float32's 24 bits)
+    ad = (a.double().view(M, K // 128, 128) * a_s.double()[:, :, None]).view(M, K).to(dev)
+    bd = (b.double().view(N, K // 128, 128) * b_s.double()[:, :, None]).view(N, K).to(dev)
+    ref = ad @ bd.t()
+    assert torch.equal(y.double(), ref), f"max abs diff {(y.double() - ref).abs().max().item()}"
+    # transposed-scale entry gives the identical result
+    yt = triton_tt_fp8_gemm(a.float().to(torch.float8_e4m3fn).to(dev), b.float().to(torch.float8_e4m3fn).to(dev),
+                            a_s.t().contiguous().to(dev), b_s.t().contiguous().to(dev), out_dtype=torch.float32,
+                            block_size=128, scales_transposed=True)
+    assert torch.equal(yt, y)
