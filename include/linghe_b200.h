@@ -216,6 +216,26 @@ int lh_batch_silu_blockquant_bwd(const void* g, const void* x, const void* w, in
                                  void* dx_q, float* dx_s, void* dw, void* dx_qt, float* dx_st,
                                  int round_scale, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* ---- routing helpers around the permute + quantise step --------------------------- */
+
+/* Destination row of every routed (token, expert) pair with each expert padded to a multiple of
+ * `multiple_of` rows, and the inverse list of source tokens.
+ * Replaces triton_make_row_id_map_and_index, linghe/utils/gather.py:161.
+ * routing_map [tokens, experts]: 1-byte (bool) elements, or int32 when map_is_i32 != 0.
+ * row_id_map [tokens, experts] int32 (-1 = not routed); row_index [sum of padded counts] int32: written
+ * for real rows only (the caller zero-fills it, as the reference does).
+ * scratch: lh_scratch_bytes("row_id_map", tokens, experts) bytes. */
+int lh_make_row_id_map_and_index(const void* routing_map, int map_is_i32, int64_t tokens, int64_t experts,
+                                 int multiple_of, int32_t* row_id_map, int32_t* row_index, void* scratch,
+                                 int64_t scratch_bytes, void* stream);
+
+/* out[t] = sum over experts (in expert order, float32) of grad[row_id_map[t,e]]; prob_out[t,e] =
+ * probs[row_id_map[t,e]] or 0.  Replaces triton_unpermute_with_mask_map, linghe/utils/scatter.py:193.
+ * grad [rows, n] in `dtype`; probs / prob_out optional (both or neither), probs_dtype LH_F32 / LH_BF16. */
+int lh_unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_id_map, const void* probs,
+                               int probs_dtype, int64_t tokens, int64_t experts, int64_t n, void* out,
+                               void* prob_out, void* stream);
+
 /* ---- consumer of the wire format ------------------------------------------------- */
 
 /* Blockwise-scaled FP8 GEMM  c [M,N] = dequant(a) . dequant(b)^T.

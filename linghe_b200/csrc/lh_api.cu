@@ -105,6 +105,11 @@ int rows_norm_yq(const void* x, const void* gamma, int64_t M, int n, float eps, 
 int64_t router_gemm_scratch(int64_t N, int64_t K);
 int router_gemm(const void* x, const void* gamma, const void* w, const float* rms, float* logits, int64_t M, int64_t N,
                 int64_t K, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
+int64_t route_scratch_bytes(int64_t E);
+int make_row_id_map_and_index(const void* map, int map_is_i32, int64_t T, int64_t E, int multiple_of, int32_t* row_map,
+                              int32_t* row_index, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
+int unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_map, const void* probs, int probs_dtype,
+                            int64_t tokens, int64_t E, int64_t n, void* out, void* prob_out, cudaStream_t stream);
 int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
              int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
@@ -185,6 +190,7 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!strcmp(what, "rmsnorm_bwd")) return rows_norm_bwd_scratch(cols);
     if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
     if (!strcmp(what, "rmsnorm_bwd_static")) return 0;  // it carries its own
+    if (!strcmp(what, "row_id_map")) return route_scratch_bytes(cols);          // cols = experts
     if (!strcmp(what, "rmsnorm_gemm")) return router_gemm_scratch(rows, cols);   // rows = N, cols = K
     return -1;
 }
@@ -266,6 +272,20 @@ int lh_rmsnorm_gemm_blockquant_fwd(const void* x, const void* gamma, const void*
     if (!aligned16(y) || !aligned16(q)) return fail_arg("rmsnorm_gemm_blockquant_fwd: pointers must be 16-byte aligned");
     if (int rc = rows_norm_yq(x, gamma, M, int(K), eps, y, q, s, rms, round_scale, cs)) return rc;
     return router_gemm(x, gamma, route_w, rms, logits, M, N, K, scratch, scratch_bytes, cs);
+}
+
+int lh_make_row_id_map_and_index(const void* routing_map, int map_is_i32, int64_t tokens, int64_t experts,
+                                 int multiple_of, int32_t* row_id_map, int32_t* row_index, void* scratch,
+                                 int64_t scratch_bytes, void* stream) {
+    return make_row_id_map_and_index(routing_map, map_is_i32, tokens, experts, multiple_of, row_id_map, row_index,
+                                     scratch, scratch_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int lh_unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_id_map, const void* probs,
+                               int probs_dtype, int64_t tokens, int64_t experts, int64_t n, void* out,
+                               void* prob_out, void* stream) {
+    return unpermute_with_mask_map(grad, dtype, row_id_map, probs, probs_dtype, tokens, experts, n, out, prob_out,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 int lh_fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,

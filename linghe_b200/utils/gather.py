@@ -45,3 +45,29 @@ def triton_batch_block_pad_permute_with_indices(xs, token_count_per_expert, indi
               _lib.ptr(x_q), _lib.ptr(x_scale), _lib.ptr(xt_q), _lib.ptr(xt_scale), _lib.ptr(prob_output),
               int(bool(round_scale)))
     return x_q, x_scale, xt_q, xt_scale, prob_output
+
+
+def triton_make_row_id_map_and_index(routing_map: torch.Tensor, num_out_tokens: int, multiple_of: int = 1):
+    """Destination rows of a routing map with per-expert padding (linghe/utils/gather.py:161).
+
+    routing_map [n_tokens, n_experts] (bool / uint8 / int32); num_out_tokens = sum over experts
+    of the token count rounded up to `multiple_of`.
+    Returns (row_id_map [n_tokens, n_experts] int32: row of the token in the permuted output or
+    -1; row_indices [num_out_tokens] int32: source token of every output row, 0 in padding rows)."""
+    assert routing_map.is_contiguous()
+    n_tokens, n_experts = routing_map.shape
+    device = routing_map.device
+    if routing_map.dtype in (torch.bool, torch.uint8, torch.int8):
+        is_i32 = 0
+    else:
+        assert routing_map.dtype == torch.int32, f"unsupported routing map dtype {routing_map.dtype}"
+        is_i32 = 1
+    row_id_map = torch.empty((n_tokens, n_experts), dtype=torch.int32, device=device)
+    row_id_indices = torch.zeros((num_out_tokens,), dtype=torch.int32, device=device)
+    if n_tokens == 0:
+        return row_id_map, row_id_indices
+    nbytes = _lib.scratch_bytes("row_id_map", n_tokens, n_experts)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    _lib.call("lh_make_row_id_map_and_index", routing_map, _lib.ptr(routing_map), is_i32, n_tokens, n_experts,
+              int(multiple_of), _lib.ptr(row_id_map), _lib.ptr(row_id_indices), _lib.ptr(scratch), nbytes)
+    return row_id_map, row_id_indices

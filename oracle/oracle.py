@@ -343,3 +343,47 @@ def batch_block_pad_permute_with_indices(x, indices, probs, counts, round_scale:
         return z8, torch.empty(0), z8.clone(), torch.empty(0), torch.empty(0)
     return (torch.cat(qs), torch.cat(ss), torch.cat(qts), torch.cat(sts),
             torch.cat(ps) if probs is not None else None)
+
+
+# --------------------------------------------------------------------------- #
+# routing helpers around the permute step
+# --------------------------------------------------------------------------- #
+def make_row_id_map_and_index(route_map: torch.Tensor, multiple_of: int = 1):
+    """Destination row of every routed (token, expert) pair, experts padded to `multiple_of` rows.
+
+    For multiple_of = 1 this is ``torch_make_indices`` (linghe/tools/util.py:182-194): the
+    cumulative count over the expert-major flattening of the routing map, minus one, -1 where
+    not routed, and the expert-major list of routed tokens.  With padding each expert's first
+    row moves to the sum of the padded counts before it, as
+    ``make_row_id_map_and_index_kernel`` does (linghe/utils/gather.py:133-158); padding rows of
+    the index list stay 0.  Returns (row_id_map [T,E] int32, row_indices [sum padded] int32).
+    """
+    T, E = route_map.shape
+    rm = route_map.bool()
+    counts = rm.sum(0)
+    padded = (counts + multiple_of - 1) // multiple_of * multiple_of
+    starts = torch.cumsum(padded, 0) - padded
+    rank = torch.cumsum(rm.t().contiguous().int(), dim=1) - 1            # [E, T] rank inside the expert
+    row_map = (starts[:, None] + rank).t().contiguous()
+    row_map[~rm] = -1
+    index = torch.zeros(int(padded.sum().item()), dtype=torch.int32)
+    tok = torch.arange(T).unsqueeze(1).expand(T, E)
+    index[row_map[rm].long()] = tok[rm].int()
+    return row_map.int(), index
+
+
+def unpermute_with_mask_map(grad: torch.Tensor, row_id_map: torch.Tensor, probs=None):
+    """out[t] = float32 sum over the experts of token t of grad[row_id_map[t, e]] cast to grad.dtype,
+    restore_probs[t, e] = probs[row_id_map[t, e]] or 0 -- what ``unpermute_with_mask_map_kernel``
+    computes (linghe/utils/scatter.py:152-190)."""
+    T, E = row_id_map.shape
+    valid = row_id_map >= 0
+    idx = row_id_map.clamp_min(0).long()
+    g = grad.float()[idx] * valid[:, :, None]                            # [T, E, n]
+    out = torch.zeros((T, grad.shape[1]), dtype=torch.float32)
+    for e in range(E):                                                   # expert order, as the kernel
+        out += g[:, e]
+    rp = None
+    if probs is not None:
+        rp = torch.where(valid, probs[idx], torch.zeros((), dtype=probs.dtype))
+    return out.to(grad.dtype), rp

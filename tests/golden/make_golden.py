@@ -213,7 +213,17 @@ def main():
         out[f"y{B}_f32"] = f32(y)
         out[f"y{B}_bf16"] = u16(y.to(torch.bfloat16))
     np.savez_compressed(os.path.join(HERE, "fp8gemm.npz"), **out)
-    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm"):
+    # ---- routing map -> destination rows and source-token list (upstream torch_make_indices) ----
+    out = {}
+    logits = torch.randn((200, 8), generator=gen, dtype=torch.float32)
+    logits[:, 3] -= 1000                                  # an expert nobody picks
+    probs, route_map, counts, indices, row_id_map = U.torch_make_indices(logits, topk=2, bias=-0.01)
+    out["route_map"] = route_map.numpy().astype(np.uint8)
+    out["counts"] = counts.numpy().astype(np.int64)
+    out["indices"] = indices.numpy().astype(np.int64)
+    out["row_id_map"] = row_id_map.numpy().astype(np.int64)
+    np.savez_compressed(os.path.join(HERE, "route.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route"):
         p = os.path.join(HERE, f + ".npz")
         print(p, os.path.getsize(p))
 

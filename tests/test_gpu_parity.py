@@ -675,3 +675,94 @@ def test_fp8_gemm_errors():
         triton_tt_fp8_gemm(a, a, s[:, :1].contiguous(), s, block_size=128)
     with pytest.raises(AssertionError):
         triton_tt_fp8_gemm(a.to(torch.bfloat16), a, s, s)
+
+
+# ------------------------------------------------------------------------------------
+# routing helpers and the padded-permute facade
+# ------------------------------------------------------------------------------------
+def _route_map(T, E, topk, seed, empty=()):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn((T, E), generator=g)
+    for e in empty:
+        logits[:, e] -= 1000
+    top = torch.topk(logits, topk, dim=1).indices
+    rm = torch.zeros((T, E), dtype=torch.bool)
+    rm.scatter_(1, top, True)
+    return rm
+
+
+def test_golden_row_id_map():
+    from linghe_b200.utils.gather import triton_make_row_id_map_and_index
+    G = golden("route")
+    rm = torch.from_numpy(G["route_map"]).bool()
+    row_map, index = triton_make_row_id_map_and_index(_cuda(rm), int(G["counts"].sum()))
+    assert torch.equal(row_map.cpu().long(), torch.from_numpy(G["row_id_map"]))
+    assert torch.equal(index.cpu().long(), torch.from_numpy(G["indices"]))
+
+
+@pytest.mark.parametrize("T,E,topk,mult,dt", [(4098, 32, 2, 16, torch.bool), (8192, 256, 8, 16, torch.bool),
+                                              (777, 1500, 3, 1, torch.int32), (1, 8, 2, 16, torch.uint8)])
+def test_row_id_map_and_index(T, E, topk, mult, dt):
+    from linghe_b200.utils.gather import triton_make_row_id_map_and_index
+    rm = _route_map(T, E, topk, 81, empty=(1,))
+    ref_map, ref_index = O.make_row_id_map_and_index(rm, mult)
+    row_map, index = triton_make_row_id_map_and_index(_cuda(rm.to(dt)), ref_index.numel(), multiple_of=mult)
+    assert row_map.dtype == torch.int32 and index.dtype == torch.int32
+    assert torch.equal(row_map.cpu(), ref_map)
+    assert torch.equal(index.cpu(), ref_index)
+
+
+@pytest.mark.parametrize("T,E,topk,n,dt,with_probs", [(1024, 32, 2, 2048, torch.bfloat16, True),
+                                                      (300, 8, 3, 136, torch.float16, False),
+                                                      (257, 64, 8, 512, torch.float32, True)])
+def test_unpermute_with_mask_map(T, E, topk, n, dt, with_probs):
+    from linghe_b200.utils.scatter import triton_unpermute_with_mask_map
+    rm = _route_map(T, E, topk, 82)
+    row_map, index = O.make_row_id_map_and_index(rm, 16)
+    g = torch.Generator().manual_seed(83)
+    grad = torch.randn((index.numel(), n), generator=g).to(dt)
+    probs = torch.rand((index.numel(),), generator=g) if with_probs else None
+    ref, ref_p = O.unpermute_with_mask_map(grad, row_map, probs)
+    out, rp = triton_unpermute_with_mask_map(_cuda(grad), _cuda(row_map), _cuda(probs) if with_probs else None)
+    assert out.dtype == dt
+    assert torch.equal(out.cpu().view(torch.uint8), ref.contiguous().view(torch.uint8))   # same order of float32 sums
+    if with_probs:
+        assert torch.equal(rp.cpu(), ref_p)
+    else:
+        assert rp is None
+
+
+def test_facade_block_padded_permute():
+    import types
+    from linghe_b200.facade import permutation as P
+    T, E, topk, H = 2048, 32, 2, 1024
+    rm = _route_map(T, E, topk, 84, empty=(5,))
+    counts = rm.sum(0).tolist()
+    x = randn_bf16((T, H), 85)
+    probs = torch.rand((T, E), generator=torch.Generator().manual_seed(86)) * rm
+    ct = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    out, pp, row_map, row_index = P.block_padded_permute(_cuda(x), _cuda(rm), ct, counts, [_Quantizer()], _Box,
+                                                         probs=_cuda(probs))
+    ref_map, ref_index = O.make_row_id_map_and_index(rm, 16)
+    assert torch.equal(row_map.cpu(), ref_map) and torch.equal(row_index.cpu(), ref_index)
+    src = torch.cat([row_index.cpu()[s:s + c] for s, c in zip(np.cumsum([0] + [(c + 15) // 16 * 16 for c in counts[:-1]]), counts)])
+    rq, rs, rqt, rst, rp = O.batch_block_pad_permute_with_indices(x, src.long(), probs, counts, False)
+    assert_bits_equal(out.rowwise_data.reshape(-1), rq, "q")
+    assert_bits_equal(out.columnwise_data.reshape(-1)[:rqt.numel()], rqt, "qt")
+    assert_f32_equal(out.rowwise_scale_inv.reshape(-1)[:rs.numel()], rs, "s")
+    assert_f32_equal(pp.reshape(-1), rp, "probs")
+    # backward of the permute = un-permute of the incoming gradient
+    g = torch.Generator().manual_seed(87)
+    go = torch.randn((ref_index.numel(), H), generator=g).to(torch.bfloat16)
+    gp = torch.rand((ref_index.numel(),), generator=g)
+    ctx = types.SimpleNamespace(saved_tensors=(row_map,), shape=x.shape, prob_shape=probs.shape)
+    gx, gprob = P._BlockPaddedPermute.backward(ctx, _cuda(go), _cuda(gp), None, None)[:2]
+    rgx, rgp = O.unpermute_with_mask_map(go, ref_map, gp)
+    assert torch.equal(gx.cpu().view(torch.uint8), rgx.contiguous().view(torch.uint8)) and torch.equal(gprob.cpu(), rgp)
+    # un-permute facade: forward sums the experts' rows, backward permutes + quantises the gradient
+    y = P.block_padded_unpermute(_cuda(go), row_map, row_index, ct, counts, x.shape, [_Quantizer()], _Box)
+    assert torch.equal(y.cpu().view(torch.uint8), rgx.contiguous().view(torch.uint8))
+    ctx = types.SimpleNamespace(saved_tensors=(row_index,), tokens_per_expert=ct, splits=counts,
+                                quantizers=[_Quantizer()], cls=_Box)
+    gq = P._BlockPaddedUnpermute.backward(ctx, _cuda(x))[0]
+    assert_bits_equal(gq.rowwise_data.reshape(-1), rq, "unpermute bwd q")

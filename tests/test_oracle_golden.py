@@ -190,3 +190,38 @@ def test_tt_fp8_gemm(block):
     yb = O.tt_fp8_gemm(a_q, b_q, torch.from_numpy(G[f"a_s{block}"]), torch.from_numpy(G[f"b_s{block}"]),
                        torch.bfloat16, block)
     assert_rel_close(yb.float(), bf16(G[f"y{block}_bf16"]).float(), "y bf16", 1e-2)
+
+
+def test_row_id_map_and_unpermute():
+    G = golden("route")
+    rm = torch.from_numpy(G["route_map"]).bool()
+    row_map, index = O.make_row_id_map_and_index(rm, 1)
+    assert torch.equal(row_map.long(), torch.from_numpy(G["row_id_map"]))
+    assert torch.equal(index.long(), torch.from_numpy(G["indices"]))
+    # padded variant: same order inside every expert, experts start at multiples of 16
+    row16, index16 = O.make_row_id_map_and_index(rm, 16)
+    counts = G["counts"].tolist()
+    starts, s = [], 0
+    for c in counts:
+        starts.append(s)
+        s += (c + 15) // 16 * 16
+    assert index16.numel() == s
+    src = torch.from_numpy(G["indices"])
+    off = 0
+    for e, c in enumerate(counts):
+        assert torch.equal(index16[starts[e]:starts[e] + c].long(), src[off:off + c])
+        assert index16[starts[e] + c:starts[e] + (c + 15) // 16 * 16].abs().sum() == 0
+        off += c
+    t = torch.arange(rm.shape[0]).unsqueeze(1).expand_as(rm)
+    assert torch.equal(index16[row16[rm].long()].long(), t[rm])
+    # un-permute is the adjoint of the gather
+    g = torch.randn((s, 32), generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    p = torch.rand((s,), generator=torch.Generator().manual_seed(4))
+    out, rp = O.unpermute_with_mask_map(g, row16, p)
+    ref = torch.zeros((rm.shape[0], 32))
+    for tok in range(rm.shape[0]):
+        for e in range(rm.shape[1]):
+            if rm[tok, e]:
+                ref[tok] += g[row16[tok, e]].float()
+    assert torch.equal(out, ref.to(torch.bfloat16))
+    assert torch.equal(rp[rm], p[row16[rm].long()]) and rp[~rm].abs().sum() == 0
