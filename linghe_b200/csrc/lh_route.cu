@@ -131,53 +131,83 @@ template <> struct Chunk<float> {
 
 // out[t, :] = sum over the experts of token t (in expert order) of grad[row_map[t, e], :],
 // accumulated in float32; prob_out[t, e] = probs[row_map[t, e]] or 0.
+// One warp per token: the lanes compact the token's valid rows into a shared list (ballot),
+// then walk the rows with 16 independent 16-byte loads per lane in flight.
 template <typename T>
 __global__ void __launch_bounds__(256)
 unpermute_kernel(const uint8_t* __restrict__ grad, const int32_t* __restrict__ row_map, const void* __restrict__ probs,
                  int probs_dtype, int64_t tokens, int E, int64_t n, uint8_t* __restrict__ out,
                  void* __restrict__ prob_out) {
-    extern __shared__ int32_t rows[];        // valid destination rows of this token, in expert order
-    __shared__ int nvalid;
-    for (int64_t t = blockIdx.x; t < tokens; t += gridDim.x) {
-        __syncthreads();
-        if (threadIdx.x == 0) nvalid = 0;
-        __syncthreads();
-        // ordered compaction: one warp walks the experts 32 at a time
-        if (threadIdx.x < 32) {
-            int cnt = 0;
-            for (int base = 0; base < E; base += 32) {
-                const int e = base + threadIdx.x;
-                const int r = e < E ? row_map[t * E + e] : -1;
-                const unsigned m = __ballot_sync(0xffffffffu, r >= 0);
-                if (r >= 0) rows[cnt + __popc(m & ((1u << threadIdx.x) - 1u))] = r;
-                cnt += __popc(m);
+    extern __shared__ int32_t lists[];       // [warps][E] valid destination rows, in expert order
+    constexpr int EB = Chunk<T>::EB, VEC = Chunk<T>::VEC;
+    constexpr int CPL = 4, RU = 4;           // 16-byte chunks per lane and pass; rows fetched together
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    int32_t* rows = lists + warp * E;
+    const int64_t chunks = n / VEC;
+    for (int64_t t = int64_t(blockIdx.x) * warps + warp; t < tokens; t += int64_t(gridDim.x) * warps) {
+        int nv = 0;
+        for (int base = 0; base < E; base += 32 * 8) {           // 8 independent map loads per lane, then the ballots
+            int r[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int e = base + 32 * k + lane;
+                r[k] = e < E ? row_map[t * E + e] : -1;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const int e = base + 32 * k + lane;
+                const unsigned m = __ballot_sync(0xffffffffu, r[k] >= 0);
+                if (r[k] >= 0) rows[nv + __popc(m & ((1u << lane) - 1u))] = r[k];
+                nv += __popc(m);
                 if (prob_out != nullptr && e < E) {
                     if (probs_dtype == LH_BF16) {
                         reinterpret_cast<__nv_bfloat16*>(prob_out)[t * E + e] =
-                            r >= 0 ? reinterpret_cast<const __nv_bfloat16*>(probs)[r] : __float2bfloat16_rn(0.f);
+                            r[k] >= 0 ? reinterpret_cast<const __nv_bfloat16*>(probs)[r[k]] : __float2bfloat16_rn(0.f);
                     } else {
-                        reinterpret_cast<float*>(prob_out)[t * E + e] = r >= 0 ? reinterpret_cast<const float*>(probs)[r] : 0.f;
+                        reinterpret_cast<float*>(prob_out)[t * E + e] =
+                            r[k] >= 0 ? reinterpret_cast<const float*>(probs)[r[k]] : 0.f;
                     }
                 }
             }
-            if (threadIdx.x == 0) nvalid = cnt;
         }
-        __syncthreads();
-        const int nv = nvalid;
-        constexpr int EB = Chunk<T>::EB, VEC = Chunk<T>::VEC;  // elements per 16-byte chunk
-        for (int64_t c = threadIdx.x; c < n / VEC; c += blockDim.x) {
-            float acc[VEC];
+        __syncwarp();
+        for (int64_t c0 = 0; c0 < chunks; c0 += 32 * CPL) {      // 128 chunks (2 KB) of the row per pass
+            float acc[CPL][VEC];
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) acc[j] = 0.f;
-            for (int i = 0; i < nv; ++i) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(grad + (int64_t(rows[i]) * n + c * VEC) * EB);
-                float v[VEC];
-                Chunk<T>::unpack(raw, v);
+            for (int k = 0; k < CPL; ++k)
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) acc[j] += v[j];
+                for (int j = 0; j < VEC; ++j) acc[k][j] = 0.f;
+            for (int i0 = 0; i0 < nv; i0 += RU) {                // RU rows' loads in flight together
+                uint4 raw[RU][CPL];
+#pragma unroll
+                for (int u = 0; u < RU; ++u) {
+                    const bool on = i0 + u < nv;
+                    const uint8_t* src = grad + (int64_t(on ? rows[i0 + u] : 0) * n + c0 * VEC) * EB;
+#pragma unroll
+                    for (int k = 0; k < CPL; ++k) {
+                        const int64_t c = c0 + k * 32 + lane;
+                        raw[u][k] = (on && c < chunks) ? *reinterpret_cast<const uint4*>(src + (k * 32 + lane) * 16)
+                                                       : make_uint4(0, 0, 0, 0);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < RU; ++u) {                   // rows are added in list order
+#pragma unroll
+                    for (int k = 0; k < CPL; ++k) {
+                        float v[VEC];
+                        Chunk<T>::unpack(raw[u][k], v);
+#pragma unroll
+                        for (int j = 0; j < VEC; ++j) acc[k][j] += v[j];
+                    }
+                }
             }
-            *reinterpret_cast<uint4*>(out + (t * n + c * VEC) * EB) = Chunk<T>::pack(acc);
+#pragma unroll
+            for (int k = 0; k < CPL; ++k) {
+                const int64_t c = c0 + k * 32 + lane;
+                if (c < chunks) *reinterpret_cast<uint4*>(out + (t * n + c * VEC) * EB) = Chunk<T>::pack(acc[k]);
+            }
         }
+        __syncwarp();
     }
 }
 
@@ -217,19 +247,24 @@ int unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_map,
     if ((n * eb) % 16 != 0) return fail_arg("unpermute_with_mask_map: row length must be a multiple of 16 bytes");
     if ((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(out)) & 15)
         return fail_arg("unpermute_with_mask_map: pointers must be 16-byte aligned");
-    int64_t grid = tokens < 148 * 16 ? tokens : 148 * 16;
-    const size_t smem = size_t(E) * 4;
+    int warps = 8;
+    while (warps > 1 && size_t(warps) * size_t(E) * 4 > 48 * 1024) warps >>= 1;
+    const size_t smem = size_t(warps) * size_t(E) * 4;
+    if (smem > 48 * 1024) return fail_arg("unpermute_with_mask_map: too many experts (%lld)", (long long)E);
+    int64_t grid = (tokens + warps - 1) / warps;
+    if (grid > int64_t(sm_count()) * 16) grid = int64_t(sm_count()) * 16;
     const uint8_t* g = static_cast<const uint8_t*>(grad);
     uint8_t* o = static_cast<uint8_t*>(out);
+    const dim3 blk(unsigned(warps * 32));
     switch (dtype) {
         case LH_BF16:
-            unpermute_kernel<__nv_bfloat16><<<unsigned(grid), 256, smem, stream>>>(g, row_map, probs, probs_dtype, tokens, int(E), n, o, prob_out);
+            unpermute_kernel<__nv_bfloat16><<<unsigned(grid), blk, smem, stream>>>(g, row_map, probs, probs_dtype, tokens, int(E), n, o, prob_out);
             break;
         case LH_F16:
-            unpermute_kernel<__half><<<unsigned(grid), 256, smem, stream>>>(g, row_map, probs, probs_dtype, tokens, int(E), n, o, prob_out);
+            unpermute_kernel<__half><<<unsigned(grid), blk, smem, stream>>>(g, row_map, probs, probs_dtype, tokens, int(E), n, o, prob_out);
             break;
         case LH_F32:
-            unpermute_kernel<float><<<unsigned(grid), 256, smem, stream>>>(g, row_map, probs, probs_dtype, tokens, int(E), n, o, prob_out);
+            unpermute_kernel<float><<<unsigned(grid), blk, smem, stream>>>(g, row_map, probs, probs_dtype, tokens, int(E), n, o, prob_out);
             break;
         default:
             return fail_arg("unpermute_with_mask_map: unsupported dtype %d", dtype);

@@ -110,7 +110,7 @@ FLOPS = {}   # case name -> floating-point operations, for the GEMM rows
 
 def build_cases(mods):
     """name -> (make_args, callable, algorithmic bytes, ring bytes per set)"""
-    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute, router, gemm = mods
+    norm_q, rms_bwd, bq, silu_f, silu_b, wsilu_b, bsilu_f, bsilu_b, fused_bwd, permute, router, gemm, route = mods
     cases = {}
 
     def add(name, make_args, fn, nbytes, set_bytes=None):
@@ -153,12 +153,12 @@ def build_cases(mods):
         pe = rng.dirichlet(np.full(256, 0.3))
         gum = -np.log(-np.log(rng.random((8192, 256))))
         top = np.argsort(-(np.log(pe + 1e-30)[None, :] + gum), axis=1)[:, :8]
-        route = np.zeros((8192, 256), dtype=bool)
-        np.put_along_axis(route, top, True, axis=1)
-        pcounts = route.sum(0)
+        route_np = np.zeros((8192, 256), dtype=bool)
+        np.put_along_axis(route_np, top, True, axis=1)
+        pcounts = route_np.sum(0)
         idx_parts = []
         for e in range(256):
-            rows_e = np.nonzero(route[:, e])[0]
+            rows_e = np.nonzero(route_np[:, e])[0]
             padn = (-len(rows_e)) % 16
             idx_parts.append(np.concatenate([rows_e, np.zeros(padn, dtype=rows_e.dtype)]))
         pidx = torch.tensor(np.concatenate(idx_parts), dtype=torch.int32, device="cuda")
@@ -166,6 +166,14 @@ def build_cases(mods):
         Mp = int(pidx.numel())
         add(f"next pad-permute+quant 8192x2048 -> {Mp} rows both", lambda i: (bf16_randn((8192, 2048), i),),
             lambda x: permute(x, pct, pidx, pcounts.tolist()), Mp * 2048 * 4 + 2 * Mp * 2048 * 4 // 128)
+        if route is not None:
+            make_map, unpermute = route
+            rmap = torch.from_numpy(route_np).to("cuda")
+            add("next row-id map + index 8192 tokens x 256 experts", lambda i: (rmap,),
+                lambda m: make_map(m, Mp, multiple_of=16), 8192 * 256 * 5 + Mp * 4)
+            rid, _ = make_map(rmap, Mp, multiple_of=16)
+            add(f"next un-permute {Mp} rows -> 8192x2048", lambda i: (bf16_randn((Mp, 2048), i),),
+                lambda g: unpermute(g, rid, None), Mp * 2048 * 2 + 8192 * 2048 * 2 + 8192 * 256 * 4)
     # the step beside cfg1 in the MoE block: RMSNorm + float32 router logits (256 experts) + row quant
     if router is not None:
         M, K, N = 8192, 2048, 256
@@ -222,7 +230,19 @@ def ours():
             lambda g, x: triton_silu_and_block_quant_backward(g, x, return_bf16=True),
             triton_weighted_silu_backward, triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, rms_norm_backward_and_block_quant,
-            _ours_permute(), _ours_router(), _ours_gemm())
+            _ours_permute(), _ours_router(), _ours_gemm(), _ours_route())
+
+
+def _ours_route():
+    from linghe_b200.utils.gather import triton_make_row_id_map_and_index
+    from linghe_b200.utils.scatter import triton_unpermute_with_mask_map
+    return triton_make_row_id_map_and_index, triton_unpermute_with_mask_map
+
+
+def _upstream_route():
+    from linghe.utils.gather import triton_make_row_id_map_and_index
+    from linghe.utils.scatter import triton_unpermute_with_mask_map
+    return triton_make_row_id_map_and_index, triton_unpermute_with_mask_map
 
 
 def _ours_gemm():
@@ -259,7 +279,7 @@ def upstream(path):
             triton_silu_and_block_quant_forward, silu_b, triton_weighted_silu_backward,
             triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, fused_bwd, _upstream_permute(),
-            _upstream_router(), _upstream_gemm())
+            _upstream_router(), _upstream_gemm(), _upstream_route())
 
 
 def _upstream_gemm():
