@@ -43,7 +43,7 @@ def bf16_randn(gen, shape, power=1, coef=1.0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the upstream linghe checkout")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.path.insert(0, os.path.join(args.reference, "tests"))
