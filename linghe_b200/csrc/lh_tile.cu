@@ -265,6 +265,14 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
         for (int k = 0; k < C::NMAP; ++k) tma_prefetch_desc(&p.tmap[k]);
     }
+    // counts -> shared memory with one load per thread (a single round trip to L2), then
+    // warp 0 scans them from there
+    if (p.counts != nullptr) {
+        for (int e = tid; e < E; e += C::NTHREADS)
+            segC[e] = p.counts_i64 ? int(reinterpret_cast<const int64_t*>(p.counts)[e])
+                                   : reinterpret_cast<const int32_t*>(p.counts)[e];
+    }
+    __syncthreads();
     if (warp == 0) {
         if (p.counts == nullptr) {
             if (lane == 0) {
@@ -277,8 +285,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             const int e0 = lane * per;
             int64_t sumS = 0, sumB = 0;
             for (int e = e0; e < e0 + per && e < E; ++e) {
-                const int64_t c = p.counts_i64 ? reinterpret_cast<const int64_t*>(p.counts)[e]
-                                               : int64_t(reinterpret_cast<const int32_t*>(p.counts)[e]);
+                const int64_t c = segC[e];
                 sumS += p.pad16 ? ((c + 15) >> 4) << 4 : c;
                 sumB += (c + 127) >> 7;
             }
@@ -291,9 +298,8 @@ tile_kernel(const __grid_constant__ TileParams p) {
             }
             int64_t accS = preS - sumS, accB = preB - sumB;
             for (int e = e0; e < e0 + per && e < E; ++e) {
-                const int64_t c = p.counts_i64 ? reinterpret_cast<const int64_t*>(p.counts)[e]
-                                               : int64_t(reinterpret_cast<const int32_t*>(p.counts)[e]);
-                segS[e] = accS; segB[e] = int(accB); segC[e] = int(c);
+                const int64_t c = segC[e];
+                segS[e] = accS; segB[e] = int(accB);
                 accS += p.pad16 ? ((c + 15) >> 4) << 4 : c; accB += (c + 127) >> 7;
             }
             if (lane == 31) { segS[E] = preS; segB[E] = int(preB); }
