@@ -29,6 +29,7 @@ struct TileParams {
     const float* r;        // OP_NORM: 1/rms per row
     const void* gamma;     // OP_NORM: weight per column
     const void* counts;    // per-expert row counts (NULL = dense)
+    int rt_cap;            // entries of the row-tile -> expert table that fit in shared memory (0: none)
     int pad16;             // segments are padded to multiples of 16 rows (OP_GATHER)
     const uint8_t* gx;     // OP_GATHER: source matrix [m, n]
     const void* indices;   // OP_GATHER: source row of every padded output row
@@ -90,16 +91,23 @@ struct TileLoc {
     int e;       // segment (expert) index
 };
 
-__device__ __forceinline__ TileLoc locate(int tile, int col_tiles, const int64_t* segS, const int* segB,
-                                          int E) {
-    TileLoc t;
-    const int rt = tile / col_tiles;
-    t.ct = tile - rt * col_tiles;
+__device__ __forceinline__ int find_expert(int rt, const int* segB, int E) {
     int lo = 0, hi = E - 1;
     while (lo < hi) {  // smallest e with segB[e+1] > rt
         const int mid = (lo + hi) >> 1;
         if (segB[mid + 1] > rt) hi = mid; else lo = mid + 1;
     }
+    return lo;
+}
+
+// `tab` (optional): expert of every 128-row tile, filled once per CTA, so that the per-tile
+// lookup is one shared-memory read instead of a binary search
+__device__ __forceinline__ TileLoc locate(int tile, int col_tiles, const int64_t* segS, const int* segB,
+                                          int E, const uint16_t* tab = nullptr) {
+    TileLoc t;
+    const int rt = tile / col_tiles;
+    t.ct = tile - rt * col_tiles;
+    const int lo = tab != nullptr ? int(tab[rt]) : find_expert(rt, segB, E);
     t.e = lo;
     t.S = segS[lo];
     t.c = segS[lo + 1] - t.S;
@@ -307,6 +315,13 @@ tile_kernel(const __grid_constant__ TileParams p) {
     }
     __syncthreads();
 
+    const uint16_t* tab = nullptr;
+    if (E > 1 && segB[E] <= p.rt_cap) {
+        uint16_t* tw = reinterpret_cast<uint16_t*>(smem + ((C::OFF_SEG + 15) & ~15) + size_t(E + 1) * 16);
+        for (int rt = tid; rt < segB[E]; rt += C::NTHREADS) tw[rt] = uint16_t(find_expert(rt, segB, E));
+        tab = tw;
+        __syncthreads();
+    }
     const int col_tiles = int(p.n >> 7);
     const int64_t total_tiles = int64_t(segB[E]) * col_tiles;
     const int64_t nb = p.n >> 7;
@@ -317,7 +332,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
     // the matrix read as zero, rows of a following expert segment are masked by `valid`.
     auto issue = [&](int tile, int stage) {
         if constexpr (OP == OP_GATHER) return;   // gathered rows are loaded straight into registers
-        const TileLoc t = locate(tile, col_tiles, segS, segB, E);
+        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
         const int r0 = int(t.S + int64_t(t.T) * 128);
         const int c0 = t.ct * 128;
@@ -351,7 +366,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
         for (int s = 0; s < RPT; ++s) idx[s] = -1;           // -1: padding row (zeros) or no tile
         if (tile < 0) return;
-        const TileLoc tl = locate(tile, col_tiles, segS, segB, E);
+        const TileLoc tl = locate(tile, col_tiles, segS, segB, E, tab);
         const int cnt = segC[tl.e] - tl.T * 128 - row0;      // real (unpadded) rows left for this thread
         const int64_t g0 = tl.S + int64_t(tl.T) * 128 + row0;
 #pragma unroll
@@ -397,7 +412,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             const int64_t nxt = int64_t(tile) + int64_t(STAGES - 1) * gridDim.x;
             if (nxt < n_tiles && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(int(nxt), prev_stage);
         }
-        const TileLoc t = locate(tile, col_tiles, segS, segB, E);
+        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab);
         const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
         const int64_t gcol0 = int64_t(t.ct) * 128;        // column inside a half
         // Per-row and per-column side inputs come straight from global memory: fetch them
@@ -731,8 +746,20 @@ template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int C
 static int launch_tile(const TileParams& p, cudaStream_t stream) {
     using C = TileCfg<OP, InT, RPT, STAGES>;
     auto kern = tile_kernel<OP, InT, MODE, EXACT, RPT, STAGES, CTAS_PER_SM, WEIGHTED>;
-    const size_t smem = C::smem_bytes(p.E);
+    size_t smem = C::smem_bytes(p.E);
     if (smem > 227 * 1024) return fail_arg("too many experts for the shared-memory segment table (E=%d)", p.E);
+    TileParams pp = p;
+    pp.rt_cap = 0;
+    if (p.counts != nullptr && p.E > 1 && p.E < 65536) {   // room for the row-tile -> expert table?
+        const size_t budget = size_t(CTAS_PER_SM == 2 ? 113 : 227) * 1024;
+        int64_t want = (p.M + 127) / 128 + p.E;
+        if (smem + 16 < budget) {
+            const int64_t fit = int64_t((budget - smem - 16) / 2);
+            if (want > fit) want = 0;                       // does not fit: binary search per tile
+            pp.rt_cap = int(want);
+            smem += size_t(want) * 2 + 16;
+        }
+    }
     if (((p.M + 127) / 128 + p.E) * (p.n / 128) >= (int64_t(1) << 31)) return fail_arg("tensor too large: tile count exceeds 2^31");
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
@@ -743,7 +770,7 @@ static int launch_tile(const TileParams& p, cudaStream_t stream) {
         if (tiles < grid) grid = tiles;
     }
     if (grid <= 0) return LH_OK;
-    kern<<<dim3(unsigned(grid)), dim3(C::NTHREADS), smem, stream>>>(p);
+    kern<<<dim3(unsigned(grid)), dim3(C::NTHREADS), smem, stream>>>(pp);
     return check_launch("tile_kernel");
 }
 
