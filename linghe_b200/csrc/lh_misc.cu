@@ -29,31 +29,36 @@ __device__ __forceinline__ float load_w(const void* w, int w_bf16, int64_t row) 
                   : reinterpret_cast<const float*>(w)[row];
 }
 
-// one thread = 8 consecutive outputs
+// one thread = 8 consecutive outputs per step; (row, column group) advance by a fixed step, so
+// the only 64-bit division is the one that places the thread.  Same arithmetic as the fused
+// kernels: packed float32x2, sigmoid = rcp.approx(1 + ex2.approx(-x log2 e)).
 __global__ void __launch_bounds__(256)
 weighted_silu_fwd_kernel(const uint8_t* __restrict__ x, const void* __restrict__ w, int w_bf16, int64_t M,
                          int64_t n, uint8_t* __restrict__ y) {
-    const int64_t groups_per_row = n >> 3;
-    const int64_t total = M * groups_per_row;
-    for (int64_t gidx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; gidx < total;
-         gidx += int64_t(gridDim.x) * blockDim.x) {
-        const int64_t row = gidx / groups_per_row;
-        const int64_t col = (gidx - row * groups_per_row) << 3;
-        const uint4 r1 = *reinterpret_cast<const uint4*>(x + (row * 2 * n + col) * 2);
-        const uint4 r2 = *reinterpret_cast<const uint4*>(x + (row * 2 * n + n + col) * 2);
-        float x1[8], x2[8], o[8];
-        Elem<__nv_bfloat16>::unpack8(r1, x1);
-        Elem<__nv_bfloat16>::unpack8(r2, x2);
-        const bool has_w = w != nullptr;
-        const float wv = has_w ? load_w(w, w_bf16, row) : 1.f;
+    const int64_t gpr = n >> 3;                                   // 8-element groups per row
+    const int64_t step = int64_t(gridDim.x) * blockDim.x;
+    const int64_t dq = step / gpr, dr = step - dq * gpr;
+    const int64_t g0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    int64_t row = g0 / gpr, cg = g0 - row * gpr;
+    const bool has_w = w != nullptr;
+    for (; row < M;) {
+        const uint8_t* xr = x + (row * 2 * n + (cg << 3)) * 2;
+        const uint4 r1 = *reinterpret_cast<const uint4*>(xr);
+        const uint4 r2 = *reinterpret_cast<const uint4*>(xr + n * 2);
+        const float2 w2 = splat2(has_w ? load_w(w, w_bf16, row) : 1.f);
+        const uint32_t a1[4] = {r1.x, r1.y, r1.z, r1.w}, a2[4] = {r2.x, r2.y, r2.z, r2.w};
+        uint32_t o[4];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            float v = __fmul_rn(__fmul_rn(sigmoid_ref(x1[c]), x1[c]), x2[c]);
-            o[c] = has_w ? __fmul_rn(v, wv) : v;
+        for (int c = 0; c < 4; ++c) {
+            const float2 x1 = bf16x2_to_f2(a1[c]), x2 = bf16x2_to_f2(a2[c]);
+            float2 v = mul2(mul2(sigmoid_fast2(x1), x1), x2);
+            if (has_w) v = mul2(v, w2);
+            o[c] = pack_bf16x2(v.x, v.y);
         }
-        *reinterpret_cast<uint4*>(y + (row * n + col) * 2) =
-            make_uint4(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]), pack_bf16x2(o[4], o[5]),
-                       pack_bf16x2(o[6], o[7]));
+        *reinterpret_cast<uint4*>(y + (row * n + (cg << 3)) * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+        row += dq;
+        cg += dr;
+        if (cg >= gpr) { cg -= gpr; ++row; }
     }
 }
 
@@ -66,40 +71,38 @@ weighted_silu_bwd_kernel(const uint8_t* __restrict__ g, const uint8_t* __restric
     const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
     const bool has_w = w != nullptr;
     for (int64_t row = warp0; row < M; row += nwarps) {
-        const float wv = has_w ? load_w(w, w_bf16, row) : 1.f;
-        float acc = 0.f;
+        const float2 w2 = splat2(has_w ? load_w(w, w_bf16, row) : 1.f);
+        float2 acc = make_float2(0.f, 0.f);
         for (int64_t col = int64_t(lane) * 8; col < n; col += 256) {
             const uint4 rg = *reinterpret_cast<const uint4*>(g + (row * n + col) * 2);
             const uint4 r1 = *reinterpret_cast<const uint4*>(x + (row * 2 * n + col) * 2);
             const uint4 r2 = *reinterpret_cast<const uint4*>(x + (row * 2 * n + n + col) * 2);
-            float gg[8], x1[8], x2[8], d1[8], d2[8];
-            Elem<__nv_bfloat16>::unpack8(rg, gg);
-            Elem<__nv_bfloat16>::unpack8(r1, x1);
-            Elem<__nv_bfloat16>::unpack8(r2, x2);
+            const uint32_t ag[4] = {rg.x, rg.y, rg.z, rg.w}, a1[4] = {r1.x, r1.y, r1.z, r1.w}, a2[4] = {r2.x, r2.y, r2.z, r2.w};
+            uint32_t o1[4], o2[4];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float sg = sigmoid_ref(x1[c]);
-                const float sgg = sg * gg[c];
-                const float b2 = sgg * x1[c];
-                const float u = fmaf(x1[c], 1.f - sg, 1.f);
-                const float b1 = sgg * x2[c] * u;
-                acc = fmaf(b2, x2[c], acc);
-                d1[c] = has_w ? b1 * wv : b1;
-                d2[c] = has_w ? b2 * wv : b2;
+            for (int c = 0; c < 4; ++c) {
+                const float2 gg = bf16x2_to_f2(ag[c]), x1 = bf16x2_to_f2(a1[c]), x2 = bf16x2_to_f2(a2[c]);
+                const float2 sg = sigmoid_fast2(x1);
+                const float2 sgg = mul2(sg, gg);                                   // sigmoid * g
+                const float2 b2 = mul2(sgg, x1);                                   // d/dx2 (unweighted)
+                const float2 oms = fma2(sg, splat2(-1.f), splat2(1.f));            // 1 - sigmoid
+                const float2 u = fma2(x1, oms, splat2(1.f));
+                const float2 b1 = mul2(mul2(sgg, x2), u);                          // d/dx1 (unweighted)
+                acc = fma2(b2, x2, acc);
+                const float2 d1 = has_w ? mul2(b1, w2) : b1, d2 = has_w ? mul2(b2, w2) : b2;
+                o1[c] = pack_bf16x2(d1.x, d1.y);
+                o2[c] = pack_bf16x2(d2.x, d2.y);
             }
-            *reinterpret_cast<uint4*>(dx + (row * 2 * n + col) * 2) =
-                make_uint4(pack_bf16x2(d1[0], d1[1]), pack_bf16x2(d1[2], d1[3]), pack_bf16x2(d1[4], d1[5]),
-                           pack_bf16x2(d1[6], d1[7]));
-            *reinterpret_cast<uint4*>(dx + (row * 2 * n + n + col) * 2) =
-                make_uint4(pack_bf16x2(d2[0], d2[1]), pack_bf16x2(d2[2], d2[3]), pack_bf16x2(d2[4], d2[5]),
-                           pack_bf16x2(d2[6], d2[7]));
+            *reinterpret_cast<uint4*>(dx + (row * 2 * n + col) * 2) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+            *reinterpret_cast<uint4*>(dx + (row * 2 * n + n + col) * 2) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
         }
         if (has_w) {
+            float a = acc.x + acc.y;
 #pragma unroll
-            for (int d = 16; d >= 1; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+            for (int d = 16; d >= 1; d >>= 1) a += __shfl_xor_sync(0xffffffffu, a, d);
             if (lane == 0) {
-                if (w_bf16) reinterpret_cast<__nv_bfloat16*>(dw)[row] = __float2bfloat16_rn(acc);
-                else reinterpret_cast<float*>(dw)[row] = acc;
+                if (w_bf16) reinterpret_cast<__nv_bfloat16*>(dw)[row] = __float2bfloat16_rn(a);
+                else reinterpret_cast<float*>(dw)[row] = a;
             }
         }
     }

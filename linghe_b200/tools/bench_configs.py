@@ -135,6 +135,15 @@ def build_cases(mods):
     if silu_b is not None:
         add("cfg2 swiglu+quant bwd 8192x2816 (+bf16 dx)",
             lambda i: (bf16_randn((8192, 1408), 100 + i, 0.01), bf16_randn((8192, 2816), i)), silu_b, bw)
+    # a7: the plain (unquantised) weighted SwiGLU forward / backward at the cfg2 shape
+    if wsilu_b is not None:
+        wsf, wsb = wsilu_b
+        wrow2 = torch.randn((8192, 1), device="cuda")
+        add("cfg2 weighted swiglu fwd 8192x2816 (bf16 out)", lambda i: (bf16_randn((8192, 2816), i),),
+            lambda x: wsf(x, wrow2), M * 2 * n * 2 + M * n * 2 + M * 4)
+        add("cfg2 weighted swiglu bwd 8192x2816 (bf16 dx)",
+            lambda i: (bf16_randn((8192, 1408), 100 + i, 0.01), bf16_randn((8192, 2816), i)),
+            lambda g, x: wsb(g, x, wrow2), M * n * 2 + 2 * (M * 2 * n * 2) + 2 * M * 4)
     # cfg3: per-expert batched
     counts = moe_counts()
     R = int(counts.sum())
@@ -224,11 +233,12 @@ def ours():
     from linghe_b200.utils.silu import (triton_batch_weighted_silu_and_block_quant_backward,
                                         triton_batch_weighted_silu_and_block_quant_forward,
                                         triton_silu_and_block_quant_backward, triton_silu_and_block_quant_forward,
-                                        triton_weighted_silu_backward)
+                                        triton_weighted_silu_backward, triton_weighted_silu_forward)
     return (triton_rms_norm_and_block_quant_forward, triton_rms_norm_backward, triton_blockwise_quant,
             triton_silu_and_block_quant_forward,
             lambda g, x: triton_silu_and_block_quant_backward(g, x, return_bf16=True),
-            triton_weighted_silu_backward, triton_batch_weighted_silu_and_block_quant_forward,
+            (triton_weighted_silu_forward, triton_weighted_silu_backward),
+            triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, rms_norm_backward_and_block_quant,
             _ours_permute(), _ours_router(), _ours_gemm(), _ours_route())
 
@@ -267,7 +277,7 @@ def upstream(path):
     from linghe.utils.silu import (triton_batch_weighted_silu_and_block_quant_backward,
                                    triton_batch_weighted_silu_and_block_quant_forward,
                                    triton_silu_and_block_quant_backward, triton_silu_and_block_quant_forward,
-                                   triton_weighted_silu_backward)
+                                   triton_weighted_silu_backward, triton_weighted_silu_forward)
 
     def silu_b(g, x):  # upstream needs two passes for fp8 + bf16 dx
         return triton_silu_and_block_quant_backward(g, x), triton_weighted_silu_backward(g, x)
@@ -276,7 +286,7 @@ def upstream(path):
         return triton_rms_norm_backward(dy, x, w), triton_blockwise_quant(dy)
 
     return (triton_rms_norm_and_block_quant_forward, triton_rms_norm_backward, triton_blockwise_quant,
-            triton_silu_and_block_quant_forward, silu_b, triton_weighted_silu_backward,
+            triton_silu_and_block_quant_forward, silu_b, (triton_weighted_silu_forward, triton_weighted_silu_backward),
             triton_batch_weighted_silu_and_block_quant_forward,
             triton_batch_weighted_silu_and_block_quant_backward, fused_bwd, _upstream_permute(),
             _upstream_router(), _upstream_gemm(), _upstream_route())
