@@ -10,6 +10,8 @@
 
 namespace lh {
 
+constexpr int64_t kSmallRowElements = int64_t(24) << 20;   // output elements up to which the one-CTA-per-row kernels win (measured)
+
 __device__ int g_device_status = 0;
 
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
@@ -110,6 +112,11 @@ int make_row_id_map_and_index(const void* map, int map_is_i32, int64_t T, int64_
                               int32_t* row_index, void* scratch, int64_t scratch_bytes, cudaStream_t stream);
 int unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_map, const void* probs, int probs_dtype,
                             int64_t tokens, int64_t E, int64_t n, void* out, void* prob_out, cudaStream_t stream);
+int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, int scale_rowmajor,
+                      int round_scale, cudaStream_t stream);
+int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream);
+int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
+                     int round_scale, cudaStream_t stream);
 int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
              int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
@@ -185,6 +192,18 @@ int lh_device_status(int* status) {
     return LH_OK;
 }
 
+// Row-only outputs of small and medium problems go to the one-CTA-per-row kernels, large ones to
+// the persistent TMA-ring kernels.  LH_ROW_PATH=small|ring forces one of them (for measurements).
+static bool use_small_rows(int64_t elements) {
+    static const int forced = [] {
+        const char* e = getenv("LH_ROW_PATH");
+        if (!e) return 0;
+        return !strcmp(e, "small") ? 1 : (!strcmp(e, "ring") ? 2 : 0);
+    }();
+    if (forced) return forced == 1;
+    return elements <= kSmallRowElements;
+}
+
 int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!what) return -1;
     if (!strcmp(what, "rmsnorm_bwd")) return rows_norm_bwd_scratch(cols);
@@ -198,12 +217,18 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
 int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, void* qt, float* st,
                        int round_scale, int output_mode, void* stream) {
     if (output_mode < 0 || output_mode > 2) return fail_arg("blockwise_quant: output_mode must be 0, 1 or 2");
+    if (output_mode == 0 && dtype != LH_F32 && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) &&
+        aligned16(q) && use_small_rows(M * N))
+        return small_group_quant(x, dtype, M, N, q, s, 0, round_scale, static_cast<cudaStream_t>(stream));
     return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, qt, st, round_scale, output_mode, 0,
                       static_cast<cudaStream_t>(stream));
 }
 
 int lh_group_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
                    void* stream) {
+    if (dtype != LH_F32 && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) && aligned16(q) &&
+        use_small_rows(M * N))
+        return small_group_quant(x, dtype, M, N, q, s, 1, round_scale, static_cast<cudaStream_t>(stream));
     return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, nullptr, nullptr, round_scale, 0, 1,
                       static_cast<cudaStream_t>(stream));
 }
@@ -242,7 +267,13 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (!rms) return fail_arg("rmsnorm_blockquant_fwd: rms is NULL");
     if (output_mode == 0 || output_mode == 2) {
-        if (int rc = rows_norm_quant(x, gamma, dtype, M, n, eps, q, s, rms, round_scale, cs)) return rc;
+        const bool small = M > 0 && use_small_rows(M * n) && x && gamma && q && s && dtype == LH_BF16 && aligned16(x) &&
+                           aligned16(q) && aligned16(gamma);
+        if (small) {
+            if (int rc = small_norm_quant(x, gamma, M, n, eps, q, s, rms, round_scale, cs)) return rc;
+        } else if (int rc = rows_norm_quant(x, gamma, dtype, M, n, eps, q, s, rms, round_scale, cs)) {
+            return rc;
+        }
     }
     if (output_mode == 1 || output_mode == 2) {
         if (!qt || !st || !x || !gamma) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
@@ -333,7 +364,10 @@ int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void*
     if (!x || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("silu_blockquant_fwd: NULL or unaligned pointer");
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
-    if (output_mode == 0) return rows_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
+    if (output_mode == 0) {
+        if (use_small_rows(M * n)) return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
+        return rows_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
+    }
     return tile_silu_fwd(x, nullptr, LH_F32, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
                          static_cast<cudaStream_t>(stream));
 }

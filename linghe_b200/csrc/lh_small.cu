@@ -1,0 +1,204 @@
+// One-CTA-per-row kernels for the row-only outputs of small and medium problems.
+//
+// A persistent TMA ring (lh_rows.cu) reaches the copy bandwidth once every CTA streams dozens
+// of slabs, but a problem of a few tens of megabytes is over before the ring is in steady
+// state.  Here the grid is one small CTA (128 threads) per row: the hardware block scheduler
+// keeps up to 16 CTAs per SM in flight, each thread issues its loads at once, and nothing
+// is staged through shared memory.  Thread t owns 16 consecutive elements (two 16-byte
+// chunks) of every 2048-element span of its row, so a 1x128 block is 8 consecutive lanes.
+#include "lh_common.cuh"
+
+namespace lh {
+
+namespace {
+
+enum : int { SOP_GROUP = 0, SOP_NORM = 1, SOP_SILU = 2 };
+
+struct SmallParams {
+    const uint8_t* x;
+    const uint8_t* gamma;
+    int64_t M;
+    int n;              // output columns
+    float eps, inv_n;
+    uint8_t* q;         // [M, n] codes
+    float* s;           // scales: [M, n/128] when scale_rowmajor, else [n/128, M]
+    float* rms;         // SOP_NORM: [M] 1/rms (written)
+    int scale_rowmajor;
+    int round_scale;
+};
+
+template <typename InT>
+__device__ __forceinline__ void unpack8(const uint4& r, float2* v) {
+    if constexpr (std::is_same<InT, __half>::value) {
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    } else {
+        v[0] = bf16x2_to_f2(r.x); v[1] = bf16x2_to_f2(r.y); v[2] = bf16x2_to_f2(r.z); v[3] = bf16x2_to_f2(r.w);
+    }
+}
+
+// 16 values of one thread (half... an eighth of a 1x128 block) -> block scale -> 16 codes, stored
+template <bool EXACT>
+__device__ __forceinline__ void quant16(const SmallParams& p, int64_t row, int col, bool valid, float2* v) {
+    float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+        a0 = max3abs(v[j].x, v[j].y, a0);
+        a1 = max3abs(v[j + 1].x, v[j + 1].y, a1);
+    }
+    float amax = valid ? fmaxf(a0, a1) : 0.f;
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const float scale = scale_from_amax(amax, p.round_scale != 0);
+    if (!valid) return;
+    if constexpr (EXACT) {
+        if (scale < 8.0e-28f && amax > 0.f) {          // rare: residual of the exact quotient could underflow
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = make_float2(__fdiv_rn(v[j].x, scale), __fdiv_rn(v[j].y, scale));
+        } else {
+            const float y = __frcp_rn(scale);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float q0 = v[j].x * y, q1 = v[j].y * y;
+                v[j] = make_float2(fmaf(fmaf(scale, q0, -v[j].x), -y, q0), fmaf(fmaf(scale, q1, -v[j].y), -y, q1));
+            }
+        }
+    } else {
+        const float2 y2 = splat2(rcp_approx(scale));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = mul2(v[j], y2);
+    }
+    *reinterpret_cast<uint4*>(p.q + row * p.n + col) =
+        make_uint4(cvt_e4m3x4(v[0].x, v[0].y, v[1].x, v[1].y), cvt_e4m3x4(v[2].x, v[2].y, v[3].x, v[3].y),
+                   cvt_e4m3x4(v[4].x, v[4].y, v[5].x, v[5].y), cvt_e4m3x4(v[6].x, v[6].y, v[7].x, v[7].y));
+    if ((threadIdx.x & 7) == 0) {
+        const int b = col >> 7;
+        if (p.scale_rowmajor) p.s[row * (p.n >> 7) + b] = scale;
+        else p.s[int64_t(b) * p.M + row] = scale;
+    }
+}
+
+// SOP_GROUP / SOP_SILU: spans of 2048 output elements are independent
+template <int SOP, typename InT>
+__global__ void __launch_bounds__(128)
+small_stream_kernel(const __grid_constant__ SmallParams p) {
+    const int64_t row = blockIdx.x;
+    const int64_t in_row = SOP == SOP_SILU ? 2 * int64_t(p.n) : int64_t(p.n);
+    const uint8_t* xr = p.x + row * in_row * 2;
+    for (int c0 = 0; c0 < p.n; c0 += 2048) {
+        const int col = c0 + threadIdx.x * 16;
+        const bool valid = col < p.n;
+        uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
+        if (valid) {
+            a0 = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
+            a1 = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+            if constexpr (SOP == SOP_SILU) {
+                b0 = *reinterpret_cast<const uint4*>(xr + (int64_t(p.n) + col) * 2);
+                b1 = *reinterpret_cast<const uint4*>(xr + (int64_t(p.n) + col) * 2 + 16);
+            }
+        }
+        float2 v[8];
+        unpack8<InT>(a0, v);
+        unpack8<InT>(a1, v + 4);
+        if constexpr (SOP == SOP_SILU) {
+            float2 g[8];
+            unpack8<InT>(b0, g);
+            unpack8<InT>(b1, g + 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(sigmoid_fast2(v[j]), v[j]), g[j]);
+        }
+        quant16<SOP == SOP_GROUP>(p, row, col, valid, v);
+    }
+}
+
+// SOP_NORM: the row (n <= 2048 * SPANS) stays in registers as packed 16-bit words
+template <int SPANS>
+__global__ void __launch_bounds__(128, SPANS == 1 ? 8 : 1)
+small_norm_kernel(const __grid_constant__ SmallParams p) {
+    __shared__ float wsum[4];
+    const int64_t row = blockIdx.x;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const uint8_t* xr = p.x + row * int64_t(p.n) * 2;
+    uint4 raw[2 * SPANS], graw[2 * SPANS];
+#pragma unroll
+    for (int i = 0; i < SPANS; ++i) {
+        const int col = i * 2048 + t * 16;
+        raw[2 * i] = raw[2 * i + 1] = graw[2 * i] = graw[2 * i + 1] = make_uint4(0, 0, 0, 0);
+        if (col < p.n) {
+            raw[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
+            raw[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+            graw[2 * i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
+            graw[2 * i + 1] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+        }
+    }
+    float2 s0 = make_float2(0.f, 0.f), s1 = s0;
+#pragma unroll
+    for (int i = 0; i < 2 * SPANS; ++i) {
+        float2 v[4];
+        unpack8<__nv_bfloat16>(raw[i], v);
+        s0 = fma2(v[0], v[0], s0); s1 = fma2(v[1], v[1], s1);
+        s0 = fma2(v[2], v[2], s0); s1 = fma2(v[3], v[3], s1);
+    }
+    s0 = add2(s0, s1);
+    float ss = s0.x + s0.y;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+    if (lane == 0) wsum[warp] = ss;
+    __syncthreads();
+    const float tot = (wsum[0] + wsum[1]) + (wsum[2] + wsum[3]);
+    const float r = rsqrt_nr(fmaf(tot, p.inv_n, p.eps));
+    if (t == 0) p.rms[row] = r;
+    const float2 r2 = splat2(r);
+#pragma unroll
+    for (int i = 0; i < SPANS; ++i) {
+        const int col = i * 2048 + t * 16;
+        if (i * 2048 >= p.n) break;                       // uniform
+        float2 v[8], g[8];
+        unpack8<__nv_bfloat16>(raw[2 * i], v);
+        unpack8<__nv_bfloat16>(raw[2 * i + 1], v + 4);
+        unpack8<__nv_bfloat16>(graw[2 * i], g);
+        unpack8<__nv_bfloat16>(graw[2 * i + 1], g + 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(v[j], r2), g[j]);
+        quant16<false>(p, row, col, col < p.n, v);
+    }
+}
+
+}  // namespace
+
+int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, int scale_rowmajor,
+                      int round_scale, cudaStream_t stream) {
+    if (M > 0x7fffffff) return fail_arg("too many rows");
+    SmallParams p{};
+    p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.scale_rowmajor = scale_rowmajor; p.round_scale = round_scale;
+    if (dtype == LH_F16) small_stream_kernel<SOP_GROUP, __half><<<unsigned(M), 128, 0, stream>>>(p);
+    else small_stream_kernel<SOP_GROUP, __nv_bfloat16><<<unsigned(M), 128, 0, stream>>>(p);
+    return check_launch("small_stream_kernel");
+}
+
+int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream) {
+    if (M > 0x7fffffff) return fail_arg("too many rows");
+    SmallParams p{};
+    p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
+    small_stream_kernel<SOP_SILU, __nv_bfloat16><<<unsigned(M), 128, 0, stream>>>(p);
+    return check_launch("small_stream_kernel");
+}
+
+int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
+                     int round_scale, cudaStream_t stream) {
+    if (M > 0x7fffffff || n > 8192) return fail_arg("small_norm_quant: size out of range");
+    SmallParams p{};
+    p.x = static_cast<const uint8_t*>(x); p.gamma = static_cast<const uint8_t*>(gamma); p.M = M; p.n = int(n);
+    p.eps = eps; p.inv_n = 1.0f / float(n);
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.rms = rms; p.round_scale = round_scale;
+    if (n <= 2048) small_norm_kernel<1><<<unsigned(M), 128, 0, stream>>>(p);
+    else if (n <= 4096) small_norm_kernel<2><<<unsigned(M), 128, 0, stream>>>(p);
+    else small_norm_kernel<4><<<unsigned(M), 128, 0, stream>>>(p);
+    return check_launch("small_norm_kernel");
+}
+
+}  // namespace lh
