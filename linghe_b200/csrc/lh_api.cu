@@ -117,6 +117,8 @@ int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, f
 int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream);
 int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
                      int round_scale, cudaStream_t stream);
+int small_norm_y(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* y, float* rms, int reuse_rms,
+                 cudaStream_t stream);
 int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
              int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
@@ -194,6 +196,11 @@ int lh_device_status(int* status) {
 
 // Row-only outputs of small and medium problems go to the one-CTA-per-row kernels, large ones to
 // the persistent TMA-ring kernels.  LH_ROW_PATH=small|ring forces one of them (for measurements).
+// The one-CTA-per-row kernels give every thread 16 elements of each 2048-element span of the row:
+// rows that are a whole number of spans keep every thread busy, and then the streaming kernels
+// (SwiGLU+quant, plain norm) are ahead of the ring at every size (measured up to 65536 x 8192).
+static bool whole_spans(int64_t n) { return (n % 2048) == 0; }
+
 static bool use_small_rows(int64_t elements) {
     static const int forced = [] {
         const char* e = getenv("LH_ROW_PATH");
@@ -257,6 +264,9 @@ int lh_batch_block_pad_permute(const void* x, int dtype, const void* probs, int 
 
 int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
                    float* rms, int reuse_rms, void* stream) {
+    if (dtype == LH_BF16 && M > 0 && n > 0 && n <= 8192 && (n % 128) == 0 && x && gamma && y && (!reuse_rms || rms) &&
+        aligned16(x) && aligned16(y) && aligned16(gamma) && use_small_rows(whole_spans(n) ? 0 : M * n))
+        return small_norm_y(x, gamma, M, n, eps, y, rms, reuse_rms, static_cast<cudaStream_t>(stream));
     return rows_norm_y(x, gamma, dtype, M, n, eps, y, rms, reuse_rms, static_cast<cudaStream_t>(stream));
 }
 
@@ -365,7 +375,8 @@ int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void*
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
     if (output_mode == 0) {
-        if (use_small_rows(M * n)) return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
+        if (use_small_rows(whole_spans(n) ? 0 : M * n))
+            return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
         return rows_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
     }
     return tile_silu_fwd(x, nullptr, LH_F32, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
