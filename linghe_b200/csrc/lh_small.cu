@@ -126,16 +126,22 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
     const int64_t row = blockIdx.x;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const uint8_t* xr = p.x + row * int64_t(p.n) * 2;
-    uint4 raw[2 * SPANS], graw[2 * SPANS];
+    // gamma is fetched up front for narrow rows; for wide rows (4 spans) that would cost 32 more
+    // registers and a fifth of the resident warps, so it is read (from L1) when it is needed
+    constexpr bool GAMMA_EARLY = SPANS < 4;
+    uint4 raw[2 * SPANS], graw[GAMMA_EARLY ? 2 * SPANS : 2];
 #pragma unroll
     for (int i = 0; i < SPANS; ++i) {
         const int col = i * SPAN + t * 16;
-        raw[2 * i] = raw[2 * i + 1] = graw[2 * i] = graw[2 * i + 1] = make_uint4(0, 0, 0, 0);
+        raw[2 * i] = raw[2 * i + 1] = make_uint4(0, 0, 0, 0);
+        if constexpr (GAMMA_EARLY) graw[2 * i] = graw[2 * i + 1] = make_uint4(0, 0, 0, 0);
         if (col < p.n) {
             raw[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
             raw[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
-            graw[2 * i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
-            graw[2 * i + 1] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+            if constexpr (GAMMA_EARLY) {
+                graw[2 * i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
+                graw[2 * i + 1] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+            }
         }
     }
     float2 s0 = make_float2(0.f, 0.f), s1 = s0;
@@ -170,8 +176,18 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
         float2 v[8], g[8];
         unpack8<__nv_bfloat16>(raw[2 * i], v);
         unpack8<__nv_bfloat16>(raw[2 * i + 1], v + 4);
-        unpack8<__nv_bfloat16>(graw[2 * i], g);
-        unpack8<__nv_bfloat16>(graw[2 * i + 1], g + 4);
+        if constexpr (GAMMA_EARLY) {
+            unpack8<__nv_bfloat16>(graw[2 * i], g);
+            unpack8<__nv_bfloat16>(graw[2 * i + 1], g + 4);
+        } else {
+            uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
+            if (col < p.n) {
+                g0 = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
+                g1 = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+            }
+            unpack8<__nv_bfloat16>(g0, g);
+            unpack8<__nv_bfloat16>(g1, g + 4);
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(v[j], r2), g[j]);
         if constexpr (QUANT) {
