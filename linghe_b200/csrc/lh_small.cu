@@ -129,28 +129,53 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
     // gamma is fetched up front for narrow rows; for wide rows (4 spans) that would cost 32 more
     // registers and a fifth of the resident warps, so it is read (from L1) when it is needed
     constexpr bool GAMMA_EARLY = SPANS < 4;
-    uint4 raw[2 * SPANS], graw[GAMMA_EARLY ? 2 * SPANS : 2];
+    // Wide rows with the quantising epilogue: keeping the row in registers leaves room for only
+    // five CTAs per SM and the kernel waits on its own latency chain.  Instead the sum pass streams
+    // the row and the second pass reads it again -- the 16 KB row is still in L1 (no shared memory
+    // is used, so the whole 256 KB is cache) -- which halves the registers.
+    constexpr bool REREAD = QUANT && SPANS >= 4;
+    uint4 raw[REREAD ? 2 : 2 * SPANS], graw[GAMMA_EARLY ? 2 * SPANS : 2];
+    float2 s0 = make_float2(0.f, 0.f), s1 = s0;
+    if constexpr (REREAD) {
+        uint4 tmp[2 * SPANS];
 #pragma unroll
-    for (int i = 0; i < SPANS; ++i) {
-        const int col = i * SPAN + t * 16;
-        raw[2 * i] = raw[2 * i + 1] = make_uint4(0, 0, 0, 0);
-        if constexpr (GAMMA_EARLY) graw[2 * i] = graw[2 * i + 1] = make_uint4(0, 0, 0, 0);
-        if (col < p.n) {
-            raw[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
-            raw[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
-            if constexpr (GAMMA_EARLY) {
-                graw[2 * i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
-                graw[2 * i + 1] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+        for (int i = 0; i < SPANS; ++i) {
+            const int col = i * SPAN + t * 16;
+            tmp[2 * i] = tmp[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if (col < p.n) {
+                tmp[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
+                tmp[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
             }
         }
-    }
-    float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
-    for (int i = 0; i < 2 * SPANS; ++i) {
-        float2 v[4];
-        unpack8<__nv_bfloat16>(raw[i], v);
-        s0 = fma2(v[0], v[0], s0); s1 = fma2(v[1], v[1], s1);
-        s0 = fma2(v[2], v[2], s0); s1 = fma2(v[3], v[3], s1);
+        for (int i = 0; i < 2 * SPANS; ++i) {
+            float2 v[4];
+            unpack8<__nv_bfloat16>(tmp[i], v);
+            s0 = fma2(v[0], v[0], s0); s1 = fma2(v[1], v[1], s1);
+            s0 = fma2(v[2], v[2], s0); s1 = fma2(v[3], v[3], s1);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < SPANS; ++i) {
+            const int col = i * SPAN + t * 16;
+            raw[2 * i] = raw[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if constexpr (GAMMA_EARLY) graw[2 * i] = graw[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if (col < p.n) {
+                raw[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
+                raw[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+                if constexpr (GAMMA_EARLY) {
+                    graw[2 * i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
+                    graw[2 * i + 1] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) {
+            float2 v[4];
+            unpack8<__nv_bfloat16>(raw[i], v);
+            s0 = fma2(v[0], v[0], s0); s1 = fma2(v[1], v[1], s1);
+            s0 = fma2(v[2], v[2], s0); s1 = fma2(v[3], v[3], s1);
+        }
     }
     s0 = add2(s0, s1);
     float ss = s0.x + s0.y;
@@ -174,8 +199,18 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
         const int col = i * SPAN + t * 16;
         if (i * SPAN >= p.n) break;                       // uniform
         float2 v[8], g[8];
-        unpack8<__nv_bfloat16>(raw[2 * i], v);
-        unpack8<__nv_bfloat16>(raw[2 * i + 1], v + 4);
+        if constexpr (REREAD) {
+            raw[0] = raw[1] = make_uint4(0, 0, 0, 0);
+            if (col < p.n) {
+                raw[0] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
+                raw[1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+            }
+            unpack8<__nv_bfloat16>(raw[0], v);
+            unpack8<__nv_bfloat16>(raw[1], v + 4);
+        } else {
+            unpack8<__nv_bfloat16>(raw[2 * i], v);
+            unpack8<__nv_bfloat16>(raw[2 * i + 1], v + 4);
+        }
         if constexpr (GAMMA_EARLY) {
             unpack8<__nv_bfloat16>(graw[2 * i], g);
             unpack8<__nv_bfloat16>(graw[2 * i + 1], g + 4);
