@@ -116,7 +116,7 @@ int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, f
                       int round_scale, cudaStream_t stream);
 int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream);
 int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
-                     int round_scale, cudaStream_t stream);
+                     int round_scale, cudaStream_t stream, void* y = nullptr);
 int small_norm_y(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* y, float* rms, int reuse_rms,
                  cudaStream_t stream);
 int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
@@ -311,7 +311,11 @@ int lh_rmsnorm_gemm_blockquant_fwd(const void* x, const void* gamma, const void*
     }
     if (!y || !q || !s || !logits || !route_w) return fail_arg("rmsnorm_gemm_blockquant_fwd: NULL pointer");
     if (!aligned16(y) || !aligned16(q)) return fail_arg("rmsnorm_gemm_blockquant_fwd: pointers must be 16-byte aligned");
-    if (int rc = rows_norm_yq(x, gamma, M, int(K), eps, y, q, s, rms, round_scale, cs)) return rc;
+    if (use_small_rows(M * K)) {
+        if (int rc = small_norm_quant(x, gamma, M, K, eps, q, s, rms, round_scale, cs, y)) return rc;
+    } else if (int rc = rows_norm_yq(x, gamma, M, int(K), eps, y, q, s, rms, round_scale, cs)) {
+        return rc;
+    }
     return router_gemm(x, gamma, route_w, rms, logits, M, N, K, scratch, scratch_bytes, cs);
 }
 

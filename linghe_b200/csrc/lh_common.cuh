@@ -268,6 +268,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int co
     return mbar_wait_slow(bar, parity, code);
 }
 
+// Bounded wait without a function call: a call makes the compiler save every live register
+// around it, which costs spills where many values are live across the wait.
+__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, int code) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < (1u << 22); ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicCAS(&g_device_status, 0, code);
+    return false;
+}
+
 // global -> shared bulk copy, completion counted in bytes on `bar`.
 // src, dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {

@@ -67,14 +67,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
-// Bounded wait without a function call (a call would spill the accumulators around it).
-__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, int code) {
-#pragma unroll 1
-    for (uint32_t i = 0; i < (1u << 22); ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicCAS(&g_device_status, 0, code);
-    return false;
-}
 // One lane polls; the others then observe the completed phase with one try_wait of their own.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int code, int lane) {
     bool ok = true;

@@ -226,6 +226,13 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(v[j], r2), g[j]);
         if constexpr (QUANT) {
+            if (p.y != nullptr && col < p.n) {           // the 16-bit y as well (RMSNorm + router logits + quant)
+                uint8_t* yo = p.y + (row * p.n + col) * 2;
+                *reinterpret_cast<uint4*>(yo) = make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
+                                                           pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y));
+                *reinterpret_cast<uint4*>(yo + 16) = make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
+                                                                pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y));
+            }
             quant16<false>(p, row, col, col < p.n, v);
         } else if (col < p.n) {
             uint8_t* yo = p.y + (row * p.n + col) * 2;
@@ -269,13 +276,14 @@ int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int
     return check_launch("small_stream_kernel");
 }
 
+// y (optional, bf16 [M, n]) is written next to the codes when given
 int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
-                     int round_scale, cudaStream_t stream) {
+                     int round_scale, cudaStream_t stream, void* y) {
     if (M > 0x7fffffff || n > 8192) return fail_arg("small_norm_quant: size out of range");
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.gamma = static_cast<const uint8_t*>(gamma); p.M = M; p.n = int(n);
     p.eps = eps; p.inv_n = 1.0f / float(n);
-    p.q = static_cast<uint8_t*>(q); p.s = s; p.rms = rms; p.round_scale = round_scale;
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.rms = rms; p.round_scale = round_scale; p.y = static_cast<uint8_t*>(y);
     launch_small_norm<true>(p, stream);
     return check_launch("small_norm_kernel");
 }

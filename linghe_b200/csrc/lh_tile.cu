@@ -315,11 +315,16 @@ tile_kernel(const __grid_constant__ TileParams p) {
     }
     __syncthreads();
 
-    const uint16_t* tab = nullptr;
-    if (E > 1 && segB[E] <= p.rt_cap) {
-        uint16_t* tw = reinterpret_cast<uint16_t*>(smem + ((C::OFF_SEG + 15) & ~15) + size_t(E + 1) * 16);
+    // The table's presence is a predicate and its address is recomputed per tile, so that the
+    // dense instantiations do not carry a pointer through the main loop.
+    const bool has_tab = E > 1 && segB[E] <= p.rt_cap;
+    auto tab_ptr = [&]() -> const uint16_t* {
+        return has_tab ? reinterpret_cast<const uint16_t*>(smem + ((C::OFF_SEG + 15) & ~15) + size_t(E + 1) * 16)
+                       : nullptr;
+    };
+    if (has_tab) {
+        uint16_t* tw = const_cast<uint16_t*>(tab_ptr());
         for (int rt = tid; rt < segB[E]; rt += C::NTHREADS) tw[rt] = uint16_t(find_expert(rt, segB, E));
-        tab = tw;
         __syncthreads();
     }
     const int col_tiles = int(p.n >> 7);
@@ -332,7 +337,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
     // the matrix read as zero, rows of a following expert segment are masked by `valid`.
     auto issue = [&](int tile, int stage) {
         if constexpr (OP == OP_GATHER) return;   // gathered rows are loaded straight into registers
-        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab);
+        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab_ptr());
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
         const int r0 = int(t.S + int64_t(t.T) * 128);
         const int c0 = t.ct * 128;
@@ -361,12 +366,12 @@ tile_kernel(const __grid_constant__ TileParams p) {
     const bool rs = p.round_scale != 0;
 
     // ---- OP_GATHER: per-thread index registers and cp.async row fetches ----------------------
-    int gidx_cur[OP == OP_GATHER ? RPT : 1], gidx_next[OP == OP_GATHER ? RPT : 1];   // source rows fit 31 bits
+    int gidx_next[OP == OP_GATHER ? RPT : 1];   // source rows fit 31 bits
     auto gather_indices = [&](int tile, int* idx) {      // source rows of this thread's rows of `tile`
 #pragma unroll
         for (int s = 0; s < RPT; ++s) idx[s] = -1;           // -1: padding row (zeros) or no tile
         if (tile < 0) return;
-        const TileLoc tl = locate(tile, col_tiles, segS, segB, E, tab);
+        const TileLoc tl = locate(tile, col_tiles, segS, segB, E, tab_ptr());
         const int cnt = segC[tl.e] - tl.T * 128 - row0;      // real (unpadded) rows left for this thread
         const int64_t g0 = tl.S + int64_t(tl.T) * 128 + row0;
 #pragma unroll
@@ -376,9 +381,30 @@ tile_kernel(const __grid_constant__ TileParams p) {
                                        : reinterpret_cast<const int32_t*>(p.indices)[g0 + s];
         }
     };
+    // Also writes the gathered routing probabilities of the tile's rows (first column tile only),
+    // so that the indices need not stay in registers until the tile is processed.
     auto gather_issue = [&](int tile, const int* idx, int stg) {
         if (tile >= 0) {
             const int ct = tile % col_tiles;
+            if (p.prob_out != nullptr && ct == 0 && l16 == 0) {
+                const TileLoc tl = locate(tile, col_tiles, segS, segB, E, tab_ptr());
+                const int64_t g0 = tl.S + int64_t(tl.T) * 128 + row0;
+                const int nr = tl.valid - row0;
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    if (s < nr) {
+                        float pv = 0.f;
+                        if (idx[s] >= 0)
+                            pv = p.probs_dtype == LH_BF16
+                                     ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.probs)[int64_t(idx[s]) * E + tl.e])
+                                     : reinterpret_cast<const float*>(p.probs)[int64_t(idx[s]) * E + tl.e];
+                        if (p.probs_dtype == LH_BF16)
+                            reinterpret_cast<__nv_bfloat16*>(p.prob_out)[g0 + s] = __float2bfloat16_rn(pv);
+                        else
+                            reinterpret_cast<float*>(p.prob_out)[g0 + s] = pv;
+                    }
+                }
+            }
             uint8_t* dst = stages + size_t(stg) * C::STAGEB + row0 * C::ROWB + l16 * (8 * C::EB);
 #pragma unroll
             for (int s = 0; s < RPT; ++s) {
@@ -395,8 +421,8 @@ tile_kernel(const __grid_constant__ TileParams p) {
     };
     if constexpr (OP == OP_GATHER) {
         const int t0 = int(blockIdx.x);
-        gather_indices(t0 < n_tiles ? t0 : -1, gidx_cur);
-        gather_issue(t0 < n_tiles ? t0 : -1, gidx_cur, 0);
+        gather_indices(t0 < n_tiles ? t0 : -1, gidx_next);
+        gather_issue(t0 < n_tiles ? t0 : -1, gidx_next, 0);
         const int64_t t1 = int64_t(t0) + gridDim.x;
         gather_indices(t1 < n_tiles ? int(t1) : -1, gidx_next);
     }
@@ -412,7 +438,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             const int64_t nxt = int64_t(tile) + int64_t(STAGES - 1) * gridDim.x;
             if (nxt < n_tiles && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(int(nxt), prev_stage);
         }
-        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab);
+        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab_ptr());
         const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
         const int64_t gcol0 = int64_t(t.ct) * 128;        // column inside a half
         // Per-row and per-column side inputs come straight from global memory: fetch them
@@ -440,7 +466,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             gam[2] = bf16x2_to_f2(graw.z); gam[3] = bf16x2_to_f2(graw.w);
         }
         if constexpr (OP != OP_GATHER) {
-            if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+            if (!mbar_wait_inline(&full[stage], phase, DEVERR_FULL_WAIT)) return;
         }
         const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
 
@@ -456,26 +482,8 @@ tile_kernel(const __grid_constant__ TileParams p) {
             // cp.async during the previous iteration; now fetch the next tile with the indices
             // read one iteration ago, and read the indices of the tile after that.  Every
             // thread copies exactly the 16-byte chunks it later reads, so no barrier is needed.
-            if (p.prob_out != nullptr && t.ct == 0 && l16 == 0) {
-#pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    if (s < nrows) {
-                        float pv = 0.f;
-                        if (gidx_cur[s] >= 0)
-                            pv = p.probs_dtype == LH_BF16
-                                     ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.probs)[int64_t(gidx_cur[s]) * E + t.e])
-                                     : reinterpret_cast<const float*>(p.probs)[int64_t(gidx_cur[s]) * E + t.e];
-                        if (p.probs_dtype == LH_BF16)
-                            reinterpret_cast<__nv_bfloat16*>(p.prob_out)[grow0 + row0 + s] = __float2bfloat16_rn(pv);
-                        else
-                            reinterpret_cast<float*>(p.prob_out)[grow0 + row0 + s] = pv;
-                    }
-                }
-            }
             const int64_t t1 = int64_t(tile) + gridDim.x, t2 = t1 + gridDim.x;
             gather_issue(t1 < n_tiles ? int(t1) : -1, gidx_next, stage);            // `stage` already points at the next slot
-#pragma unroll
-            for (int s = 0; s < RPT; ++s) gidx_cur[s] = gidx_next[s];
             gather_indices(t2 < n_tiles ? int(t2) : -1, gidx_next);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         }
