@@ -207,7 +207,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
         if (warp == 0 && !first_it) {
             // every warp released the previous stage early in the previous iteration
             const int64_t nxt = slab + int64_t(STAGES - 1) * gridDim.x;
-            if (nxt < slabs && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
+            if (nxt < slabs && mbar_wait_inline(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
         }
         SlabLoc L = locate(slab);
         int slab_elems = L.rows * n;                       // valid elements in this slab
@@ -218,7 +218,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
             col0 = scolb * 128 + (t % LPB) * EPT;
         }
         const bool active = NORM ? (in_slab && my_row < L.rows) : (e0 < slab_elems);
-        if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+        if (!mbar_wait_inline(&full[stage], phase, DEVERR_FULL_WAIT)) return;
         const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
 
         float2 x[NP];

@@ -436,7 +436,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
             // the tile STAGES-1 steps ahead.  Copies issued here are consumed by this CTA, so
             // none is in flight when the loop ends.
             const int64_t nxt = int64_t(tile) + int64_t(STAGES - 1) * gridDim.x;
-            if (nxt < n_tiles && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(int(nxt), prev_stage);
+            if (nxt < n_tiles && mbar_wait_inline(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(int(nxt), prev_stage);
         }
         const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab_ptr());
         const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
@@ -466,7 +466,10 @@ tile_kernel(const __grid_constant__ TileParams p) {
             gam[2] = bf16x2_to_f2(graw.z); gam[3] = bf16x2_to_f2(graw.w);
         }
         if constexpr (OP != OP_GATHER) {
-            if (!mbar_wait_inline(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+            // Inline wait where a call would spill live registers around it; the transposed-only
+            // norm instantiation has none to spill and measures 2 % faster with the call.
+            if (!(OP == OP_NORM && MODE == 1 ? mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)
+                                             : mbar_wait_inline(&full[stage], phase, DEVERR_FULL_WAIT))) return;
         }
         const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
 
