@@ -198,7 +198,8 @@ int lh_device_status(int* status) {
 // the persistent TMA-ring kernels.  LH_ROW_PATH=small|ring forces one of them (for measurements).
 // The one-CTA-per-row kernels give every thread 16 elements of each 2048-element span of the row:
 // rows that are a whole number of spans keep every thread busy, and then the streaming kernels
-// (SwiGLU+quant, plain norm) are ahead of the ring at every size (measured up to 65536 x 8192).
+// (SwiGLU+quant, plain norm, the pure 1x128 quantiser) are ahead of the ring and tile kernels at
+// every size (measured up to 65536 x 8192).
 static bool whole_spans(int64_t n) { return (n % 2048) == 0; }
 
 static bool use_small_rows(int64_t elements) {
@@ -225,7 +226,7 @@ int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, 
                        int round_scale, int output_mode, void* stream) {
     if (output_mode < 0 || output_mode > 2) return fail_arg("blockwise_quant: output_mode must be 0, 1 or 2");
     if (output_mode == 0 && dtype != LH_F32 && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) &&
-        aligned16(q) && use_small_rows(M * N))
+        aligned16(q) && use_small_rows(whole_spans(N) ? 0 : M * N))
         return small_group_quant(x, dtype, M, N, q, s, 0, round_scale, static_cast<cudaStream_t>(stream));
     return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, qt, st, round_scale, output_mode, 0,
                       static_cast<cudaStream_t>(stream));
@@ -234,7 +235,7 @@ int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, 
 int lh_group_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
                    void* stream) {
     if (dtype != LH_F32 && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) && aligned16(q) &&
-        use_small_rows(M * N))
+        use_small_rows(whole_spans(N) ? 0 : M * N))
         return small_group_quant(x, dtype, M, N, q, s, 1, round_scale, static_cast<cudaStream_t>(stream));
     return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, nullptr, nullptr, round_scale, 0, 1,
                       static_cast<cudaStream_t>(stream));

@@ -201,6 +201,24 @@ __device__ __forceinline__ float2 bf16x2_to_f2(uint32_t w) {
     return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 
+// two bf16 packed in a word -> the NEGATED pair as float2.  Flipping the sign bit rides on the
+// widening itself: adding 2^31 to (w << 16) and xor-ing it into the masked high half are the
+// same integer instructions as the plain conversion, with one more constant operand.
+__device__ __forceinline__ float2 bf16x2_to_neg_f2(uint32_t w) {
+    return make_float2(__uint_as_float((w << 16) + 0x80000000u), __uint_as_float((w & 0xffff0000u) ^ 0x80000000u));
+}
+
+// Exact quotients, two at a time.  The pure quantisers keep the NEGATED inputs nv = -x in
+// registers (the negation is free in the load), so that the whole Markstein sequence runs on
+// packed instructions without a separate negation: with ny = -RN(1/s),
+//   q0 = nv * ny = x * y,   r' = s * q0 + nv = s*q0 - x (exact in an FMA),   q = r' * ny + q0.
+// This equals IEEE x / s bit for bit unless the residual underflows, which needs a scale below
+// ~2^-90, and the negated-residual form keeps the sign of a zero quotient (x = -0 gives -0).
+__device__ __forceinline__ float2 quot_exact2(float2 nv, float2 s, float2 ny) {
+    const float2 q0 = mul2(nv, ny);
+    const float2 r = fma2(s, q0, nv);
+    return fma2(r, ny, q0);
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

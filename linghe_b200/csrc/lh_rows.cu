@@ -15,10 +15,13 @@
 
 namespace lh {
 
+int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
+                   void* dx, float* partial, int max_parts, int* parts, cudaStream_t stream);
+
 enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3, ROP_NORM_YQ = 4 };
 
 constexpr int kSlabElems = 8192;
-constexpr int kMaxRowCtas = 296;
+constexpr int kMaxRowCtas = 444;   // three CTAs per SM at most
 
 struct RowParams {
     const uint8_t* x;
@@ -670,12 +673,36 @@ normq_kernel(const __grid_constant__ RowParams p) {
     if (lane == 0) bulk_wait_all();
 }
 
-__global__ void dgamma_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ out) {
-    const int j = blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= n) return;
-    float a = 0.f;
-    for (int b = 0; b < parts; ++b) a += partial[int64_t(b) * n + j];
-    out[j] = a;
+// dgamma[j] = sum over the per-CTA partial rows, added in a fixed order (deterministic).  One CTA
+// covers 128 columns: lane = 4 columns (one 16-byte load per partial row), the 32 warps split the
+// partial rows among themselves so that every thread has only a handful of independent loads,
+// and warp 0 then adds the 32 sub-sums.  A single thread walking all the rows would pay the
+// L2 latency dozens of times in a row.  n is a multiple of 128 and the scratch rows are
+// 16-byte aligned.
+__global__ void __launch_bounds__(1024)
+dgamma_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ out) {
+    __shared__ float4 red[32][32];
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int col = blockIdx.x * 128 + lane * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < n) {
+#pragma unroll 4
+        for (int b = grp; b < parts; b += 32) {
+            const float4 v = *reinterpret_cast<const float4*>(partial + int64_t(b) * n + col);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+    }
+    red[grp][lane] = a;
+    __syncthreads();
+    if (grp == 0 && col < n) {
+        float4 s = red[0][lane];
+#pragma unroll
+        for (int g = 1; g < 32; ++g) {
+            const float4 v = red[g][lane];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        out[col] = s.x; out[col + 1] = s.y; out[col + 2] = s.z; out[col + 3] = s.w;
+    }
 }
 
 // ------------------------------------------------------------------------------------
@@ -793,8 +820,13 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr; p.eps = eps; p.M = M; p.n = int(n);
     p.hp = static_cast<uint8_t*>(dx); p.partial = static_cast<float*>(scratch);
     int grid = 0;
-    if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream)) return rc;
-    dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(128), 0, stream>>>(p.partial, grid, int(n), dgamma);
+    const char* pe = getenv("LH_BWD_PATH");
+    if (pe != nullptr && !strcmp(pe, "small") && dtype == LH_BF16) {
+        if (int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, stream)) return rc;
+    } else if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream)) {
+        return rc;
+    }
+    dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(1024), 0, stream>>>(p.partial, grid, int(n), dgamma);
     return check_launch("dgamma_reduce_kernel");
 }
 
@@ -850,7 +882,7 @@ int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const
     // Every launched CTA overwrites its whole partial row [0, n) and the reduction reads only
     // the `grid` rows written by this call, so nothing in the array has to start at zero.
     if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream, kStaticCtas)) return rc;
-    dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(128), 0, stream>>>(partial, grid, int(n), dgamma);
+    dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(1024), 0, stream>>>(partial, grid, int(n), dgamma);
     return check_launch("dgamma_reduce_kernel");
 }
 

@@ -115,6 +115,100 @@ small_stream_kernel(const __grid_constant__ SmallParams p) {
     }
 }
 
+// Pure 1x128 quantiser (bit-exact).  A unit is one 2048-element span of one row; a CTA takes U
+// consecutive units and every thread issues the loads of all of them before it touches the
+// first, which is what keeps enough bytes in flight per SM when the whole problem is a few
+// waves of CTAs.  Values are held negated so that the exact quotients are packed instructions.
+template <typename InT>
+__device__ __forceinline__ void unpack8_neg(const uint4& r, float2* v) {
+    if constexpr (std::is_same<InT, __half>::value) {
+        const uint32_t w[4] = {r.x ^ 0x80008000u, r.y ^ 0x80008000u, r.z ^ 0x80008000u, r.w ^ 0x80008000u};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    } else {
+        v[0] = bf16x2_to_neg_f2(r.x); v[1] = bf16x2_to_neg_f2(r.y);
+        v[2] = bf16x2_to_neg_f2(r.z); v[3] = bf16x2_to_neg_f2(r.w);
+    }
+}
+
+template <int SOP, typename InT, int U>
+__global__ void __launch_bounds__(128)
+small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t units) {
+    constexpr bool SILU = SOP == SOP_SILU;
+    const int64_t u0 = int64_t(blockIdx.x) * U;
+    int64_t row = u0 / spans;
+    int span = int(u0 - row * spans);
+    const int64_t in_row = SILU ? 2 * int64_t(p.n) : int64_t(p.n);
+    uint4 raw[2 * U], rawb[SILU ? 2 * U : 1];
+    int64_t rows[U];
+    int cols[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+        rows[k] = row;
+        cols[k] = span * 2048 + threadIdx.x * 16;
+        raw[2 * k] = raw[2 * k + 1] = make_uint4(0, 0, 0, 0);
+        if constexpr (SILU) rawb[2 * k] = rawb[2 * k + 1] = make_uint4(0, 0, 0, 0);
+        if (u0 + k < units && cols[k] < p.n) {
+            const uint8_t* src = p.x + (row * in_row + cols[k]) * 2;
+            raw[2 * k] = *reinterpret_cast<const uint4*>(src);
+            raw[2 * k + 1] = *reinterpret_cast<const uint4*>(src + 16);
+            if constexpr (SILU) {
+                rawb[2 * k] = *reinterpret_cast<const uint4*>(src + int64_t(p.n) * 2);
+                rawb[2 * k + 1] = *reinterpret_cast<const uint4*>(src + int64_t(p.n) * 2 + 16);
+            }
+        } else {
+            cols[k] = p.n;   // nothing to do for this unit
+        }
+        if (++span == spans) { span = 0; ++row; }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+        float2 v[8];
+        const bool valid = cols[k] < p.n;
+        if constexpr (SILU) {
+            float2 g[8];
+            unpack8<InT>(raw[2 * k], v);
+            unpack8<InT>(raw[2 * k + 1], v + 4);
+            unpack8<InT>(rawb[2 * k], g);
+            unpack8<InT>(rawb[2 * k + 1], g + 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(sigmoid_fast2(v[j]), v[j]), g[j]);
+            quant16<false>(p, rows[k], cols[k], valid, v);
+        } else {
+            unpack8_neg<InT>(raw[2 * k], v);
+            unpack8_neg<InT>(raw[2 * k + 1], v + 4);
+            float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                a0 = max3abs(v[j].x, v[j].y, a0);
+                a1 = max3abs(v[j + 1].x, v[j + 1].y, a1);
+            }
+            float amax = fmaxf(a0, a1);                   // zeros where there is nothing
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            const float scale = scale_from_amax(amax, p.round_scale != 0);
+            if (!valid) continue;
+            if (scale < 8.0e-28f && amax > 0.f) {          // rare: residual of the exact quotient could underflow
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = make_float2(__fdiv_rn(-v[j].x, scale), __fdiv_rn(-v[j].y, scale));
+            } else {
+                const float2 s2 = splat2(scale), ny2 = splat2(-__frcp_rn(scale));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = quot_exact2(v[j], s2, ny2);
+            }
+            *reinterpret_cast<uint4*>(p.q + rows[k] * p.n + cols[k]) =
+                make_uint4(cvt_e4m3x4(v[0].x, v[0].y, v[1].x, v[1].y), cvt_e4m3x4(v[2].x, v[2].y, v[3].x, v[3].y),
+                           cvt_e4m3x4(v[4].x, v[4].y, v[5].x, v[5].y), cvt_e4m3x4(v[6].x, v[6].y, v[7].x, v[7].y));
+            if ((threadIdx.x & 7) == 0) {
+                const int b = cols[k] >> 7;
+                if (p.scale_rowmajor) p.s[rows[k] * (p.n >> 7) + b] = scale;
+                else p.s[int64_t(b) * p.M + rows[k]] = scale;
+            }
+        }
+    }
+}
+
 // SOP_NORM: the row (n <= 2048 * SPANS) stays in registers as packed 16-bit words
 // QUANT: codes + scales; otherwise the 16-bit y itself (plain RMSNorm forward).  NT threads
 // per row, thread t owns 16 consecutive elements of every span of 16*NT elements.
@@ -244,6 +338,127 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
     }
 }
 
+// RMSNorm backward, streaming: dx = r*g*gamma - r^3 * x * sum(x*g*gamma)/n, dgamma += x*g*r.
+// A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...; thread t owns 16 consecutive elements
+// of every span of 16*NT elements and keeps their dgamma sums in registers for the whole walk.
+// The loads of the next row are issued before the second pass over the current one, so every
+// resident CTA always has a row in flight.  Per-CTA sums go to partial[blockIdx.x][n]; a second
+// kernel adds them in a fixed order.
+template <int SPANS, int NT, int MINB>
+__global__ void __launch_bounds__(NT, MINB)
+small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
+    constexpr int SPAN = 16 * NT, NW = NT / 32;
+    __shared__ float wsum[2][2][NW];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    // gamma stays in registers for one span per thread; with two it is re-read (L1 hits) so that
+    // three CTAs fit an SM without spills
+    constexpr bool GAM_REG = SPANS == 1;
+    uint4 xr[2 * SPANS], gr[2 * SPANS], gam[GAM_REG ? 2 * SPANS : 1];
+    float2 acc[8 * SPANS];
+#pragma unroll
+    for (int i = 0; i < 8 * SPANS; ++i) acc[i] = make_float2(0.f, 0.f);
+    auto gamma_at = [&](int i) -> uint4 {     // i-th 16-byte chunk of this thread's gamma
+        if constexpr (GAM_REG) {
+            return gam[i];
+        } else {
+            const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
+            return col < p.n ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    if constexpr (GAM_REG) {
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) {
+            const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
+            gam[i] = col < p.n ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    auto fetch = [&](int64_t row) {
+#pragma unroll
+        for (int i = 0; i < SPANS; ++i) {
+            const int col = i * SPAN + t * 16;
+            xr[2 * i] = xr[2 * i + 1] = gr[2 * i] = gr[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if (row < p.M && col < p.n) {
+                const int64_t off = (row * p.n + col) * 2;
+                xr[2 * i] = *reinterpret_cast<const uint4*>(p.x + off);
+                xr[2 * i + 1] = *reinterpret_cast<const uint4*>(p.x + off + 16);
+                gr[2 * i] = *reinterpret_cast<const uint4*>(dy + off);
+                gr[2 * i + 1] = *reinterpret_cast<const uint4*>(dy + off + 16);
+            }
+        }
+    };
+    int64_t row = blockIdx.x;
+    fetch(row);
+    int par = 0;
+    for (; row < p.M; row += gridDim.x, par ^= 1) {
+        // pass 1: sum x^2 and sum x*g*gamma; keep the packed words, the floats are rebuilt in pass 2
+        float2 sc = make_float2(0.f, 0.f), ss = sc;
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) {
+            float2 x[4], g[4], w[4];
+            unpack8<__nv_bfloat16>(xr[i], x);
+            unpack8<__nv_bfloat16>(gr[i], g);
+            unpack8<__nv_bfloat16>(gamma_at(i), w);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                sc = fma2(x[j], mul2(g[j], w[j]), sc);
+                ss = fma2(x[j], x[j], ss);
+            }
+        }
+        float c = sc.x + sc.y, s = ss.x + ss.y;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) {
+            c += __shfl_xor_sync(0xffffffffu, c, d);
+            s += __shfl_xor_sync(0xffffffffu, s, d);
+        }
+        if (lane == 0) { wsum[par][0][warp] = c; wsum[par][1][warp] = s; }
+        __syncthreads();   // the buffer of the other parity was last read before the previous barrier
+        float ctot = 0.f, stot = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) { ctot += wsum[par][0][w]; stot += wsum[par][1][w]; }
+        const float r = p.reuse_rms ? p.rms[row] : rsqrt_nr(fmaf(stot, p.inv_n, p.eps));
+        const float2 ncoef = splat2(-(r * r * r * ctot * p.inv_n));
+        const float2 r2 = splat2(r);
+        // pass 2 on copies, so that the next row's loads can already land in xr / gr
+        uint4 xc[2 * SPANS], gc[2 * SPANS];
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) { xc[i] = xr[i]; gc[i] = gr[i]; }
+        fetch(row + gridDim.x);
+#pragma unroll
+        for (int i = 0; i < SPANS; ++i) {
+            const int col = i * SPAN + t * 16;
+            uint32_t o[8];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float2 x[4], g[4], w[4];
+                unpack8<__nv_bfloat16>(xc[2 * i + h], x);
+                unpack8<__nv_bfloat16>(gc[2 * i + h], g);
+                unpack8<__nv_bfloat16>(gamma_at(2 * i + h), w);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 d = fma2(ncoef, x[j], mul2(r2, mul2(g[j], w[j])));
+                    acc[8 * i + 4 * h + j] = fma2(mul2(x[j], g[j]), r2, acc[8 * i + 4 * h + j]);
+                    o[4 * h + j] = pack_bf16x2(d.x, d.y);
+                }
+            }
+            if (col < p.n) {
+                uint8_t* dst = p.y + (row * p.n + col) * 2;
+                *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < SPANS; ++i) {
+        const int col = i * SPAN + t * 16;
+        if (col < p.n) {
+            float4* dst = reinterpret_cast<float4*>(partial + int64_t(blockIdx.x) * p.n + col);
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                dst[k] = make_float4(acc[8 * i + 2 * k].x, acc[8 * i + 2 * k].y, acc[8 * i + 2 * k + 1].x, acc[8 * i + 2 * k + 1].y);
+        }
+    }
+}
+
 template <bool QUANT>
 static void launch_small_norm(const SmallParams& p, cudaStream_t stream) {
     const unsigned grid = unsigned(p.M);
@@ -262,9 +477,21 @@ int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, f
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.scale_rowmajor = scale_rowmajor; p.round_scale = round_scale;
-    if (dtype == LH_F16) small_stream_kernel<SOP_GROUP, __half><<<unsigned(M), 128, 0, stream>>>(p);
-    else small_stream_kernel<SOP_GROUP, __nv_bfloat16><<<unsigned(M), 128, 0, stream>>>(p);
-    return check_launch("small_stream_kernel");
+    const int spans = int((n + 2047) / 2048);
+    const int64_t units = M * spans;
+    // three units per CTA once the problem is many waves long (measured: 251 vs 259 us at
+    // 65536 x 8192), two below that (10.1 vs 10.8 us with one at 8192 x 2048)
+    const int U = M * n > (int64_t(96) << 20) ? 3 : 2;
+    const int64_t grid = (units + U - 1) / U;
+    if (grid > 0x7fffffff) return fail_arg("too many rows");
+    if (dtype == LH_F16) {
+        if (U == 3) small_units_kernel<SOP_GROUP, __half, 3><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+        else small_units_kernel<SOP_GROUP, __half, 2><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+    } else {
+        if (U == 3) small_units_kernel<SOP_GROUP, __nv_bfloat16, 3><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+        else small_units_kernel<SOP_GROUP, __nv_bfloat16, 2><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+    }
+    return check_launch("small_units_kernel");
 }
 
 int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream) {
@@ -272,6 +499,17 @@ int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
+    // Long runs over whole spans: two spans per CTA with all four loads of both issued up front
+    // (384 vs 393 us at 65536 x 16384).  Short runs and partly filled spans are faster with one
+    // CTA per row walking its spans (12.0 vs 13.0 us at 8192 x 2816).
+    if ((n % 2048) == 0 && M * n >= (int64_t(128) << 20)) {
+        const int spans = int(n / 2048);
+        const int64_t units = M * spans;
+        const int64_t grid = (units + 1) / 2;
+        if (grid > 0x7fffffff) return fail_arg("too many rows");
+        small_units_kernel<SOP_SILU, __nv_bfloat16, 2><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+        return check_launch("small_units_kernel");
+    }
     small_stream_kernel<SOP_SILU, __nv_bfloat16><<<unsigned(M), 128, 0, stream>>>(p);
     return check_launch("small_stream_kernel");
 }
@@ -298,6 +536,38 @@ int small_norm_y(const void* x, const void* gamma, int64_t M, int64_t n, float e
     p.y = static_cast<uint8_t*>(y); p.rms = rms; p.reuse_rms = reuse_rms;
     launch_small_norm<false>(p, stream);
     return check_launch("small_norm_kernel");
+}
+
+// dx as bf16 [M, n]; partial: [grid, n] fp32 scratch rows (grid <= max_parts); returns the grid
+// in *parts.  n <= 8192, 16-byte aligned pointers, bf16 inputs.
+int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
+                   void* dx, float* partial, int max_parts, int* parts, cudaStream_t stream) {
+    SmallParams p{};
+    p.x = static_cast<const uint8_t*>(x); p.gamma = static_cast<const uint8_t*>(gamma); p.M = M; p.n = int(n);
+    p.eps = eps; p.inv_n = 1.0f / float(n); p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr;
+    p.y = static_cast<uint8_t*>(dx);
+    const uint8_t* g = static_cast<const uint8_t*>(dy);
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const char* ve = getenv("LH_BWD_VARIANT");
+    const int var = ve ? atoi(ve) : 0;
+    int per_sm = n <= 4096 ? 3 : 1;
+    if (var == 1 && n > 2048 && n <= 4096) per_sm = 2;
+    if (var == 2 && n > 4096) per_sm = 2;
+    int64_t grid = int64_t(sms) * per_sm;
+    if (grid > max_parts) grid = max_parts;
+    if (grid > M) grid = M;
+    *parts = int(grid);
+    if (n <= 2048) small_norm_bwd_kernel<1, 128, 3><<<unsigned(grid), 128, 0, stream>>>(p, g, partial);
+    else if (n <= 4096 && var == 1) small_norm_bwd_kernel<1, 256, 2><<<unsigned(grid), 256, 0, stream>>>(p, g, partial);
+    else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3><<<unsigned(grid), 128, 0, stream>>>(p, g, partial);
+    else if (var == 2) small_norm_bwd_kernel<1, 512, 2><<<unsigned(grid), 512, 0, stream>>>(p, g, partial);
+    else small_norm_bwd_kernel<2, 256, 1><<<unsigned(grid), 256, 0, stream>>>(p, g, partial);
+    return check_launch("small_norm_bwd_kernel");
 }
 
 }  // namespace lh

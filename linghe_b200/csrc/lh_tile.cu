@@ -118,20 +118,28 @@ __device__ __forceinline__ TileLoc locate(int tile, int col_tiles, const int64_t
     return t;
 }
 
-// 8 consecutive elements of a tile row -> 4 float2 pairs
-template <typename InT>
+// 8 consecutive elements of a tile row -> 4 float2 pairs (NEG: the negated values)
+template <typename InT, bool NEG = false>
 __device__ __forceinline__ void load8p(const uint8_t* row_base, int l16, float2* f) {
     if constexpr (sizeof(InT) == 4) {
         const float4 a = *reinterpret_cast<const float4*>(row_base + l16 * 32);
         const float4 b = *reinterpret_cast<const float4*>(row_base + l16 * 32 + 16);
         f[0] = make_float2(a.x, a.y); f[1] = make_float2(a.z, a.w);
         f[2] = make_float2(b.x, b.y); f[3] = make_float2(b.z, b.w);
+        if constexpr (NEG) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f[i] = mul2(f[i], splat2(-1.f));
+        }
     } else {
         const uint4 raw = *reinterpret_cast<const uint4*>(row_base + l16 * 16);
         if constexpr (std::is_same<InT, __half>::value) {
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            const uint32_t w[4] = {raw.x ^ (NEG ? 0x80008000u : 0u), raw.y ^ (NEG ? 0x80008000u : 0u),
+                                   raw.z ^ (NEG ? 0x80008000u : 0u), raw.w ^ (NEG ? 0x80008000u : 0u)};
 #pragma unroll
             for (int i = 0; i < 4; ++i) f[i] = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+        } else if constexpr (NEG) {
+            f[0] = bf16x2_to_neg_f2(raw.x); f[1] = bf16x2_to_neg_f2(raw.y);
+            f[2] = bf16x2_to_neg_f2(raw.z); f[3] = bf16x2_to_neg_f2(raw.w);
         } else {
             f[0] = bf16x2_to_f2(raw.x); f[1] = bf16x2_to_f2(raw.y);
             f[2] = bf16x2_to_f2(raw.z); f[3] = bf16x2_to_f2(raw.w);
@@ -169,29 +177,37 @@ __device__ __forceinline__ float sum16(float a) {
     return a;
 }
 
-// exact quotient of one value: q0 = x*y with y = RN(1/s), residual r' = s*q0 - x (exact in
-// an FMA), q = q0 - r'*y.  Equals IEEE x / s bit for bit (Markstein) unless the residual
-// underflows, which needs a scale below ~2^-90; the negated-residual form keeps the sign
-// of a zero quotient.
-__device__ __forceinline__ float quot_exact(float x, float s, float y) {
-    const float q0 = x * y;
+// the same quotient for one value that is held as x itself (ny = -RN(1/s)); operand negations
+// are instruction modifiers
+__device__ __forceinline__ float quot_exact(float x, float s, float ny) {
+    const float q0 = x * -ny;
     const float r = fmaf(s, q0, -x);
-    return fmaf(r, -y, q0);
+    return fmaf(r, ny, q0);
 }
 constexpr float kTinyScale = 8.0e-28f;   // ~2^-90: below this take IEEE division
 
-// 8 values of one row, one scale (and its reciprocal) -> 8 codes.  A negative `y` marks a
-// block whose scale is so small that the residual of the exact quotient could underflow
-// (0 < amax < ~3.6e-25): those take IEEE division.  All-zero blocks do not need it.
-template <bool EXACT>
+// 8 values of one row, one scale -> 8 codes.
+//   EXACT: `y` is -RN(1/s) and v holds the negated values (NEGV) or the values; a positive
+//          `y` marks a block whose scale is so small that the residual of the exact quotient
+//          could underflow (0 < amax < ~3.6e-25): those take IEEE division.  All-zero blocks
+//          do not need it.
+//   else:  v holds the values and `y` an approximate 1/s.
+template <bool EXACT, bool NEGV>
 __device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) {
     float2 q[4];
     if constexpr (EXACT) {
+        if constexpr (NEGV) {
+            const float2 s2 = splat2(sc), ny2 = splat2(y);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) q[j] = make_float2(quot_exact(v[j].x, sc, y), quot_exact(v[j].y, sc, y));
-        if (y < 0.f) {   // rare
+            for (int j = 0; j < 4; ++j) q[j] = quot_exact2(v[j], s2, ny2);
+        } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(v[j].x, sc), __fdiv_rn(v[j].y, sc));
+            for (int j = 0; j < 4; ++j) q[j] = make_float2(quot_exact(v[j].x, sc, y), quot_exact(v[j].y, sc, y));
+        }
+        if (y > 0.f) {   // rare
+            const float sg = NEGV ? -1.f : 1.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(sg * v[j].x, sc), __fdiv_rn(sg * v[j].y, sc));
         }
     } else {
         const float2 y2 = splat2(y);
@@ -201,11 +217,12 @@ __device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) 
     return make_uint2(cvt_e4m3x4(q[0].x, q[0].y, q[1].x, q[1].y), cvt_e4m3x4(q[2].x, q[2].y, q[3].x, q[3].y));
 }
 
-// reciprocal of a scale: correctly rounded where exact quotients are required, and -1 as the
-// "use IEEE division" marker for non-zero blocks with a denormal-range scale
+// the multiplier quant_row8 takes: the negated correctly rounded reciprocal where exact
+// quotients are required (+1 as the "use IEEE division" marker for non-zero blocks with a
+// denormal-range scale), else an approximate reciprocal
 template <bool EXACT>
 __device__ __forceinline__ float scale_rcp(float sc, float amax) {
-    if constexpr (EXACT) return (sc < kTinyScale && amax > 0.f) ? -1.f : __frcp_rn(sc);
+    if constexpr (EXACT) return (sc < kTinyScale && amax > 0.f) ? 1.f : -__frcp_rn(sc);
     return rcp_approx(sc);
 }
 
@@ -245,6 +262,10 @@ __device__ __forceinline__ float row_max_transposed(float* a, int l16) {
 template <int OP, typename InT, int MODE, bool EXACT, int RPT, int STAGES, int MINB, bool WEIGHTED>
 __global__ void __launch_bounds__(TileCfg<OP, InT, RPT, STAGES>::NTHREADS, MINB)
 tile_kernel(const __grid_constant__ TileParams p) {
+    static_assert(!EXACT || OP == OP_IDENT || OP == OP_GATHER, "exact quotients: pure quantisers only");
+    // The plain quantiser keeps negated values so that its exact quotients are packed; the
+    // gathering one has no registers to spare for the register pairs that packed math needs.
+    constexpr bool NEGV = EXACT && OP == OP_IDENT;
     using C = TileCfg<OP, InT, RPT, STAGES>;
     constexpr int K = C::K, NHALF = C::NHALF, NW = C::NW, NCONS = C::NCONS;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -494,7 +515,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
         for (int s = 0; s < RPT; ++s) {
             const uint8_t* srow = sbase + (row0 + s) * C::ROWB;
             if constexpr (OP == OP_IDENT || OP == OP_GATHER) {
-                load8p<InT>(srow, l16, v[0][s]);
+                load8p<InT, NEGV>(srow, l16, v[0][s]);
             } else if constexpr (OP == OP_NORM) {
                 float2 x[4];
                 load8p<InT>(srow, l16, x);
@@ -542,7 +563,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
                     for (int h = 0; h < NHALF; ++h)
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) v[h][s][j] = make_float2(0.f, 0.f);
+                        for (int j = 0; j < 4; ++j) v[h][s][j] = NEGV ? make_float2(-0.f, -0.f) : make_float2(0.f, 0.f);
                     if constexpr (OP == OP_SILU_B) dwp[s] = 0.f;
                 }
             }
@@ -597,7 +618,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     const int rr = row0 + s;
-                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc, y);
+                    const uint2 codes = quant_row8<EXACT, NEGV>(v[h][s], sc, y);
                     if (rr < t.valid) st_global_v2(p.q + (grow0 + rr) * p.n + gcol0 + l16 * 8, codes.x, codes.y);
                 }
                 if (tid == 0) p.s[(t.B + t.T) * nb + t.ct] = sc;
@@ -632,7 +653,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
                 for (int s = 0; s < RPT; ++s) {
                     const float sc = __shfl_sync(0xffffffffu, mysc, s * G, 16);
                     const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
-                    const uint2 codes = quant_row8<EXACT>(v[h][s], sc, y);
+                    const uint2 codes = quant_row8<EXACT, NEGV>(v[h][s], sc, y);
                     if (s < nrows) st_global_v2(qrow, codes.x, codes.y);
                     qrow += ldq;
                 }
@@ -684,12 +705,14 @@ tile_kernel(const __grid_constant__ TileParams p) {
                     if constexpr (EXACT) {
 #pragma unroll
                         for (int s = 0; s < RPT; ++s)
-                            q[s] = make_float2(quot_exact(v[h][s][j].x, sc2[j].x, y2[j].x),
-                                               quot_exact(v[h][s][j].y, sc2[j].y, y2[j].y));
-                        if (y2[j].x < 0.f || y2[j].y < 0.f) {   // rare: denormal-range scale, IEEE division
+                            q[s] = NEGV ? quot_exact2(v[h][s][j], sc2[j], y2[j])
+                                        : make_float2(quot_exact(v[h][s][j].x, sc2[j].x, y2[j].x),
+                                                      quot_exact(v[h][s][j].y, sc2[j].y, y2[j].y));
+                        if (y2[j].x > 0.f || y2[j].y > 0.f) {   // rare: denormal-range scale, IEEE division
+                            const float sg = NEGV ? -1.f : 1.f;
 #pragma unroll
                             for (int s = 0; s < RPT; ++s)
-                                q[s] = make_float2(__fdiv_rn(v[h][s][j].x, sc2[j].x), __fdiv_rn(v[h][s][j].y, sc2[j].y));
+                                q[s] = make_float2(__fdiv_rn(sg * v[h][s][j].x, sc2[j].x), __fdiv_rn(sg * v[h][s][j].y, sc2[j].y));
                         }
                     } else {
 #pragma unroll
