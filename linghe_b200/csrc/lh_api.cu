@@ -278,8 +278,12 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (!rms) return fail_arg("rmsnorm_blockquant_fwd: rms is NULL");
     if (output_mode == 0 || output_mode == 2) {
-        const bool small = M > 0 && use_small_rows(M * n) && x && gamma && q && s && dtype == LH_BF16 && aligned16(x) &&
-                           aligned16(q) && aligned16(gamma);
+        // The ring kernel's slab holds whole rows of at most 8192 elements in all; rows that fill
+        // less than three quarters of it (e.g. n = 5120: 135 vs 102 us at 32768 rows) and long runs of
+        // rows wider than 4096 go to the register kernels, like every small problem.
+        const bool poor_fill = (8192 / n) * n * 4 < 8192 * 3;
+        const bool small = M > 0 && use_small_rows((poor_fill || n > 4096) ? 0 : M * n) && x && gamma && q && s &&
+                           dtype == LH_BF16 && aligned16(x) && aligned16(q) && aligned16(gamma);
         if (small) {
             if (int rc = small_norm_quant(x, gamma, M, n, eps, q, s, rms, round_scale, cs)) return rc;
         } else if (int rc = rows_norm_quant(x, gamma, dtype, M, n, eps, q, s, rms, round_scale, cs)) {

@@ -21,7 +21,7 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
 enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3, ROP_NORM_YQ = 4 };
 
 constexpr int kSlabElems = 8192;
-constexpr int kMaxRowCtas = 444;   // three CTAs per SM at most
+constexpr int kMaxRowCtas = 592;   // four CTAs per SM at most
 
 struct RowParams {
     const uint8_t* x;
@@ -820,8 +820,15 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr; p.eps = eps; p.M = M; p.n = int(n);
     p.hp = static_cast<uint8_t*>(dx); p.partial = static_cast<float*>(scratch);
     int grid = 0;
-    const char* pe = getenv("LH_BWD_PATH");
-    if (pe != nullptr && !strcmp(pe, "small") && dtype == LH_BF16) {
+    // Rows wider than 2048 take the streaming register kernel (77 vs 83 us at 16384 x 4096, 279 vs
+    // 301 us at 65536 x 4096, 354 vs 370 us at 32768 x 8192), narrower ones the TMA ring (159 vs
+    // 174 us at 65536 x 2048).  LH_BWD_PATH=small|ring forces one of them (for measurements).
+    static const int forced = [] {
+        const char* e = getenv("LH_BWD_PATH");
+        if (!e) return 0;
+        return !strcmp(e, "small") ? 1 : (!strcmp(e, "ring") ? 2 : 0);
+    }();
+    if (forced ? forced == 1 : n > 2048) {
         if (int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, stream)) return rc;
     } else if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream)) {
         return rc;

@@ -459,6 +459,84 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
     }
 }
 
+// RMSNorm + 1x128 quantisation for long runs of wide rows: a persistent walk.  A CTA of 128
+// threads takes rows blockIdx.x, blockIdx.x + gridDim.x, ... with the whole row in registers as
+// packed words; the loads of the next row are issued as soon as the row sum is known, before
+// the normalise + quantise pass over a copy of the current one, so each of the four resident CTAs
+// per SM always has a row (up to 16 KB) in flight and only pays its own barrier.
+template <int SPANS>
+__global__ void __launch_bounds__(128, 4)
+small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
+    constexpr int SPAN = 2048;
+    __shared__ float wsum[2][4];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    uint4 xr[2 * SPANS];
+    auto fetch = [&](int64_t row) {
+#pragma unroll
+        for (int i = 0; i < SPANS; ++i) {
+            const int col = i * SPAN + t * 16;
+            xr[2 * i] = xr[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if (row < p.M && col < p.n) {
+                const uint8_t* src = p.x + (row * p.n + col) * 2;
+                xr[2 * i] = *reinterpret_cast<const uint4*>(src);
+                xr[2 * i + 1] = *reinterpret_cast<const uint4*>(src + 16);
+            }
+        }
+    };
+    int64_t row = blockIdx.x;
+    fetch(row);
+    int par = 0;
+    for (; row < p.M; row += gridDim.x, par ^= 1) {
+        float2 s0 = make_float2(0.f, 0.f), s1 = s0;
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) {
+            float2 v[4];
+            unpack8<__nv_bfloat16>(xr[i], v);
+            s0 = fma2(v[0], v[0], s0); s1 = fma2(v[1], v[1], s1);
+            s0 = fma2(v[2], v[2], s0); s1 = fma2(v[3], v[3], s1);
+        }
+        s0 = add2(s0, s1);
+        float ss = s0.x + s0.y;
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
+        if (lane == 0) wsum[par][warp] = ss;
+        __syncthreads();   // the buffer of the other parity was last read before the previous barrier
+        const float tot = (wsum[par][0] + wsum[par][1]) + (wsum[par][2] + wsum[par][3]);
+        const float r = rsqrt_nr(fmaf(tot, p.inv_n, p.eps));
+        if (t == 0 && p.rms != nullptr) p.rms[row] = r;
+        const float2 r2 = splat2(r);
+        uint4 xc[2 * SPANS];
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) xc[i] = xr[i];
+        fetch(row + gridDim.x);
+#pragma unroll
+        for (int i = 0; i < SPANS; ++i) {
+            const int col = i * SPAN + t * 16;
+            if (i * SPAN >= p.n) break;                       // uniform
+            float2 v[8], g[8];
+            unpack8<__nv_bfloat16>(xc[2 * i], v);
+            unpack8<__nv_bfloat16>(xc[2 * i + 1], v + 4);
+            uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
+            if (col < p.n) {
+                g0 = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
+                g1 = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
+            }
+            unpack8<__nv_bfloat16>(g0, g);
+            unpack8<__nv_bfloat16>(g1, g + 4);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(v[j], r2), g[j]);
+            if (p.y != nullptr && col < p.n) {
+                uint8_t* yo = p.y + (row * p.n + col) * 2;
+                *reinterpret_cast<uint4*>(yo) = make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
+                                                           pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y));
+                *reinterpret_cast<uint4*>(yo + 16) = make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
+                                                                pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y));
+            }
+            quant16<false>(p, row, col, col < p.n, v);
+        }
+    }
+}
+
 template <bool QUANT>
 static void launch_small_norm(const SmallParams& p, cudaStream_t stream) {
     const unsigned grid = unsigned(p.M);
@@ -502,7 +580,7 @@ int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int
     // Long runs over whole spans: two spans per CTA with all four loads of both issued up front
     // (384 vs 393 us at 65536 x 16384).  Short runs and partly filled spans are faster with one
     // CTA per row walking its spans (12.0 vs 13.0 us at 8192 x 2816).
-    if ((n % 2048) == 0 && M * n >= (int64_t(128) << 20)) {
+    if ((n % 2048) == 0 && M * n >= (int64_t(64) << 20)) {
         const int spans = int(n / 2048);
         const int64_t units = M * spans;
         const int64_t grid = (units + 1) / 2;
@@ -522,6 +600,18 @@ int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, flo
     p.x = static_cast<const uint8_t*>(x); p.gamma = static_cast<const uint8_t*>(gamma); p.M = M; p.n = int(n);
     p.eps = eps; p.inv_n = 1.0f / float(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.rms = rms; p.round_scale = round_scale; p.y = static_cast<uint8_t*>(y);
+    // Long runs of wide rows: the persistent walk (263 vs 271 us at 65536 x 8192, and 266 us for
+    // the TMA ring); everything else one CTA per row.
+    if (p.n > 4096 && M * n > (int64_t(24) << 20)) {
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        small_norm_walk_kernel<4><<<unsigned(4 * sms), 128, 0, stream>>>(p);
+        return check_launch("small_norm_walk_kernel");
+    }
     launch_small_norm<true>(p, stream);
     return check_launch("small_norm_kernel");
 }
@@ -553,19 +643,12 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
-    const char* ve = getenv("LH_BWD_VARIANT");
-    const int var = ve ? atoi(ve) : 0;
-    int per_sm = n <= 4096 ? 3 : 1;
-    if (var == 1 && n > 2048 && n <= 4096) per_sm = 2;
-    if (var == 2 && n > 4096) per_sm = 2;
-    int64_t grid = int64_t(sms) * per_sm;
+    int64_t grid = int64_t(sms) * (n <= 4096 ? 3 : 1);
     if (grid > max_parts) grid = max_parts;
     if (grid > M) grid = M;
     *parts = int(grid);
     if (n <= 2048) small_norm_bwd_kernel<1, 128, 3><<<unsigned(grid), 128, 0, stream>>>(p, g, partial);
-    else if (n <= 4096 && var == 1) small_norm_bwd_kernel<1, 256, 2><<<unsigned(grid), 256, 0, stream>>>(p, g, partial);
     else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3><<<unsigned(grid), 128, 0, stream>>>(p, g, partial);
-    else if (var == 2) small_norm_bwd_kernel<1, 512, 2><<<unsigned(grid), 512, 0, stream>>>(p, g, partial);
     else small_norm_bwd_kernel<2, 256, 1><<<unsigned(grid), 256, 0, stream>>>(p, g, partial);
     return check_launch("small_norm_bwd_kernel");
 }

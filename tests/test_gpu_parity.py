@@ -160,7 +160,7 @@ def test_blockwise_quant_extremes():
     check_exact(triton_blockwise_quant(_cuda(xb)), O.blockwise_quant(xb, False), ("q", "s", "qt", "st"))
 
 
-@pytest.mark.parametrize("M,N", [(2049, 1024), (16, 128), (300, 2048)])
+@pytest.mark.parametrize("M,N", [(2049, 1024), (16, 128), (300, 2048), (3, 4224), (5, 6144), (1, 128)])
 def test_group_quant(M, N):
     from linghe_b200.quant.group import triton_group_quant
     x = randn_bf16((M, N), 2, 3)
@@ -208,7 +208,10 @@ def test_golden_rms_block_quant(tag, rs):
     check_fused(qt, fp8(G[p + "qt"]), st, torch.from_numpy(G[p + "st"]), "col", bool(rs))
 
 
-@pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (384, 4096), (130, 8192), (64, 128), (2048, 1664)])
+# (4200, 8192) is past the size where wide rows switch to the persistent-walk kernel; (600, 5120)
+# fills the ring kernel's slab poorly and takes the one-CTA-per-row kernel at any size
+@pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (384, 4096), (130, 8192), (64, 128), (2048, 1664),
+                                 (4200, 8192), (600, 5120)])
 def test_rms_block_quant_modes(M, n):
     from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
     x = randn_bf16((M, n), 7, 2)
@@ -232,7 +235,10 @@ def test_rms_block_quant_modes(M, n):
     check_fused(qt, rqt, st, rst, "pow2 col", True)
 
 
-@pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (4096, 4096), (130, 8192), (96, 256)])
+# n > 2048 takes the streaming backward kernel (two spans per thread; 2304 and 5120 leave the
+# second span partly empty), narrower rows the ring kernel
+@pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (4096, 4096), (130, 8192), (96, 256), (778, 2304),
+                                 (2000, 5120)])
 def test_rms_fwd_bwd(M, n):
     from linghe_b200.utils.norm import triton_rms_norm_forward, triton_rms_norm_backward
     x = randn_bf16((M, n), 11)
