@@ -204,8 +204,13 @@ __device__ __forceinline__ float2 bf16x2_to_f2(uint32_t w) {
 // two bf16 packed in a word -> the NEGATED pair as float2.  Flipping the sign bit rides on the
 // widening itself: adding 2^31 to (w << 16) and xor-ing it into the masked high half are the
 // same integer instructions as the plain conversion, with one more constant operand.
+// (Written as inline PTX: from C++ the compiler recognises the sign flip as a float negation and
+// spends a separate FADD on it.)
 __device__ __forceinline__ float2 bf16x2_to_neg_f2(uint32_t w) {
-    return make_float2(__uint_as_float((w << 16) + 0x80000000u), __uint_as_float((w & 0xffff0000u) ^ 0x80000000u));
+    uint32_t lo, hi;
+    asm("mad.lo.u32 %0, %1, 65536, 0x80000000;" : "=r"(lo) : "r"(w));
+    asm("lop3.b32 %0, %1, 0xffff0000, 0x80000000, 0x6a;" : "=r"(hi) : "r"(w));   // (w & 0xffff0000) ^ 0x80000000
+    return make_float2(__uint_as_float(lo), __uint_as_float(hi));
 }
 
 // Exact quotients, two at a time.  The pure quantisers keep the NEGATED inputs nv = -x in
@@ -338,6 +343,14 @@ __device__ __forceinline__ void named_bar() {
 
 __device__ __forceinline__ void st_global_v2(void* p, uint32_t a, uint32_t b) {
     *reinterpret_cast<uint2*>(p) = make_uint2(a, b);
+}
+// the same store under a predicate (one predicated instruction instead of a branch around it)
+__device__ __forceinline__ void st_global_v2_if(bool pred, void* p, uint32_t a, uint32_t b) {
+    asm volatile("{\n\t.reg .pred q;\n\t"
+                 "setp.ne.u32 q, %3, 0;\n\t"
+                 "@q st.global.v2.b32 [%0], {%1, %2};\n\t}"
+                 ::"l"(p), "r"(a), "r"(b), "r"(uint32_t(pred))
+                 : "memory");
 }
 
 }  // namespace lh

@@ -192,7 +192,7 @@ constexpr float kTinyScale = 8.0e-28f;   // ~2^-90: below this take IEEE divisio
 //          could underflow (0 < amax < ~3.6e-25): those take IEEE division.  All-zero blocks
 //          do not need it.
 //   else:  v holds the values and `y` an approximate 1/s.
-template <bool EXACT, bool NEGV>
+template <bool EXACT, bool NEGV, bool CHECK = true>
 __device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) {
     float2 q[4];
     if constexpr (EXACT) {
@@ -204,7 +204,7 @@ __device__ __forceinline__ uint2 quant_row8(const float2* v, float sc, float y) 
 #pragma unroll
             for (int j = 0; j < 4; ++j) q[j] = make_float2(quot_exact(v[j].x, sc, y), quot_exact(v[j].y, sc, y));
         }
-        if (y > 0.f) {   // rare
+        if (CHECK && y > 0.f) {   // rare; CHECK = false: the caller knows no block of the warp needs it
             const float sg = NEGV ? -1.f : 1.f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(sg * v[j].x, sc), __fdiv_rn(sg * v[j].y, sc));
@@ -649,14 +649,19 @@ tile_kernel(const __grid_constant__ TileParams p) {
                 }
                 const int64_t ldq = NHALF * p.n;
                 uint8_t* qrow = p.q + (grow0 + row0) * ldq + h * p.n + gcol0 + l16 * 8;
+                // one warp-uniform test for the IEEE-division fallback instead of one per row
+                auto row_pass = [&](auto check) {
 #pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    const float sc = __shfl_sync(0xffffffffu, mysc, s * G, 16);
-                    const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
-                    const uint2 codes = quant_row8<EXACT, NEGV>(v[h][s], sc, y);
-                    if (s < nrows) st_global_v2(qrow, codes.x, codes.y);
-                    qrow += ldq;
-                }
+                    for (int s = 0; s < RPT; ++s) {
+                        const float sc = __shfl_sync(0xffffffffu, mysc, s * G, 16);
+                        const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
+                        const uint2 codes = quant_row8<EXACT, NEGV, decltype(check)::value>(v[h][s], sc, y);
+                        st_global_v2_if(s < nrows, qrow, codes.x, codes.y);
+                        qrow += ldq;
+                    }
+                };
+                if (EXACT && __any_sync(0xffffffffu, myy > 0.f)) row_pass(std::true_type{});
+                else row_pass(std::false_type{});
             }
             // ------------------------ column-wise 128x1, transposed -----------------
             if constexpr (MODE == MODE_COL || MODE == MODE_BOTH) {
