@@ -131,7 +131,7 @@ __device__ __forceinline__ void unpack8_neg(const uint4& r, float2* v) {
     }
 }
 
-template <int SOP, typename InT, int U>
+template <int SOP, typename InT, int U, bool WIDE>
 __global__ void __launch_bounds__(128)
 small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t units) {
     constexpr bool SILU = SOP == SOP_SILU;
@@ -150,11 +150,16 @@ small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t uni
         if constexpr (SILU) rawb[2 * k] = rawb[2 * k + 1] = make_uint4(0, 0, 0, 0);
         if (u0 + k < units && cols[k] < p.n) {
             const uint8_t* src = p.x + (row * in_row + cols[k]) * 2;
-            raw[2 * k] = *reinterpret_cast<const uint4*>(src);
-            raw[2 * k + 1] = *reinterpret_cast<const uint4*>(src + 16);
-            if constexpr (SILU) {
-                rawb[2 * k] = *reinterpret_cast<const uint4*>(src + int64_t(p.n) * 2);
-                rawb[2 * k + 1] = *reinterpret_cast<const uint4*>(src + int64_t(p.n) * 2 + 16);
+            if constexpr (WIDE) {   // x is 32-byte aligned: one 256-bit load per 16 elements
+                ld_global_256(src, raw[2 * k], raw[2 * k + 1]);
+                if constexpr (SILU) ld_global_256(src + int64_t(p.n) * 2, rawb[2 * k], rawb[2 * k + 1]);
+            } else {
+                raw[2 * k] = *reinterpret_cast<const uint4*>(src);
+                raw[2 * k + 1] = *reinterpret_cast<const uint4*>(src + 16);
+                if constexpr (SILU) {
+                    rawb[2 * k] = *reinterpret_cast<const uint4*>(src + int64_t(p.n) * 2);
+                    rawb[2 * k + 1] = *reinterpret_cast<const uint4*>(src + int64_t(p.n) * 2 + 16);
+                }
             }
         } else {
             cols[k] = p.n;   // nothing to do for this unit
@@ -547,6 +552,13 @@ static void launch_small_norm(const SmallParams& p, cudaStream_t stream) {
     else small_norm_kernel<4, QUANT, 128><<<grid, 128, 0, stream>>>(p);
 }
 
+// WIDE (256-bit loads) needs a 32-byte aligned input
+template <int SOP, typename InT, int U>
+static void launch_units(const SmallParams& p, int spans, int64_t units, unsigned grid, bool wide, cudaStream_t stream) {
+    if (wide) small_units_kernel<SOP, InT, U, true><<<grid, 128, 0, stream>>>(p, spans, units);
+    else small_units_kernel<SOP, InT, U, false><<<grid, 128, 0, stream>>>(p, spans, units);
+}
+
 }  // namespace
 
 int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, int scale_rowmajor,
@@ -555,6 +567,7 @@ int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, f
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.scale_rowmajor = scale_rowmajor; p.round_scale = round_scale;
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
     const int spans = int((n + 2047) / 2048);
     const int64_t units = M * spans;
     // three units per CTA once the problem is many waves long (measured: 251 vs 259 us at
@@ -562,12 +575,13 @@ int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, f
     const int U = M * n > (int64_t(96) << 20) ? 3 : 2;
     const int64_t grid = (units + U - 1) / U;
     if (grid > 0x7fffffff) return fail_arg("too many rows");
+    const unsigned g = unsigned(grid);
     if (dtype == LH_F16) {
-        if (U == 3) small_units_kernel<SOP_GROUP, __half, 3><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
-        else small_units_kernel<SOP_GROUP, __half, 2><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+        if (U == 3) launch_units<SOP_GROUP, __half, 3>(p, spans, units, g, wide, stream);
+        else launch_units<SOP_GROUP, __half, 2>(p, spans, units, g, wide, stream);
     } else {
-        if (U == 3) small_units_kernel<SOP_GROUP, __nv_bfloat16, 3><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
-        else small_units_kernel<SOP_GROUP, __nv_bfloat16, 2><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+        if (U == 3) launch_units<SOP_GROUP, __nv_bfloat16, 3>(p, spans, units, g, wide, stream);
+        else launch_units<SOP_GROUP, __nv_bfloat16, 2>(p, spans, units, g, wide, stream);
     }
     return check_launch("small_units_kernel");
 }
@@ -577,6 +591,7 @@ int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
+    const bool wide = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
     // Long runs over whole spans: two spans per CTA with all four loads of both issued up front
     // (384 vs 393 us at 65536 x 16384).  Short runs and partly filled spans are faster with one
     // CTA per row walking its spans (12.0 vs 13.0 us at 8192 x 2816).
@@ -585,7 +600,7 @@ int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int
         const int64_t units = M * spans;
         const int64_t grid = (units + 1) / 2;
         if (grid > 0x7fffffff) return fail_arg("too many rows");
-        small_units_kernel<SOP_SILU, __nv_bfloat16, 2><<<unsigned(grid), 128, 0, stream>>>(p, spans, units);
+        launch_units<SOP_SILU, __nv_bfloat16, 2>(p, spans, units, unsigned(grid), wide, stream);
         return check_launch("small_units_kernel");
     }
     small_stream_kernel<SOP_SILU, __nv_bfloat16><<<unsigned(M), 128, 0, stream>>>(p);

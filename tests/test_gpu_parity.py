@@ -169,6 +169,15 @@ def test_group_quant(M, N):
         rq, rsx = O.group_quant(x, rs)
         assert_bits_equal(q, rq, "q")
         assert_f32_equal(s, rsx, "s")
+    # an input that is 16- but not 32-byte aligned takes the 128-bit loads
+    buf = torch.empty(M * N + 8, dtype=torch.bfloat16, device="cuda")
+    xo = buf[8:].view(M, N)
+    xo.copy_(x)
+    assert xo.data_ptr() % 32 == 16
+    q, s = triton_group_quant(xo)
+    rq, rsx = O.group_quant(x, False)
+    assert_bits_equal(q, rq, "q (offset input)")
+    assert_f32_equal(s, rsx, "s (offset input)")
 
 
 def test_block_quant():
