@@ -469,7 +469,7 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
 // packed words; the loads of the next row are issued as soon as the row sum is known, before
 // the normalise + quantise pass over a copy of the current one, so each of the four resident CTAs
 // per SM always has a row (up to 16 KB) in flight and only pays its own barrier.
-template <int SPANS>
+template <int SPANS, bool WIDE>
 __global__ void __launch_bounds__(128, 4)
 small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
     constexpr int SPAN = 2048;
@@ -483,8 +483,12 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
             xr[2 * i] = xr[2 * i + 1] = make_uint4(0, 0, 0, 0);
             if (row < p.M && col < p.n) {
                 const uint8_t* src = p.x + (row * p.n + col) * 2;
-                xr[2 * i] = *reinterpret_cast<const uint4*>(src);
-                xr[2 * i + 1] = *reinterpret_cast<const uint4*>(src + 16);
+                if constexpr (WIDE) {   // x is 32-byte aligned
+                    ld_global_256(src, xr[2 * i], xr[2 * i + 1]);
+                } else {
+                    xr[2 * i] = *reinterpret_cast<const uint4*>(src);
+                    xr[2 * i + 1] = *reinterpret_cast<const uint4*>(src + 16);
+                }
             }
         }
     };
@@ -624,7 +628,8 @@ int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, flo
             cudaGetDevice(&dev);
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         }
-        small_norm_walk_kernel<4><<<unsigned(4 * sms), 128, 0, stream>>>(p);
+        if ((reinterpret_cast<uintptr_t>(x) & 31) == 0) small_norm_walk_kernel<4, true><<<unsigned(4 * sms), 128, 0, stream>>>(p);
+        else small_norm_walk_kernel<4, false><<<unsigned(4 * sms), 128, 0, stream>>>(p);
         return check_launch("small_norm_walk_kernel");
     }
     launch_small_norm<true>(p, stream);
