@@ -40,6 +40,26 @@ __device__ __forceinline__ void unpack8(const uint4& r, float2* v) {
     }
 }
 
+// 32 contiguous bytes of a thread's span: one 256-bit load when the tensor is 32-byte aligned
+template <bool WIDE>
+__device__ __forceinline__ void load32(const uint8_t* src, uint4& a, uint4& b) {
+    if constexpr (WIDE) {
+        ld_global_256(src, a, b);
+    } else {
+        a = *reinterpret_cast<const uint4*>(src);
+        b = *reinterpret_cast<const uint4*>(src + 16);
+    }
+}
+template <bool WIDE>
+__device__ __forceinline__ void store32(uint8_t* dst, const uint4& a, const uint4& b) {
+    if constexpr (WIDE) {
+        st_global_256(dst, a, b);
+    } else {
+        *reinterpret_cast<uint4*>(dst) = a;
+        *reinterpret_cast<uint4*>(dst + 16) = b;
+    }
+}
+
 // 16 values of one thread (half... an eighth of a 1x128 block) -> block scale -> 16 codes, stored
 template <bool EXACT>
 __device__ __forceinline__ void quant16(const SmallParams& p, int64_t row, int col, bool valid, float2* v) {
@@ -83,7 +103,7 @@ __device__ __forceinline__ void quant16(const SmallParams& p, int64_t row, int c
 }
 
 // SOP_GROUP / SOP_SILU: spans of 2048 output elements are independent
-template <int SOP, typename InT>
+template <int SOP, typename InT, bool WIDE>
 __global__ void __launch_bounds__(128)
 small_stream_kernel(const __grid_constant__ SmallParams p) {
     const int64_t row = blockIdx.x;
@@ -94,12 +114,8 @@ small_stream_kernel(const __grid_constant__ SmallParams p) {
         const bool valid = col < p.n;
         uint4 a0 = make_uint4(0, 0, 0, 0), a1 = a0, b0 = a0, b1 = a0;
         if (valid) {
-            a0 = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
-            a1 = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
-            if constexpr (SOP == SOP_SILU) {
-                b0 = *reinterpret_cast<const uint4*>(xr + (int64_t(p.n) + col) * 2);
-                b1 = *reinterpret_cast<const uint4*>(xr + (int64_t(p.n) + col) * 2 + 16);
-            }
+            load32<WIDE>(xr + int64_t(col) * 2, a0, a1);
+            if constexpr (SOP == SOP_SILU) load32<WIDE>(xr + (int64_t(p.n) + col) * 2, b0, b1);
         }
         float2 v[8];
         unpack8<InT>(a0, v);
@@ -217,7 +233,7 @@ small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t uni
 // SOP_NORM: the row (n <= 2048 * SPANS) stays in registers as packed 16-bit words
 // QUANT: codes + scales; otherwise the 16-bit y itself (plain RMSNorm forward).  NT threads
 // per row, thread t owns 16 consecutive elements of every span of 16*NT elements.
-template <int SPANS, bool QUANT, int NT>
+template <int SPANS, bool QUANT, int NT, bool WIDE>
 __global__ void __launch_bounds__(NT, (SPANS == 1 && NT == 128) ? 8 : 1)
 small_norm_kernel(const __grid_constant__ SmallParams p) {
     constexpr int SPAN = 16 * NT;
@@ -242,8 +258,7 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
             const int col = i * SPAN + t * 16;
             tmp[2 * i] = tmp[2 * i + 1] = make_uint4(0, 0, 0, 0);
             if (col < p.n) {
-                tmp[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
-                tmp[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+                load32<WIDE>(xr + int64_t(col) * 2, tmp[2 * i], tmp[2 * i + 1]);
             }
         }
 #pragma unroll
@@ -260,8 +275,7 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
             raw[2 * i] = raw[2 * i + 1] = make_uint4(0, 0, 0, 0);
             if constexpr (GAMMA_EARLY) graw[2 * i] = graw[2 * i + 1] = make_uint4(0, 0, 0, 0);
             if (col < p.n) {
-                raw[2 * i] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
-                raw[2 * i + 1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+                load32<WIDE>(xr + int64_t(col) * 2, raw[2 * i], raw[2 * i + 1]);
                 if constexpr (GAMMA_EARLY) {
                     graw[2 * i] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
                     graw[2 * i + 1] = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
@@ -301,8 +315,7 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
         if constexpr (REREAD) {
             raw[0] = raw[1] = make_uint4(0, 0, 0, 0);
             if (col < p.n) {
-                raw[0] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2);
-                raw[1] = *reinterpret_cast<const uint4*>(xr + int64_t(col) * 2 + 16);
+                load32<WIDE>(xr + int64_t(col) * 2, raw[0], raw[1]);
             }
             unpack8<__nv_bfloat16>(raw[0], v);
             unpack8<__nv_bfloat16>(raw[1], v + 4);
@@ -326,19 +339,19 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
         for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(v[j], r2), g[j]);
         if constexpr (QUANT) {
             if (p.y != nullptr && col < p.n) {           // the 16-bit y as well (RMSNorm + router logits + quant)
-                uint8_t* yo = p.y + (row * p.n + col) * 2;
-                *reinterpret_cast<uint4*>(yo) = make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
-                                                           pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y));
-                *reinterpret_cast<uint4*>(yo + 16) = make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
-                                                                pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y));
+                store32<WIDE>(p.y + (row * p.n + col) * 2,
+                              make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
+                                         pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y)),
+                              make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
+                                         pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y)));
             }
             quant16<false>(p, row, col, col < p.n, v);
         } else if (col < p.n) {
-            uint8_t* yo = p.y + (row * p.n + col) * 2;
-            *reinterpret_cast<uint4*>(yo) = make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
-                                                       pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y));
-            *reinterpret_cast<uint4*>(yo + 16) = make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
-                                                            pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y));
+            store32<WIDE>(p.y + (row * p.n + col) * 2,
+                          make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
+                                     pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y)),
+                          make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
+                                     pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y)));
         }
     }
 }
@@ -349,7 +362,7 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
 // The loads of the next row are issued before the second pass over the current one, so every
 // resident CTA always has a row in flight.  Per-CTA sums go to partial[blockIdx.x][n]; a second
 // kernel adds them in a fixed order.
-template <int SPANS, int NT, int MINB>
+template <int SPANS, int NT, int MINB, bool WIDE>
 __global__ void __launch_bounds__(NT, MINB)
 small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
     constexpr int SPAN = 16 * NT, NW = NT / 32;
@@ -384,10 +397,15 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
             xr[2 * i] = xr[2 * i + 1] = gr[2 * i] = gr[2 * i + 1] = make_uint4(0, 0, 0, 0);
             if (row < p.M && col < p.n) {
                 const int64_t off = (row * p.n + col) * 2;
-                xr[2 * i] = *reinterpret_cast<const uint4*>(p.x + off);
-                xr[2 * i + 1] = *reinterpret_cast<const uint4*>(p.x + off + 16);
-                gr[2 * i] = *reinterpret_cast<const uint4*>(dy + off);
-                gr[2 * i + 1] = *reinterpret_cast<const uint4*>(dy + off + 16);
+                if constexpr (WIDE) {   // x, dy and dx are 32-byte aligned
+                    ld_global_256(p.x + off, xr[2 * i], xr[2 * i + 1]);
+                    ld_global_256(dy + off, gr[2 * i], gr[2 * i + 1]);
+                } else {
+                    xr[2 * i] = *reinterpret_cast<const uint4*>(p.x + off);
+                    xr[2 * i + 1] = *reinterpret_cast<const uint4*>(p.x + off + 16);
+                    gr[2 * i] = *reinterpret_cast<const uint4*>(dy + off);
+                    gr[2 * i + 1] = *reinterpret_cast<const uint4*>(dy + off + 16);
+                }
             }
         }
     };
@@ -447,8 +465,12 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
             }
             if (col < p.n) {
                 uint8_t* dst = p.y + (row * p.n + col) * 2;
-                *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-                *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+                if constexpr (WIDE) {
+                    st_global_256(dst, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
+                } else {
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
             }
         }
     }
@@ -551,9 +573,16 @@ static void launch_small_norm(const SmallParams& p, cudaStream_t stream) {
     const unsigned grid = unsigned(p.M);
     // 128 threads per row at every width: fewer, fatter threads beat 256 (measured: 331 vs 381 us
     // for the plain norm at 65536 x 8192)
-    if (p.n <= 2048) small_norm_kernel<1, QUANT, 128><<<grid, 128, 0, stream>>>(p);
-    else if (p.n <= 4096) small_norm_kernel<2, QUANT, 128><<<grid, 128, 0, stream>>>(p);
-    else small_norm_kernel<4, QUANT, 128><<<grid, 128, 0, stream>>>(p);
+    const bool wide = ((reinterpret_cast<uintptr_t>(p.x) | reinterpret_cast<uintptr_t>(p.y)) & 31) == 0;
+    if (wide) {
+        if (p.n <= 2048) small_norm_kernel<1, QUANT, 128, true><<<grid, 128, 0, stream>>>(p);
+        else if (p.n <= 4096) small_norm_kernel<2, QUANT, 128, true><<<grid, 128, 0, stream>>>(p);
+        else small_norm_kernel<4, QUANT, 128, true><<<grid, 128, 0, stream>>>(p);
+    } else {
+        if (p.n <= 2048) small_norm_kernel<1, QUANT, 128, false><<<grid, 128, 0, stream>>>(p);
+        else if (p.n <= 4096) small_norm_kernel<2, QUANT, 128, false><<<grid, 128, 0, stream>>>(p);
+        else small_norm_kernel<4, QUANT, 128, false><<<grid, 128, 0, stream>>>(p);
+    }
 }
 
 // WIDE (256-bit loads) needs a 32-byte aligned input
@@ -607,7 +636,8 @@ int small_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int
         launch_units<SOP_SILU, __nv_bfloat16, 2>(p, spans, units, unsigned(grid), wide, stream);
         return check_launch("small_units_kernel");
     }
-    small_stream_kernel<SOP_SILU, __nv_bfloat16><<<unsigned(M), 128, 0, stream>>>(p);
+    if (wide) small_stream_kernel<SOP_SILU, __nv_bfloat16, true><<<unsigned(M), 128, 0, stream>>>(p);
+    else small_stream_kernel<SOP_SILU, __nv_bfloat16, false><<<unsigned(M), 128, 0, stream>>>(p);
     return check_launch("small_stream_kernel");
 }
 
@@ -667,9 +697,17 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
     if (grid > max_parts) grid = max_parts;
     if (grid > M) grid = M;
     *parts = int(grid);
-    if (n <= 2048) small_norm_bwd_kernel<1, 128, 3><<<unsigned(grid), 128, 0, stream>>>(p, g, partial);
-    else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3><<<unsigned(grid), 128, 0, stream>>>(p, g, partial);
-    else small_norm_bwd_kernel<2, 256, 1><<<unsigned(grid), 256, 0, stream>>>(p, g, partial);
+    const bool wide = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) & 31) == 0;
+    const unsigned gd = unsigned(grid);
+    if (wide) {
+        if (n <= 2048) small_norm_bwd_kernel<1, 128, 3, true><<<gd, 128, 0, stream>>>(p, g, partial);
+        else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3, true><<<gd, 128, 0, stream>>>(p, g, partial);
+        else small_norm_bwd_kernel<2, 256, 1, true><<<gd, 256, 0, stream>>>(p, g, partial);
+    } else {
+        if (n <= 2048) small_norm_bwd_kernel<1, 128, 3, false><<<gd, 128, 0, stream>>>(p, g, partial);
+        else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3, false><<<gd, 128, 0, stream>>>(p, g, partial);
+        else small_norm_bwd_kernel<2, 256, 1, false><<<gd, 256, 0, stream>>>(p, g, partial);
+    }
     return check_launch("small_norm_bwd_kernel");
 }
 
