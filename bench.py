@@ -301,7 +301,7 @@ def run_ours(args, rank, world, device):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the SwiGLU+quant kernel at the
 # bench size, scaled from an ncu capture of a smaller case (see profiles/); None until measured.
-TRAFFIC_SWIGLU_BYTES = 2561144832
+TRAFFIC_SWIGLU_BYTES = 2564161536
 
 
 def cpu_baseline(rows, repeats=1):
