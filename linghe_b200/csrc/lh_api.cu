@@ -143,7 +143,8 @@ int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t 
 int64_t rows_norm_bwd_scratch(int64_t n);
 int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
-                  cudaStream_t stream);
+                  cudaStream_t stream, void* dy_q = nullptr, float* dy_s = nullptr, int round_scale = 0,
+                  int* dy_rows_done = nullptr);
 int64_t rows_norm_bwd_static_bytes();
 int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                          int64_t n, float eps, void* dx, float* dgamma, cudaStream_t stream);
@@ -361,8 +362,13 @@ int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, 
                               void* dy_qt, float* dy_st, int round_scale, void* scratch, int64_t scratch_bytes,
                               void* stream) {
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (int rc = rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes, cs)) return rc;
-    return tile_quant(dy, dtype, nullptr, 0, 1, M, n, dy_q, dy_s, dy_qt, dy_st, round_scale, 2, 0, cs);
+    // Where the backward runs as the streaming kernel it also quantises dy row-wise from the registers
+    // it already holds, and the tile kernel is left with the transposed copy only.
+    int rows_done = 0;
+    if (int rc = rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes, cs, dy_q, dy_s,
+                               round_scale, &rows_done))
+        return rc;
+    return tile_quant(dy, dtype, nullptr, 0, 1, M, n, dy_q, dy_s, dy_qt, dy_st, round_scale, rows_done ? 1 : 2, 0, cs);
 }
 
 int lh_weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,

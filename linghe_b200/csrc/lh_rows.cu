@@ -16,7 +16,8 @@
 namespace lh {
 
 int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
-                   void* dx, float* partial, int max_parts, int* parts, cudaStream_t stream);
+                   void* dx, float* partial, int max_parts, int* parts, void* dy_q, float* dy_s, int round_scale,
+                   cudaStream_t stream);
 
 enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3, ROP_NORM_YQ = 4 };
 
@@ -804,9 +805,12 @@ int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t 
 
 int64_t rows_norm_bwd_scratch(int64_t n) { return int64_t(kMaxRowCtas) * n * 4; }
 
+// dy_q / dy_s (optional): where the streaming kernel runs it also writes the row-wise 1x128 codes
+// and scales ([n/128, M]) of dy and sets *dy_rows_done; otherwise they are left untouched.
 int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, void* dy_q, float* dy_s, int round_scale, int* dy_rows_done) {
+    if (dy_rows_done) *dy_rows_done = 0;
     if (int rc = check_rows("rmsnorm_bwd", dtype, M, n)) return rc;
     if (!x || !dy || !gamma || !dx || !dgamma) return fail_arg("rmsnorm_bwd: NULL pointer");
     if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(gamma)) return fail_arg("rmsnorm_bwd: pointers must be 16-byte aligned");
@@ -829,7 +833,11 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
         return !strcmp(e, "small") ? 1 : (!strcmp(e, "ring") ? 2 : 0);
     }();
     if (forced ? forced == 1 : n > 2048) {
-        if (int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, stream)) return rc;
+        const bool qdy = dy_q != nullptr && dy_s != nullptr && aligned16(dy_q) && dy_rows_done != nullptr;
+        if (int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, qdy ? dy_q : nullptr,
+                                    dy_s, round_scale, stream))
+            return rc;
+        if (qdy) *dy_rows_done = 1;
     } else if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream)) {
         return rc;
     }

@@ -362,7 +362,7 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
 // The loads of the next row are issued before the second pass over the current one, so every
 // resident CTA always has a row in flight.  Per-CTA sums go to partial[blockIdx.x][n]; a second
 // kernel adds them in a fixed order.
-template <int SPANS, int NT, int MINB, bool WIDE>
+template <int SPANS, int NT, int MINB, bool WIDE, bool QDY>
 __global__ void __launch_bounds__(NT, MINB)
 small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
     constexpr int SPAN = 16 * NT, NW = NT / 32;
@@ -450,6 +450,30 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
         for (int i = 0; i < SPANS; ++i) {
             const int col = i * SPAN + t * 16;
             uint32_t o[8];
+            // QDY: the row-wise 1x128 codes and scales of dy from the same registers (bit-exact):
+            // block maximum on the packed words (8 lanes = one block), then exact quotients
+            float qs = 0.f, qny = 0.f;
+            bool qtiny = false;
+            uint32_t qc[4];
+            if constexpr (QDY) {
+                const uint32_t w8[8] = {gc[2 * i].x, gc[2 * i].y, gc[2 * i].z, gc[2 * i].w,
+                                        gc[2 * i + 1].x, gc[2 * i + 1].y, gc[2 * i + 1].z, gc[2 * i + 1].w};
+                uint32_t m0 = w8[0] & 0x7fff7fffu, m1 = w8[1] & 0x7fff7fffu;
+#pragma unroll
+                for (int j = 2; j < 8; j += 2) {
+                    asm("max.bf16x2 %0, %0, %1;" : "+r"(m0) : "r"(w8[j] & 0x7fff7fffu));
+                    asm("max.bf16x2 %0, %0, %1;" : "+r"(m1) : "r"(w8[j + 1] & 0x7fff7fffu));
+                }
+                asm("max.bf16x2 %0, %0, %1;" : "+r"(m0) : "r"(m1));
+                float amax = fmaxf(__uint_as_float(m0 << 16), __uint_as_float(m0 & 0xffff0000u));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                qs = scale_from_amax(amax, p.round_scale != 0);
+                qtiny = qs < 8.0e-28f && amax > 0.f;      // residual of the exact quotient could underflow
+                qny = -__frcp_rn(qs);
+                if ((t & 7) == 0 && col < p.n) p.s[int64_t(col >> 7) * p.M + row] = qs;
+            }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 float2 x[4], g[4], w[4];
@@ -462,6 +486,20 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
                     acc[8 * i + 4 * h + j] = fma2(mul2(x[j], g[j]), r2, acc[8 * i + 4 * h + j]);
                     o[4 * h + j] = pack_bf16x2(d.x, d.y);
                 }
+                if constexpr (QDY) {
+                    float2 q[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) q[j] = quot_exact2(mul2(g[j], splat2(-1.f)), splat2(qs), splat2(qny));
+                    if (qtiny) {   // rare
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(g[j].x, qs), __fdiv_rn(g[j].y, qs));
+                    }
+                    qc[2 * h] = cvt_e4m3x4(q[0].x, q[0].y, q[1].x, q[1].y);
+                    qc[2 * h + 1] = cvt_e4m3x4(q[2].x, q[2].y, q[3].x, q[3].y);
+                }
+            }
+            if constexpr (QDY) {
+                if (col < p.n) *reinterpret_cast<uint4*>(p.q + row * p.n + col) = make_uint4(qc[0], qc[1], qc[2], qc[3]);
             }
             if (col < p.n) {
                 uint8_t* dst = p.y + (row * p.n + col) * 2;
@@ -681,11 +719,13 @@ int small_norm_y(const void* x, const void* gamma, int64_t M, int64_t n, float e
 // dx as bf16 [M, n]; partial: [grid, n] fp32 scratch rows (grid <= max_parts); returns the grid
 // in *parts.  n <= 8192, 16-byte aligned pointers, bf16 inputs.
 int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
-                   void* dx, float* partial, int max_parts, int* parts, cudaStream_t stream) {
+                   void* dx, float* partial, int max_parts, int* parts, void* dy_q, float* dy_s, int round_scale,
+                   cudaStream_t stream) {
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.gamma = static_cast<const uint8_t*>(gamma); p.M = M; p.n = int(n);
     p.eps = eps; p.inv_n = 1.0f / float(n); p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr;
     p.y = static_cast<uint8_t*>(dx);
+    p.q = static_cast<uint8_t*>(dy_q); p.s = dy_s; p.round_scale = round_scale;
     const uint8_t* g = static_cast<const uint8_t*>(dy);
     static int sms = 0;
     if (sms == 0) {
@@ -699,15 +739,20 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
     *parts = int(grid);
     const bool wide = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) & 31) == 0;
     const unsigned gd = unsigned(grid);
-    if (wide) {
-        if (n <= 2048) small_norm_bwd_kernel<1, 128, 3, true><<<gd, 128, 0, stream>>>(p, g, partial);
-        else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3, true><<<gd, 128, 0, stream>>>(p, g, partial);
-        else small_norm_bwd_kernel<2, 256, 1, true><<<gd, 256, 0, stream>>>(p, g, partial);
-    } else {
-        if (n <= 2048) small_norm_bwd_kernel<1, 128, 3, false><<<gd, 128, 0, stream>>>(p, g, partial);
-        else if (n <= 4096) small_norm_bwd_kernel<2, 128, 3, false><<<gd, 128, 0, stream>>>(p, g, partial);
-        else small_norm_bwd_kernel<2, 256, 1, false><<<gd, 256, 0, stream>>>(p, g, partial);
-    }
+    const bool qdy = dy_q != nullptr;
+#define LH_BWD_LAUNCH(S, NT_, MB, W, Q) small_norm_bwd_kernel<S, NT_, MB, W, Q><<<gd, NT_, 0, stream>>>(p, g, partial)
+#define LH_BWD_PICK(W, Q)                                              \
+    do {                                                               \
+        if (n <= 2048) LH_BWD_LAUNCH(1, 128, 3, W, Q);                 \
+        else if (n <= 4096) LH_BWD_LAUNCH(2, 128, 3, W, Q);            \
+        else LH_BWD_LAUNCH(2, 256, 1, W, Q);                           \
+    } while (0)
+    if (wide && qdy) LH_BWD_PICK(true, true);
+    else if (wide) LH_BWD_PICK(true, false);
+    else if (qdy) LH_BWD_PICK(false, true);
+    else LH_BWD_PICK(false, false);
+#undef LH_BWD_PICK
+#undef LH_BWD_LAUNCH
     return check_launch("small_norm_bwd_kernel");
 }
 

@@ -282,9 +282,11 @@ def test_golden_rms_fwd_bwd():
         assert_rel_close(dw.to(torch.bfloat16), bf16(G[f"rmsbwd_{tag}_dw"]), "dw", 1e-2)
 
 
-def test_rms_bwd_fused_dy_quant():
+# rows wider than 2048: the streaming backward also writes dy's row-wise codes and scales, the tile
+# kernel only the transposed copy; (640, 2304) leaves the second span of a thread partly empty
+@pytest.mark.parametrize("M,n", [(1024, 2048), (1024, 4096), (640, 2304), (384, 8192)])
+def test_rms_bwd_fused_dy_quant(M, n):
     from linghe_b200.utils.norm import rms_norm_backward_and_block_quant
-    M, n = 1024, 2048
     x = randn_bf16((M, n), 21)
     g = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(22))).to(torch.bfloat16)
     dy = randn_bf16((M, n), 23, 1, 0.01)
@@ -293,6 +295,13 @@ def test_rms_bwd_fused_dy_quant():
     assert_rel_close(dx, rdx, "dx", 1e-2)
     assert_rel_close(dw, rdw, "dgamma", 1e-3, 1e-5)
     check_exact((q, s, qt, st), O.blockwise_quant(dy, False), ("dy q", "dy s", "dy qt", "dy st"))
+    # power-of-two scales, and zero / negative-zero / tiny blocks in dy
+    dy2 = dy.clone()
+    dy2[0, :128] = 0
+    dy2[1, :128] = -0.0
+    dy2[2, :256] = dy2[2, :256] * 1e-30
+    _, _, q, s, qt, st = rms_norm_backward_and_block_quant(_cuda(dy2), _cuda(x), _cuda(g), round_scale=True)
+    check_exact((q, s, qt, st), O.blockwise_quant(dy2, True), ("dy q", "dy s", "dy qt", "dy st"))
 
 
 # ------------------------------------------------------------------------------------
