@@ -390,7 +390,7 @@ int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void*
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
     if (output_mode == 0) {
-        if (use_small_rows(whole_spans(n) ? 0 : M * n))
+        if (use_small_rows(0))   // the register kernels at every size and width; the ring only when forced
             return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
         return rows_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
     }

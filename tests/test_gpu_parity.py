@@ -336,6 +336,12 @@ def test_silu_fwd_modes(M, N, coef):
     check_fused(q, rq, s, rs, "mode0 row")
     _, _, qt, st = triton_silu_and_block_quant_forward(xd, output_mode=1)
     check_fused(qt, rqt, st, rst, "mode1 col")
+    # an input that is 16- but not 32-byte aligned takes the 128-bit loads
+    buf = torch.empty(M * N + 8, dtype=torch.bfloat16, device="cuda")
+    xo = buf[8:].view(M, N)
+    xo.copy_(x)
+    q, s, _, _ = triton_silu_and_block_quant_forward(xo, output_mode=0)
+    check_fused(q, rq, s, rs, "mode0 row (offset input)")
 
 
 @pytest.mark.parametrize("M,N,coef,gcoef", [(1024, 1024, 1.0, 1.0), (512, 2816, 1.0, 0.01), (256, 4096, 100.0, 100.0),
