@@ -651,6 +651,21 @@ int small_group_quant(const void* x, int dtype, int64_t M, int64_t n, void* q, f
     p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
     p.q = static_cast<uint8_t*>(q); p.s = s; p.scale_rowmajor = scale_rowmajor; p.round_scale = round_scale;
     const bool wide = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+    if ((n % 2048) != 0) {   // any width: 16 consecutive 1x128 blocks per unit (see small_units_kernel)
+        const int nb = int(n / 128);
+        const int64_t funits = (M * nb + 15) / 16;
+        const int64_t fgrid = (funits + 1) / 2;
+        if (fgrid > 0x7fffffff) return fail_arg("too many rows");
+        const unsigned fg = unsigned(fgrid);
+        if (dtype == LH_F16) {
+            if (wide) small_units_kernel<SOP_GROUP, __half, 2, true, true><<<fg, 128, 0, stream>>>(p, nb, funits);
+            else small_units_kernel<SOP_GROUP, __half, 2, false, true><<<fg, 128, 0, stream>>>(p, nb, funits);
+        } else {
+            if (wide) small_units_kernel<SOP_GROUP, __nv_bfloat16, 2, true, true><<<fg, 128, 0, stream>>>(p, nb, funits);
+            else small_units_kernel<SOP_GROUP, __nv_bfloat16, 2, false, true><<<fg, 128, 0, stream>>>(p, nb, funits);
+        }
+        return check_launch("small_units_kernel");
+    }
     const int spans = int((n + 2047) / 2048);
     const int64_t units = M * spans;
     // three units per CTA once the problem is many waves long (measured: 251 vs 259 us at
