@@ -330,6 +330,12 @@ def run_reference(args, rank, world):
     """Reference arm: the reference's own CPU math (oracle port) on the host cores."""
     if rank != 0:
         return None
+    # torchrun sets OMP_NUM_THREADS=1 for multi-rank launches; the CPU arm uses every core it may run on
+    try:
+        ncores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        ncores = os.cpu_count() or 1
+    torch.set_num_threads(max(ncores, 1))
     rows = args.cpu_rows
     from oracle import oracle as O  # noqa: F401
     res = []
@@ -384,8 +390,6 @@ def main():
     device = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL's own log lines (its version banner) go to stderr, so that stdout carries the JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
         line = run_ours(args, rank, world, device)
