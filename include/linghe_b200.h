@@ -64,6 +64,19 @@ int lh_device_check(int device);
  * gave up on a bounded wait) and clears it.  Synchronises the device. */
 int lh_device_status(int* status);
 
+/* Self-test of the give-up path of the kernels' bounded waits.  Launches one warp that
+ * waits `polls` polls (1..65536) on a barrier nobody arrives at, records the status code
+ * of a timed-out tile wait (1) in the device status word and returns, as a production
+ * kernel whose copy never landed would.  lh_device_status() then reports 1 once and 0
+ * afterwards.  No counterpart in the reference (Triton kernels have no such waits).
+ *
+ * Every wait inside the kernels is bounded (about two seconds of SM clock).  A wait that
+ * runs out does not abort the kernel: the kernel finishes with undefined outputs and the
+ * status word set, and entry points keep returning 0 because they never synchronise.
+ * Callers that want to detect this poll lh_device_status() at a point where they
+ * synchronise anyway (end of a step). */
+int lh_selftest_wait_timeout(int polls, void* stream);
+
 /* Scratch bytes needed by the entry point named `what` ("rmsnorm_bwd",
  * "batch_silu_bwd") for the given sizes; 0 if it needs none, <0 if unknown. */
 int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols);
@@ -161,8 +174,11 @@ int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float
  *     in it.  Nothing needs clearing (each call overwrites every partial row it later
  *     reads), but two calls whose kernels overlap on the GPU -- different streams, or
  *     different host threads on different streams -- race on it: serialise them.
- * Arguments as lh_rmsnorm_bwd without the scratch pair; results match it (bit for bit on
- * a 148-SM B200, where both run the same grid). */
+ * Arguments as lh_rmsnorm_bwd without the scratch pair.  dx and dgamma agree with
+ * lh_rmsnorm_bwd to within float32 summation order: for n <= 2048 on a 148-SM device both
+ * run the same kernel on the same grid and the results are bit-identical; for wider rows
+ * lh_rmsnorm_bwd takes a different kernel, so the last bits of dgamma (and, through the
+ * row sums, of a few dx values) may differ. */
 int lh_rmsnorm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype,
                           int64_t M, int64_t n, float eps, void* dx, float* dgamma, void* stream);
 

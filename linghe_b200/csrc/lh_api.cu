@@ -27,6 +27,20 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int 
     }
 }
 
+// One warp waits on a barrier that never completes, with a short poll limit: exercises the
+// give-up path (status word, normal return) without any production kernel having to fail.
+__global__ void __launch_bounds__(32) selftest_wait_kernel(uint32_t polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    bool dead = false;
+    if (!mbar_wait_polls(&bar, 0, DEVERR_FULL_WAIT, polls)) dead = true;
+    mbar_wait_or_mark<true>(&bar, 0, DEVERR_EMPTY_WAIT, dead);   // a dead thread skips later waits
+}
+
 static thread_local char tl_error[512] = "";
 
 void set_error(const char* fmt, ...) {
@@ -137,7 +151,6 @@ int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, cons
                   float* dws, int round_scale, cudaStream_t stream);
 int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* q,
                     float* s, float* rms, int round_scale, cudaStream_t stream);
-int rows_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream);
 int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
                 float* rms, int reuse_rms, cudaStream_t stream);
 int64_t rows_norm_bwd_scratch(int64_t n);
@@ -195,23 +208,21 @@ int lh_device_status(int* status) {
     return LH_OK;
 }
 
+int lh_selftest_wait_timeout(int polls, void* stream) {
+    if (polls < 1 || polls > 65536) return fail_arg("selftest_wait_timeout: polls must be in 1..65536");
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(uint32_t(polls));
+    return check_launch("selftest_wait_kernel");
+}
+
 // Row-only outputs of small and medium problems go to the one-CTA-per-row kernels, large ones to
-// the persistent TMA-ring kernels.  LH_ROW_PATH=small|ring forces one of them (for measurements).
+// the persistent TMA-ring kernels.
 // The one-CTA-per-row kernels give every thread 16 elements of each 2048-element span of the row:
 // rows that are a whole number of spans keep every thread busy, and then the streaming kernels
 // (SwiGLU+quant, plain norm, the pure 1x128 quantiser) are ahead of the ring and tile kernels at
 // every size (measured up to 65536 x 8192).
 static bool whole_spans(int64_t n) { return (n % 2048) == 0; }
 
-static bool use_small_rows(int64_t elements) {
-    static const int forced = [] {
-        const char* e = getenv("LH_ROW_PATH");
-        if (!e) return 0;
-        return !strcmp(e, "small") ? 1 : (!strcmp(e, "ring") ? 2 : 0);
-    }();
-    if (forced) return forced == 1;
-    return elements <= kSmallRowElements;
-}
+static bool use_small_rows(int64_t elements) { return elements <= kSmallRowElements; }
 
 int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!what) return -1;
@@ -226,7 +237,7 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
 int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, void* qt, float* st,
                        int round_scale, int output_mode, void* stream) {
     if (output_mode < 0 || output_mode > 2) return fail_arg("blockwise_quant: output_mode must be 0, 1 or 2");
-    if (output_mode == 0 && dtype != LH_F32 && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) &&
+    if (output_mode == 0 && (dtype == LH_BF16 || dtype == LH_F16) && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) &&
         aligned16(q) && use_small_rows(whole_spans(N) ? 0 : M * N))
         return small_group_quant(x, dtype, M, N, q, s, 0, round_scale, static_cast<cudaStream_t>(stream));
     return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, qt, st, round_scale, output_mode, 0,
@@ -235,7 +246,7 @@ int lh_blockwise_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, 
 
 int lh_group_quant(const void* x, int dtype, int64_t M, int64_t N, void* q, float* s, int round_scale,
                    void* stream) {
-    if (dtype != LH_F32 && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) && aligned16(q) &&
+    if ((dtype == LH_BF16 || dtype == LH_F16) && M > 0 && N > 0 && (N % 128) == 0 && x && q && s && aligned16(x) && aligned16(q) &&
         use_small_rows(whole_spans(N) ? 0 : M * N))
         return small_group_quant(x, dtype, M, N, q, s, 1, round_scale, static_cast<cudaStream_t>(stream));
     return tile_quant(x, dtype, nullptr, 0, 1, M, N, q, s, nullptr, nullptr, round_scale, 0, 1,
@@ -389,11 +400,8 @@ int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void*
     if (!x || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("silu_blockquant_fwd: NULL or unaligned pointer");
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
-    if (output_mode == 0) {
-        if (use_small_rows(0))   // the register kernels at every size and width; the ring only when forced
-            return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
-        return rows_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
-    }
+    if (output_mode == 0)   // the register kernels at every size and width
+        return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
     return tile_silu_fwd(x, nullptr, LH_F32, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
                          static_cast<cudaStream_t>(stream));
 }

@@ -301,6 +301,28 @@ __device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity,
     return false;
 }
 
+// Wait used by the persistent kernels.  A wait that gives up does NOT make its thread leave the
+// kernel: the thread records the code, marks itself `dead` and carries on with whatever the
+// buffer holds, so every thread of the CTA still reaches every barrier, drains its stores and
+// writes its partial results.  A dead thread skips all later waits, so a kernel spends at most
+// one time limit per thread (they run out in parallel) before it finishes with the status word
+// set; outputs of such a launch are undefined and the host learns of it from lh_device_status().
+template <bool INLINE>
+__device__ __forceinline__ void mbar_wait_or_mark(uint64_t* bar, uint32_t parity, int code, bool& dead) {
+    if (dead) return;
+    const bool ok = INLINE ? mbar_wait_inline(bar, parity, code) : mbar_wait(bar, parity, code);
+    if (!ok) dead = true;
+}
+
+// The same bounded wait with a caller-chosen number of polls (self-test of the give-up path).
+__device__ __forceinline__ bool mbar_wait_polls(uint64_t* bar, uint32_t parity, int code, uint32_t polls) {
+#pragma unroll 1
+    for (uint32_t i = 0; i < polls; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicCAS(&g_device_status, 0, code);
+    return false;
+}
+
 // global -> shared bulk copy, completion counted in bytes on `bar`.
 // src, dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {

@@ -1,12 +1,10 @@
-// Row-slab kernels: RMSNorm forward (+1x128 FP8 quantisation, or plain), RMSNorm backward,
-// and SwiGLU forward + 1x128 quantisation -- the operations whose outputs depend on a
-// whole row or on nothing outside a 1x128 block, so they stream rows through the SM.
+// Row-slab kernels: RMSNorm forward (+1x128 FP8 quantisation, or plain) and RMSNorm backward
+// -- the operations whose outputs depend on a whole row, so they stream rows through the SM.
 //
-// Execution model (sm_100a): persistent CTAs walk slabs of at most 8192 output elements
-// (RB complete rows for the norm kernels; 64 consecutive 1x128 blocks of the row-major
-// output, whatever rows they fall in, for SwiGLU).  Warp 0 brings each slab into a
-// shared-memory ring with bulk asynchronous copies (TMA; rows are contiguous, so one copy
-// per operand and row run) that complete on an mbarrier.  Every thread owns EPT
+// Execution model (sm_100a): persistent CTAs walk slabs of at most 8192 elements (RB complete
+// rows).  Thread 0 of warp 0 brings each slab into a shared-memory ring with bulk asynchronous
+// copies (TMA; the rows of a slab are contiguous, so one copy per operand) that complete on an
+// mbarrier.  Every thread owns EPT
 // contiguous elements: it pulls them into registers (freeing the ring slot at once), does
 // the arithmetic with packed float32x2 instructions, reduces per-row sums through
 // shuffles and one named barrier, and stages the outputs in shared memory from where one
@@ -19,7 +17,7 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
                    void* dx, float* partial, int max_parts, int* parts, void* dy_q, float* dy_s, int round_scale,
                    cudaStream_t stream);
 
-enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_SILU_Q = 3, ROP_NORM_YQ = 4 };
+enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_NORM_YQ = 4 };
 
 constexpr int kSlabElems = 8192;
 constexpr int kMaxRowCtas = 592;   // four CTAs per SM at most
@@ -44,8 +42,8 @@ struct RowParams {
 
 template <int ROP, int EPT, int STAGES>
 struct RowCfg {
-    static constexpr int NIN = (ROP == ROP_NORM_BWD || ROP == ROP_SILU_Q) ? 2 : 1;
-    static constexpr bool QUANT = ROP == ROP_NORM_Q || ROP == ROP_SILU_Q || ROP == ROP_NORM_YQ;
+    static constexpr int NIN = ROP == ROP_NORM_BWD ? 2 : 1;
+    static constexpr bool QUANT = ROP == ROP_NORM_Q || ROP == ROP_NORM_YQ;
     static constexpr int NT = kSlabElems / EPT;       // threads
     static constexpr int NW = NT / 32;
     static constexpr int SLABB = kSlabElems * 2;      // bytes of one operand slab (16-bit inputs)
@@ -71,7 +69,6 @@ rows_kernel(const __grid_constant__ RowParams p) {
     constexpr int NCH = EPT / 8;     // 16-byte chunks per thread and operand
     constexpr int NP = EPT / 2;      // float2 pairs per thread
     constexpr int LPB = 128 / EPT;   // lanes per 128-element block
-    constexpr bool NORM = ROP != ROP_SILU_Q;
     constexpr int OB = C::QUANT ? 1 : 2;          // bytes per output element
     constexpr int WSPAN = 32 * EPT;               // elements owned by one warp in a slab
     extern __shared__ __align__(128) uint8_t smem[];
@@ -85,11 +82,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
     const int warp = t >> 5, lane = t & 31;
     const int n = p.n;
     const int RB = p.RB;
-    const int nbk = n >> 7;                                   // 128-element blocks per row
-    // SwiGLU+quant has no row coupling: its slabs are 64 consecutive 1x128 blocks of the
-    // row-major output, whatever rows they fall in (full thread use for any n)
-    const int64_t total_blocks = p.M * int64_t(nbk);
-    const int64_t slabs = NORM ? (p.M + RB - 1) / RB : (total_blocks + 63) / 64;
+    const int64_t slabs = (p.M + RB - 1) / RB;
 
     if (t == 0) {
         for (int i = 0; i < STAGES; ++i) {
@@ -108,50 +101,15 @@ rows_kernel(const __grid_constant__ RowParams p) {
         return L;
     };
 
-    // Warp 0 doubles as the producer.  For SwiGLU+quant it walks (row, column block) of the
-    // first block of the slab it issues next, advanced by a fixed step per issue.
-    const int64_t sstep = 64 * int64_t(gridDim.x);
-    const int64_t sdq = NORM ? 0 : sstep / nbk;
-    const int sdr = NORM ? 0 : int(sstep - sdq * nbk);
-    int64_t prow = 0;
-    int pcb = 0;
-    if constexpr (!NORM) {
-        const int64_t b = int64_t(blockIdx.x) * 64;
-        prow = b / nbk;
-        pcb = int(b - prow * nbk);
-    }
+    // Lane 0 of warp 0 doubles as the producer.
     auto issue = [&](int64_t slab, int stage) {
         const SlabLoc L = locate(slab);
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
-        if constexpr (ROP == ROP_SILU_Q) {
-            // x is [M, 2n]: the slab's blocks cover a few (partial) rows; per row one run from
-            // the gate half and one from the up half, laid out in slab order
-            const int64_t bl = total_blocks - slab * 64;
-            const int nblk = bl < 64 ? int(bl) : 64;
-            if (lane == 0) mbar_expect_tx(&full[stage], uint32_t(nblk) * 128u * 2u * 2u);
-            __syncwarp();
-            for (int i = lane; ; i += 32) {                     // i-th row touched by the slab
-                const int first = i == 0 ? 0 : i * nbk - pcb;   // its first block, slab-relative
-                if (first >= nblk) break;
-                const int lo = i == 0 ? pcb : 0;
-                const int left = nblk - first;
-                const int cnt = left < nbk - lo ? left : nbk - lo;
-                const uint32_t run = uint32_t(cnt) * 256u;
-                const uint8_t* src = p.x + ((prow + i) * 2 * int64_t(n) + int64_t(lo) * 128) * 2;
-                const size_t off = size_t(first) * 256;
-                bulk_g2s(dst + off, src, run, &full[stage]);
-                bulk_g2s(dst + C::SLABB + off, src + size_t(n) * 2, run, &full[stage]);
-            }
-            prow += sdq;
-            pcb += sdr;
-            if (pcb >= nbk) { pcb -= nbk; ++prow; }
-        } else {
-            if (lane == 0) {
-                const uint32_t bytes = uint32_t(L.rows) * uint32_t(n) * 2u;
-                mbar_expect_tx(&full[stage], bytes * C::NIN);
-                bulk_g2s(dst, p.x + L.row0 * n * 2, bytes, &full[stage]);
-                if constexpr (ROP == ROP_NORM_BWD) bulk_g2s(dst + C::SLABB, p.dy + L.row0 * n * 2, bytes, &full[stage]);
-            }
+        if (lane == 0) {
+            const uint32_t bytes = uint32_t(L.rows) * uint32_t(n) * 2u;
+            mbar_expect_tx(&full[stage], bytes * C::NIN);
+            bulk_g2s(dst, p.x + L.row0 * n * 2, bytes, &full[stage]);
+            if constexpr (ROP == ROP_NORM_BWD) bulk_g2s(dst + C::SLABB, p.dy + L.row0 * n * 2, bytes, &full[stage]);
         }
     };
     if (warp == 0) {
@@ -164,65 +122,49 @@ rows_kernel(const __grid_constant__ RowParams p) {
     const bool rs = p.round_scale != 0;
     const bool reuse = ROP != ROP_NORM_Q && ROP != ROP_NORM_YQ && p.reuse_rms != 0;
 
-    // For the norm kernels a slab is RB full rows, so a thread's columns never change:
-    // keep gamma for them in registers, in the (swizzled) chunk order used for x.
-    float2 gam[NORM ? NP : 1];
-    int my_row = 0, col0 = 0;
-    bool in_slab = true;
-    if constexpr (NORM) {
-        my_row = e0 / n;
-        col0 = e0 - my_row * n;
-        in_slab = my_row < RB;
+    // A slab is RB full rows, so a thread's columns never change: keep gamma for them in
+    // registers, in the (swizzled) chunk order used for x.
+    float2 gam[NP];
+    const int my_row = e0 / n;
+    const int col0 = e0 - my_row * n;
+    const bool in_slab = my_row < RB;
 #pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-            uint4 raw = make_uint4(0, 0, 0, 0);
-            if (in_slab)
-                raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.gamma) + (col0 + 8 * (k ^ sw)) * 2);
-            gam[4 * k + 0] = bf16x2_to_f2(raw.x);
-            gam[4 * k + 1] = bf16x2_to_f2(raw.y);
-            gam[4 * k + 2] = bf16x2_to_f2(raw.z);
-            gam[4 * k + 3] = bf16x2_to_f2(raw.w);
-        }
+    for (int k = 0; k < NCH; ++k) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (in_slab)
+            raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.gamma) + (col0 + 8 * (k ^ sw)) * 2);
+        gam[4 * k + 0] = bf16x2_to_f2(raw.x);
+        gam[4 * k + 1] = bf16x2_to_f2(raw.y);
+        gam[4 * k + 2] = bf16x2_to_f2(raw.z);
+        gam[4 * k + 3] = bf16x2_to_f2(raw.w);
     }
     const int TPR = n / EPT;                       // threads per row (norm kernels)
     const bool warp_rows = (TPR % 32) == 0;        // rows are made of whole warps
     const int red_cnt = warp_rows ? TPR / 32 : (n >> 7);
     const int red_first = my_row * red_cnt;
-    const bool row_bar = NORM && warp_rows && RB <= 8 && RB * TPR == NT;   // the same for every thread
+    const bool row_bar = warp_rows && RB <= 8 && RB * TPR == NT;   // the same for every thread
     float2 acc[ROP == ROP_NORM_BWD ? NP : 1];
 #pragma unroll
     for (int i = 0; i < (ROP == ROP_NORM_BWD ? NP : 1); ++i) acc[i] = make_float2(0.f, 0.f);
-
-    // SwiGLU+quant: row / column block of this thread's 1x128 block, advanced incrementally
-    // from slab to slab (one 64-bit division per thread for the whole kernel)
-    int64_t srow = 0;
-    int scolb = 0;
-    if constexpr (!NORM) {
-        const int64_t b = int64_t(blockIdx.x) * 64 + t / LPB;
-        srow = b / nbk;
-        scolb = int(b - srow * nbk);
-    }
 
     int stage = 0, prev_stage = 0;
     uint32_t phase = 0, prev_phase = 0;
     int buf = 0;
     bool first_it = true;
+    bool dead = false;   // a bounded wait of this thread gave up (see mbar_wait_or_mark)
     for (int64_t slab = blockIdx.x; slab < slabs; slab += gridDim.x) {
         if (warp == 0 && !first_it) {
             // every warp released the previous stage early in the previous iteration
             const int64_t nxt = slab + int64_t(STAGES - 1) * gridDim.x;
-            if (nxt < slabs && mbar_wait_inline(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
+            if (nxt < slabs) {
+                mbar_wait_or_mark<true>(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT, dead);
+                if (!dead) issue(nxt, prev_stage);
+            }
         }
-        SlabLoc L = locate(slab);
-        int slab_elems = L.rows * n;                       // valid elements in this slab
-        if constexpr (!NORM) {
-            const int64_t bl = total_blocks - slab * 64;
-            slab_elems = (bl < 64 ? int(bl) : 64) * 128;
-            L.row0 = srow;                                 // this thread's row
-            col0 = scolb * 128 + (t % LPB) * EPT;
-        }
-        const bool active = NORM ? (in_slab && my_row < L.rows) : (e0 < slab_elems);
-        if (!mbar_wait_inline(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+        const SlabLoc L = locate(slab);
+        const int slab_elems = L.rows * n;                 // valid elements in this slab
+        const bool active = in_slab && my_row < L.rows;
+        mbar_wait_or_mark<true>(&full[stage], phase, DEVERR_FULL_WAIT, dead);
         const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
 
         float2 x[NP];
@@ -262,7 +204,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
         __syncwarp();
 
         float r = 0.f, tot_sc = 0.f;
-        if constexpr (NORM) {
+        {
             // ---- per-row sums: sum x^2 (unless 1/rms is given) and, backward, sum x*g*gamma
             float2 ss2 = make_float2(0.f, 0.f), ss3 = ss2, sc2 = ss2, sc3 = ss2;
             if (!reuse) {
@@ -330,7 +272,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
 
         uint8_t* so = outb + buf * C::OUTB + size_t(e0) * OB;
         if constexpr (C::QUANT) {
-            if constexpr (ROP == ROP_NORM_Q || ROP == ROP_NORM_YQ) {
+            {
                 const float2 r2 = splat2(r);
 #pragma unroll
                 for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(x[i], r2), gam[i]);
@@ -345,9 +287,6 @@ rows_kernel(const __grid_constant__ RowParams p) {
                                            pack_bf16x2(x[4 * k + 2].x, x[4 * k + 2].y), pack_bf16x2(x[4 * k + 3].x, x[4 * k + 3].y));
                     }
                 }
-            } else {
-#pragma unroll
-                for (int i = 0; i < NP; ++i) x[i] = mul2(mul2(sigmoid_fast2(x[i]), x[i]), g[i]);
             }
             float a0 = 0.f, a1 = 0.f;
 #pragma unroll
@@ -405,7 +344,7 @@ rows_kernel(const __grid_constant__ RowParams p) {
             cnt = cnt > WSPAN ? WSPAN : cnt;
             if (cnt > 0) {
                 uint8_t* gbase = C::QUANT ? p.q : p.hp;
-                const int64_t gofs = NORM ? L.row0 * n : slab * int64_t(kSlabElems);
+                const int64_t gofs = L.row0 * n;
                 bulk_s2g(gbase + (gofs + warp * WSPAN) * OB,
                          outb + buf * C::OUTB + size_t(warp) * WSPAN * OB, uint32_t(cnt) * OB);
             }
@@ -415,11 +354,6 @@ rows_kernel(const __grid_constant__ RowParams p) {
         prev_stage = stage; prev_phase = phase;
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         buf ^= 1;
-        if constexpr (!NORM) {
-            srow += sdq;
-            scolb += sdr;
-            if (scolb >= nbk) { scolb -= nbk; ++srow; }
-        }
     }
     if (lane == 0) bulk_wait_all();
 
@@ -544,15 +478,19 @@ normq_kernel(const __grid_constant__ RowParams p) {
     int stage = 0, prev_stage = 0, buf = 0;
     uint32_t phase = 0, prev_phase = 0;
     bool first_it = true;
+    bool dead = false;   // a bounded wait of this thread gave up (see mbar_wait_or_mark)
     for (int64_t grp = blockIdx.x; grp < groups; grp += gridDim.x) {
         if (t == 0 && !first_it) {
             const int64_t nxt = grp + int64_t(STAGES - 1) * gridDim.x;
-            if (nxt < groups && mbar_wait(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(nxt, prev_stage);
+            if (nxt < groups) {
+                mbar_wait_or_mark<false>(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT, dead);
+                if (!dead) issue(nxt, prev_stage);
+            }
         }
         const int64_t r0 = grp * GR;
         const int64_t left = p.M - r0;
         const int rows = int(left < GR ? left : GR);        // valid rows in this group
-        if (!mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)) return;
+        mbar_wait_or_mark<false>(&full[stage], phase, DEVERR_FULL_WAIT, dead);
         const uint8_t* sx = stages + size_t(stage) * C::STAGEB + size_t(e0) * 2;
         float* red_b = red + buf * (U * 64);
 
@@ -714,13 +652,8 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid
     using C = RowCfg<ROP, EPT, STAGES>;
     int64_t slabs;
     p.inv_n = 1.0f / float(p.n);
-    if (ROP == ROP_SILU_Q) {
-        p.RB = 1;
-        slabs = (p.M * (p.n / 128) + 63) / 64;      // 64 blocks of 1x128 per slab
-    } else {
-        p.RB = kSlabElems / p.n;
-        slabs = (p.M + p.RB - 1) / p.RB;
-    }
+    p.RB = kSlabElems / p.n;
+    slabs = (p.M + p.RB - 1) / p.RB;
     int64_t grid = int64_t(sm_count()) * CTAS_PER_SM;
     if (grid > grid_cap) grid = grid_cap;
     if (slabs < grid) grid = slabs;
@@ -784,13 +717,6 @@ int rows_norm_yq(const void* x, const void* gamma, int64_t M, int n, float eps, 
     return launch_rows<ROP_NORM_YQ, 32, 4, 2>(p, nullptr, stream);
 }
 
-int rows_silu_quant(const void* x, int64_t M, int64_t n, void* q, float* s, int round_scale, cudaStream_t stream) {
-    RowParams p{};
-    p.x = static_cast<const uint8_t*>(x); p.M = M; p.n = int(n);
-    p.q = static_cast<uint8_t*>(q); p.s = s; p.round_scale = round_scale;
-    return launch_rows<ROP_SILU_Q, 32, 2, 2>(p, nullptr, stream);
-}
-
 int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
                 float* rms, int reuse_rms, cudaStream_t stream) {
     if (int rc = check_rows("rmsnorm_fwd", dtype, M, n)) return rc;
@@ -826,13 +752,8 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     int grid = 0;
     // Rows wider than 2048 take the streaming register kernel (77 vs 83 us at 16384 x 4096, 279 vs
     // 301 us at 65536 x 4096, 354 vs 370 us at 32768 x 8192), narrower ones the TMA ring (159 vs
-    // 174 us at 65536 x 2048).  LH_BWD_PATH=small|ring forces one of them (for measurements).
-    static const int forced = [] {
-        const char* e = getenv("LH_BWD_PATH");
-        if (!e) return 0;
-        return !strcmp(e, "small") ? 1 : (!strcmp(e, "ring") ? 2 : 0);
-    }();
-    if (forced ? forced == 1 : n > 2048) {
+    // 174 us at 65536 x 2048).
+    if (n > 2048) {
         const bool qdy = dy_q != nullptr && dy_s != nullptr && aligned16(dy_q) && dy_rows_done != nullptr;
         if (int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, qdy ? dy_q : nullptr,
                                     dy_s, round_scale, stream))

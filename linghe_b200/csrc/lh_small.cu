@@ -729,12 +729,7 @@ int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, flo
     // Long runs of wide rows: the persistent walk (263 vs 271 us at 65536 x 8192, and 266 us for
     // the TMA ring); everything else one CTA per row.
     if (p.n > 4096 && M * n > (int64_t(24) << 20)) {
-        static int sms = 0;
-        if (sms == 0) {
-            int dev = 0;
-            cudaGetDevice(&dev);
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        }
+        const int sms = sm_count();
         if ((reinterpret_cast<uintptr_t>(x) & 31) == 0) small_norm_walk_kernel<4, true><<<unsigned(4 * sms), 128, 0, stream>>>(p);
         else small_norm_walk_kernel<4, false><<<unsigned(4 * sms), 128, 0, stream>>>(p);
         return check_launch("small_norm_walk_kernel");
@@ -766,12 +761,7 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
     p.y = static_cast<uint8_t*>(dx);
     p.q = static_cast<uint8_t*>(dy_q); p.s = dy_s; p.round_scale = round_scale;
     const uint8_t* g = static_cast<const uint8_t*>(dy);
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
+    const int sms = sm_count();
     int64_t grid = int64_t(sms) * (n <= 4096 ? 3 : 1);
     if (grid > max_parts) grid = max_parts;
     if (grid > M) grid = M;

@@ -451,13 +451,17 @@ tile_kernel(const __grid_constant__ TileParams p) {
     int stage = 0, prev_stage = 0;
     uint32_t phase = 0, prev_phase = 0;
     bool first_it = true;
+    bool dead = false;   // a bounded wait of this thread gave up (see mbar_wait_or_mark)
     for (int tile = int(blockIdx.x); tile < n_tiles; tile += int(gridDim.x)) {
         if (OP != OP_GATHER && tid == 0 && !first_it) {
             // the previous tile's stage is free once every warp has released it: refill it with
             // the tile STAGES-1 steps ahead.  Copies issued here are consumed by this CTA, so
             // none is in flight when the loop ends.
             const int64_t nxt = int64_t(tile) + int64_t(STAGES - 1) * gridDim.x;
-            if (nxt < n_tiles && mbar_wait_inline(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT)) issue(int(nxt), prev_stage);
+            if (nxt < n_tiles) {
+                mbar_wait_or_mark<true>(&empty[prev_stage], prev_phase, DEVERR_EMPTY_WAIT, dead);
+                if (!dead) issue(int(nxt), prev_stage);
+            }
         }
         const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab_ptr());
         const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
@@ -489,8 +493,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
         if constexpr (OP != OP_GATHER) {
             // Inline wait where a call would spill live registers around it; the transposed-only
             // norm instantiation has none to spill and measures 2 % faster with the call.
-            if (!(OP == OP_NORM && MODE == 1 ? mbar_wait(&full[stage], phase, DEVERR_FULL_WAIT)
-                                             : mbar_wait_inline(&full[stage], phase, DEVERR_FULL_WAIT))) return;
+            mbar_wait_or_mark<!(OP == OP_NORM && MODE == 1)>(&full[stage], phase, DEVERR_FULL_WAIT, dead);
         }
         const uint8_t* sbase = stages + size_t(stage) * C::STAGEB;
 
