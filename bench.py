@@ -60,59 +60,114 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken during the timed region."""
+    """SM clock / throttle-reason samples (read-only NVML queries from a thread, every few
+    milliseconds, each with a time stamp so that a phase of the run can be summarised by itself).
+    Falls back to an `nvidia-smi -lms` child process when NVML cannot be loaded."""
 
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, gpu_index):
-        self.idx = gpu_index
-        self.rows = []
-        self.proc = None
+    def __init__(self, cuda_index):
+        self.cuda_index = cuda_index
+        self.samples = []          # (t, sm_mhz, max_mhz, power_w, reasons bitmask)
+        self.stop_flag = threading.Event()
         self.thread = None
+        self.nv = None
+        self.handle = None
+        self.smi = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.idx}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            props = torch.cuda.get_device_properties(self.cuda_index)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(props.uuid)).encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(gpu_index())
+            self.nv = pynvml
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._pump_nvml, daemon=True)
+            self.thread.start()
             return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
-
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.rows.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
         except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            f = [c.strip() for c in r.split(",")]
+            self.nv = None
+        try:
+            q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+                 "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                 "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+            self.smi = subprocess.Popen(
+                ["nvidia-smi", f"--id={gpu_index()}", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump_smi, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.smi = None
+
+    def _pump_nvml(self):
+        nv = self.nv
+        bits = [(getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8), 0),
+                (getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40), 1),
+                (getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20), 2),
+                (getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4), 3)]
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons",
+                              getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None))
+        while not self.stop_flag.is_set():
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                raw = int(get_reasons(self.handle)) if get_reasons else 0
+                mask = 0
+                for bit, i in bits:
+                    if raw & bit:
+                        mask |= 1 << i
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((time.perf_counter(), mhz, self.max_mhz, watts, mask))
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def _pump_smi(self):
+        for line in self.smi.stdout:
+            f = [c.strip() for c in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
+                mask = 0
+                for i, v in enumerate(f[5:9]):
+                    if v.lower().startswith("active"):
+                        mask |= 1 << i
+                self.samples.append((time.perf_counter(), float(f[1]), float(f[2]), float(f[3]), mask))
             except ValueError:
                 continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+
+    def stop(self):
+        self.stop_flag.set()
+        if self.smi is not None:
+            time.sleep(0.15)
+            self.smi.terminate()
+            try:
+                self.smi.wait(timeout=5)
+            except Exception:
+                self.smi.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+
+    def summary(self, t0=None, t1=None):
+        """median SM clock and the throttle reasons seen among the samples taken in [t0, t1]"""
+        if self.nv is None and self.smi is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML and no nvidia-smi"], "samples": 0}
+        rows = [r for r in self.samples if (t0 is None or r[0] >= t0) and (t1 is None or r[0] <= t1)]
+        sm = sorted(r[1] for r in rows)
+        mask = 0
+        for r in rows:
+            mask |= r[4]
+        watts = [r[3] for r in rows if r[3] is not None]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max((r[2] for r in rows), default=None),
+                "reasons": [n for i, n in enumerate(self.NAMES) if mask & (1 << i)], "samples": len(sm),
+                "power_w_max": round(max(watts), 1) if watts else None,
+                "source": "nvml" if self.nv is not None else "nvidia-smi"}
 
 
 def gpu_index():
@@ -175,6 +230,7 @@ def run_ours(args, rank, world, device):
     torch.cuda.synchronize()
     t_start = torch.cuda.Event(enable_timing=True)
     t_stop = torch.cuda.Event(enable_timing=True)
+    t_timed0 = time.perf_counter()
     t_start.record()
     for i in range(K):
         ev[i][0].record()
@@ -184,10 +240,28 @@ def run_ours(args, rank, world, device):
         ev[i][2].record()
     t_stop.record()
     torch.cuda.synchronize()
+    t_timed1 = time.perf_counter()
     barrier()
     total_ms = t_start.elapsed_time(t_stop)
     norm_ms = sum(e[0].elapsed_time(e[1]) for e in ev) / K
     silu_ms = sum(e[1].elapsed_time(e[2]) for e in ev) / K
+
+    # ---- sustained: the same step back to back for about two seconds, with the clocks sampled
+    # over exactly that window (the K-step region above is shorter than most sampling periods)
+    n_sus = max(K, int(args.sustained_s * 1e3 / max(total_ms / K, 1e-3)) + 1) if args.sustained_s > 0 else 0
+    sus_ms, sus_t0, sus_t1 = 0.0, None, None
+    if n_sus:
+        u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        sus_t0 = time.perf_counter()
+        u0.record()
+        for _ in range(n_sus):
+            step()
+        u1.record()
+        torch.cuda.synchronize()
+        sus_t1 = time.perf_counter()
+        sus_ms = u0.elapsed_time(u1)
+    barrier()
 
     # ---- end to end through the public API with host buffers --------------------------
     Ke = min(K, args.e2e_steps)
@@ -251,12 +325,19 @@ def run_ours(args, rank, world, device):
     torch.cuda.synchronize()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()   # samples span warm-up, the timed loop and the end-to-end loop
+    sampler.stop()
+    # the K-step region and the sustained loop run the same two kernels back to back: their
+    # samples together describe the clocks the reported numbers were taken at
+    clocks = sampler.summary(t_timed0, sus_t1 if sus_t1 is not None else t_timed1)
+    clocks["window"] = "timed K steps + sustained loop"
+    clocks["whole_run"] = sampler.summary()
 
-    times = torch.tensor([total_ms, e2e_ms, norm_ms, silu_ms], device=device, dtype=torch.float64)
+    times = torch.tensor([total_ms, e2e_ms, norm_ms, silu_ms, sus_ms], device=device, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    total_ms, e2e_ms, norm_ms, silu_ms = times.tolist()
+    total_ms, e2e_ms, norm_ms, silu_ms, sus_ms = times.tolist()
+
+    validated = validate_sharding(rank, world, device, gamma)
 
     if rank != 0:
         return None
@@ -288,20 +369,160 @@ def run_ours(args, rank, world, device):
                          "swiglu_quant": round(bytes_silu / silu_ms / 1e6, 1)},
         "roofline": {"bound": "hbm", "kernel": "small_units_kernel<SILU, 2> (SwiGLU + 1x128 quant, dominant launch of the step)",
                      "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {peak_kind}",
-                     "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": int(TRAFFIC_SWIGLU_BYTES * rows / ROWS)},
+                     "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": int(TRAFFIC_SWIGLU_BYTES * rows / TRAFFIC_CAPTURE_ROWS),
+                     "traffic_note": TRAFFIC_NOTE,
+                     "second_kernel": {"kernel": "RMSNorm + 1x128 quant launch of the step",
+                                       "achieved": round(bytes_norm / norm_ms / 1e6, 1),
+                                       "frac": round(bytes_norm / norm_ms / 1e6 / peak, 4),
+                                       "frac_of_nominal_8TBs": round(bytes_norm / norm_ms / 1e6 / NOMINAL_HBM_GBS, 4)}},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": Ke},
         "gpu_launches": 2 * K,
         "clocks": clocks,
+        "validated": validated,
     }
+    if n_sus:
+        sus_value = world * step_bytes * n_sus / (sus_ms * 1e-3) / 1e9
+        line["sustained"] = {"gbs": round(sus_value, 1), "seconds": round(sus_ms * 1e-3, 2), "steps": n_sus,
+                             "ms_per_step": round(sus_ms / n_sus, 4),
+                             "pct_of_nominal_8TBs_per_gpu": round(100 * sus_value / world / NOMINAL_HBM_GBS, 1),
+                             "clocks": sampler.summary(sus_t0, sus_t1)}
+    if world == 1 and not args.no_configs:
+        line.update(other_configs(args, peak))
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(args.cpu_rows, repeats=1)
     return line
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the SwiGLU+quant kernel at the
-# bench size, scaled from an ncu capture of a smaller case (see profiles/); None until measured.
+def validate_sharding(rank, world, device, gamma):
+    """Outside every timed region: both kernels (row-wise and transposed outputs) on this rank's
+    128-aligned row slice of one seeded 4096-row tensor; the slices are all-gathered over NCCL and
+    rank 0 compares the assembled tensors bit for bit with its own single-GPU run on all 4096
+    rows.  With one GPU the same code runs as two virtual shards, one after the other."""
+    from linghe_b200.tools import shard as S
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward as norm_q
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward as silu_q
+    rows = 4096
+    try:
+        g = torch.Generator().manual_seed(4242)
+        x = torch.randn((rows, HIDDEN), generator=g).to(torch.bfloat16)
+        xs = torch.randn((rows, 2 * HIDDEN), generator=g).to(torch.bfloat16)
+
+        def f_norm(xl):
+            q, s_, _, qt, st = norm_q(xl, gamma, output_mode=2)
+            return q, s_, qt, st
+
+        def f_silu(xl):
+            return silu_q(xl, output_mode=2)
+
+        def u8(t):
+            return t.view(torch.uint8) if t.dtype == torch.float8_e4m3fn else t
+
+        if world > 1:
+            got = [S.run_sharded(f, t, world, rank, device) for f, t in ((f_norm, x), (f_silu, xs))]
+        else:
+            got = []
+            for f, t in ((f_norm, x), (f_silu, xs)):
+                parts = [f(t[a:b].contiguous().to(device)) for a, b in (S.shard_rows(rows, 2, 0), S.shard_rows(rows, 2, 1))]
+                got.append((torch.cat([u8(p[0]) for p in parts], 0), torch.cat([p[1] for p in parts], 1),
+                            torch.cat([u8(p[2]) for p in parts], 1), torch.cat([p[3] for p in parts], 0)))
+        ok = True
+        if rank == 0:
+            ref = [f_norm(x.to(device)), f_silu(xs.to(device))]
+            for gt, rf in zip(got, ref):
+                for a, b in zip(gt, rf):
+                    ok = ok and bool(torch.equal(u8(a), u8(b)))
+        torch.cuda.synchronize()
+        return {"ranks": world, "shards": max(world, 2), "rows": rows, "ok": ok,
+                "what": "RMSNorm+quant and SwiGLU+quant, codes + scales on both axes, sharded == single GPU bit for bit",
+                "gather": "NCCL all_gather" if world > 1 else "none (two virtual shards on one GPU)"}
+    except Exception as e:  # validation must not lose the measurement
+        return {"ranks": world, "ok": False, "error": f"{type(e).__name__}: {e}"}
+
+
+def other_configs(args, peak):
+    """Per-call times of the remaining benchmark configurations (cfg1-cfg4: the other shapes the
+    metric names) with the same harness as linghe_b200/tools/bench_configs.py: CUDA-graph replay
+    over rotating input/output sets larger than twice L2, plus the un-graphed CUDA-event time of
+    a single call through the Python API.  With the upstream package installed under
+    baseline/_ref its Triton kernels are timed in the same process on the same tensors, for the
+    two calls of the benchmark step and for every configuration."""
+    out = {}
+    t_begin = time.perf_counter()
+    try:
+        from linghe_b200.tools import bench_configs as BC
+    except Exception as e:
+        return {"configs": {"error": f"{type(e).__name__}: {e}"}}
+
+    def run_cases(mods, only_prefix, budget_s, suffix=""):
+        res = {}
+        for name, (make_args, fn, nbytes, set_bytes) in BC.build_cases(mods).items():
+            if not (name.startswith(only_prefix) and name.endswith(suffix)):
+                continue
+            if time.perf_counter() - t_begin > budget_s:
+                res[name] = {"skipped": "time budget of the default run"}
+                continue
+            try:
+                ev_us, gr_us, nsets = BC.time_call(make_args, fn, set_bytes, 50 if nbytes < 1e9 else 12)
+            except Exception as e:
+                res[name] = {"error": f"{type(e).__name__}: {e}"[:200]}
+                continue
+            us = gr_us if gr_us is not None else ev_us
+            gbs = nbytes / us / 1e3
+            res[name] = {"us": round(us, 2), "event_us": round(ev_us, 2), "gbs": round(gbs, 1),
+                         "frac_nominal": round(gbs / NOMINAL_HBM_GBS, 4), "frac_measured": round(gbs / peak, 4)}
+        return res
+
+    prefixes = ("cfg1", "cfg2", "cfg3", "cfg4")
+    mine = {}
+    for pfx in prefixes:
+        mine.update(run_cases(BC.ours(), pfx, args.configs_budget_s))
+    out["configs"] = mine
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if args.no_upstream:
+        out["upstream_triton"] = {"unavailable": "--no-upstream"}
+        return out
+    try:
+        ups = BC.upstream(ref_dir)
+    except Exception as e:
+        out["upstream_triton"] = {"unavailable": f"cannot import upstream from baseline/_ref: {type(e).__name__}: {e}"[:240]}
+        return out
+    try:
+        rows_case = run_cases(ups, "cfg5", args.configs_budget_s * 2, " rows")   # the two calls of the benchmark step first
+        mine5 = run_cases(BC.ours(), "cfg5", args.configs_budget_s * 2, " rows")
+        up = {"source": "baseline/_ref (pip --target install of the unmodified reference), same process, same harness",
+              "us_per_call": {}, "gbs": {}, "speedup": {}}
+        for k, v in rows_case.items():
+            short = "rmsnorm_quant" if "rmsnorm" in k else "swiglu_quant"
+            if "us" in v and "us" in mine5.get(k, {}):
+                up["us_per_call"][short] = v["us"]
+                up["gbs"][short] = v["gbs"]
+                up["speedup"][short] = round(v["us"] / mine5[k]["us"], 3)
+                up.setdefault("ours_us_per_call", {})[short] = mine5[k]["us"]
+            else:
+                up["us_per_call"][short] = v
+        for pfx in prefixes:
+            for k, v in run_cases(ups, pfx, args.configs_budget_s * 3).items():
+                if k in mine and "us" in v and "us" in mine[k]:
+                    mine[k]["upstream_us"] = v["us"]
+                    mine[k]["upstream_event_us"] = v["event_us"]
+                    mine[k]["speedup"] = round(v["us"] / mine[k]["us"], 3)
+                elif k in mine:
+                    mine[k]["upstream"] = v
+        out["upstream_triton"] = up
+    except Exception as e:
+        out["upstream_triton"] = {"unavailable": f"{type(e).__name__}: {e}"[:240]}
+    return out
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the SwiGLU+quant kernel in an ncu
+# capture at TRAFFIC_CAPTURE_ROWS rows (profiles/); traffic grows in proportion to the rows, so the
+# bench line scales it by rows / TRAFFIC_CAPTURE_ROWS.
 TRAFFIC_SWIGLU_BYTES = 2564161536
+TRAFFIC_CAPTURE_ROWS = 65536
+TRAFFIC_NOTE = ("scaled from an 8192-row ncu capture; reads equal the algorithmic input bytes, writes read low "
+                "because part of the output is still dirty in L2 when the kernel ends (not a saving)")
 
 
 def cpu_baseline(rows, repeats=1):
@@ -372,6 +593,10 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--cpu-rows", type=int, default=4096)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sustained-s", type=float, default=2.0, help="length of the back-to-back loop (0: skip)")
+    ap.add_argument("--no-configs", action="store_true", help="skip the cfg1-cfg4 rows and the upstream column")
+    ap.add_argument("--no-upstream", action="store_true", help="do not time the upstream Triton kernels")
+    ap.add_argument("--configs-budget-s", type=float, default=60.0)
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))

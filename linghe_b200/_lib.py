@@ -106,31 +106,48 @@ def ptr(t):
     return None if t is None else t.data_ptr()
 
 
-def _check_device(dev: torch.device):
-    idx = dev.index if dev.index is not None else torch.cuda.current_device()
-    if idx in _checked_devices:
-        return
+def _check_device(idx: int):
     rc = load().lh_device_check(idx)
     if rc != 0:
         raise RuntimeError(f"linghe_b200: {last_error()}")
     _checked_devices.add(idx)
 
 
+_fn_cache = {}
+# raw cudaStream_t of torch's current stream on a device, without building a Stream object
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def _stream_of(idx: int) -> int:
+    if _raw_stream is not None:
+        return _raw_stream(idx)
+    return torch.cuda.current_stream(idx).cuda_stream
+
+
 def call(name: str, ref: torch.Tensor, *args):
     """Invoke entry point `name` on the device and current stream of tensor `ref`.
 
     Argument errors raise AssertionError (the upstream wrappers use bare asserts);
-    CUDA launch errors raise RuntimeError."""
-    if not ref.is_cuda:
+    CUDA launch errors raise RuntimeError.  The host cost of a call is part of the
+    product (a training step is not graph-captured), so the common case -- tensor on the
+    current device -- takes no context manager and builds no stream object."""
+    dev = ref.device
+    if dev.type != "cuda":
         raise RuntimeError("linghe_b200 runs on CUDA tensors only (no CPU fallback)")
-    lib = load()
-    _check_device(ref.device)
-    with torch.cuda.device(ref.device):
-        stream = torch.cuda.current_stream().cuda_stream
-        rc = getattr(lib, name)(*args, stream)
+    fn = _fn_cache.get(name)
+    if fn is None:
+        fn = _fn_cache[name] = getattr(load(), name)
+    idx = dev.index
+    if idx not in _checked_devices:
+        _check_device(idx)
+    if idx == torch.cuda.current_device():
+        rc = fn(*args, _stream_of(idx))
+    else:
+        with torch.cuda.device(idx):
+            rc = fn(*args, _stream_of(idx))
     if rc == 0:
         return
-    msg = lib.lh_last_error().decode()
+    msg = load().lh_last_error().decode()
     if rc == LH_ERR_ARG:
         raise AssertionError(msg)
     raise RuntimeError(f"linghe_b200 {name}: CUDA error {rc}: {msg}")

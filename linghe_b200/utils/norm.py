@@ -75,8 +75,10 @@ def triton_rms_norm_and_block_quant_forward(
         out = torch.empty((M, n), device=device, dtype=E4M3)
     if scale is None and output_mode in (0, 2):
         scale = torch.empty((n // 128, M), device=device, dtype=torch.float32)
-    transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
-    transpose_scale = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
+    transpose_output = transpose_scale = None
+    if output_mode != 0:
+        transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
+        transpose_scale = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
     if output_mode == 0:
         assert rms is None
         rms = torch.empty((M,), dtype=torch.float32, device=device)
@@ -88,6 +90,11 @@ def triton_rms_norm_and_block_quant_forward(
               float(eps), _lib.ptr(out) if output_mode != 1 else None,
               _lib.ptr(scale) if output_mode != 1 else None, _lib.ptr(rms), _lib.ptr(transpose_output),
               _lib.ptr(transpose_scale), int(bool(round_scale)), int(output_mode))
+    if transpose_output is None:
+        # mode 0 does not write the transposed pair; upstream still returns it (uninitialised), so it is
+        # allocated here, after the launch, where the allocator no longer delays the kernel
+        transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
+        transpose_scale = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
     return out, scale, rms, transpose_output, transpose_scale
 
 

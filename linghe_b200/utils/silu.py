@@ -56,15 +56,22 @@ def triton_silu_and_block_quant_forward(x, out=None, scale=None, round_scale=Fal
     M, N = x.shape
     n = N // 2
     device = x.device
+    assert n % 128 == 0
     if out is None:
         out = torch.empty((M, n), device=device, dtype=E4M3)
     if scale is None:
         scale = torch.empty((n // 128, M), device=device, dtype=torch.float32)
-    transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
-    transpose_scale = torch.empty((_cdiv(M, 128), n), device=device, dtype=torch.float32)
-    assert n % 128 == 0
+    transpose_output = transpose_scale = None
+    if output_mode != 0:
+        transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
+        transpose_scale = torch.empty((_cdiv(M, 128), n), device=device, dtype=torch.float32)
     _lib.call("lh_silu_blockquant_fwd", x, _lib.ptr(x), _lib.dtype_code(x), M, n, _lib.ptr(out), _lib.ptr(scale),
               _lib.ptr(transpose_output), _lib.ptr(transpose_scale), int(bool(round_scale)), int(output_mode))
+    if transpose_output is None:
+        # mode 0 does not write the transposed pair; upstream still returns it (uninitialised), so it is
+        # allocated here, after the launch, where the allocator no longer delays the kernel
+        transpose_output = torch.empty((n, M), device=device, dtype=E4M3)
+        transpose_scale = torch.empty((_cdiv(M, 128), n), device=device, dtype=torch.float32)
     return out, scale, transpose_output, transpose_scale
 
 
