@@ -141,14 +141,17 @@ int tile_quant(const void* x, int dtype, const void* counts, int counts_type, in
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
                       int idx_type, const void* counts, int counts_type, int E, int64_t m, int64_t Mout, int64_t N,
                       void* q, float* s, void* qt, float* st, void* prob_out, int round_scale, cudaStream_t stream);
-int tile_norm_col(const void* x, const void* gamma, const float* r, int64_t M, int64_t n, void* qt, float* st,
-                  int round_scale, cudaStream_t stream);
-int tile_silu_fwd(const void* x, const void* w, int w_dtype, const void* counts, int counts_type, int E,
+int tile_norm(const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n, void* q, float* s,
+              void* qt, float* st, int round_scale, int mode, cudaStream_t stream);
+int tile_silu_fwd(const void* x, const void* w, int w_dtype, int dtype, const void* counts, int counts_type, int E,
                   int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
                   cudaStream_t stream);
-int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, const void* counts, int counts_type,
-                  int E, int64_t M, int64_t n, void* dx_q, float* dx_s, void* dx_qt, float* dx_st, void* hp,
-                  float* dws, int round_scale, cudaStream_t stream);
+int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, int dtype, const void* counts,
+                  int counts_type, int E, int64_t M, int64_t n, void* dx_q, float* dx_s, void* dx_qt, float* dx_st,
+                  void* hp, float* dws, int round_scale, cudaStream_t stream);
+int any_rms(const void* x, int dtype, int64_t M, int64_t n, float eps, float* rms, cudaStream_t stream);
+int any_weighted_silu(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n,
+                      void* out, void* dw, int backward, cudaStream_t stream);
 int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* q,
                     float* s, float* rms, int round_scale, cudaStream_t stream);
 int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y,
@@ -170,7 +173,7 @@ int weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype, in
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int check_fused(const char* what, int dtype, int64_t M, int64_t n, int mode) {
-    if (dtype != LH_BF16) return fail_arg("%s: only bf16 inputs are supported", what);
+    if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
     if (M < 0 || n <= 0 || (n % 128) != 0) return fail_arg("%s: need n %% 128 == 0 (M=%lld n=%lld)", what, (long long)M, (long long)n);
     if (mode < 0 || mode > 2) return fail_arg("%s: output_mode must be 0, 1 or 2", what);
     return LH_OK;
@@ -289,6 +292,18 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
     if (int rc = check_fused("rmsnorm_blockquant_fwd", dtype, M, n, output_mode)) return rc;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (!rms) return fail_arg("rmsnorm_blockquant_fwd: rms is NULL");
+    if (dtype != LH_BF16) {
+        // float16 / float32: 1/rms per row from a plain row kernel, then the tile kernel in the
+        // requested mode (one pass over x for every output)
+        if (n > 8192) return fail_arg("rmsnorm_blockquant_fwd: need n <= 8192");
+        if (!x || !gamma || !aligned16(x) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: NULL or unaligned pointer");
+        if ((output_mode != 1 && (!q || !s || !aligned16(q))) || (output_mode != 0 && (!qt || !st || !aligned16(qt))))
+            return fail_arg("rmsnorm_blockquant_fwd: NULL or unaligned output pointer");
+        if (M == 0) return LH_OK;
+        if (output_mode != 1)
+            if (int rc = any_rms(x, dtype, M, n, eps, rms, cs)) return rc;
+        return tile_norm(x, gamma, rms, dtype, M, n, q, s, qt, st, round_scale, output_mode, cs);
+    }
     if (output_mode == 0 || output_mode == 2) {
         // The ring kernel's slab holds whole rows of at most 8192 elements in all; rows that fill
         // less than three quarters of it (e.g. n = 5120: 135 vs 102 us at 32768 rows) and long runs of
@@ -306,7 +321,7 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
         if (!qt || !st || !x || !gamma) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
         if (!aligned16(x) || !aligned16(qt) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: pointers must be 16-byte aligned");
         if (M == 0) return LH_OK;
-        return tile_norm_col(x, gamma, rms, M, n, qt, st, round_scale, cs);
+        return tile_norm(x, gamma, rms, LH_BF16, M, n, nullptr, nullptr, qt, st, round_scale, 1, cs);
     }
     return LH_OK;
 }
@@ -324,7 +339,7 @@ int lh_rmsnorm_gemm_blockquant_fwd(const void* x, const void* gamma, const void*
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (output_mode == 1) {
         if (!qt || !st || !aligned16(qt)) return fail_arg("rmsnorm_gemm_blockquant_fwd: NULL or unaligned transposed output");
-        return tile_norm_col(x, gamma, rms, M, K, qt, st, round_scale, cs);
+        return tile_norm(x, gamma, rms, LH_BF16, M, K, nullptr, nullptr, qt, st, round_scale, 1, cs);
     }
     if (!y || !q || !s || !logits || !route_w) return fail_arg("rmsnorm_gemm_blockquant_fwd: NULL pointer");
     if (!aligned16(y) || !aligned16(q)) return fail_arg("rmsnorm_gemm_blockquant_fwd: pointers must be 16-byte aligned");
@@ -385,12 +400,23 @@ int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, 
 int lh_weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,
                          void* stream) {
     if (!x || !y || !aligned16(x) || !aligned16(y)) return fail_arg("weighted_silu_fwd: NULL or unaligned pointer");
+    if (dtype == LH_F16 || dtype == LH_F32) {
+        if (n <= 0 || (n % 128) != 0 || M < 0) return fail_arg("weighted_silu_fwd: need n %% 128 == 0");
+        if (M == 0) return LH_OK;
+        return any_weighted_silu(nullptr, x, w, dtype, w_dtype, M, n, y, nullptr, 0, static_cast<cudaStream_t>(stream));
+    }
     return weighted_silu_fwd(x, w, dtype, w_dtype, M, n, y, static_cast<cudaStream_t>(stream));
 }
 
 int lh_weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n,
                          void* dx, void* dw, void* stream) {
     if (!g || !x || !dx || !aligned16(g) || !aligned16(x) || !aligned16(dx)) return fail_arg("weighted_silu_bwd: NULL or unaligned pointer");
+    if (dtype == LH_F16 || dtype == LH_F32) {
+        if (n <= 0 || (n % 128) != 0 || M < 0) return fail_arg("weighted_silu_bwd: need n %% 128 == 0");
+        if (w != nullptr && dw == nullptr) return fail_arg("weighted_silu_bwd: dw is NULL");
+        if (M == 0) return LH_OK;
+        return any_weighted_silu(g, x, w, dtype, w_dtype, M, n, dx, dw, 1, static_cast<cudaStream_t>(stream));
+    }
     return weighted_silu_bwd(g, x, w, dtype, w_dtype, M, n, dx, dw, static_cast<cudaStream_t>(stream));
 }
 
@@ -400,9 +426,9 @@ int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void*
     if (!x || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("silu_blockquant_fwd: NULL or unaligned pointer");
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
-    if (output_mode == 0)   // the register kernels at every size and width
+    if (output_mode == 0 && dtype == LH_BF16)   // the register kernels at every size and width
         return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
-    return tile_silu_fwd(x, nullptr, LH_F32, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
+    return tile_silu_fwd(x, nullptr, LH_F32, dtype, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,
                          static_cast<cudaStream_t>(stream));
 }
 
@@ -412,7 +438,7 @@ int lh_silu_blockquant_bwd(const void* g, const void* x, int dtype, int64_t M, i
     if (!g || !x || !dx_q || !dx_s || !dx_qt || !dx_st) return fail_arg("silu_blockquant_bwd: NULL pointer");
     if (!aligned16(g) || !aligned16(x) || !aligned16(dx_q) || !aligned16(dx_qt) || !aligned16(dx_hp)) return fail_arg("silu_blockquant_bwd: pointers must be 16-byte aligned");
     if (M == 0) return LH_OK;
-    return tile_silu_bwd(g, x, nullptr, LH_F32, nullptr, 0, 1, M, n, dx_q, dx_s, dx_qt, dx_st, dx_hp, nullptr,
+    return tile_silu_bwd(g, x, nullptr, LH_F32, dtype, nullptr, 0, 1, M, n, dx_q, dx_s, dx_qt, dx_st, dx_hp, nullptr,
                          round_scale, static_cast<cudaStream_t>(stream));
 }
 
@@ -424,7 +450,7 @@ int lh_batch_silu_blockquant_fwd(const void* x, const void* w, int dtype, int w_
     if (R == 0) return LH_OK;
     if (!x || !w || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("batch_silu_blockquant_fwd: NULL or unaligned pointer");
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("batch_silu_blockquant_fwd: output pointer is NULL");
-    return tile_silu_fwd(x, w, w_dtype, counts, counts_type, E, R, n, q, s, qt, st, round_scale, output_mode,
+    return tile_silu_fwd(x, w, w_dtype, dtype, counts, counts_type, E, R, n, q, s, qt, st, round_scale, output_mode,
                          static_cast<cudaStream_t>(stream));
 }
 
@@ -440,7 +466,7 @@ int lh_batch_silu_blockquant_bwd(const void* g, const void* x, const void* w, in
     const int64_t need = R * (n / 128) * 4;
     if (!scratch || scratch_bytes < need) return fail_arg("batch_silu_blockquant_bwd: scratch too small (%lld < %lld)", (long long)scratch_bytes, (long long)need);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (int rc = tile_silu_bwd(g, x, w, w_dtype, counts, counts_type, E, R, n, dx_q, dx_s, dx_qt, dx_st, nullptr,
+    if (int rc = tile_silu_bwd(g, x, w, w_dtype, dtype, counts, counts_type, E, R, n, dx_q, dx_s, dx_qt, dx_st, nullptr,
                                static_cast<float*>(scratch), round_scale, cs)) return rc;
     return dw_reduce(static_cast<const float*>(scratch), R, n / 128, dw, w_dtype, cs);
 }

@@ -16,6 +16,11 @@ namespace lh {
 int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
                    void* dx, float* partial, int max_parts, int* parts, void* dy_q, float* dy_s, int round_scale,
                    cudaStream_t stream);
+// float16 / float32 inputs (lh_anytype.cu)
+int any_norm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* y, float* rms,
+                 int reuse_rms, cudaStream_t stream);
+int any_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M, int64_t n,
+                 float eps, void* dx, float* dgamma, float* partial, int max_parts, cudaStream_t stream);
 
 enum : int { ROP_NORM_Q = 0, ROP_NORM_Y = 1, ROP_NORM_BWD = 2, ROP_NORM_YQ = 4 };
 
@@ -644,6 +649,11 @@ dgamma_reduce_kernel(const float* __restrict__ partial, int parts, int n, float*
     }
 }
 
+int dgamma_reduce(const float* partial, int parts, int64_t n, float* dgamma, cudaStream_t stream) {
+    dgamma_reduce_kernel<<<dim3(unsigned((n + 127) / 128)), dim3(1024), 0, stream>>>(partial, parts, int(n), dgamma);
+    return check_launch("dgamma_reduce_kernel");
+}
+
 // ------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------
@@ -670,7 +680,7 @@ static int launch_rows(RowParams p, int* grid_out, cudaStream_t stream, int grid
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int check_rows(const char* what, int dtype, int64_t M, int64_t n) {
-    if (dtype != LH_BF16) return fail_arg("%s: only bf16 inputs are supported", what);
+    if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
     if (M < 0 || n <= 0 || (n % 128) != 0 || n > kSlabElems)
         return fail_arg("%s: need n %% 128 == 0 and n <= 8192 (M=%lld n=%lld)", what, (long long)M, (long long)n);
     return LH_OK;
@@ -679,6 +689,7 @@ static int check_rows(const char* what, int dtype, int64_t M, int64_t n) {
 int rows_norm_quant(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps, void* q,
                     float* s, float* rms, int round_scale, cudaStream_t stream) {
     if (int rc = check_rows("rmsnorm_blockquant_fwd", dtype, M, n)) return rc;
+    if (dtype != LH_BF16) return fail_arg("rmsnorm_blockquant_fwd: the ring kernel takes bf16 only");
     if (!x || !gamma || !q || !s || !rms) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
     if (!aligned16(x) || !aligned16(q) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: pointers must be 16-byte aligned");
     if (M == 0) return LH_OK;
@@ -723,6 +734,7 @@ int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t 
     if (!x || !gamma || !y || (reuse_rms && !rms)) return fail_arg("rmsnorm_fwd: NULL pointer");
     if (!aligned16(x) || !aligned16(y) || !aligned16(gamma)) return fail_arg("rmsnorm_fwd: pointers must be 16-byte aligned");
     if (M == 0) return LH_OK;
+    if (dtype != LH_BF16) return any_norm_fwd(x, gamma, dtype, M, n, eps, y, rms, reuse_rms, stream);
     RowParams p{};
     p.x = static_cast<const uint8_t*>(x); p.gamma = gamma; p.rms = rms; p.reuse_rms = reuse_rms; p.eps = eps;
     p.M = M; p.n = int(n); p.hp = static_cast<uint8_t*>(y);
@@ -745,6 +757,8 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
         cudaError_t e = cudaMemsetAsync(dgamma, 0, size_t(n) * 4, stream);
         return e == cudaSuccess ? LH_OK : int(e);
     }
+    if (dtype != LH_BF16)
+        return any_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, static_cast<float*>(scratch), kMaxRowCtas, stream);
     RowParams p{};
     p.x = static_cast<const uint8_t*>(x); p.dy = static_cast<const uint8_t*>(dy); p.gamma = gamma;
     p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr; p.eps = eps; p.M = M; p.n = int(n);
@@ -810,6 +824,8 @@ int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const
         cudaError_t e = cudaMemsetAsync(dgamma, 0, size_t(n) * 4, stream);
         return e == cudaSuccess ? LH_OK : int(e);
     }
+    if (dtype != LH_BF16)
+        return any_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, partial, kStaticCtas, stream);
     RowParams p{};
     p.x = static_cast<const uint8_t*>(x); p.dy = static_cast<const uint8_t*>(dy); p.gamma = gamma;
     p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr; p.eps = eps; p.M = M; p.n = int(n);

@@ -54,8 +54,10 @@ def test_argument_validation_needs_no_gpu():
     assert rc == _lib.LH_ERR_ARG and b"128" in lib.lh_last_error()
     rc = lib.lh_blockwise_quant(null, 0, 128, 128, null, null, null, null, 0, 7, null)
     assert rc == _lib.LH_ERR_ARG
+    rc = lib.lh_silu_blockquant_fwd(null, 3, 128, 128, null, null, null, null, 0, 0, null)
+    assert rc == _lib.LH_ERR_ARG and b"dtype" in lib.lh_last_error()     # raw bytes are not a float type
     rc = lib.lh_silu_blockquant_fwd(null, 2, 128, 128, null, null, null, null, 0, 0, null)
-    assert rc == _lib.LH_ERR_ARG and b"bf16" in lib.lh_last_error()
+    assert rc == _lib.LH_ERR_ARG and b"NULL" in lib.lh_last_error()      # float32 is accepted, NULL x is not
     rc = lib.lh_rmsnorm_blockquant_fwd(null, null, 0, 16, 16384, 1e-6, null, null, null, null, null, 0, 0, null)
     assert rc == _lib.LH_ERR_ARG
 

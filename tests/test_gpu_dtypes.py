@@ -1,0 +1,143 @@
+"""float16 and float32 inputs on the fused entry points.  The upstream kernels up-cast whatever
+they load (linghe/utils/norm.py:37,123-124,213; linghe/utils/silu.py:45-46,84-85), so every
+fused wrapper takes the three floating types; the oracle computes in float32 from the same
+inputs and the tolerances are those of the bfloat16 path."""
+
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.common import assert_codes_close, assert_rel_close, assert_scales_close
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float16, torch.float32]
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _status_clean():
+    from linghe_b200 import _lib
+    yield
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0, "a kernel gave up on a bounded wait"
+
+
+def rnd(shape, seed, dtype, coef=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * coef).to(dtype)
+
+
+def fused(got_q, ref_q, got_s, ref_s, what):
+    assert_scales_close(got_s, ref_s, what + " scale")
+    assert_codes_close(got_q, ref_q, what + " codes")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,n", [(300, 1536), (256, 4096), (130, 8192), (64, 128)])
+def test_rms_block_quant_modes_other_dtypes(dtype, M, n):
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    x = rnd((M, n), 5, dtype)
+    g = (1 + 0.1 * rnd((n,), 6, torch.float32)).to(dtype)
+    rq, rs, rr, rqt, rst = O.rms_norm_and_block_quant_forward(x, g, 1e-6, False)
+    xd, gd = x.to(DEV), g.to(DEV)
+    q, s, r, _, _ = triton_rms_norm_and_block_quant_forward(xd, gd, output_mode=0)
+    assert_scales_close(r, rr, "rms")
+    fused(q, rq, s, rs, "mode0 row")
+    o = triton_rms_norm_and_block_quant_forward(xd, gd, rms=r, output_mode=1)
+    fused(o[3], rqt, o[4], rst, "mode1 col")
+    q, s, r2, qt, st = triton_rms_norm_and_block_quant_forward(xd, gd, output_mode=2)
+    assert_scales_close(r2, rr, "rms mode2")
+    fused(q, rq, s, rs, "mode2 row")
+    fused(qt, rqt, st, rst, "mode2 col")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,n", [(500, 1536), (256, 2048), (96, 8192)])
+def test_rms_fwd_bwd_other_dtypes(dtype, M, n):
+    from linghe_b200.utils.norm import (rms_norm_backward_and_block_quant, triton_rms_norm_backward,
+                                        triton_rms_norm_forward)
+    x = rnd((M, n), 11, dtype)
+    g = (1 + 0.1 * rnd((n,), 12, torch.float32)).to(dtype)
+    dy = rnd((M, n), 13, dtype, 0.01)
+    xd, gd, dyd = x.to(DEV), g.to(DEV), dy.to(DEV)
+    y, r = triton_rms_norm_forward(xd, gd)
+    assert y.dtype == dtype
+    assert_rel_close(y, O.rms_norm_forward(x, g), "y", 1e-2)
+    assert_scales_close(r, O.rms_recip(x), "rms")
+    y2, _ = triton_rms_norm_forward(xd, gd, rms=r)
+    assert torch.equal(y2, y)
+    rdx, rdw = O.rms_norm_backward(x, g, dy)
+    for rms in (r, None):
+        dx, dw = triton_rms_norm_backward(dyd, xd, gd, rms=rms)
+        assert dx.dtype == dtype and dw.dtype == torch.float32
+        assert_rel_close(dx, rdx, "dx", 1e-2)
+        assert_rel_close(dw, rdw, "dgamma", 1e-3, 1e-5)
+    if M % 16 == 0:
+        dx, dw, q, s, qt, st = rms_norm_backward_and_block_quant(dyd, xd, gd)
+        assert_rel_close(dx, rdx, "fused dx", 1e-2)
+        rq, rs, rqt, rst = O.blockwise_quant(dy, False)
+        for a, b in ((q, rq), (qt, rqt)):
+            assert torch.equal(a.view(torch.uint8).cpu(), b.view(torch.uint8))
+        assert torch.equal(s.cpu(), rs) and torch.equal(st.cpu(), rst)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,coef", [(512, 1024, 1.0), (300, 2816, 1.0), (128, 4096, 100.0), (67, 16640, 1.0)])
+def test_silu_fwd_modes_other_dtypes(dtype, M, N, coef):
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward
+    x = rnd((M, N), 31, dtype, coef)
+    rq, rs, rqt, rst = O.silu_and_block_quant_forward(x, False)
+    xd = x.to(DEV)
+    q, s, qt, st = triton_silu_and_block_quant_forward(xd, output_mode=2)
+    fused(q, rq, s, rs, "mode2 row")
+    fused(qt, rqt, st, rst, "mode2 col")
+    q, s, _, _ = triton_silu_and_block_quant_forward(xd, output_mode=0)
+    fused(q, rq, s, rs, "mode0 row")
+    _, _, qt, st = triton_silu_and_block_quant_forward(xd, output_mode=1)
+    fused(qt, rqt, st, rst, "mode1 col")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_bwd_and_weighted_other_dtypes(dtype):
+    from linghe_b200.utils.silu import (triton_silu_and_block_quant_backward, triton_weighted_silu_backward,
+                                        triton_weighted_silu_forward)
+    M, N = 256, 1024
+    x = rnd((M, N), 41, dtype)
+    g = rnd((M, N // 2), 42, dtype, 0.01)
+    w = rnd((M, 1), 43, torch.float32)
+    rq, rs, rqt, rst, rdx = O.silu_and_block_quant_backward(g, x, False)
+    q, s, qt, st, dx = triton_silu_and_block_quant_backward(g.to(DEV), x.to(DEV), return_bf16=True)
+    fused(q, rq, s, rs, "bwd row")
+    fused(qt, rqt, st, rst, "bwd col")
+    assert dx.dtype == dtype
+    assert_rel_close(dx, rdx.to(dtype), "bwd dx", 1e-2)
+    y = triton_weighted_silu_forward(x.to(DEV), w.to(DEV))
+    assert y.dtype == dtype
+    assert_rel_close(y, O.weighted_silu_forward(x, w), "weighted fwd", 1e-2)
+    dxw, dw = triton_weighted_silu_backward(g.to(DEV), x.to(DEV), w.to(DEV))
+    rdxw, rdw = O.weighted_silu_backward(g, x, w)
+    assert_rel_close(dxw, rdxw.to(dtype), "weighted dx", 1e-2)
+    assert_rel_close(dw.float().view(-1), rdw.view(-1), "weighted dw", 1e-3, 1e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batch_silu_other_dtypes(dtype):
+    from linghe_b200.utils.silu import (triton_batch_weighted_silu_and_block_quant_backward,
+                                        triton_batch_weighted_silu_and_block_quant_forward)
+    counts = [128, 0, 7, 130, 256]
+    R, N = sum(counts), 512
+    n = N // 2
+    x = rnd((R, N), 51, dtype)
+    g = rnd((R, n), 52, dtype, 0.01)
+    w = rnd((R, 1), 53, torch.float32)
+    ct = torch.tensor(counts, dtype=torch.int64, device=DEV)
+    rq, rs, rqt, rst = O.batch_weighted_silu_and_block_quant_forward(x, w, counts, False)
+    xd, gd, wd = x.to(DEV), g.to(DEV), w.to(DEV)
+    q, s, qt, st = triton_batch_weighted_silu_and_block_quant_forward(xd, wd, ct, counts, output_mode=2)
+    fused(q, rq, s, rs, "batch fwd row")
+    fused(qt, rqt, st, rst, "batch fwd col")
+    rq, rs, rdw, rqt, rst = O.batch_weighted_silu_and_block_quant_backward(g, x, w, counts, False)
+    q, s, dw, qt, st = triton_batch_weighted_silu_and_block_quant_backward(gd, xd, wd, ct, splits=counts)
+    fused(q, rq, s, rs, "batch bwd row")
+    fused(qt, rqt, st, rst, "batch bwd col")
+    assert_rel_close(dw, rdw, "batch dw", 1e-3, 1e-3)
