@@ -428,13 +428,16 @@ def validate_sharding(rank, world, device, gamma):
                 got.append((torch.cat([u8(p[0]) for p in parts], 0), torch.cat([p[1] for p in parts], 1),
                             torch.cat([u8(p[2]) for p in parts], 1), torch.cat([p[3] for p in parts], 0)))
         ok = True
+        differing = []
         if rank == 0:
             ref = [f_norm(x.to(device)), f_silu(xs.to(device))]
-            for gt, rf in zip(got, ref):
-                for a, b in zip(gt, rf):
-                    ok = ok and bool(torch.equal(u8(a), u8(b)))
+            for kname, gt, rf in zip(("rmsnorm", "swiglu"), got, ref):
+                for tname, a, b in zip(("q", "s", "qT", "sT"), gt, rf):
+                    if not bool(torch.equal(u8(a), u8(b))):
+                        ok = False
+                        differing.append(f"{kname}.{tname}: {int((u8(a) != u8(b)).sum())} of {a.numel()}")
         torch.cuda.synchronize()
-        return {"ranks": world, "shards": max(world, 2), "rows": rows, "ok": ok,
+        return {"ranks": world, "shards": max(world, 2), "rows": rows, "ok": ok, "differing": differing,
                 "what": "RMSNorm+quant and SwiGLU+quant, codes + scales on both axes, sharded == single GPU bit for bit",
                 "gather": "NCCL all_gather" if world > 1 else "none (two virtual shards on one GPU)"}
     except Exception as e:  # validation must not lose the measurement

@@ -308,9 +308,15 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
     for (int d = 16; d >= 1; d >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, d);
     if (lane == 0) wsum[warp] = ss;
     __syncthreads();
+    // four warps: the same pairing as the persistent walk kernel, so that both give the same bits
+    // for a row and a result does not depend on which of the two a problem size selects
     float tot = 0.f;
+    if constexpr (NT == 128) {
+        tot = (wsum[0] + wsum[1]) + (wsum[2] + wsum[3]);
+    } else {
 #pragma unroll
-    for (int w = 0; w < NT / 32; ++w) tot += wsum[w];
+        for (int w = 0; w < NT / 32; ++w) tot += wsum[w];
+    }
     float r;
     if (!QUANT && p.reuse_rms) {
         r = p.rms[row];

@@ -107,6 +107,12 @@ def assert_rel_close(got, ref, what, rtol, atol=0.0, max_floor_frac=1e-3):
     return err.max().item()
 
 
+# The SwiGLU kernels evaluate the sigmoid with flush-to-zero hardware approximations: where the
+# reference's float32 result is a denormal (|x1| of roughly 87 to 103, reached only by the
+# coef = 100 stress inputs) the kernels produce an exact zero.  The relative checks of SwiGLU
+# values and gradients therefore carry this absolute allowance, far below any normal float32.
+SILU_DENORMAL_ATOL = 1e-30
+
 # ---- observed parity statistics (worst value per test and quantity), printed once per session ----
 STATS = {}
 

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
-from tests.common import (golden, bf16, fp8, bits, assert_bits_equal, assert_f32_equal, assert_codes_close,
+from tests.common import (SILU_DENORMAL_ATOL, golden, bf16, fp8, bits, assert_bits_equal, assert_f32_equal, assert_codes_close,
                           assert_scales_close, assert_rel_close, assert_fused_pow2)
 
 pytestmark = pytest.mark.gpu
@@ -351,7 +351,7 @@ def test_silu_bwd(M, N, coef, gcoef):
     check_fused(q, rq, s, rs, "row")
     check_fused(qt, rqt, st, rst, "col")
     assert dx.dtype == torch.bfloat16
-    assert_rel_close(dx, rdx.to(torch.bfloat16), "dx bf16", 1e-2)
+    assert_rel_close(dx, rdx.to(torch.bfloat16), "dx bf16", 1e-2, SILU_DENORMAL_ATOL)
     out4 = triton_silu_and_block_quant_backward(_cuda(g), _cuda(x))
     assert len(out4) == 4 and torch.equal(out4[0].view(torch.uint8), q.view(torch.uint8))
 
@@ -363,18 +363,18 @@ def test_golden_weighted_silu(tag):
     x, g = _cuda(bf16(G[f"x_{tag}"])), _cuda(bf16(G[f"g_{tag}"]))
     w = _cuda(torch.from_numpy(G[f"wrow_{tag}"]))
     y = triton_weighted_silu_forward(x, w)
-    assert_rel_close(y, bf16(G[f"wsilu_{tag}_y"]), "y", 1e-2)
+    assert_rel_close(y, bf16(G[f"wsilu_{tag}_y"]), "y", 1e-2, SILU_DENORMAL_ATOL)
     dx, dw = triton_weighted_silu_backward(g, x, w)
-    assert_rel_close(dx, bf16(G[f"wsilubwd_{tag}_dx"]), "dx", 1e-2)
+    assert_rel_close(dx, bf16(G[f"wsilubwd_{tag}_dx"]), "dx", 1e-2, SILU_DENORMAL_ATOL)
     assert dw.shape == w.shape and dw.dtype == w.dtype
     rate = 100.0 ** 1.5 if tag == "c100" else 1.0
     assert_rel_close(dw, torch.from_numpy(G[f"wsilubwd_{tag}_dw"]), "dw", 1e-3, 1e-3 * rate)
     y0 = triton_weighted_silu_forward(x)
-    assert_rel_close(y0, O.weighted_silu_forward(bf16(G[f"x_{tag}"])), "y unweighted", 1e-2)
+    assert_rel_close(y0, O.weighted_silu_forward(bf16(G[f"x_{tag}"])), "y unweighted", 1e-2, SILU_DENORMAL_ATOL)
     dx0, dw0 = triton_weighted_silu_backward(g, x)
     assert dw0 is None
     assert_rel_close(dx0, O.weighted_silu_backward(bf16(G[f"g_{tag}"]), bf16(G[f"x_{tag}"]))[0].to(torch.bfloat16),
-                     "dx unweighted", 1e-2)
+                     "dx unweighted", 1e-2, SILU_DENORMAL_ATOL)
 
 
 # ------------------------------------------------------------------------------------
