@@ -77,6 +77,12 @@ int lh_device_status(int* status);
  * synchronise anyway (end of a step). */
 int lh_selftest_wait_timeout(int polls, void* stream);
 
+/* Measurement switch: sets the named dispatch option and returns its previous value
+ * (LH_ERR_ARG for an unknown key).  "rmsnorm_both_single_pass": 1 (default) = mode 2 of
+ * lh_rmsnorm_blockquant_fwd runs the single-pass kernel, 0 = the row kernel followed by the
+ * column kernel.  Process-wide; meant for A/B timing, not for production use. */
+int lh_tuning(const char* key, int value);
+
 /* Scratch bytes needed by the entry point named `what` ("rmsnorm_bwd",
  * "batch_silu_bwd") for the given sizes; 0 if it needs none, <0 if unknown. */
 int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols);
@@ -130,7 +136,9 @@ int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64
 
 /* RMSNorm + blockwise quantisation.
  * Replaces triton_rms_norm_and_block_quant_forward, linghe/utils/norm.py:343.
- * mode 0: writes q, s, rms.  mode 1: reads rms, writes qT, sT.  mode 2: writes all. */
+ * mode 0: writes q, s, rms.  mode 1: reads rms, writes qT, sT.  mode 2: writes all.
+ * Mode 2 with bf16 inputs is ONE kernel that reads x from HBM once (upstream runs two kernels,
+ * linghe/utils/norm.py:464-500, and reads x twice). */
 int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps,
                               void* q, float* s, float* rms, void* qt, float* st, int round_scale,
                               int output_mode, void* stream);

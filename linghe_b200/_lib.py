@@ -34,6 +34,7 @@ SIGNATURES = {
     "lh_device_check": (_i, [_i]),
     "lh_device_status": (_i, [ctypes.POINTER(_i)]),
     "lh_selftest_wait_timeout": (_i, [_i, _p]),
+    "lh_tuning": (_i, [ctypes.c_char_p, _i]),
     "lh_scratch_bytes": (_l, [ctypes.c_char_p, _l, _l]),
     "lh_blockwise_quant": (_i, [_p, _i, _l, _l, _p, _p, _p, _p, _i, _i, _p]),
     "lh_group_quant": (_i, [_p, _i, _l, _l, _p, _p, _i, _p]),

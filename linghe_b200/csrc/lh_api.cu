@@ -14,6 +14,11 @@ constexpr int64_t kSmallRowElements = int64_t(24) << 20;   // output elements up
 
 __device__ int g_device_status = 0;
 
+extern int g_band_l2_budget_mb;
+// measurement hook of lh_tuning(): 0 = the two-launch path for both-axes RMSNorm + quant
+static int g_band_kernel = 1;
+static bool use_band_kernel() { return g_band_kernel != 0; }
+
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
     const long long t0 = clock64();
     while (true) {
@@ -149,6 +154,8 @@ int tile_silu_fwd(const void* x, const void* w, int w_dtype, int dtype, const vo
 int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, int dtype, const void* counts,
                   int counts_type, int E, int64_t M, int64_t n, void* dx_q, float* dx_s, void* dx_qt, float* dx_st,
                   void* hp, float* dws, int round_scale, cudaStream_t stream);
+int band_norm_fwd(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
+                  void* qt, float* st, int round_scale, cudaStream_t stream);
 int any_rms(const void* x, int dtype, int64_t M, int64_t n, float eps, float* rms, cudaStream_t stream);
 int any_weighted_silu(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n,
                       void* out, void* dw, int backward, cudaStream_t stream);
@@ -211,6 +218,12 @@ int lh_device_status(int* status) {
     return LH_OK;
 }
 
+int lh_tuning(const char* key, int value) {
+    if (key && !strcmp(key, "rmsnorm_both_single_pass")) { const int old = g_band_kernel; g_band_kernel = value; return old; }
+    if (key && !strcmp(key, "band_l2_budget_mb")) { const int old = g_band_l2_budget_mb; g_band_l2_budget_mb = value; return old; }
+    return fail_arg("tuning: unknown key");
+}
+
 int lh_selftest_wait_timeout(int polls, void* stream) {
     if (polls < 1 || polls > 65536) return fail_arg("selftest_wait_timeout: polls must be in 1..65536");
     selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(uint32_t(polls));
@@ -226,6 +239,7 @@ int lh_selftest_wait_timeout(int polls, void* stream) {
 static bool whole_spans(int64_t n) { return (n % 2048) == 0; }
 
 static bool use_small_rows(int64_t elements) { return elements <= kSmallRowElements; }
+
 
 int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!what) return -1;
@@ -303,6 +317,15 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
         if (output_mode != 1)
             if (int rc = any_rms(x, dtype, M, n, eps, rms, cs)) return rc;
         return tile_norm(x, gamma, rms, dtype, M, n, q, s, qt, st, round_scale, output_mode, cs);
+    }
+    if (output_mode == 2 && M > 0 && n <= 8192 && use_band_kernel()) {
+        // both axes from one pass over x in HBM (lh_band.cu); where thread-block clusters cannot be
+        // launched the two-launch path below runs instead
+        if (!x || !gamma || !q || !s || !qt || !st) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
+        if (!aligned16(x) || !aligned16(gamma) || !aligned16(q) || !aligned16(qt))
+            return fail_arg("rmsnorm_blockquant_fwd: pointers must be 16-byte aligned");
+        const int rc = band_norm_fwd(x, gamma, M, n, eps, q, s, rms, qt, st, round_scale, cs);
+        if (rc != -999) return rc;
     }
     if (output_mode == 0 || output_mode == 2) {
         // The ring kernel's slab holds whole rows of at most 8192 elements in all; rows that fill

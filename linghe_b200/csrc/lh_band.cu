@@ -1,0 +1,444 @@
+// Single-pass both-axes kernel: RMSNorm forward + row-wise AND column-wise FP8 quantisation with
+// x read from HBM exactly once.
+//
+// Every output of a row needs the row's sum of squares, while a column block needs 128 rows.  The
+// unit of work is a 128-row band of x.  A band (128 * n * 2 bytes, 2 MB at n = 8192) is shared by
+// the C CTAs of a thread-block cluster, CTA r taking the 128 x 128 tiles r, r + C, ... of the band,
+// and is processed in two passes:
+//   pass A  the CTA streams its tiles through shared memory (TMA tensor copies) and adds up, per
+//           row, the squares of its columns; the 128 partial sums go to every CTA of the cluster
+//           through distributed shared memory, one cluster barrier makes them visible, and every
+//           CTA adds the C partials in rank order (deterministic) to get 1/rms of the 128 rows;
+//   pass B  the CTA streams the same tiles again and produces all four outputs of each (row codes /
+//           scales, transposed codes / scales).  The second read is served by L2: the clusters in
+//           flight hold (clusters x band) bytes, and C is chosen so that this stays a fraction of
+//           the 126 MB L2, so HBM sees x once.
+// The exchange costs one cluster barrier per band and CTA (under a microsecond against tens of
+// microseconds of work), no scratch memory and no inter-CTA polling.
+//
+// A CTA is 16 warps in two groups of eight (8 rows x 8 columns per thread, as in the tile kernels).
+// The groups take alternate tiles and synchronise only within themselves, so one group computes
+// while the other waits at a barrier.  Each group owns three of the six tile buffers; its first
+// thread refills the buffer the group has just left with the tile three of its own operations
+// ahead -- across the A/B boundary and into the next band, so the rings never drain.  The
+// transposed codes are staged in the tile's own buffer once the tile is in registers.
+// Every mbarrier wait is bounded and reports through the device status word; the cluster barrier
+// is reached by every thread of the cluster unconditionally.
+// No tensor cores: the path is bound by HBM and by instruction issue, not by arithmetic.
+#include "lh_tile.cuh"
+
+namespace lh {
+
+namespace {
+
+constexpr int kComputeWarps = 16;
+constexpr int kComputeThreads = kComputeWarps * 32;
+constexpr int kBandThreads = kComputeThreads;
+constexpr int kGroupThreads = 256;
+constexpr int kTileBytes = 128 * 128 * 2;
+constexpr int kSlots = 6;
+constexpr int kMaxCluster = 8;
+
+struct BandParams {
+    CUtensorMap tmap_x;     // x [M, n] bf16, box 128 x 128
+    const uint8_t* gamma;   // [n] bf16
+    float eps, inv_n;
+    int64_t M;
+    int n;
+    int S;                  // tiles per band = n / 128
+    int bands;
+    uint8_t* q;             // [M, n]
+    float* s;               // [n/128, M]
+    float* rms;             // [M]
+    uint8_t* qt;            // [n, M]
+    float* st;              // [ceil(M/128), n]
+    int round_scale;
+};
+
+struct BandCfg {
+    static constexpr int OFF_PART = kSlots * kTileBytes;          // [2 groups][8][128] column maxima
+    static constexpr int OFF_CS = OFF_PART + 2 * 8 * 128 * 4;     // [2][128] column scale
+    static constexpr int OFF_CY = OFF_CS + 2 * 512;               // [2][128] 1/scale
+    static constexpr int OFF_RSUM = OFF_CY + 2 * 512;             // [2 groups][128] row sums of this CTA's tiles
+    static constexpr int OFF_RINV = OFF_RSUM + 2 * 512;           // [128] 1/rms of the band's rows
+    static constexpr int OFF_PEER = OFF_RINV + 512;               // [2 parities][kMaxCluster][128] partials of every rank
+    static constexpr int OFF_BAR = OFF_PEER + 2 * kMaxCluster * 512;   // full[6], empty[6]
+    static constexpr int SMEM = OFF_BAR + 2 * kSlots * 8 + 16;
+};
+
+// sum over the 16 lanes that share a tile row, for eight rows at once (transposing butterfly);
+// on return lane l16 holds the sum of row (l16 >> 1)
+__device__ __forceinline__ float row_sum_transposed8(float* a, int l16) {
+    {
+        const bool up = (l16 & 8) != 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float recv = __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 4], 8);
+            a[i] = (up ? a[i + 4] : a[i]) + recv;
+        }
+    }
+    {
+        const bool up = (l16 & 4) != 0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float recv = __shfl_xor_sync(0xffffffffu, up ? a[i] : a[i + 2], 4);
+            a[i] = (up ? a[i + 2] : a[i]) + recv;
+        }
+    }
+    {
+        const bool up = (l16 & 2) != 0;
+        const float recv = __shfl_xor_sync(0xffffffffu, up ? a[0] : a[1], 2);
+        a[0] = (up ? a[1] : a[0]) + recv;
+    }
+    a[0] += __shfl_xor_sync(0xffffffffu, a[0], 1);
+    return a[0];
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_nctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// store a float into the shared memory of CTA `rank` of the cluster, at the address `local` has in this CTA
+__device__ __forceinline__ void st_cluster_f32(const float* local, uint32_t rank, float v) {
+    uint32_t raddr;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(raddr), "f"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(kBandThreads, 1)
+band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
+    using C = BandCfg;
+    constexpr int RPT = 8, GW = 8, NG = kGroupThreads;
+    extern __shared__ __align__(128) uint8_t smem[];
+    float* rsum = reinterpret_cast<float*>(smem + C::OFF_RSUM);
+    float* rinv = reinterpret_cast<float*>(smem + C::OFF_RINV);
+    float* peer = reinterpret_cast<float*>(smem + C::OFF_PEER);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
+    uint64_t* empty = full + kSlots;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int CS = int(cluster_nctarank()), rank = int(cluster_ctarank());
+    const int S = p.S;
+    const int cluster_id = int(blockIdx.x) / CS, nclusters = int(gridDim.x) / CS;
+    const int Tc = (S - rank + CS - 1) / CS;          // tiles of this CTA in every band: rank, rank + CS, ...
+    // bands of this cluster: cluster_id, cluster_id + nclusters, ...
+    const int nbands = cluster_id < p.bands ? (p.bands - cluster_id + nclusters - 1) / nclusters : 0;
+
+    if (tid == 0) {
+        for (int i = 0; i < kSlots; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], GW); }
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tmap_x);
+    }
+    __syncthreads();
+    // every CTA of the cluster has its barriers and buffers before any peer writes into them
+    cluster_arrive();
+    cluster_wait();
+
+    bool dead = false;   // a bounded wait of this thread gave up: later waits are skipped (see mbar_wait_or_mark)
+
+    // Operation n of this CTA (counted over all its bands): band index n / (2 Tc), then pass A over the
+    // Tc tiles, then pass B over them; consumed by group n & 1 from buffer n % 6 (so group g cycles
+    // through the buffers g, g + 2, g + 4).
+    const int g = warp >> 3, gw = warp & 7, gtid = tid & (NG - 1);
+    const int hw = lane >> 4, l16 = lane & 15;
+    const int row0 = gw * (2 * RPT) + hw * RPT;
+    const bool rs = p.round_scale != 0;
+    float* part = reinterpret_cast<float*>(smem + C::OFF_PART) + g * GW * 128;
+    float* cs = reinterpret_cast<float*>(smem + C::OFF_CS) + g * 128;
+    float* cy = reinterpret_cast<float*>(smem + C::OFF_CY) + g * 128;
+    auto group_bar = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "n"(NG) : "memory"); };
+    auto compute_bar = [&]() { asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory"); };
+
+    const int64_t total_ops = int64_t(nbands) * 2 * Tc;
+    auto issue = [&](int64_t n) {   // first thread of the group: the tile of operation n into its buffer
+        if (n >= total_ops) return;
+        const int64_t bi = n / (2 * Tc);
+        const int o = int(n - bi * 2 * Tc);
+        const int b = cluster_id + int(bi) * nclusters;
+        const int ct = rank + (o % Tc) * CS;
+        const int slot = int(n % kSlots);
+        mbar_expect_tx(&full[slot], uint32_t(kTileBytes));
+        tma_load_2d(smem + size_t(slot) * kTileBytes, &p.tmap_x, ct * 128, b * 128, &full[slot]);
+    };
+    // At the start of its operation n the group's first thread refills the buffer of operation n - 2
+    // (which every warp of the group has released, or is about to) with operation n + 4.
+    auto refill = [&](int64_t n) {
+        if (gtid == 0 && n >= 2 && n + 4 < total_ops) {
+            const int64_t prev = n - 2;
+            mbar_wait_or_mark<false>(&empty[prev % kSlots], uint32_t((prev / kSlots) & 1), DEVERR_EMPTY_WAIT, dead);
+            if (!dead) issue(n + 4);
+        }
+    };
+    if (gtid == 0) {
+        issue(g); issue(g + 2); issue(g + 4);
+    }
+
+    int64_t n = 0;
+    for (int bi = 0; bi < nbands; ++bi) {
+        const int b = cluster_id + bi * nclusters;
+        const int par = bi & 1;
+        // ---------------- pass A: row sums of squares over this group's tiles ----------------
+        float a[RPT];
+#pragma unroll
+        for (int s = 0; s < RPT; ++s) a[s] = 0.f;
+        for (int o = 0; o < Tc; ++o, ++n) {
+            if (int(n & 1) != g) continue;
+            refill(n);
+            const int slot = int(n % kSlots);
+            mbar_wait_or_mark<true>(&full[slot], uint32_t((n / kSlots) & 1), DEVERR_FULL_WAIT, dead);
+            const uint8_t* base = smem + size_t(slot) * kTileBytes + row0 * 256 + l16 * 16;
+#pragma unroll
+            for (int s = 0; s < RPT; ++s) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(base + s * 256);
+                const float2 v0 = bf16x2_to_f2(raw.x), v1 = bf16x2_to_f2(raw.y);
+                const float2 v2 = bf16x2_to_f2(raw.z), v3 = bf16x2_to_f2(raw.w);
+                float2 acc = mul2(v0, v0);
+                acc = fma2(v1, v1, acc); acc = fma2(v2, v2, acc); acc = fma2(v3, v3, acc);
+                a[s] += acc.x + acc.y;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+        {
+            const float tot = row_sum_transposed8(a, l16);
+            if ((l16 & 1) == 0) rsum[g * 128 + row0 + (l16 >> 1)] = tot;
+        }
+        compute_bar();
+        if (tid < 128) {
+            const float mine = rsum[tid] + rsum[128 + tid];
+            for (int r = 0; r < CS; ++r) st_cluster_f32(peer + (par * kMaxCluster + rank) * 128 + tid, uint32_t(r), mine);
+        }
+        cluster_arrive();
+        cluster_wait();
+        if (tid < 128) {
+            float tot = 0.f;
+            for (int r = 0; r < CS; ++r) tot += peer[(par * kMaxCluster + r) * 128 + tid];
+            const float r1 = rsqrt_nr(fmaf(tot, p.inv_n, p.eps));
+            const int64_t grow = int64_t(b) * 128 + tid;
+            const bool in = grow < p.M;
+            rinv[tid] = in ? r1 : 0.f;           // rows past the end of the matrix count as zeros
+            if (rank == 0 && in) p.rms[grow] = r1;
+        }
+        compute_bar();
+        // ---------------- pass B: all four outputs of this group's tiles ----------------
+        for (int o = 0; o < Tc; ++o, ++n) {
+            if (int(n & 1) != g) continue;
+            refill(n);
+            const int slot = int(n % kSlots);
+            const int ct = rank + o * CS;
+            mbar_wait_or_mark<true>(&full[slot], uint32_t((n / kSlots) & 1), DEVERR_FULL_WAIT, dead);
+            uint8_t* tile = smem + size_t(slot) * kTileBytes;
+            uint8_t* qts = tile;                 // reused once the tile is in registers
+            const int64_t grow0 = int64_t(b) * 128;
+            const int64_t gcol0 = int64_t(ct) * 128;
+            const int64_t left = p.M - grow0;
+            const int valid = left < 128 ? int(left) : 128;
+            const int nrows = valid - row0;
+            float2 v[RPT][4];
+            {
+                float2 gam[4];
+                load8p<__nv_bfloat16>(p.gamma + gcol0 * 2, l16, gam);
+                const float4 ra = *reinterpret_cast<const float4*>(rinv + row0);
+                const float4 rb = *reinterpret_cast<const float4*>(rinv + row0 + 4);
+                const float ri[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    float2 x[4];
+                    load8p<__nv_bfloat16>(tile + (row0 + s) * 256, l16, x);
+                    const float2 r2 = splat2(ri[s]);   // 0 for rows past the end of the matrix
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) v[s][j] = mul2(mul2(x[j], r2), gam[j]);
+                }
+            }
+            // ---- row-wise 1x128 ----
+            {
+                constexpr int G = 16 / RPT;
+                float a[RPT];
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    float m = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) m = max3abs(v[s][j].x, v[s][j].y, m);
+                    a[s] = m;
+                }
+                const float mymax = row_max_transposed<RPT>(a, l16);
+                const float mysc = scale_from_amax(mymax, rs);
+                const float myy = rcp_approx(mysc);
+                const int rr = row0 + l16 / G;
+                if ((l16 % G) == 0 && rr < valid) p.s[int64_t(ct) * p.M + grow0 + rr] = mysc;
+                uint8_t* qrow = p.q + (grow0 + row0) * p.n + gcol0 + l16 * 8;
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) {
+                    const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
+                    const uint2 codes = quant_row8<false, false>(v[s], 0.f, y);
+                    st_global_v2_if(s < nrows, qrow, codes.x, codes.y);
+                    qrow += p.n;
+                }
+            }
+            // ---- column-wise 128x1, transposed ----
+            float2 cm[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float mx = 0.f, my = 0.f;
+#pragma unroll
+                for (int s = 0; s < RPT; s += 2) {
+                    mx = max3abs(v[s][j].x, v[s + 1][j].x, mx);
+                    my = max3abs(v[s][j].y, v[s + 1][j].y, my);
+                }
+                cm[j].x = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                cm[j].y = fmaxf(my, __shfl_xor_sync(0xffffffffu, my, 16));
+            }
+            if (hw == 0) {
+                float4* dst = reinterpret_cast<float4*>(part + gw * 128 + l16 * 8);
+                dst[0] = make_float4(cm[0].x, cm[0].y, cm[1].x, cm[1].y);
+                dst[1] = make_float4(cm[2].x, cm[2].y, cm[3].x, cm[3].y);
+            }
+            group_bar();   // every thread of the group has its tile values in registers: the tile buffer is free
+            if (gtid < 128) {
+                float m = part[gtid];
+#pragma unroll
+                for (int w2 = 1; w2 < GW; ++w2) m = fmaxf(m, part[w2 * 128 + gtid]);
+                const float sc = scale_from_amax(m, rs);
+                cs[gtid] = sc;
+                cy[gtid] = rcp_approx(sc);
+                p.st[int64_t(b) * p.n + gcol0 + gtid] = sc;
+            }
+            group_bar();
+            float2 y2[4];
+            {
+                const float4 c = *reinterpret_cast<const float4*>(cy + l16 * 8);
+                const float4 e = *reinterpret_cast<const float4*>(cy + l16 * 8 + 4);
+                y2[0] = make_float2(c.x, c.y); y2[1] = make_float2(c.z, c.w);
+                y2[2] = make_float2(e.x, e.y); y2[3] = make_float2(e.z, e.w);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 qv[RPT];
+#pragma unroll
+                for (int s = 0; s < RPT; ++s) qv[s] = mul2(v[s][j], y2[j]);
+                const int colx = l16 * 8 + 2 * j;
+                const int rc = gw * 2 + hw;
+                const uint32_t off = uint32_t((rc ^ l16) << 3);
+                *reinterpret_cast<uint2*>(qts + colx * 128 + off) = make_uint2(
+                    cvt_e4m3x4(qv[0].x, qv[1].x, qv[2].x, qv[3].x), cvt_e4m3x4(qv[4].x, qv[5].x, qv[6].x, qv[7].x));
+                *reinterpret_cast<uint2*>(qts + (colx + 1) * 128 + off) = make_uint2(
+                    cvt_e4m3x4(qv[0].y, qv[1].y, qv[2].y, qv[3].y), cvt_e4m3x4(qv[4].y, qv[5].y, qv[6].y, qv[7].y));
+            }
+            group_bar();
+            // copy-out: 128 columns x 16 chunks of 8 rows; thread u handles chunk (u & 15) of columns (u >> 4) + 16 k
+            {
+                const int rc = gtid & 15, colb = gtid >> 4;
+                uint8_t* dst = p.qt + (gcol0 + colb) * p.M + grow0 + rc * 8;
+                const int64_t dstep = int64_t(NG / 16) * p.M;
+                const uint8_t* src = qts + colb * 128;
+                const int nvalid = valid - rc * 8;
+                if ((p.M & 7) == 0 && valid == 128) {   // the common case, free of per-store tests
+                    uint2 val[2048 / NG];
+#pragma unroll
+                    for (int kk = 0; kk < 2048 / NG; ++kk) {
+                        const int col = colb + kk * (NG / 16);
+                        val[kk] = *reinterpret_cast<const uint2*>(src + kk * (NG / 16) * 128 + ((rc ^ ((col >> 3) & 15)) << 3));
+                    }
+#pragma unroll
+                    for (int kk = 0; kk < 2048 / NG; ++kk) {
+                        *reinterpret_cast<uint2*>(dst) = val[kk];
+                        dst += dstep;
+                    }
+                } else {
+                    const bool vec = (p.M & 7) == 0 && nvalid >= 8;
+                    for (int kk = 0; kk < 2048 / NG; ++kk) {
+                        const int col = colb + kk * (NG / 16);
+                        const uint2 val = *reinterpret_cast<const uint2*>(src + kk * (NG / 16) * 128 + ((rc ^ ((col >> 3) & 15)) << 3));
+                        if (vec) {
+                            *reinterpret_cast<uint2*>(dst) = val;
+                        } else if (nvalid > 0) {
+                            const uint64_t bits = (uint64_t(val.y) << 32) | val.x;
+                            for (int b2 = 0; b2 < 8 && b2 < nvalid; ++b2) dst[b2] = uint8_t(bits >> (8 * b2));
+                        }
+                        dst += dstep;
+                    }
+                }
+            }
+            fence_async_smem();   // the buffer's next writer is a TMA copy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+        // No barrier here: rsum and rinv are rewritten only behind the next band's barriers, which no
+        // thread passes before every compute thread has finished this pass.
+    }
+}
+
+}  // namespace
+
+// Cluster size for a band of `n` columns: the smallest power of two that keeps the bands in flight
+// (active clusters x 128 n 2 bytes) within a budget of L2, given the active clusters per size.
+int g_band_l2_budget_mb = 40;   // lh_tuning("band_l2_budget_mb")
+
+static int pick_cluster(int64_t n, const int* active /* [4]: sizes 1, 2, 4, 8 */) {
+    const int64_t band_bytes = 128 * n * 2;
+    const int64_t budget = int64_t(g_band_l2_budget_mb) << 20;
+    for (int i = 0; i < 4; ++i) {
+        const int c = 1 << i;
+        if (active[i] <= 0) continue;
+        if ((n / 128) < c) break;
+        if (int64_t(active[i]) * band_bytes <= budget) return c;
+    }
+    for (int i = 3; i >= 0; --i)
+        if (active[i] > 0 && (n / 128) >= (1 << i)) return 1 << i;
+    return 1;
+}
+
+// x bf16 [M, n], n % 128 == 0; all five outputs.  Returns LH_ERR_ARG + 1000 (-999) when clusters
+// cannot be launched on this device, in which case nothing was enqueued.
+int band_norm_fwd(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
+                  void* qt, float* st, int round_scale, cudaStream_t stream) {
+    const int64_t bands = (M + 127) / 128;
+    const int64_t S = n / 128;
+    BandParams p{};
+    if (int rc = make_tensor_map(&p.tmap_x, x, LH_BF16, uint64_t(M), uint64_t(n), uint64_t(n) * 2, 128, 128)) return rc;
+    p.gamma = static_cast<const uint8_t*>(gamma); p.eps = eps; p.inv_n = 1.0f / float(n);
+    p.M = M; p.n = int(n); p.S = int(S); p.bands = int(bands);
+    p.q = static_cast<uint8_t*>(q); p.s = s; p.rms = rms; p.qt = static_cast<uint8_t*>(qt); p.st = st;
+    p.round_scale = round_scale;
+    // active clusters per cluster size, once per device
+    static int active_cache[64][4];
+    static bool have[64];
+    int dev = 0;
+    sm_count(&dev);
+    if (dev < 0 || dev >= 64) return -999;
+    if (!have[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(band_norm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(BandCfg::SMEM));
+        if (e != cudaSuccess) { cudaGetLastError(); return -999; }
+        for (int i = 0; i < 4; ++i) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(unsigned(8 << i)); cfg.blockDim = dim3(kBandThreads); cfg.dynamicSmemBytes = BandCfg::SMEM;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = unsigned(1 << i); at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            int ncl = 0;
+            if (cudaOccupancyMaxActiveClusters(&ncl, band_norm_fwd_kernel, &cfg) != cudaSuccess) { cudaGetLastError(); ncl = 0; }
+            active_cache[dev][i] = ncl;
+        }
+        have[dev] = true;
+    }
+    const int* active = active_cache[dev];
+    if (active[0] <= 0) return -999;
+    const int CSZ = pick_cluster(n, active);
+    int idx = 0;
+    while ((1 << idx) < CSZ) ++idx;
+    int64_t nclusters = active[idx];
+    if (bands < nclusters) nclusters = bands;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(nclusters * CSZ)); cfg.blockDim = dim3(kBandThreads); cfg.dynamicSmemBytes = BandCfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = unsigned(CSZ); at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, band_norm_fwd_kernel, p);
+    if (e != cudaSuccess) { set_error("band_norm_fwd_kernel: %s", cudaGetErrorString(e)); cudaGetLastError(); return int(e); }
+    return LH_OK;
+}
+
+}  // namespace lh
