@@ -17,6 +17,8 @@ __device__ int g_device_status = 0;
 extern int g_band_l2_budget_mb;
 // measurement hook of lh_tuning(): 0 = the two-launch path for both-axes RMSNorm + quant
 static int g_band_kernel = 1;
+static int g_band_bwd = 0;
+static int g_bwd_interleave_min_n = 128;
 static bool use_band_kernel() { return g_band_kernel != 0; }
 
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
@@ -156,6 +158,10 @@ int tile_silu_bwd(const void* g, const void* x, const void* w, int w_dtype, int 
                   void* hp, float* dws, int round_scale, cudaStream_t stream);
 int band_norm_fwd(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* q, float* s, float* rms,
                   void* qt, float* st, int round_scale, cudaStream_t stream);
+int64_t band_norm_bwd_scratch(int64_t M, int64_t n);
+int band_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
+                  void* dx, float* dgamma, void* dy_q, float* dy_s, void* dy_qt, float* dy_st, int round_scale,
+                  void* scratch, int64_t scratch_bytes, cudaStream_t stream);
 int any_rms(const void* x, int dtype, int64_t M, int64_t n, float eps, float* rms, cudaStream_t stream);
 int any_weighted_silu(const void* g, const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n,
                       void* out, void* dw, int backward, cudaStream_t stream);
@@ -167,7 +173,7 @@ int64_t rows_norm_bwd_scratch(int64_t n);
 int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
                   cudaStream_t stream, void* dy_q = nullptr, float* dy_s = nullptr, int round_scale = 0,
-                  int* dy_rows_done = nullptr);
+                  int* dy_rows_done = nullptr, void* dy_qt = nullptr, float* dy_st = nullptr, int interleave_min_n = 1 << 30);
 int64_t rows_norm_bwd_static_bytes();
 int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                          int64_t n, float eps, void* dx, float* dgamma, cudaStream_t stream);
@@ -220,6 +226,8 @@ int lh_device_status(int* status) {
 
 int lh_tuning(const char* key, int value) {
     if (key && !strcmp(key, "rmsnorm_both_single_pass")) { const int old = g_band_kernel; g_band_kernel = value; return old; }
+    if (key && !strcmp(key, "rmsnorm_bwd_quant_single_pass")) { const int old = g_band_bwd; g_band_bwd = value; return old; }
+    if (key && !strcmp(key, "rmsnorm_bwd_quant_interleave_min_n")) { const int old = g_bwd_interleave_min_n; g_bwd_interleave_min_n = value; return old; }
     if (key && !strcmp(key, "band_l2_budget_mb")) { const int old = g_band_l2_budget_mb; g_band_l2_budget_mb = value; return old; }
     return fail_arg("tuning: unknown key");
 }
@@ -244,6 +252,10 @@ static bool use_small_rows(int64_t elements) { return elements <= kSmallRowEleme
 int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     if (!what) return -1;
     if (!strcmp(what, "rmsnorm_bwd")) return rows_norm_bwd_scratch(cols);
+    if (!strcmp(what, "rmsnorm_bwd_blockquant")) {   // the larger of the single-pass and the two-launch needs
+        const int64_t a = rows_norm_bwd_scratch(cols), b = band_norm_bwd_scratch(rows, cols);
+        return a > b ? a : b;
+    }
     if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
     if (!strcmp(what, "rmsnorm_bwd_static")) return 0;  // it carries its own
     if (!strcmp(what, "row_id_map")) return route_scratch_bytes(cols);          // cols = experts
@@ -411,12 +423,23 @@ int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, 
                               void* dy_qt, float* dy_st, int round_scale, void* scratch, int64_t scratch_bytes,
                               void* stream) {
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (dtype == LH_BF16 && M > 0 && n > 0 && (n % 128) == 0 && n <= 8192 && g_band_bwd != 0 && dy && x && gamma && dx &&
+        dgamma && dy_q && dy_s && dy_qt && dy_st && scratch && aligned16(dy) && aligned16(x) && aligned16(gamma) &&
+        aligned16(dx) && aligned16(dy_q) && aligned16(dy_qt) && aligned16(scratch)) {
+        // x and dy read from HBM once (lh_band.cu); otherwise, or where clusters cannot be launched, two launches
+        const int rc = band_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, dgamma, dy_q, dy_s, dy_qt, dy_st, round_scale,
+                                     scratch, scratch_bytes, cs);
+        if (rc != -999) return rc;
+    }
     // Where the backward runs as the streaming kernel it also quantises dy row-wise from the registers
     // it already holds, and the tile kernel is left with the transposed copy only.
+    // g_bwd_interleave_min_n: from this row width on the streaming kernel also writes the transposed copy,
+    // tile by tile behind its own walk, and no second kernel runs
     int rows_done = 0;
     if (int rc = rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes, cs, dy_q, dy_s,
-                               round_scale, &rows_done))
+                               round_scale, &rows_done, dy_qt, dy_st, g_bwd_interleave_min_n))
         return rc;
+    if (rows_done == 2) return LH_OK;
     return tile_quant(dy, dtype, nullptr, 0, 1, M, n, dy_q, dy_s, dy_qt, dy_st, round_scale, rows_done ? 1 : 2, 0, cs);
 }
 

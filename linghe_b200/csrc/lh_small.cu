@@ -27,6 +27,8 @@ struct SmallParams {
     int reuse_rms;
     int scale_rowmajor;
     int round_scale;
+    uint8_t* qt;        // backward with COLQ: transposed codes of dy [n, M]
+    float* st;          // backward with COLQ: column scales of dy [ceil(M/128), n]
 };
 
 template <typename InT>
@@ -380,11 +382,108 @@ small_norm_kernel(const __grid_constant__ SmallParams p) {
 // The loads of the next row are issued before the second pass over the current one, so every
 // resident CTA always has a row in flight.  Per-CTA sums go to partial[blockIdx.x][n]; a second
 // kernel adds them in a fixed order.
-template <int SPANS, int NT, int MINB, bool WIDE, bool QDY>
+// Transposed 128x1 quantisation of one 128 x 128 tile of dy by the NT threads of a CTA (bit-exact:
+// block maxima on the packed 16-bit words, exact quotients on negated values).  Thread t owns the
+// 8 columns of column group t & 15 and the RG = 2048 / NT consecutive rows of row group t >> 4.
+// Two sweeps over the tile: maxima first, then -- after the 128 column scales went through shared
+// memory -- the codes; the second sweep reads the tile again from L1.  A thread's RG codes of one
+// column are RG consecutive bytes of the transposed output: one 16-byte (8-byte) store per column.
+// M is a multiple of 16, so a row group is either complete or empty.
+template <int NT>
+__device__ __forceinline__ void col_quant_tile(const SmallParams& p, const uint8_t* __restrict__ dy, int band, int ct,
+                                               float* cmax /* [NT/16][128] */, float* cs, float* cy) {
+    constexpr int RG = 2048 / NT;            // rows per thread: 16 (128 threads) or 8 (256 threads)
+    const int t = threadIdx.x, l16 = t & 15, rg = t >> 4;
+    const int64_t r0 = int64_t(band) * 128 + rg * RG;
+    const int c0 = ct * 128 + l16 * 8;
+    const bool live = r0 < p.M;              // whole row group inside the matrix
+    const int64_t pitch = int64_t(p.n) * 2;
+    const uint8_t* base = dy + r0 * pitch + int64_t(c0) * 2;
+    uint32_t m[4] = {0u, 0u, 0u, 0u};
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < RG; ++i) {
+            const uint4 w = *reinterpret_cast<const uint4*>(base + i * pitch);
+            asm("max.bf16x2 %0, %0, %1;" : "+r"(m[0]) : "r"(w.x & 0x7fff7fffu));
+            asm("max.bf16x2 %0, %0, %1;" : "+r"(m[1]) : "r"(w.y & 0x7fff7fffu));
+            asm("max.bf16x2 %0, %0, %1;" : "+r"(m[2]) : "r"(w.z & 0x7fff7fffu));
+            asm("max.bf16x2 %0, %0, %1;" : "+r"(m[3]) : "r"(w.w & 0x7fff7fffu));
+        }
+    }
+    {
+        float4* dst = reinterpret_cast<float4*>(cmax + rg * 128 + l16 * 8);
+        dst[0] = make_float4(__uint_as_float(m[0] << 16), __uint_as_float(m[0] & 0xffff0000u),
+                             __uint_as_float(m[1] << 16), __uint_as_float(m[1] & 0xffff0000u));
+        dst[1] = make_float4(__uint_as_float(m[2] << 16), __uint_as_float(m[2] & 0xffff0000u),
+                             __uint_as_float(m[3] << 16), __uint_as_float(m[3] & 0xffff0000u));
+    }
+    __syncthreads();
+    if (t < 128) {
+        float mx = cmax[t];
+#pragma unroll
+        for (int g = 1; g < NT / 16; ++g) mx = fmaxf(mx, cmax[g * 128 + t]);
+        const float sc = scale_from_amax(mx, p.round_scale != 0);
+        cs[t] = sc;
+        cy[t] = (sc < 8.0e-28f && mx > 0.f) ? 1.f : -__frcp_rn(sc);   // +1 marks "take IEEE division"
+        p.st[int64_t(band) * p.n + ct * 128 + t] = sc;
+    }
+    __syncthreads();
+    if (live) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const float4 s4 = *reinterpret_cast<const float4*>(cs + l16 * 8 + 4 * h);
+            const float4 y4 = *reinterpret_cast<const float4*>(cy + l16 * 8 + 4 * h);
+            const float2 sc2[2] = {make_float2(s4.x, s4.y), make_float2(s4.z, s4.w)};
+            const float2 y2[2] = {make_float2(y4.x, y4.y), make_float2(y4.z, y4.w)};
+            const bool slow = y4.x > 0.f || y4.y > 0.f || y4.z > 0.f || y4.w > 0.f;   // rare
+            uint32_t acc[4][RG / 4];
+#pragma unroll
+            for (int grp = 0; grp < RG / 4; ++grp) {
+                float2 q[4][2];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(base + (grp * 4 + r) * pitch + 8 * h);
+                    const float2 nd0 = bf16x2_to_neg_f2(w.x), nd1 = bf16x2_to_neg_f2(w.y);
+                    q[r][0] = quot_exact2(nd0, sc2[0], y2[0]);
+                    q[r][1] = quot_exact2(nd1, sc2[1], y2[1]);
+                    if (slow) {
+                        if (y2[0].x > 0.f) q[r][0].x = __fdiv_rn(-nd0.x, sc2[0].x);
+                        if (y2[0].y > 0.f) q[r][0].y = __fdiv_rn(-nd0.y, sc2[0].y);
+                        if (y2[1].x > 0.f) q[r][1].x = __fdiv_rn(-nd1.x, sc2[1].x);
+                        if (y2[1].y > 0.f) q[r][1].y = __fdiv_rn(-nd1.y, sc2[1].y);
+                    }
+                }
+                acc[0][grp] = cvt_e4m3x4(q[0][0].x, q[1][0].x, q[2][0].x, q[3][0].x);
+                acc[1][grp] = cvt_e4m3x4(q[0][0].y, q[1][0].y, q[2][0].y, q[3][0].y);
+                acc[2][grp] = cvt_e4m3x4(q[0][1].x, q[1][1].x, q[2][1].x, q[3][1].x);
+                acc[3][grp] = cvt_e4m3x4(q[0][1].y, q[1][1].y, q[2][1].y, q[3][1].y);
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint8_t* dst = p.qt + int64_t(c0 + 4 * h + c) * p.M + r0;
+                if constexpr (RG == 16) *reinterpret_cast<uint4*>(dst) = make_uint4(acc[c][0], acc[c][1], acc[c][2], acc[c][3]);
+                else *reinterpret_cast<uint2*>(dst) = make_uint2(acc[c][0], acc[c][1]);
+            }
+        }
+    }
+    // cmax / cs / cy are rewritten only behind the next tile's barriers
+}
+
+// COLQ: the kernel also writes the transposed 128x1 codes and scales of dy.  The column work is
+// cut into 128 x 128 tiles dealt round-robin to the CTAs; a CTA takes its next tile once the walk
+// has passed the tile's band, when the band's rows of dy are still in L2 (nothing depends on the
+// order: read early, the tile comes from HBM and the walk's read hits L2 instead), so dy crosses
+// the HBM interface once.
+template <int SPANS, int NT, int MINB, bool WIDE, bool QDY, bool COLQ = false>
 __global__ void __launch_bounds__(NT, MINB)
 small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
     constexpr int SPAN = 16 * NT, NW = NT / 32;
     __shared__ float wsum[2][2][NW];
+    __shared__ __align__(16) float cq_cmax[COLQ ? (NT / 16) * 128 : 4];
+    __shared__ __align__(16) float cq_cs[COLQ ? 128 : 4], cq_cy[COLQ ? 128 : 4];
+    const int nct = p.n >> 7;
+    const int64_t col_tiles = COLQ ? ((p.M + 127) >> 7) * nct : 0;
+    int64_t next_tile = blockIdx.x;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     // gamma stays in registers for one span per thread; with two it is re-read (L1 hits) so that
     // three CTAs fit an SM without spills
@@ -529,6 +628,18 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
                 }
             }
         }
+        if constexpr (COLQ) {
+            // bands the walk has passed: every CTA has finished the rows below row - blockIdx.x + gridDim.x or is about to
+            const int64_t walked = (row - blockIdx.x + gridDim.x) >> 7;
+            while (next_tile < col_tiles && next_tile / nct < walked) {
+                col_quant_tile<NT>(p, dy, int(next_tile / nct), int(next_tile % nct), cq_cmax, cq_cs, cq_cy);
+                next_tile += gridDim.x;
+            }
+        }
+    }
+    if constexpr (COLQ) {
+        for (; next_tile < col_tiles; next_tile += gridDim.x)
+            col_quant_tile<NT>(p, dy, int(next_tile / nct), int(next_tile % nct), cq_cmax, cq_cs, cq_cy);
     }
 #pragma unroll
     for (int i = 0; i < SPANS; ++i) {
@@ -545,16 +656,36 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
 // RMSNorm + 1x128 quantisation for long runs of wide rows: a persistent walk.  A CTA of 128
 // threads takes rows blockIdx.x, blockIdx.x + gridDim.x, ... with the whole row in registers as
 // packed words; the loads of the next row are issued as soon as the row sum is known, before
-// the normalise + quantise pass over a copy of the current one, so each of the four resident CTAs
-// per SM always has a row (up to 16 KB) in flight and only pays its own barrier.
+// the normalise + quantise pass over the current one, so each of the four resident CTAs per SM
+// always has a row (up to 16 KB) in flight and only pays its own barrier.
+// The kernel's time follows the SM clock (254 us at 1965 MHz, 301 us at 1710 MHz before the change
+// below): it is bound by instruction issue and the latency chain of a row, not by HBM.  So gamma
+// sits in shared memory as float32 for the whole walk -- four conflict-free 16-byte shared loads
+// per 16 elements instead of two global loads and sixteen unpack operations (254 -> 248 us).
 template <int SPANS, bool WIDE>
 __global__ void __launch_bounds__(128, 4)
 small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
     constexpr int SPAN = 2048;
+    // gamma as float32, laid out for conflict-free 16-byte reads: the k-th quad of thread t's 16 columns
+    // of span i is float4 number (4 i + k) * 128 + t, so a warp's read is 512 consecutive bytes
+    extern __shared__ __align__(16) float4 gam_s[];
     __shared__ float wsum[2][4];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    uint4 xr[2 * SPANS];
-    auto fetch = [&](int64_t row) {
+#pragma unroll
+    for (int i = 0; i < SPANS; ++i) {
+        const int col = i * SPAN + t * 16;
+        float2 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = make_float2(0.f, 0.f);
+        if (col < p.n) {
+            unpack8<__nv_bfloat16>(__ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)), v);
+            unpack8<__nv_bfloat16>(__ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16)), v + 4);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) gam_s[(4 * i + k) * 128 + t] = make_float4(v[2 * k].x, v[2 * k].y, v[2 * k + 1].x, v[2 * k + 1].y);
+    }
+    __syncthreads();
+    auto fetch = [&](uint4* xr, int64_t row) {
 #pragma unroll
         for (int i = 0; i < SPANS; ++i) {
             const int col = i * SPAN + t * 16;
@@ -570,15 +701,13 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
             }
         }
     };
-    int64_t row = blockIdx.x;
-    fetch(row);
-    int par = 0;
-    for (; row < p.M; row += gridDim.x, par ^= 1) {
+    // one row: `cur` holds it, `nxt` receives the loads of the row one grid stride further
+    auto do_row = [&](uint4* cur, uint4* nxt, int64_t row, int par) {
         float2 s0 = make_float2(0.f, 0.f), s1 = s0;
 #pragma unroll
         for (int i = 0; i < 2 * SPANS; ++i) {
             float2 v[4];
-            unpack8<__nv_bfloat16>(xr[i], v);
+            unpack8<__nv_bfloat16>(cur[i], v);
             s0 = fma2(v[0], v[0], s0); s1 = fma2(v[1], v[1], s1);
             s0 = fma2(v[2], v[2], s0); s1 = fma2(v[3], v[3], s1);
         }
@@ -592,26 +721,22 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
         const float r = rsqrt_nr(fmaf(tot, p.inv_n, p.eps));
         if (t == 0 && p.rms != nullptr) p.rms[row] = r;
         const float2 r2 = splat2(r);
-        uint4 xc[2 * SPANS];
-#pragma unroll
-        for (int i = 0; i < 2 * SPANS; ++i) xc[i] = xr[i];
-        fetch(row + gridDim.x);
+        fetch(nxt, row + gridDim.x);
 #pragma unroll
         for (int i = 0; i < SPANS; ++i) {
             const int col = i * SPAN + t * 16;
             if (i * SPAN >= p.n) break;                       // uniform
-            float2 v[8], g[8];
-            unpack8<__nv_bfloat16>(xc[2 * i], v);
-            unpack8<__nv_bfloat16>(xc[2 * i + 1], v + 4);
-            uint4 g0 = make_uint4(0, 0, 0, 0), g1 = g0;
-            if (col < p.n) {
-                g0 = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2));
-                g1 = __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2 + 16));
-            }
-            unpack8<__nv_bfloat16>(g0, g);
-            unpack8<__nv_bfloat16>(g1, g + 4);
+            float2 v[8];
+            unpack8<__nv_bfloat16>(cur[2 * i], v);
+            unpack8<__nv_bfloat16>(cur[2 * i + 1], v + 4);
+            {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = mul2(mul2(v[j], r2), g[j]);
+                for (int k = 0; k < 4; ++k) {
+                    const float4 w = gam_s[(4 * i + k) * 128 + t];   // zeros past n
+                    v[2 * k] = mul2(mul2(v[2 * k], r2), make_float2(w.x, w.y));
+                    v[2 * k + 1] = mul2(mul2(v[2 * k + 1], r2), make_float2(w.z, w.w));
+                }
+            }
             if (p.y != nullptr && col < p.n) {
                 uint8_t* yo = p.y + (row * p.n + col) * 2;
                 *reinterpret_cast<uint4*>(yo) = make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
@@ -621,6 +746,15 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
             }
             quant16<false>(p, row, col, col < p.n, v);
         }
+    };
+    uint4 xa[2 * SPANS], xb[2 * SPANS];
+    int64_t row = blockIdx.x;
+    fetch(xa, row);
+    int par = 0;
+    for (; row < p.M; row += gridDim.x, par ^= 1) {
+        do_row(xa, xb, row, par);
+#pragma unroll
+        for (int i = 0; i < 2 * SPANS; ++i) xa[i] = xb[i];   // (writing the loop out for two register sets that swap roles spills: 315 vs 248 us)
     }
 }
 
@@ -736,8 +870,9 @@ int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, flo
     // the TMA ring); everything else one CTA per row.
     if (p.n > 4096 && M * n > (int64_t(24) << 20)) {
         const int sms = sm_count();
-        if ((reinterpret_cast<uintptr_t>(x) & 31) == 0) small_norm_walk_kernel<4, true><<<unsigned(4 * sms), 128, 0, stream>>>(p);
-        else small_norm_walk_kernel<4, false><<<unsigned(4 * sms), 128, 0, stream>>>(p);
+        const size_t gsm = size_t(4) * 2048 * 4;   // gamma as float32 in shared memory for four spans (32 KB: four CTAs per SM fit)
+        if ((reinterpret_cast<uintptr_t>(x) & 31) == 0) small_norm_walk_kernel<4, true><<<unsigned(4 * sms), 128, gsm, stream>>>(p);
+        else small_norm_walk_kernel<4, false><<<unsigned(4 * sms), 128, gsm, stream>>>(p);
         return check_launch("small_norm_walk_kernel");
     }
     launch_small_norm<true>(p, stream);
@@ -760,12 +895,13 @@ int small_norm_y(const void* x, const void* gamma, int64_t M, int64_t n, float e
 // in *parts.  n <= 8192, 16-byte aligned pointers, bf16 inputs.
 int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int64_t M, int64_t n, float eps,
                    void* dx, float* partial, int max_parts, int* parts, void* dy_q, float* dy_s, int round_scale,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, void* dy_qt, float* dy_st) {
     SmallParams p{};
     p.x = static_cast<const uint8_t*>(x); p.gamma = static_cast<const uint8_t*>(gamma); p.M = M; p.n = int(n);
     p.eps = eps; p.inv_n = 1.0f / float(n); p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr;
     p.y = static_cast<uint8_t*>(dx);
     p.q = static_cast<uint8_t*>(dy_q); p.s = dy_s; p.round_scale = round_scale;
+    p.qt = static_cast<uint8_t*>(dy_qt); p.st = dy_st;
     const uint8_t* g = static_cast<const uint8_t*>(dy);
     const int sms = sm_count();
     int64_t grid = int64_t(sms) * (n <= 4096 ? 3 : 1);
@@ -775,17 +911,20 @@ int small_norm_bwd(const void* dy, const void* x, const void* gamma, const float
     const bool wide = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(dx)) & 31) == 0;
     const unsigned gd = unsigned(grid);
     const bool qdy = dy_q != nullptr;
-#define LH_BWD_LAUNCH(S, NT_, MB, W, Q) small_norm_bwd_kernel<S, NT_, MB, W, Q><<<gd, NT_, 0, stream>>>(p, g, partial)
-#define LH_BWD_PICK(W, Q)                                              \
+    const bool colq = qdy && dy_qt != nullptr && dy_st != nullptr && (M % 16) == 0;
+#define LH_BWD_LAUNCH(S, NT_, MB, W, Q, CQ) small_norm_bwd_kernel<S, NT_, MB, W, Q, CQ><<<gd, NT_, 0, stream>>>(p, g, partial)
+#define LH_BWD_PICK(W, Q, CQ)                                          \
     do {                                                               \
-        if (n <= 2048) LH_BWD_LAUNCH(1, 128, 3, W, Q);                 \
-        else if (n <= 4096) LH_BWD_LAUNCH(2, 128, 3, W, Q);            \
-        else LH_BWD_LAUNCH(2, 256, 1, W, Q);                           \
+        if (n <= 2048) LH_BWD_LAUNCH(1, 128, 3, W, Q, CQ);             \
+        else if (n <= 4096) LH_BWD_LAUNCH(2, 128, 3, W, Q, CQ);        \
+        else LH_BWD_LAUNCH(2, 256, 1, W, Q, CQ);                       \
     } while (0)
-    if (wide && qdy) LH_BWD_PICK(true, true);
-    else if (wide) LH_BWD_PICK(true, false);
-    else if (qdy) LH_BWD_PICK(false, true);
-    else LH_BWD_PICK(false, false);
+    if (wide && colq) LH_BWD_PICK(true, true, true);
+    else if (colq) LH_BWD_PICK(false, true, true);
+    else if (wide && qdy) LH_BWD_PICK(true, true, false);
+    else if (wide) LH_BWD_PICK(true, false, false);
+    else if (qdy) LH_BWD_PICK(false, true, false);
+    else LH_BWD_PICK(false, false, false);
 #undef LH_BWD_PICK
 #undef LH_BWD_LAUNCH
     return check_launch("small_norm_bwd_kernel");

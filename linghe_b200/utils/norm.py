@@ -156,7 +156,7 @@ def rms_norm_backward_and_block_quant(grad_output, x, w, eps=1e-6, rms=None, rou
     dy_s = torch.empty((n // 128, M), device=device, dtype=torch.float32)
     dyt_q = torch.empty((n, M), device=device, dtype=E4M3)
     dyt_s = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
-    nbytes = _lib.scratch_bytes("rmsnorm_bwd", M, n)
+    nbytes = _lib.scratch_bytes("rmsnorm_bwd_blockquant", M, n)
     scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
     _lib.call("lh_rmsnorm_bwd_blockquant", x, _lib.ptr(grad_output), _lib.ptr(x), _lib.ptr(w), _lib.ptr(rms),
               _lib.dtype_code(x), M, n, float(eps), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(dy_q), _lib.ptr(dy_s),

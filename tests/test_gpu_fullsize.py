@@ -189,7 +189,11 @@ def test_cfg4_rmsnorm_bwd_dual_quant_16384x4096():
     g = (1 + 0.1 * torch.randn(n, device=DEV, generator=torch.Generator(device=DEV).manual_seed(10))).to(torch.bfloat16)
     dx, dw, q, s, qt, st = rms_norm_backward_and_block_quant(dy, x, g)
     dx2, dw2 = triton_rms_norm_backward(dy, x, g)
-    assert same(dx, dx2) and same(dw, dw2), "fused entry differs from the plain backward"
+    # the fused entry is its own single-pass kernel: same math, another summation order
+    assert_rel_close(dx, dx2.float(), "fused dx vs plain backward", 1e-2)
+    assert_rel_close(dw, dw2, "fused dgamma vs plain backward", 1e-4, 1e-5)
+    dx3, dw3, *_ = rms_norm_backward_and_block_quant(dy, x, g)
+    assert same(dx, dx3) and same(dw, dw3), "not deterministic"
     pq = triton_blockwise_quant(dy)
     assert all(same(a, b) for a, b in zip((q, s, qt, st), pq)), "fused dy copies differ from blockwise_quant"
     assert checksum(q) == checksum(pq[0]) and checksum(qt) == checksum(pq[2])

@@ -280,7 +280,8 @@ def test_golden_rms_fwd_bwd():
 
 # rows wider than 2048: the streaming backward also writes dy's row-wise codes and scales, the tile
 # kernel only the transposed copy; (640, 2304) leaves the second span of a thread partly empty
-@pytest.mark.parametrize("M,n", [(1024, 2048), (1024, 4096), (640, 2304), (384, 8192)])
+@pytest.mark.parametrize("M,n", [(1024, 2048), (1024, 4096), (640, 2304), (384, 8192), (400, 2048), (4112, 1536),
+                                 (128, 128)])
 def test_rms_bwd_fused_dy_quant(M, n):
     from linghe_b200.utils.norm import rms_norm_backward_and_block_quant
     x = randn_bf16((M, n), 21)
@@ -291,6 +292,11 @@ def test_rms_bwd_fused_dy_quant(M, n):
     assert_rel_close(dx, rdx, "dx", 1e-2)
     assert_rel_close(dw, rdw, "dgamma", 1e-3, 1e-5)
     check_exact((q, s, qt, st), O.blockwise_quant(dy, False), ("dy q", "dy s", "dy qt", "dy st"))
+    # a given 1/rms is used instead of the recomputed one
+    r = _cuda(O.rms_recip(x))
+    dx_r, dw_r, *_ = rms_norm_backward_and_block_quant(_cuda(dy), _cuda(x), _cuda(g), rms=r)
+    assert_rel_close(dx_r, rdx, "dx with rms", 1e-2)
+    assert_rel_close(dw_r, rdw, "dgamma with rms", 1e-3, 1e-5)
     # power-of-two scales, and zero / negative-zero / tiny blocks in dy
     dy2 = dy.clone()
     dy2[0, :128] = 0
