@@ -15,11 +15,13 @@ constexpr int64_t kSmallRowElements = int64_t(24) << 20;   // output elements up
 __device__ int g_device_status = 0;
 
 extern int g_band_l2_budget_mb;
-// measurement hook of lh_tuning(): 0 = the two-launch path for both-axes RMSNorm + quant
+// lh_tuning("rmsnorm_both_single_pass"): 0 = always the two-launch path for both-axes RMSNorm + quant,
+// 1 = the single-pass kernel where it is ahead (rows narrower than 4096: 1.05-1.2x at n = 1024 ... 3584,
+// level at 2048; from 4096 on the two launches win, 0.95x at 4096 down to 0.7-0.8x at 8192), 2 = always
 static int g_band_kernel = 1;
 static int g_band_bwd = 0;
-static int g_bwd_interleave_min_n = 128;
-static bool use_band_kernel() { return g_band_kernel != 0; }
+static int g_bwd_interleave_min_n = 1 << 30;
+static bool use_band_kernel(int64_t n) { return g_band_kernel == 2 || (g_band_kernel == 1 && n < 4096); }
 
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
     const long long t0 = clock64();
@@ -330,7 +332,7 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
             if (int rc = any_rms(x, dtype, M, n, eps, rms, cs)) return rc;
         return tile_norm(x, gamma, rms, dtype, M, n, q, s, qt, st, round_scale, output_mode, cs);
     }
-    if (output_mode == 2 && M > 0 && n <= 8192 && use_band_kernel()) {
+    if (output_mode == 2 && M > 0 && n <= 8192 && use_band_kernel(n)) {
         // both axes from one pass over x in HBM (lh_band.cu); where thread-block clusters cannot be
         // launched the two-launch path below runs instead
         if (!x || !gamma || !q || !s || !qt || !st) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");

@@ -278,12 +278,61 @@ def test_golden_rms_fwd_bwd():
         assert_rel_close(dw.to(torch.bfloat16), bf16(G[f"rmsbwd_{tag}_dw"]), "dw", 1e-2)
 
 
+class tuning:
+    """set a dispatch option of the library for the duration of a with-block"""
+
+    def __init__(self, key, value):
+        self.key, self.value = key.encode(), value
+
+    def __enter__(self):
+        from linghe_b200 import _lib
+        self.old = _lib.load().lh_tuning(self.key, self.value)
+        assert self.old != _lib.LH_ERR_ARG
+
+    def __exit__(self, *exc):
+        from linghe_b200 import _lib
+        _lib.load().lh_tuning(self.key, self.old)
+
+
+# Both-axes RMSNorm + quant has two implementations (one kernel over a cluster band, x read from HBM
+# once; or a row kernel followed by a column kernel) chosen by row width: each is checked at widths
+# where the other is the default.
+@pytest.mark.parametrize("M,n,force", [(1000, 1536, 0), (512, 2048, 0), (2048, 1664, 0), (384, 4096, 2), (130, 8192, 2),
+                                       (4200, 8192, 2), (600, 5120, 2), (64, 128, 2), (128, 256, 0)])
+def test_rms_block_quant_both_paths(M, n, force):
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    x = randn_bf16((M, n), 7, 2)
+    g = randn_bf16((n,), 8)
+    xd, gd = _cuda(x), _cuda(g)
+    for rsc in (False, True):
+        rq, rs, rr, rqt, rst = O.rms_norm_and_block_quant_forward(x, g, 1e-6, rsc)
+        with tuning("rmsnorm_both_single_pass", force):
+            q, s, r, qt, st = triton_rms_norm_and_block_quant_forward(xd, gd, round_scale=rsc, output_mode=2)
+            torch.cuda.synchronize()
+        assert_scales_close(r, rr, "rms")
+        check_fused(q, rq, s, rs, "row", rsc)
+        check_fused(qt, rqt, st, rst, "col", rsc)
+
+
 # rows wider than 2048: the streaming backward also writes dy's row-wise codes and scales, the tile
-# kernel only the transposed copy; (640, 2304) leaves the second span of a thread partly empty
+# kernel only the transposed copy; (640, 2304) leaves the second span of a thread partly empty.
+# The two single-pass implementations (x and dy read from HBM once) are selectable and held to the
+# same checks: "band" = the cluster kernel, "interleave" = the streaming kernel that also writes the
+# transposed copy tile by tile behind its own walk.
+@pytest.mark.parametrize("path", ["default", "band", "interleave"])
 @pytest.mark.parametrize("M,n", [(1024, 2048), (1024, 4096), (640, 2304), (384, 8192), (400, 2048), (4112, 1536),
                                  (128, 128)])
-def test_rms_bwd_fused_dy_quant(M, n):
-    from linghe_b200.utils.norm import rms_norm_backward_and_block_quant
+def test_rms_bwd_fused_dy_quant(M, n, path):
+    from linghe_b200.utils.norm import rms_norm_backward_and_block_quant as fused_entry
+    key, val = {"default": ("band_l2_budget_mb", 40), "band": ("rmsnorm_bwd_quant_single_pass", 1),
+                "interleave": ("rmsnorm_bwd_quant_interleave_min_n", 128)}[path]
+
+    def rms_norm_backward_and_block_quant(*a, **kw):
+        with tuning(key, val):
+            out = fused_entry(*a, **kw)
+            torch.cuda.synchronize()
+        return out
+
     x = randn_bf16((M, n), 21)
     g = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(22))).to(torch.bfloat16)
     dy = randn_bf16((M, n), 23, 1, 0.01)
