@@ -522,10 +522,11 @@ def other_configs(args, peak):
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the SwiGLU+quant kernel in an ncu
 # capture at TRAFFIC_CAPTURE_ROWS rows (profiles/); traffic grows in proportion to the rows, so the
 # bench line scales it by rows / TRAFFIC_CAPTURE_ROWS.
-TRAFFIC_SWIGLU_BYTES = 2564161536
-TRAFFIC_CAPTURE_ROWS = 65536
-TRAFFIC_NOTE = ("scaled from an 8192-row ncu capture; reads equal the algorithmic input bytes, writes read low "
-                "because part of the output is still dirty in L2 when the kernel ends (not a saving)")
+TRAFFIC_SWIGLU_BYTES = 1073767680 + 258864640     # dram__bytes_read.sum + dram__bytes_write.sum
+TRAFFIC_CAPTURE_ROWS = 32768
+TRAFFIC_NOTE = ("one launch captured at 32768 rows (profiles/), scaled by rows; reads equal the algorithmic input "
+                "bytes, writes read 7 % low because the tail of the output is still dirty in L2 when the kernel "
+                "ends (not a saving)")
 
 
 def cpu_baseline(rows, repeats=1):

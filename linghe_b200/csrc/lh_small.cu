@@ -153,9 +153,12 @@ __device__ __forceinline__ void unpack8_neg(const uint4& r, float2* v) {
 // block) and a unit is 16 consecutive blocks whatever rows they fall in, so that every thread has
 // work for any n (n = 1408 fills 69 % of a 2048-element span); `spans` is then n/128.  The price is
 // one integer division per thread and unit.
-template <int SOP, typename InT, int U, bool WIDE, bool FLAT = false>
+// FULL (span form only): the row is a whole number of spans and the grid covers the units exactly, so
+// every thread of every CTA has U units of work: no bounds tests, no zero-fill of the load registers.
+template <int SOP, typename InT, int U, bool WIDE, bool FLAT = false, bool FULL = false>
 __global__ void __launch_bounds__(128)
 small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t units) {
+    static_assert(!(FLAT && FULL), "FULL is a property of the span form");
     constexpr bool SILU = SOP == SOP_SILU;
     const int64_t u0 = int64_t(blockIdx.x) * U;
     int64_t row = FLAT ? 0 : u0 / spans;
@@ -174,9 +177,11 @@ small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t uni
             cols[k] = span * 2048 + threadIdx.x * 16;
         }
         rows[k] = row;
-        raw[2 * k] = raw[2 * k + 1] = make_uint4(0, 0, 0, 0);
-        if constexpr (SILU) rawb[2 * k] = rawb[2 * k + 1] = make_uint4(0, 0, 0, 0);
-        if (u0 + k < units && cols[k] < p.n) {
+        if constexpr (!FULL) {
+            raw[2 * k] = raw[2 * k + 1] = make_uint4(0, 0, 0, 0);
+            if constexpr (SILU) rawb[2 * k] = rawb[2 * k + 1] = make_uint4(0, 0, 0, 0);
+        }
+        if (FULL || (u0 + k < units && cols[k] < p.n)) {
             const uint8_t* src = p.x + (row * in_row + cols[k]) * 2;
             if constexpr (WIDE) {   // x is 32-byte aligned: one 256-bit load per 16 elements
                 ld_global_256(src, raw[2 * k], raw[2 * k + 1]);
@@ -199,7 +204,7 @@ small_units_kernel(const __grid_constant__ SmallParams p, int spans, int64_t uni
 #pragma unroll
     for (int k = 0; k < U; ++k) {
         float2 v[8];
-        const bool valid = cols[k] < p.n;
+        const bool valid = FULL || cols[k] < p.n;
         if constexpr (SILU) {
             float2 g[8];
             unpack8<InT>(raw[2 * k], v);
@@ -662,7 +667,9 @@ small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __re
 // below): it is bound by instruction issue and the latency chain of a row, not by HBM.  So gamma
 // sits in shared memory as float32 for the whole walk -- four conflict-free 16-byte shared loads
 // per 16 elements instead of two global loads and sixteen unpack operations (254 -> 248 us).
-template <int SPANS, bool WIDE>
+// FULL: n is exactly SPANS * 2048, so no thread ever has an empty span: the column tests and the
+// zero-fill of the load registers go away.
+template <int SPANS, bool WIDE, bool FULL>
 __global__ void __launch_bounds__(128, 4)
 small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
     constexpr int SPAN = 2048;
@@ -689,8 +696,8 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
 #pragma unroll
         for (int i = 0; i < SPANS; ++i) {
             const int col = i * SPAN + t * 16;
-            xr[2 * i] = xr[2 * i + 1] = make_uint4(0, 0, 0, 0);
-            if (row < p.M && col < p.n) {
+            if constexpr (!FULL) xr[2 * i] = xr[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if (row < p.M && (FULL || col < p.n)) {   // past the last row nothing is loaded and nothing is used
                 const uint8_t* src = p.x + (row * p.n + col) * 2;
                 if constexpr (WIDE) {   // x is 32-byte aligned
                     ld_global_256(src, xr[2 * i], xr[2 * i + 1]);
@@ -725,7 +732,8 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
 #pragma unroll
         for (int i = 0; i < SPANS; ++i) {
             const int col = i * SPAN + t * 16;
-            if (i * SPAN >= p.n) break;                       // uniform
+            if (!FULL && i * SPAN >= p.n) break;              // uniform
+            const bool valid = FULL || col < p.n;
             float2 v[8];
             unpack8<__nv_bfloat16>(cur[2 * i], v);
             unpack8<__nv_bfloat16>(cur[2 * i + 1], v + 4);
@@ -737,14 +745,14 @@ small_norm_walk_kernel(const __grid_constant__ SmallParams p) {
                     v[2 * k + 1] = mul2(mul2(v[2 * k + 1], r2), make_float2(w.z, w.w));
                 }
             }
-            if (p.y != nullptr && col < p.n) {
+            if (p.y != nullptr && valid) {
                 uint8_t* yo = p.y + (row * p.n + col) * 2;
                 *reinterpret_cast<uint4*>(yo) = make_uint4(pack_bf16x2(v[0].x, v[0].y), pack_bf16x2(v[1].x, v[1].y),
                                                            pack_bf16x2(v[2].x, v[2].y), pack_bf16x2(v[3].x, v[3].y));
                 *reinterpret_cast<uint4*>(yo + 16) = make_uint4(pack_bf16x2(v[4].x, v[4].y), pack_bf16x2(v[5].x, v[5].y),
                                                                 pack_bf16x2(v[6].x, v[6].y), pack_bf16x2(v[7].x, v[7].y));
             }
-            quant16<false>(p, row, col, col < p.n, v);
+            quant16<false>(p, row, col, valid, v);
         }
     };
     uint4 xa[2 * SPANS], xb[2 * SPANS];
@@ -778,7 +786,9 @@ static void launch_small_norm(const SmallParams& p, cudaStream_t stream) {
 // WIDE (256-bit loads) needs a 32-byte aligned input
 template <int SOP, typename InT, int U>
 static void launch_units(const SmallParams& p, int spans, int64_t units, unsigned grid, bool wide, cudaStream_t stream) {
-    if (wide) small_units_kernel<SOP, InT, U, true><<<grid, 128, 0, stream>>>(p, spans, units);
+    const bool full = (p.n % 2048) == 0 && (units % U) == 0;
+    if (wide && full) small_units_kernel<SOP, InT, U, true, false, true><<<grid, 128, 0, stream>>>(p, spans, units);
+    else if (wide) small_units_kernel<SOP, InT, U, true><<<grid, 128, 0, stream>>>(p, spans, units);
     else small_units_kernel<SOP, InT, U, false><<<grid, 128, 0, stream>>>(p, spans, units);
 }
 
@@ -871,8 +881,15 @@ int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, flo
     if (p.n > 4096 && M * n > (int64_t(24) << 20)) {
         const int sms = sm_count();
         const size_t gsm = size_t(4) * 2048 * 4;   // gamma as float32 in shared memory for four spans (32 KB: four CTAs per SM fit)
-        if ((reinterpret_cast<uintptr_t>(x) & 31) == 0) small_norm_walk_kernel<4, true><<<unsigned(4 * sms), 128, gsm, stream>>>(p);
-        else small_norm_walk_kernel<4, false><<<unsigned(4 * sms), 128, gsm, stream>>>(p);
+        const bool wide = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+        const unsigned wg = unsigned(4 * sms);
+        if (p.n == 8192) {
+            if (wide) small_norm_walk_kernel<4, true, true><<<wg, 128, gsm, stream>>>(p);
+            else small_norm_walk_kernel<4, false, true><<<wg, 128, gsm, stream>>>(p);
+        } else {
+            if (wide) small_norm_walk_kernel<4, true, false><<<wg, 128, gsm, stream>>>(p);
+            else small_norm_walk_kernel<4, false, false><<<wg, 128, gsm, stream>>>(p);
+        }
         return check_launch("small_norm_walk_kernel");
     }
     launch_small_norm<true>(p, stream);
