@@ -16,7 +16,8 @@
  *     launched); >0 = a cudaError_t from the launch.  lh_last_error() returns a
  *     thread-local message for the last non-zero return.
  *   - `dtype`: element type of the floating-point inputs (LH_BF16 / LH_F16 / LH_F32).
- *     Fused entry points accept LH_BF16 only; the pure quantisers accept all three.
+ *     Every entry point accepts all three except lh_rmsnorm_gemm_blockquant_fwd (LH_BF16);
+ *     gamma and the incoming gradient have the type of x, bf16 outputs that of the input.
  *   - fp8 outputs are e4m3fn codes (1 byte each); scales are float32 dequantisation
  *     multipliers: scale = max(amax/448, 1e-30), optionally rounded up to a power of 2.
  *   - `output_mode`: 0 = row-wise (1x128) outputs only, 1 = column-wise (128x1,
