@@ -81,14 +81,14 @@ int lh_selftest_wait_timeout(int polls, void* stream);
 /* Measurement switch: sets the named dispatch option and returns its previous value
  * (LH_ERR_ARG for an unknown key).  Process-wide; meant for A/B timing, not for production.
  *   "rmsnorm_both_single_pass"   mode 2 of lh_rmsnorm_blockquant_fwd: 0 = row kernel then column
- *                                kernel, 1 (default) = the single-pass kernel for n < 4096, where
+ *                                kernel, 1 (default) = the single-pass kernel for n < 6144, where
  *                                it is ahead, 2 = the single-pass kernel at every width
  *   "rmsnorm_bwd_quant_single_pass"        lh_rmsnorm_bwd_blockquant: 1 = the single-pass cluster
  *                                kernel (x and dy read from HBM once), 0 (default) = two launches
  *   "rmsnorm_bwd_quant_interleave_min_n"   lh_rmsnorm_bwd_blockquant: rows at least this wide take
  *                                the streaming kernel that also writes the transposed copy
  *                                tile by tile behind its own walk (default: never)
- *   "band_l2_budget_mb"          L2 budget the single-pass kernels size their clusters for (40) */
+ *   "band_cluster"               cluster size of the single-pass kernels: 0 = chosen per shape, else 1 / 2 / 4 / 8 */
 int lh_tuning(const char* key, int value);
 
 /* Scratch bytes needed by the entry point named `what` ("rmsnorm_bwd",
@@ -145,7 +145,7 @@ int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64
 /* RMSNorm + blockwise quantisation.
  * Replaces triton_rms_norm_and_block_quant_forward, linghe/utils/norm.py:343.
  * mode 0: writes q, s, rms.  mode 1: reads rms, writes qT, sT.  mode 2: writes all.
- * Mode 2 with bf16 inputs and n < 4096 is ONE kernel that reads x from HBM once (upstream runs
+ * Mode 2 with bf16 inputs and n < 6144 is ONE kernel that reads x from HBM once (upstream runs
  * two kernels, linghe/utils/norm.py:464-500, and reads x twice); wider rows run a row kernel
  * followed by a column kernel, which is faster there. */
 int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps,

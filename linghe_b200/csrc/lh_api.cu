@@ -14,14 +14,14 @@ constexpr int64_t kSmallRowElements = int64_t(24) << 20;   // output elements up
 
 __device__ int g_device_status = 0;
 
-extern int g_band_l2_budget_mb;
+extern int g_band_cluster;
 // lh_tuning("rmsnorm_both_single_pass"): 0 = always the two-launch path for both-axes RMSNorm + quant,
-// 1 = the single-pass kernel where it is ahead (rows narrower than 4096: 1.05-1.2x at n = 1024 ... 3584,
-// level at 2048; from 4096 on the two launches win, 0.95x at 4096 down to 0.7-0.8x at 8192), 2 = always
+// 1 = the single-pass kernel where it is ahead or level (rows narrower than 6144: 1.04-1.26x below 4096
+// columns, 1.0-1.04x from 4096 to 6144; at 8192 the two launches win by 4-9 %), 2 = always
 static int g_band_kernel = 1;
 static int g_band_bwd = 0;
 static int g_bwd_interleave_min_n = 1 << 30;
-static bool use_band_kernel(int64_t n) { return g_band_kernel == 2 || (g_band_kernel == 1 && n < 4096); }
+static bool use_band_kernel(int64_t n) { return g_band_kernel == 2 || (g_band_kernel == 1 && n < 6144); }
 
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
     const long long t0 = clock64();
@@ -230,7 +230,7 @@ int lh_tuning(const char* key, int value) {
     if (key && !strcmp(key, "rmsnorm_both_single_pass")) { const int old = g_band_kernel; g_band_kernel = value; return old; }
     if (key && !strcmp(key, "rmsnorm_bwd_quant_single_pass")) { const int old = g_band_bwd; g_band_bwd = value; return old; }
     if (key && !strcmp(key, "rmsnorm_bwd_quant_interleave_min_n")) { const int old = g_bwd_interleave_min_n; g_bwd_interleave_min_n = value; return old; }
-    if (key && !strcmp(key, "band_l2_budget_mb")) { const int old = g_band_l2_budget_mb; g_band_l2_budget_mb = value; return old; }
+    if (key && !strcmp(key, "band_cluster")) { const int old = g_band_cluster; g_band_cluster = value; return old; }
     return fail_arg("tuning: unknown key");
 }
 

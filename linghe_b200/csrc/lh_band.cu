@@ -149,31 +149,59 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
     auto group_bar = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(1 + g), "n"(NG) : "memory"); };
     auto compute_bar = [&]() { asm volatile("bar.sync 3, %0;" ::"n"(kComputeThreads) : "memory"); };
 
-    const int64_t total_ops = int64_t(nbands) * 2 * Tc;
-    auto issue = [&](int64_t n) {   // first thread of the group: the tile of operation n into its buffer
-        if (n >= total_ops) return;
-        const int64_t bi = n / (2 * Tc);
-        const int o = int(n - bi * 2 * Tc);
-        const int b = cluster_id + int(bi) * nclusters;
-        const int ct = rank + (o % Tc) * CS;
-        const int slot = int(n % kSlots);
+    // The operations of this CTA, band after band: pass A over its Tc tiles, then pass B over them.  The
+    // groups take alternate operations (2 Tc is even, so group g has the tiles o = g, g + 2, ... of pass A
+    // and o = g ^ (Tc & 1), ... of pass B) and each group runs through its own three buffers g, g + 2, g + 4.
+    struct Cursor {
+        int bi, pass, o;
+    };
+    auto settle = [&](Cursor& c) {   // skip passes in which the group has no tile
+        while (c.o >= Tc && c.bi < nbands) {
+            if (c.pass == 0) { c.pass = 1; c.o = g ^ (Tc & 1); }
+            else { c.pass = 0; ++c.bi; c.o = g; }
+        }
+    };
+    auto advance = [&](Cursor& c) { c.o += 2; settle(c); };
+    auto issue = [&](const Cursor& c, int slot) {   // first thread of the group: one tile into a buffer
+        const int b = cluster_id + c.bi * nclusters;
+        const int ct = rank + c.o * CS;
         mbar_expect_tx(&full[slot], uint32_t(kTileBytes));
         tma_load_2d(smem + size_t(slot) * kTileBytes, &p.tmap_x, ct * 128, b * 128, &full[slot]);
     };
-    // At the start of its operation n the group's first thread refills the buffer of operation n - 2
-    // (which every warp of the group has released, or is about to) with operation n + 4.
-    auto refill = [&](int64_t n) {
-        if (gtid == 0 && n >= 2 && n + 4 < total_ops) {
-            const int64_t prev = n - 2;
-            mbar_wait_or_mark<false>(&empty[prev % kSlots], uint32_t((prev / kSlots) & 1), DEVERR_EMPTY_WAIT, dead);
-            if (!dead) issue(n + 4);
-        }
-    };
+    Cursor pc{0, 0, g};          // the next operation to load
+    settle(pc);
     if (gtid == 0) {
-        issue(g); issue(g + 2); issue(g + 4);
+        for (int k = 0; k < 3 && pc.bi < nbands; ++k) { issue(pc, 2 * k + g); advance(pc); }
+    } else {
+        for (int k = 0; k < 3 && pc.bi < nbands; ++k) advance(pc);
     }
+    int js = 0;                  // buffer index of the current operation inside the group's ring (0..2)
+    uint32_t jph = 0;            // phase parity of that buffer
+    bool first_op = true;
+    // start of an operation: the group's first thread refills the buffer of the group's previous operation
+    // (released by every warp of the group, or about to be) with the operation three ahead
+    auto begin_op = [&]() -> int {
+        if (!first_op && pc.bi < nbands) {
+            if (gtid == 0) {
+                const int prev = js == 0 ? 2 : js - 1;
+                mbar_wait_or_mark<false>(&empty[2 * prev + g], js == 0 ? (jph ^ 1u) : jph, DEVERR_EMPTY_WAIT, dead);
+                if (!dead) issue(pc, 2 * prev + g);
+            }
+            advance(pc);
+        }
+        first_op = false;
+        const int slot = 2 * js + g;
+        mbar_wait_or_mark<true>(&full[slot], jph, DEVERR_FULL_WAIT, dead);
+        return slot;
+    };
+    auto end_op = [&](int slot) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+        if (++js == 3) { js = 0; jph ^= 1u; }
+    };
 
-    int64_t n = 0;
+    Cursor c{0, 0, g};
+    settle(c);
     for (int bi = 0; bi < nbands; ++bi) {
         const int b = cluster_id + bi * nclusters;
         const int par = bi & 1;
@@ -181,11 +209,8 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
         float a[RPT];
 #pragma unroll
         for (int s = 0; s < RPT; ++s) a[s] = 0.f;
-        for (int o = 0; o < Tc; ++o, ++n) {
-            if (int(n & 1) != g) continue;
-            refill(n);
-            const int slot = int(n % kSlots);
-            mbar_wait_or_mark<true>(&full[slot], uint32_t((n / kSlots) & 1), DEVERR_FULL_WAIT, dead);
+        while (c.bi == bi && c.pass == 0) {
+            const int slot = begin_op();
             const uint8_t* base = smem + size_t(slot) * kTileBytes + row0 * 256 + l16 * 16;
 #pragma unroll
             for (int s = 0; s < RPT; ++s) {
@@ -196,14 +221,19 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
                 acc = fma2(v1, v1, acc); acc = fma2(v2, v2, acc); acc = fma2(v3, v3, acc);
                 a[s] += acc.x + acc.y;
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
+            end_op(slot);
+            advance(c);
         }
         {
             const float tot = row_sum_transposed8(a, l16);
             if ((l16 & 1) == 0) rsum[g * 128 + row0 + (l16 >> 1)] = tot;
         }
-        compute_bar();
+        // gamma of the group's first pass-B tile: in flight across the exchange (each later tile's gamma is
+        // fetched one tile ahead), so that no tile waits for a global load
+        uint4 gnext = make_uint4(0, 0, 0, 0);
+        if (c.bi == bi && c.pass == 1)
+            gnext = __ldg(reinterpret_cast<const uint4*>(p.gamma + (rank + c.o * CS) * 256 + l16 * 16));
+        __syncthreads();
         if (tid < 128) {
             const float mine = rsum[tid] + rsum[128 + tid];
             for (int r = 0; r < CS; ++r) st_cluster_f32(peer + (par * kMaxCluster + rank) * 128 + tid, uint32_t(r), mine);
@@ -219,28 +249,33 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
             rinv[tid] = in ? r1 : 0.f;           // rows past the end of the matrix count as zeros
             if (rank == 0 && in) p.rms[grow] = r1;
         }
-        compute_bar();
+        __syncthreads();
         // ---------------- pass B: all four outputs of this group's tiles ----------------
-        for (int o = 0; o < Tc; ++o, ++n) {
-            if (int(n & 1) != g) continue;
-            refill(n);
-            const int slot = int(n % kSlots);
-            const int ct = rank + o * CS;
-            mbar_wait_or_mark<true>(&full[slot], uint32_t((n / kSlots) & 1), DEVERR_FULL_WAIT, dead);
+        const int64_t grow0 = int64_t(b) * 128;
+        const int64_t left = p.M - grow0;
+        const int valid = left < 128 ? int(left) : 128;
+        const int nrows = valid - row0;
+        // per-band bases of this thread's outputs; a tile adds its column offset
+        uint8_t* const q_band = p.q + (grow0 + row0) * p.n + l16 * 8;
+        float* const s_band = p.s + grow0 + row0 + (l16 >> 1);
+        uint8_t* const qt_band = p.qt + int64_t(gtid >> 4) * p.M + grow0 + (gtid & 15) * 8;
+        float* const st_band = p.st + int64_t(b) * p.n + gtid;
+        float ri[RPT];
+        {
+            const float4 ra = *reinterpret_cast<const float4*>(rinv + row0);
+            const float4 rb = *reinterpret_cast<const float4*>(rinv + row0 + 4);
+            ri[0] = ra.x; ri[1] = ra.y; ri[2] = ra.z; ri[3] = ra.w; ri[4] = rb.x; ri[5] = rb.y; ri[6] = rb.z; ri[7] = rb.w;
+        }
+        while (c.bi == bi && c.pass == 1) {
+            const int slot = begin_op();
+            const int ct = rank + c.o * CS;
             uint8_t* tile = smem + size_t(slot) * kTileBytes;
             uint8_t* qts = tile;                 // reused once the tile is in registers
-            const int64_t grow0 = int64_t(b) * 128;
-            const int64_t gcol0 = int64_t(ct) * 128;
-            const int64_t left = p.M - grow0;
-            const int valid = left < 128 ? int(left) : 128;
-            const int nrows = valid - row0;
+            const int gcol0 = ct * 128;
             float2 v[RPT][4];
             {
-                float2 gam[4];
-                load8p<__nv_bfloat16>(p.gamma + gcol0 * 2, l16, gam);
-                const float4 ra = *reinterpret_cast<const float4*>(rinv + row0);
-                const float4 rb = *reinterpret_cast<const float4*>(rinv + row0 + 4);
-                const float ri[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};
+                const float2 gam[4] = {bf16x2_to_f2(gnext.x), bf16x2_to_f2(gnext.y), bf16x2_to_f2(gnext.z), bf16x2_to_f2(gnext.w)};
+                if (c.o + 2 < Tc) gnext = __ldg(reinterpret_cast<const uint4*>(p.gamma + (ct + 2 * CS) * 256 + l16 * 16));
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     float2 x[4];
@@ -253,26 +288,35 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
             // ---- row-wise 1x128 ----
             {
                 constexpr int G = 16 / RPT;
-                float a[RPT];
+                float am[RPT];
 #pragma unroll
                 for (int s = 0; s < RPT; ++s) {
                     float m = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) m = max3abs(v[s][j].x, v[s][j].y, m);
-                    a[s] = m;
+                    am[s] = m;
                 }
-                const float mymax = row_max_transposed<RPT>(a, l16);
+                const float mymax = row_max_transposed<RPT>(am, l16);
                 const float mysc = scale_from_amax(mymax, rs);
                 const float myy = rcp_approx(mysc);
-                const int rr = row0 + l16 / G;
-                if ((l16 % G) == 0 && rr < valid) p.s[int64_t(ct) * p.M + grow0 + rr] = mysc;
-                uint8_t* qrow = p.q + (grow0 + row0) * p.n + gcol0 + l16 * 8;
+                if ((l16 % G) == 0 && row0 + l16 / G < valid) s_band[int64_t(ct) * p.M] = mysc;
+                uint8_t* qrow = q_band + gcol0;
+                if (nrows >= RPT) {   // every row of this thread exists (always, except in a ragged last band)
 #pragma unroll
-                for (int s = 0; s < RPT; ++s) {
-                    const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
-                    const uint2 codes = quant_row8<false, false>(v[s], 0.f, y);
-                    st_global_v2_if(s < nrows, qrow, codes.x, codes.y);
-                    qrow += p.n;
+                    for (int s = 0; s < RPT; ++s) {
+                        const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
+                        const uint2 codes = quant_row8<false, false>(v[s], 0.f, y);
+                        *reinterpret_cast<uint2*>(qrow) = codes;
+                        qrow += p.n;
+                    }
+                } else {
+#pragma unroll
+                    for (int s = 0; s < RPT; ++s) {
+                        const float y = __shfl_sync(0xffffffffu, myy, s * G, 16);
+                        const uint2 codes = quant_row8<false, false>(v[s], 0.f, y);
+                        if (s < nrows) *reinterpret_cast<uint2*>(qrow) = codes;
+                        qrow += p.n;
+                    }
                 }
             }
             // ---- column-wise 128x1, transposed ----
@@ -301,34 +345,34 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
                 const float sc = scale_from_amax(m, rs);
                 cs[gtid] = sc;
                 cy[gtid] = rcp_approx(sc);
-                p.st[int64_t(b) * p.n + gcol0 + gtid] = sc;
+                st_band[gcol0] = sc;
             }
             group_bar();
             float2 y2[4];
             {
-                const float4 c = *reinterpret_cast<const float4*>(cy + l16 * 8);
-                const float4 e = *reinterpret_cast<const float4*>(cy + l16 * 8 + 4);
-                y2[0] = make_float2(c.x, c.y); y2[1] = make_float2(c.z, c.w);
-                y2[2] = make_float2(e.x, e.y); y2[3] = make_float2(e.z, e.w);
+                const float4 c0 = *reinterpret_cast<const float4*>(cy + l16 * 8);
+                const float4 c1 = *reinterpret_cast<const float4*>(cy + l16 * 8 + 4);
+                y2[0] = make_float2(c0.x, c0.y); y2[1] = make_float2(c0.z, c0.w);
+                y2[2] = make_float2(c1.x, c1.y); y2[3] = make_float2(c1.z, c1.w);
             }
+            {
+                uint8_t* qw = qts + (l16 * 8) * 128 + (((gw * 2 + hw) ^ l16) << 3);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float2 qv[RPT];
+                for (int j = 0; j < 4; ++j) {
+                    float2 qv[RPT];
 #pragma unroll
-                for (int s = 0; s < RPT; ++s) qv[s] = mul2(v[s][j], y2[j]);
-                const int colx = l16 * 8 + 2 * j;
-                const int rc = gw * 2 + hw;
-                const uint32_t off = uint32_t((rc ^ l16) << 3);
-                *reinterpret_cast<uint2*>(qts + colx * 128 + off) = make_uint2(
-                    cvt_e4m3x4(qv[0].x, qv[1].x, qv[2].x, qv[3].x), cvt_e4m3x4(qv[4].x, qv[5].x, qv[6].x, qv[7].x));
-                *reinterpret_cast<uint2*>(qts + (colx + 1) * 128 + off) = make_uint2(
-                    cvt_e4m3x4(qv[0].y, qv[1].y, qv[2].y, qv[3].y), cvt_e4m3x4(qv[4].y, qv[5].y, qv[6].y, qv[7].y));
+                    for (int s = 0; s < RPT; ++s) qv[s] = mul2(v[s][j], y2[j]);
+                    *reinterpret_cast<uint2*>(qw + (2 * j) * 128) = make_uint2(
+                        cvt_e4m3x4(qv[0].x, qv[1].x, qv[2].x, qv[3].x), cvt_e4m3x4(qv[4].x, qv[5].x, qv[6].x, qv[7].x));
+                    *reinterpret_cast<uint2*>(qw + (2 * j + 1) * 128) = make_uint2(
+                        cvt_e4m3x4(qv[0].y, qv[1].y, qv[2].y, qv[3].y), cvt_e4m3x4(qv[4].y, qv[5].y, qv[6].y, qv[7].y));
+                }
             }
             group_bar();
             // copy-out: 128 columns x 16 chunks of 8 rows; thread u handles chunk (u & 15) of columns (u >> 4) + 16 k
             {
                 const int rc = gtid & 15, colb = gtid >> 4;
-                uint8_t* dst = p.qt + (gcol0 + colb) * p.M + grow0 + rc * 8;
+                uint8_t* dst = qt_band + int64_t(gcol0) * p.M;
                 const int64_t dstep = int64_t(NG / 16) * p.M;
                 const uint8_t* src = qts + colb * 128;
                 const int nvalid = valid - rc * 8;
@@ -360,14 +404,13 @@ band_norm_fwd_kernel(const __grid_constant__ BandParams p) {
                 }
             }
             fence_async_smem();   // the buffer's next writer is a TMA copy
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[slot]);
+            end_op(slot);
+            advance(c);
         }
         // No barrier here: rsum and rinv are rewritten only behind the next band's barriers, which no
         // thread passes before every compute thread has finished this pass.
     }
 }
-
 
 // ------------------------------------------------------------------------------------------------
 // RMSNorm backward + dual-axis quantisation of dy, x and dy read from HBM exactly once.
@@ -746,32 +789,38 @@ band_norm_bwd_kernel(const __grid_constant__ BandBwdParams p) {
 
 }  // namespace
 
-// Cluster size for a band of `n` columns: the smallest power of two that keeps the bands in flight
-// (active clusters x 128 n 2 bytes) within a budget of L2, given the active clusters per size.
-int g_band_l2_budget_mb = 40;   // lh_tuning("band_l2_budget_mb")
+int g_band_cluster = 0;         // lh_tuning("band_cluster"): 0 = choose, else force 1 / 2 / 4 / 8
 
-// Cluster size for bands of `cols` 16-bit columns (the forward passes n, the backward 2 n for its two
-// operands).  Two pulls: few bands want large clusters, so that bands x C covers the SMs; many
-// bands want the smallest cluster whose bands in flight (active clusters x band bytes) stay within
-// a budget of L2, because larger clusters leave SMs unused (active CTAs: 148 / 148 / 132 / 120 for
-// C = 1 / 2 / 4 / 8 at this shared-memory footprint).
-static int pick_cluster(int64_t cols, const int* active /* [4]: sizes 1, 2, 4, 8 */, int64_t bands) {
-    const int64_t band_bytes = 128 * cols * 2;
-    const int64_t budget = int64_t(g_band_l2_budget_mb) << 20;
-    const int64_t tiles = cols / 128;
-    int best = 0;
-    int64_t best_ctas = 0;
-    int largest = 1;
+// Cluster size for bands of `tiles` 128-column tiles.  A cluster of C CTAs walks a band in
+// ceil(tiles / C) tile steps plus one exchange, and min(bands, active clusters) bands are in flight,
+// so a launch costs about  ceil(bands / in flight) x (ceil(tiles / C) + 1/4)  tile steps.  The
+// measured times follow this count (active CTAs are 148 / 148 / 132 / 120 for C = 1 / 2 / 4 / 8 at
+// this shared-memory footprint, so few bands want C = 4 and many bands want C = 2); the bytes of
+// the bands in flight, which decide whether the second pass hits L2, moved the measured order only
+// between candidates that this count puts within a few percent of one another, so among those the
+// largest cluster (the smallest footprint in L2) is taken.
+static int pick_cluster(int64_t tiles, const int* active /* [4]: sizes 1, 2, 4, 8 */, int64_t bands) {
+    if (g_band_cluster == 1 || g_band_cluster == 2 || g_band_cluster == 4 || g_band_cluster == 8) {
+        int i = 0;
+        while ((1 << i) < g_band_cluster) ++i;
+        if (active[i] > 0 && tiles >= g_band_cluster) return g_band_cluster;
+    }
+    int64_t cost[4];
+    int64_t least = 0;
+    int cands = 0;
     for (int i = 0; i < 4; ++i) {
         const int c = 1 << i;
         if (active[i] <= 0 || tiles < c) break;
-        largest = c;
         const int64_t ncl = bands < active[i] ? bands : active[i];
-        if (ncl * band_bytes > budget) continue;
-        const int64_t ctas = ncl * c;
-        if (best == 0 || ctas * 100 > best_ctas * 105) { best = c; best_ctas = ctas; }   // a larger cluster must buy 5 % more CTAs
+        const int64_t waves = (bands + ncl - 1) / ncl;
+        cost[i] = waves * (4 * ((tiles + c - 1) / c) + 1);   // in quarter tile steps
+        if (cands == 0 || cost[i] < least) least = cost[i];
+        ++cands;
     }
-    return best != 0 ? best : largest;
+    int best = 1;
+    for (int i = 0; i < cands; ++i)
+        if (cost[i] * 100 <= least * 105) best = 1 << i;
+    return best;
 }
 
 // x bf16 [M, n], n % 128 == 0; all five outputs.  Returns LH_ERR_ARG + 1000 (-999) when clusters
@@ -810,7 +859,7 @@ int band_norm_fwd(const void* x, const void* gamma, int64_t M, int64_t n, float 
     }
     const int* active = active_cache[dev];
     if (active[0] <= 0) return -999;
-    const int CSZ = pick_cluster(n, active, bands);
+    const int CSZ = pick_cluster(n / 128, active, bands);
     int idx = 0;
     while ((1 << idx) < CSZ) ++idx;
     int64_t nclusters = active[idx];
@@ -869,7 +918,7 @@ int band_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     }
     const int* active = active_cache[dev];
     if (active[0] <= 0) return -999;
-    const int CSZ = pick_cluster(2 * n, active, bands);   // a band holds x and dy
+    const int CSZ = pick_cluster(n / 128, active, bands);
     int idx = 0;
     while ((1 << idx) < CSZ) ++idx;
     int64_t nclusters = active[idx];

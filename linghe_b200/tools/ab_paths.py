@@ -6,6 +6,8 @@ rotating buffers, the harness of bench_configs):
     python -m linghe_b200.tools.ab_paths --what bwd     RMSNorm backward + dy dual quant: two launches against
                                                         the single-pass cluster kernel ("band") and the
                                                         streaming kernel with interleaved column tiles
+    python -m linghe_b200.tools.ab_paths --what fwd_clusters   the single-pass forward kernel at each forced
+                                                        cluster size (1, 2, 4, 8) beside the two launches
 
 The paths are switched with lh_tuning(); the defaults are restored at the end.
 """
@@ -24,7 +26,7 @@ from linghe_b200.utils.norm import rms_norm_backward_and_block_quant, triton_rms
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", choices=["fwd", "bwd"], required=True)
+    ap.add_argument("--what", choices=["fwd", "bwd", "fwd_clusters"], required=True)
     ap.add_argument("--json", default=None)
     a = ap.parse_args()
     torch.cuda.set_device(0)
@@ -49,6 +51,26 @@ def main():
                 print(row, flush=True)
                 rows.append(row)
         lib.lh_tuning(b"rmsnorm_both_single_pass", 1)
+    elif a.what == "fwd_clusters":
+        for n in (1024, 2048, 3072, 4096, 5120, 6144, 8192):
+            for M in (4096, 16384, 65536):
+                if M * n > 600e6:
+                    continue
+                g = gam[:n].contiguous()
+                nbytes = M * n * 4
+                row = {"n": n, "M": M}
+                for name, mode, C in (("C1_us", 2, 1), ("C2_us", 2, 2), ("C4_us", 2, 4), ("C8_us", 2, 8),
+                                      ("chosen_us", 2, 0), ("two_launch_us", 0, 0)):
+                    lib.lh_tuning(b"rmsnorm_both_single_pass", mode)
+                    lib.lh_tuning(b"band_cluster", C)
+                    ev, gr, _ = BC.time_call(lambda i: (BC.bf16_randn((M, n), i), g),
+                                             lambda x, w: triton_rms_norm_and_block_quant_forward(x, w, output_mode=2),
+                                             nbytes, 30 if nbytes < 1e9 else 10)
+                    row[name] = round(gr if gr else ev, 1)
+                print(row, flush=True)
+                rows.append(row)
+        lib.lh_tuning(b"rmsnorm_both_single_pass", 1)
+        lib.lh_tuning(b"band_cluster", 0)
     else:
         for (M, n) in ((16384, 4096), (8192, 2048), (65536, 2048), (16384, 8192), (32768, 4096), (4096, 4096),
                        (16384, 1536), (8192, 5120)):

@@ -324,7 +324,7 @@ def test_rms_block_quant_both_paths(M, n, force):
                                  (128, 128)])
 def test_rms_bwd_fused_dy_quant(M, n, path):
     from linghe_b200.utils.norm import rms_norm_backward_and_block_quant as fused_entry
-    key, val = {"default": ("band_l2_budget_mb", 40), "band": ("rmsnorm_bwd_quant_single_pass", 1),
+    key, val = {"default": ("band_cluster", 0), "band": ("rmsnorm_bwd_quant_single_pass", 1),
                 "interleave": ("rmsnorm_bwd_quant_interleave_min_n", 128)}[path]
 
     def rms_norm_backward_and_block_quant(*a, **kw):
