@@ -85,9 +85,11 @@ int lh_selftest_wait_timeout(int polls, void* stream);
  *                                it is ahead, 2 = the single-pass kernel at every width
  *   "rmsnorm_bwd_quant_single_pass"        lh_rmsnorm_bwd_blockquant: 1 = the single-pass cluster
  *                                kernel (x and dy read from HBM once), 0 (default) = two launches
- *   "rmsnorm_bwd_quant_interleave_min_n"   lh_rmsnorm_bwd_blockquant: rows at least this wide take
- *                                the streaming kernel that also writes the transposed copy
- *                                tile by tile behind its own walk (default: never)
+ *   "rmsnorm_bwd_quant_two_role_min_n"   lh_rmsnorm_bwd_blockquant: rows at least this wide take
+ *                                the streaming kernel with a second role per CTA that writes the
+ *                                transposed copy tile by tile beside the walk (default: never)
+ *   "second_launch_descends"     1 (default) = the second launch of a two-launch path walks the row
+ *                                bands last to first, starting with what the first left in L2
  *   "band_cluster"               cluster size of the single-pass kernels: 0 = chosen per shape, else 1 / 2 / 4 / 8 */
 int lh_tuning(const char* key, int value);
 

@@ -25,10 +25,13 @@ LIBNAME = "liblinghe_b200.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo", "-rdc=true",
+    "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
     "--expt-relaxed-constexpr",
 ]
+
+
+WHOLE_PROGRAM = {"lh_duo.cu"}
 
 
 def nvcc_path() -> str:
@@ -60,7 +63,9 @@ def _digest() -> str:
 
 def _compile(src: str, verbose: bool) -> str:
     obj = os.path.join(OBJDIR, src[:-3] + ".o")
-    cmd = [nvcc_path(), *NVCC_FLAGS, "-dc", os.path.join(CSRC, src), "-o", obj]
+    # relocatable device code everywhere except the files that use setmaxnreg (ptxas ignores it there)
+    mode = ["-c"] if src in WHOLE_PROGRAM else ["-rdc=true", "-dc"]
+    cmd = [nvcc_path(), *NVCC_FLAGS, *mode, os.path.join(CSRC, src), "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     log = os.path.join(OBJDIR, src[:-3] + ".ptxas.log")
     with open(log, "w") as fh:

@@ -20,7 +20,8 @@ extern int g_band_cluster;
 // columns, 1.0-1.04x from 4096 to 6144; at 8192 the two launches win by 4-9 %), 2 = always
 static int g_band_kernel = 1;
 static int g_band_bwd = 0;
-static int g_bwd_interleave_min_n = 1 << 30;
+static int g_second_descends = 1;   // second launch of a two-launch path walks the row bands last to first
+static int g_bwd_two_role_min_n = 1 << 30;
 static bool use_band_kernel(int64_t n) { return g_band_kernel == 2 || (g_band_kernel == 1 && n < 6144); }
 
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
@@ -146,12 +147,12 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
              int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
-               cudaStream_t stream);
+               cudaStream_t stream, int descending = 0);
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
                       int idx_type, const void* counts, int counts_type, int E, int64_t m, int64_t Mout, int64_t N,
                       void* q, float* s, void* qt, float* st, void* prob_out, int round_scale, cudaStream_t stream);
 int tile_norm(const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n, void* q, float* s,
-              void* qt, float* st, int round_scale, int mode, cudaStream_t stream);
+              void* qt, float* st, int round_scale, int mode, cudaStream_t stream, int descending = 0);
 int tile_silu_fwd(const void* x, const void* w, int w_dtype, int dtype, const void* counts, int counts_type, int E,
                   int64_t M, int64_t n, void* q, float* s, void* qt, float* st, int round_scale, int mode,
                   cudaStream_t stream);
@@ -175,7 +176,7 @@ int64_t rows_norm_bwd_scratch(int64_t n);
 int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
                   cudaStream_t stream, void* dy_q = nullptr, float* dy_s = nullptr, int round_scale = 0,
-                  int* dy_rows_done = nullptr, void* dy_qt = nullptr, float* dy_st = nullptr, int interleave_min_n = 1 << 30);
+                  int* dy_rows_done = nullptr, void* dy_qt = nullptr, float* dy_st = nullptr, int two_role_min_n = 1 << 30);
 int64_t rows_norm_bwd_static_bytes();
 int rows_norm_bwd_static(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                          int64_t n, float eps, void* dx, float* dgamma, cudaStream_t stream);
@@ -229,7 +230,8 @@ int lh_device_status(int* status) {
 int lh_tuning(const char* key, int value) {
     if (key && !strcmp(key, "rmsnorm_both_single_pass")) { const int old = g_band_kernel; g_band_kernel = value; return old; }
     if (key && !strcmp(key, "rmsnorm_bwd_quant_single_pass")) { const int old = g_band_bwd; g_band_bwd = value; return old; }
-    if (key && !strcmp(key, "rmsnorm_bwd_quant_interleave_min_n")) { const int old = g_bwd_interleave_min_n; g_bwd_interleave_min_n = value; return old; }
+    if (key && !strcmp(key, "rmsnorm_bwd_quant_two_role_min_n")) { const int old = g_bwd_two_role_min_n; g_bwd_two_role_min_n = value; return old; }
+    if (key && !strcmp(key, "second_launch_descends")) { const int old = g_second_descends; g_second_descends = value; return old; }
     if (key && !strcmp(key, "band_cluster")) { const int old = g_band_cluster; g_band_cluster = value; return old; }
     return fail_arg("tuning: unknown key");
 }
@@ -358,7 +360,7 @@ int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64
         if (!qt || !st || !x || !gamma) return fail_arg("rmsnorm_blockquant_fwd: NULL pointer");
         if (!aligned16(x) || !aligned16(qt) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: pointers must be 16-byte aligned");
         if (M == 0) return LH_OK;
-        return tile_norm(x, gamma, rms, LH_BF16, M, n, nullptr, nullptr, qt, st, round_scale, 1, cs);
+        return tile_norm(x, gamma, rms, LH_BF16, M, n, nullptr, nullptr, qt, st, round_scale, 1, cs, output_mode == 2 ? g_second_descends : 0);
     }
     return LH_OK;
 }
@@ -435,14 +437,15 @@ int lh_rmsnorm_bwd_blockquant(const void* dy, const void* x, const void* gamma, 
     }
     // Where the backward runs as the streaming kernel it also quantises dy row-wise from the registers
     // it already holds, and the tile kernel is left with the transposed copy only.
-    // g_bwd_interleave_min_n: from this row width on the streaming kernel also writes the transposed copy,
-    // tile by tile behind its own walk, and no second kernel runs
+    // g_bwd_two_role_min_n: from this row width on the streaming kernel's CTAs carry a second role that writes
+    // the transposed copy tile by tile beside the walk, and no second kernel runs
     int rows_done = 0;
     if (int rc = rows_norm_bwd(dy, x, gamma, rms, dtype, M, n, eps, dx, dgamma, scratch, scratch_bytes, cs, dy_q, dy_s,
-                               round_scale, &rows_done, dy_qt, dy_st, g_bwd_interleave_min_n))
+                               round_scale, &rows_done, dy_qt, dy_st, g_bwd_two_role_min_n))
         return rc;
     if (rows_done == 2) return LH_OK;
-    return tile_quant(dy, dtype, nullptr, 0, 1, M, n, dy_q, dy_s, dy_qt, dy_st, round_scale, rows_done ? 1 : 2, 0, cs);
+    return tile_quant(dy, dtype, nullptr, 0, 1, M, n, dy_q, dy_s, dy_qt, dy_st, round_scale, rows_done ? 1 : 2, 0, cs,
+                      rows_done ? g_second_descends : 0);
 }
 
 int lh_weighted_silu_fwd(const void* x, const void* w, int dtype, int w_dtype, int64_t M, int64_t n, void* y,

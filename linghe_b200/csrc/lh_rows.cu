@@ -746,11 +746,11 @@ int64_t rows_norm_bwd_scratch(int64_t n) { return int64_t(kMaxRowCtas) * n * 4; 
 // dy_q / dy_s (optional): where the streaming kernel runs it also writes the row-wise 1x128 codes
 // and scales ([n/128, M]) of dy and sets *dy_rows_done = 1; with dy_qt / dy_st as well (and M a
 // multiple of 16) also the transposed 128x1 copy, *dy_rows_done = 2.  Otherwise they are left
-// untouched.  interleave_min_n: narrowest row for which the fused call prefers the streaming kernel.
+// untouched.  two_role_min_n: narrowest row for which the fused call prefers the streaming kernel.
 int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,
                   int64_t n, float eps, void* dx, float* dgamma, void* scratch, int64_t scratch_bytes,
                   cudaStream_t stream, void* dy_q, float* dy_s, int round_scale, int* dy_rows_done, void* dy_qt,
-                  float* dy_st, int interleave_min_n) {
+                  float* dy_st, int two_role_min_n) {
     if (dy_rows_done) *dy_rows_done = 0;
     if (int rc = check_rows("rmsnorm_bwd", dtype, M, n)) return rc;
     if (!x || !dy || !gamma || !dx || !dgamma) return fail_arg("rmsnorm_bwd: NULL pointer");
@@ -771,12 +771,18 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     // 301 us at 65536 x 4096, 354 vs 370 us at 32768 x 8192), narrower ones the TMA ring (159 vs
     // 174 us at 65536 x 2048).
     const bool qdy = dy_q != nullptr && dy_s != nullptr && aligned16(dy_q) && dy_rows_done != nullptr;
-    const bool colq = qdy && dy_qt != nullptr && dy_st != nullptr && aligned16(dy_qt) && (M % 16) == 0 && n >= interleave_min_n;
+    const bool colq = qdy && dy_qt != nullptr && dy_st != nullptr && aligned16(dy_qt) && (M % 16) == 0 && n >= two_role_min_n;
     if (n > 2048 || colq) {
-        if (int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, qdy ? dy_q : nullptr,
-                                    dy_s, round_scale, stream, colq ? dy_qt : nullptr, dy_st))
-            return rc;
-        if (qdy) *dy_rows_done = colq ? 2 : 1;
+        int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, qdy ? dy_q : nullptr,
+                                dy_s, round_scale, stream, colq ? dy_qt : nullptr, dy_st);
+        bool cols_done = colq;
+        if (rc == LH_ERR_ARG - 1000 && colq) {   // the two-role kernel cannot launch here: rows only, the caller adds the columns
+            cols_done = false;
+            rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, dy_q, dy_s, round_scale,
+                                stream, nullptr, nullptr);
+        }
+        if (rc) return rc;
+        if (qdy) *dy_rows_done = cols_done ? 2 : 1;
     } else if (int rc = launch_rows<ROP_NORM_BWD, 16, 3, 1>(p, &grid, stream)) {
         return rc;
     }

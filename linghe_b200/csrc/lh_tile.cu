@@ -31,7 +31,7 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
-               cudaStream_t stream) {
+               cudaStream_t stream, int descending) {
     if (M < 0 || N <= 0 || (N % 128) != 0) return fail_arg("quant: need N %% 128 == 0 (M=%lld N=%lld)", (long long)M, (long long)N);
     if (M == 0) return LH_OK;
     if (!aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("quant: pointers must be 16-byte aligned");
@@ -44,7 +44,7 @@ int tile_quant(const void* x, int dtype, const void* counts, int counts_type, in
     p.counts = counts; p.counts_i64 = counts_type == LH_I64; p.E = counts ? E : 1;
     p.M = M; p.n = N;
     p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st;
-    p.round_scale = round_scale; p.scale_rowmajor = scale_rowmajor;
+    p.round_scale = round_scale; p.scale_rowmajor = scale_rowmajor; p.descending = descending;
     return quant_any(p, dtype, mode, stream);
 }
 
@@ -93,9 +93,9 @@ int tile_silu_bwd_any(const void* g, const void* x, const void* w, int w_dtype, 
 // RMSNorm with known 1/rms + quantisation.  bfloat16: transposed outputs only (mode 1); the other
 // input types: every mode.
 int tile_norm(const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n, void* q, float* s,
-              void* qt, float* st, int round_scale, int mode, cudaStream_t stream) {
+              void* qt, float* st, int round_scale, int mode, cudaStream_t stream, int descending) {
     if (dtype != LH_BF16) return tile_norm_any(x, gamma, r, dtype, M, n, q, s, qt, st, round_scale, mode, stream);
-    return tile_norm_t<__nv_bfloat16, false>(x, gamma, r, dtype, M, n, q, s, qt, st, round_scale, mode, stream);
+    return tile_norm_t<__nv_bfloat16, false>(x, gamma, r, dtype, M, n, q, s, qt, st, round_scale, mode, stream, descending);
 }
 
 int tile_silu_fwd(const void* x, const void* w, int w_dtype, int dtype, const void* counts, int counts_type, int E,

@@ -49,6 +49,9 @@ struct TileParams {
     float* dws;            // OP_SILU_B: optional per-(row, column block) partial dw
     int round_scale;
     int scale_rowmajor;    // MODE_ROW only: s[i*nb + b] instead of s[b*M + i]
+    int descending;        // walk the tiles from the last row band to the first: for a launch that re-reads
+                           // a tensor the previous launch has just streamed in ascending order, so that it
+                           // starts with the part of it that is still in L2
 };
 
 template <int OP> struct OpTraits;
@@ -358,7 +361,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
     // the matrix read as zero, rows of a following expert segment are masked by `valid`.
     auto issue = [&](int tile, int stage) {
         if constexpr (OP == OP_GATHER) return;   // gathered rows are loaded straight into registers
-        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab_ptr());
+        const TileLoc t = locate(p.descending ? int(total_tiles) - 1 - tile : tile, col_tiles, segS, segB, E, tab_ptr());
         uint8_t* dst = stages + size_t(stage) * C::STAGEB;
         const int r0 = int(t.S + int64_t(t.T) * 128);
         const int c0 = t.ct * 128;
@@ -392,7 +395,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
 #pragma unroll
         for (int s = 0; s < RPT; ++s) idx[s] = -1;           // -1: padding row (zeros) or no tile
         if (tile < 0) return;
-        const TileLoc tl = locate(tile, col_tiles, segS, segB, E, tab_ptr());
+        const TileLoc tl = locate(p.descending ? int(total_tiles) - 1 - tile : tile, col_tiles, segS, segB, E, tab_ptr());
         const int cnt = segC[tl.e] - tl.T * 128 - row0;      // real (unpadded) rows left for this thread
         const int64_t g0 = tl.S + int64_t(tl.T) * 128 + row0;
 #pragma unroll
@@ -408,7 +411,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
         if (tile >= 0) {
             const int ct = tile % col_tiles;
             if (p.prob_out != nullptr && ct == 0 && l16 == 0) {
-                const TileLoc tl = locate(tile, col_tiles, segS, segB, E, tab_ptr());
+                const TileLoc tl = locate(p.descending ? int(total_tiles) - 1 - tile : tile, col_tiles, segS, segB, E, tab_ptr());
                 const int64_t g0 = tl.S + int64_t(tl.T) * 128 + row0;
                 const int nr = tl.valid - row0;
 #pragma unroll
@@ -463,7 +466,7 @@ tile_kernel(const __grid_constant__ TileParams p) {
                 if (!dead) issue(int(nxt), prev_stage);
             }
         }
-        const TileLoc t = locate(tile, col_tiles, segS, segB, E, tab_ptr());
+        const TileLoc t = locate(p.descending ? int(total_tiles) - 1 - tile : tile, col_tiles, segS, segB, E, tab_ptr());
         const int64_t grow0 = t.S + int64_t(t.T) * 128;   // global row of tile row 0
         const int64_t gcol0 = int64_t(t.ct) * 128;        // column inside a half
         // Per-row and per-column side inputs come straight from global memory: fetch them
@@ -835,10 +838,10 @@ struct FusedCfg {
 // transposed-output kernel (the bfloat16 row-wise outputs come from the streaming kernels)
 template <typename InT, bool ALL_MODES>
 static int tile_norm_t(const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n, void* q,
-                       float* s, void* qt, float* st, int round_scale, int mode, cudaStream_t stream) {
+                       float* s, void* qt, float* st, int round_scale, int mode, cudaStream_t stream, int descending = 0) {
     TileParams p{};
     if (int rc = make_tensor_map(&p.tmap[0], x, dtype, uint64_t(M), uint64_t(n), uint64_t(n) * sizeof(InT), 128, 128)) return rc;
-    p.r = r; p.gamma = gamma; p.E = 1; p.M = M; p.n = n;
+    p.r = r; p.gamma = gamma; p.E = 1; p.M = M; p.n = n; p.descending = descending;
     p.q = static_cast<uint8_t*>(q); p.s = s; p.qt = static_cast<uint8_t*>(qt); p.st = st; p.round_scale = round_scale;
     constexpr int CPS = FusedCfg<InT>::NORM_CPS;
     if (mode == MODE_COL) return launch_tile<OP_NORM, InT, MODE_COL, LH_FUSED_EXACT, 8, 2, CPS>(p, stream);

@@ -5,7 +5,7 @@ rotating buffers, the harness of bench_configs):
                                                         kernel ("two") against the single-pass cluster kernel
     python -m linghe_b200.tools.ab_paths --what bwd     RMSNorm backward + dy dual quant: two launches against
                                                         the single-pass cluster kernel ("band") and the
-                                                        streaming kernel with interleaved column tiles
+                                                        streaming kernel with a second, tile-quantising role per CTA
     python -m linghe_b200.tools.ab_paths --what fwd_clusters   the single-pass forward kernel at each forced
                                                         cluster size (1, 2, 4, 8) beside the two launches
 
@@ -77,16 +77,16 @@ def main():
             g = gam[:n].contiguous()
             nbytes = 3 * M * n * 2 + 2 * M * n + 2 * M * n * 4 // 128 + n * 6
             row = {"M": M, "n": n}
-            for name, band, il in (("two_launch_us", 0, 1 << 30), ("interleave_us", 0, 128), ("band_us", 1, 1 << 30)):
+            for name, band, il in (("two_launch_us", 0, 1 << 30), ("two_role_us", 0, 128), ("band_us", 1, 1 << 30)):
                 lib.lh_tuning(b"rmsnorm_bwd_quant_single_pass", band)
-                lib.lh_tuning(b"rmsnorm_bwd_quant_interleave_min_n", il)
+                lib.lh_tuning(b"rmsnorm_bwd_quant_two_role_min_n", il)
                 ev, gr, _ = BC.time_call(lambda i: (BC.bf16_randn((M, n), 100 + i, 0.01), BC.bf16_randn((M, n), i), g),
                                          rms_norm_backward_and_block_quant, nbytes, 50 if nbytes < 1e9 else 12)
                 row[name] = round(gr if gr else ev, 2)
             print(row, flush=True)
             rows.append(row)
         lib.lh_tuning(b"rmsnorm_bwd_quant_single_pass", 0)
-        lib.lh_tuning(b"rmsnorm_bwd_quant_interleave_min_n", 1 << 30)
+        lib.lh_tuning(b"rmsnorm_bwd_quant_two_role_min_n", 1 << 30)
     assert _lib.device_status(0) == 0
     if a.json:
         with open(a.json, "w") as fh:

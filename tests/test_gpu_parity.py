@@ -317,15 +317,15 @@ def test_rms_block_quant_both_paths(M, n, force):
 # rows wider than 2048: the streaming backward also writes dy's row-wise codes and scales, the tile
 # kernel only the transposed copy; (640, 2304) leaves the second span of a thread partly empty.
 # The two single-pass implementations (x and dy read from HBM once) are selectable and held to the
-# same checks: "band" = the cluster kernel, "interleave" = the streaming kernel that also writes the
-# transposed copy tile by tile behind its own walk.
-@pytest.mark.parametrize("path", ["default", "band", "interleave"])
+# same checks: "band" = the cluster kernel, "two_role" = the streaming kernel whose CTAs carry a
+# second role (four more warps) that writes the transposed copy tile by tile.
+@pytest.mark.parametrize("path", ["default", "band", "two_role"])
 @pytest.mark.parametrize("M,n", [(1024, 2048), (1024, 4096), (640, 2304), (384, 8192), (400, 2048), (4112, 1536),
                                  (128, 128)])
 def test_rms_bwd_fused_dy_quant(M, n, path):
     from linghe_b200.utils.norm import rms_norm_backward_and_block_quant as fused_entry
     key, val = {"default": ("band_cluster", 0), "band": ("rmsnorm_bwd_quant_single_pass", 1),
-                "interleave": ("rmsnorm_bwd_quant_interleave_min_n", 128)}[path]
+                "two_role": ("rmsnorm_bwd_quant_two_role_min_n", 128)}[path]
 
     def rms_norm_backward_and_block_quant(*a, **kw):
         with tuning(key, val):
