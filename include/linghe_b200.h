@@ -147,6 +147,7 @@ int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64
 /* RMSNorm + blockwise quantisation.
  * Replaces triton_rms_norm_and_block_quant_forward, linghe/utils/norm.py:343.
  * mode 0: writes q, s, rms.  mode 1: reads rms, writes qT, sT.  mode 2: writes all.
+ * n % 128 == 0, except mode 1, which takes n % 32 == 0 as upstream does (linghe/utils/norm.py:416-419).
  * Mode 2 with bf16 inputs and n < 6144 is ONE kernel that reads x from HBM once (upstream runs
  * two kernels, linghe/utils/norm.py:464-500, and reads x twice); wider rows run a row kernel
  * followed by a column kernel, which is faster there. */
@@ -224,7 +225,9 @@ int lh_weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype,
                          int64_t n, void* dx, void* dw, void* stream);
 
 /* SwiGLU + blockwise quantisation.
- * Replaces triton_silu_and_block_quant_forward, linghe/utils/silu.py:279. */
+ * Replaces triton_silu_and_block_quant_forward, linghe/utils/silu.py:279.
+ * n % 128 == 0, except mode 1 (qT, sT only), which takes n % 64 == 0 as upstream does
+ * (linghe/utils/silu.py:313-317). */
 int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, void* qt,
                            float* st, int round_scale, int output_mode, void* stream);
 

@@ -240,6 +240,88 @@ unsigned row_grid(int64_t M, int per_sm) {
     return unsigned(g < 1 ? 1 : g);
 }
 
+
+// Transposed-only (128x1) outputs for row widths that are not a multiple of 128.  The upstream
+// column-only kernels tile the width by 32 (RMSNorm) or 64 (SwiGLU) columns, so they accept such
+// widths; the 128x128 tile kernels here do not.  One CTA = the 128 rows of a band x 32 columns:
+// thread t holds row t's 32 values, column maxima by a transposing butterfly inside each warp
+// (31 shuffles for 32 columns) and a 4-way maximum through shared memory, then byte stores that
+// are consecutive across the CTA for every column.  SILU: x is [M, 2n], value = silu(x1) * x2.
+// The arithmetic is that of the tile kernel's fused variants (approximate reciprocal of the scale).
+template <typename T, bool SILU>
+__global__ void __launch_bounds__(128)
+any_col_strip_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const float* __restrict__ r, int64_t M, int n,
+                     uint8_t* __restrict__ qt, float* __restrict__ st, int round_scale) {
+    __shared__ float cmax[4][32];
+    __shared__ float cy[32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int64_t band = blockIdx.x;
+    const int c0 = int(blockIdx.y) * 32;
+    const int64_t row = band * 128 + t;
+    float v[32];
+    if (row < M) {
+        if constexpr (SILU) {
+            const T* x1 = x + row * (2 * int64_t(n)) + c0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float a[8], b[8];
+                load8(x1 + 8 * k, a);
+                load8(x1 + n + 8 * k, b);
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                    const float2 x1p = make_float2(a[j], a[j + 1]);
+                    const float2 y = mul2(mul2(sigmoid_fast2(x1p), x1p), make_float2(b[j], b[j + 1]));
+                    v[8 * k + j] = y.x; v[8 * k + j + 1] = y.y;
+                }
+            }
+        } else {
+            const float rr = r[row];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float a[8], g[8];
+                load8(x + row * n + c0 + 8 * k, a);
+                load8(gamma + c0 + 8 * k, g);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[8 * k + j] = (a[j] * rr) * g[j];
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0.f;
+    }
+    // after the butterfly lane L holds the maximum of column L over the warp's 32 rows
+    float a[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) a[j] = fabsf(v[j]);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const bool up = (lane & d) != 0;
+#pragma unroll
+        for (int i = 0; i < d; ++i) {
+            const float send = up ? a[i] : a[i + d];
+            const float keep = up ? a[i + d] : a[i];
+            a[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, d));
+        }
+    }
+    cmax[warp][lane] = a[0];
+    __syncthreads();
+    if (t < 32) {
+        const float m = fmaxf(fmaxf(cmax[0][t], cmax[1][t]), fmaxf(cmax[2][t], cmax[3][t]));
+        const float sc = scale_from_amax(m, round_scale != 0);
+        cy[t] = rcp_approx(sc);
+        st[band * n + c0 + t] = sc;
+    }
+    __syncthreads();
+    if (row < M) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            const uint32_t c4 = cvt_e4m3x4(v[j] * cy[j], v[j + 1] * cy[j + 1], v[j + 2] * cy[j + 2], v[j + 3] * cy[j + 3]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) qt[int64_t(c0 + j + k) * M + row] = uint8_t(c4 >> (8 * k));
+        }
+    }
+}
+
 }  // namespace
 
 // 1/rms per row (float32 [M]) of a float16 / float32 matrix
@@ -307,6 +389,25 @@ int any_weighted_silu(const void* g, const void* x, const void* w, int dtype, in
                 nullptr, static_cast<const float*>(x), w, w_dtype, M, n, static_cast<float*>(out), nullptr);
     }
     return check_launch("any_weighted_silu_kernel");
+}
+
+// Transposed-only outputs for n % 32 == 0 (any n).  silu: x is [M, 2n]; otherwise RMSNorm with
+// the given 1/rms per row.
+int any_col_strip(int silu, const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n,
+                  void* qt, float* st, int round_scale, cudaStream_t stream) {
+    if (M == 0) return LH_OK;
+    const dim3 grid(unsigned((M + 127) / 128), unsigned(n / 32));
+    uint8_t* q8 = static_cast<uint8_t*>(qt);
+#define LH_STRIP(T)                                                                                                   \
+    do {                                                                                                              \
+        if (silu) any_col_strip_kernel<T, true><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), nullptr, nullptr, M, int(n), q8, st, round_scale); \
+        else any_col_strip_kernel<T, false><<<grid, 128, 0, stream>>>(static_cast<const T*>(x), static_cast<const T*>(gamma), r, M, int(n), q8, st, round_scale); \
+    } while (0)
+    if (dtype == LH_F16) LH_STRIP(__half);
+    else if (dtype == LH_F32) LH_STRIP(float);
+    else LH_STRIP(__nv_bfloat16);
+#undef LH_STRIP
+    return check_launch("any_col_strip_kernel");
 }
 
 }  // namespace lh

@@ -148,6 +148,8 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
                cudaStream_t stream, int descending = 0);
+int any_col_strip(int silu, const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n,
+                  void* qt, float* st, int round_scale, cudaStream_t stream);
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
                       int idx_type, const void* counts, int counts_type, int E, int64_t m, int64_t Mout, int64_t N,
                       void* q, float* s, void* qt, float* st, void* prob_out, int round_scale, cudaStream_t stream);
@@ -188,9 +190,12 @@ int weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype, in
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-static int check_fused(const char* what, int dtype, int64_t M, int64_t n, int mode) {
+// col_only_unit: column granularity the entry point accepts in output_mode 1 (transposed outputs
+// only), where the row width need not be a whole number of 1x128 blocks; 128 = no such mode
+static int check_fused(const char* what, int dtype, int64_t M, int64_t n, int mode, int col_only_unit = 128) {
     if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
-    if (M < 0 || n <= 0 || (n % 128) != 0) return fail_arg("%s: need n %% 128 == 0 (M=%lld n=%lld)", what, (long long)M, (long long)n);
+    const int unit = mode == 1 ? col_only_unit : 128;
+    if (M < 0 || n <= 0 || (n % unit) != 0) return fail_arg("%s: need n %% %d == 0 (M=%lld n=%lld)", what, unit, (long long)M, (long long)n);
     if (mode < 0 || mode > 2) return fail_arg("%s: output_mode must be 0, 1 or 2", what);
     return LH_OK;
 }
@@ -319,9 +324,13 @@ int lh_rmsnorm_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64
 int lh_rmsnorm_blockquant_fwd(const void* x, const void* gamma, int dtype, int64_t M, int64_t n, float eps,
                               void* q, float* s, float* rms, void* qt, float* st, int round_scale,
                               int output_mode, void* stream) {
-    if (int rc = check_fused("rmsnorm_blockquant_fwd", dtype, M, n, output_mode)) return rc;
+    if (int rc = check_fused("rmsnorm_blockquant_fwd", dtype, M, n, output_mode, 32)) return rc;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (!rms) return fail_arg("rmsnorm_blockquant_fwd: rms is NULL");
+    if ((n % 128) != 0) {   // output_mode 1 on a width the 128 x 128 tiles do not cover
+        if (!x || !gamma || !qt || !st || !aligned16(x) || !aligned16(gamma)) return fail_arg("rmsnorm_blockquant_fwd: NULL or unaligned pointer");
+        return any_col_strip(0, x, gamma, rms, dtype, M, n, qt, st, round_scale, cs);
+    }
     if (dtype != LH_BF16) {
         // float16 / float32: 1/rms per row from a plain row kernel, then the tile kernel in the
         // requested mode (one pass over x for every output)
@@ -473,10 +482,12 @@ int lh_weighted_silu_bwd(const void* g, const void* x, const void* w, int dtype,
 
 int lh_silu_blockquant_fwd(const void* x, int dtype, int64_t M, int64_t n, void* q, float* s, void* qt, float* st,
                            int round_scale, int output_mode, void* stream) {
-    if (int rc = check_fused("silu_blockquant_fwd", dtype, M, n, output_mode)) return rc;
+    if (int rc = check_fused("silu_blockquant_fwd", dtype, M, n, output_mode, 64)) return rc;
     if (!x || !aligned16(x) || !aligned16(q) || !aligned16(qt)) return fail_arg("silu_blockquant_fwd: NULL or unaligned pointer");
     if ((output_mode != 1 && (!q || !s)) || (output_mode != 0 && (!qt || !st))) return fail_arg("silu_blockquant_fwd: output pointer is NULL");
     if (M == 0) return LH_OK;
+    if ((n % 128) != 0)     // output_mode 1 on a width the 128 x 128 tiles do not cover
+        return any_col_strip(1, x, nullptr, nullptr, dtype, M, n, qt, st, round_scale, static_cast<cudaStream_t>(stream));
     if (output_mode == 0 && dtype == LH_BF16)   // the register kernels at every size and width
         return small_silu_quant(x, M, n, q, s, round_scale, static_cast<cudaStream_t>(stream));
     return tile_silu_fwd(x, nullptr, LH_F32, dtype, nullptr, 0, 1, M, n, q, s, qt, st, round_scale, output_mode,

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
-from tests.common import assert_codes_close, assert_rel_close, assert_scales_close
+from tests.common import assert_codes_close, assert_fused_pow2, assert_rel_close, assert_scales_close
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -30,6 +30,13 @@ def rnd(shape, seed, dtype, coef=1.0):
 def fused(got_q, ref_q, got_s, ref_s, what):
     assert_scales_close(got_s, ref_s, what + " scale")
     assert_codes_close(got_q, ref_q, what + " codes")
+
+
+def check_fused(got_q, ref_q, got_s, ref_s, what, pow2):
+    if pow2:
+        assert_fused_pow2(got_q, ref_q, got_s, ref_s, what)
+    else:
+        fused(got_q, ref_q, got_s, ref_s, what)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -146,3 +153,32 @@ def test_batch_silu_other_dtypes(dtype):
     assert_scales_close(st, rst, "batch bwd col scale (ragged tails)", rtol=2e-5)
     assert_codes_close(qt, rqt, "batch bwd col codes")
     assert_rel_close(dw, rdw, "batch dw", 1e-3, 1e-3)
+
+
+# Transposed-only outputs (output_mode 1) on widths that are not a whole number of 1x128 blocks:
+# upstream tiles that mode by 32 columns (RMSNorm, linghe/utils/norm.py:416-419) and by 64 (SwiGLU,
+# linghe/utils/silu.py:313-317).
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,n", [(1000, 1440), (256, 32), (130, 4000)])
+def test_rms_block_quant_col_only_narrow_width(M, n, dt):
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    x = (torch.randn((M, n), generator=torch.Generator().manual_seed(21)) * 2).to(dt)
+    g = torch.randn((n,), generator=torch.Generator().manual_seed(22)).to(dt)
+    for rs in (False, True):
+        _, _, rr, rqt, rst = O.rms_norm_and_block_quant_forward(x, g, 1e-6, rs)
+        o = triton_rms_norm_and_block_quant_forward(x.cuda(), g.cuda(), rms=rr.cuda(), round_scale=rs, output_mode=1)
+        assert o[0] is None and o[1] is None
+        assert o[3].shape == (n, M) and o[4].shape == ((M + 127) // 128, n)
+        check_fused(o[3], rqt, o[4], rst, "narrow col", rs)
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,n", [(1000, 1472), (256, 64), (130, 2752)])
+def test_silu_block_quant_col_only_narrow_width(M, n, dt):
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward
+    x = torch.randn((M, 2 * n), generator=torch.Generator().manual_seed(23)).to(dt)
+    for rs in (False, True):
+        _, _, rqt, rst = O.silu_and_block_quant_forward(x, rs)
+        _, _, qt, st = triton_silu_and_block_quant_forward(x.cuda(), round_scale=rs, output_mode=1)
+        assert qt.shape == (n, M) and st.shape == ((M + 127) // 128, n)
+        check_fused(qt, rqt, st, rst, "narrow col", rs)
