@@ -13,7 +13,7 @@ namespace {
 // first NT threads walk rows (dx, the dgamma sums, the row-wise codes of dy), the last 128 threads
 // take 128 x 128 tiles of dy (tile blockIdx.x, + gridDim.x, ... in band-major order) and write
 // the transposed codes and scales.  Nothing depends on the order of the two, so there is no
-// inter-role wait for correctness; the tile role only paces itself to stay within LEAD bands of
+// inter-role wait for correctness; the tile role only paces itself to stay within LEAD (8) bands of
 // its own CTA's walk, so that whichever role touches a band second finds it in L2 and dy crosses
 // the HBM interface once.  The roles hide each other's latencies on the SM's schedulers.  The
 // register file is split by setmaxnreg: RREG per walking thread, CREG per tile thread; the host
@@ -21,7 +21,7 @@ namespace {
 template <int SPANS, int NT, int MINB, bool WIDE, int RREG, int CREG>
 __global__ void __launch_bounds__(NT + 128, MINB)
 small_norm_bwd_duo_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
-    constexpr int LEAD = 4;
+    constexpr int LEAD = 8;
     __shared__ float wsum[2][2][NT / 32];
     __shared__ __align__(16) float cq_cmax[8 * 128];
     __shared__ __align__(16) float cq_cs[128], cq_cy[128];
@@ -36,16 +36,20 @@ small_norm_bwd_duo_kernel(const __grid_constant__ SmallParams p, const uint8_t* 
         const int t = threadIdx.x - NT;
         const int nct = p.n >> 7;
         const int64_t col_tiles = ((p.M + 127) >> 7) * nct;
-        bool pace = true;
+        bool pace = true;   // used by the role's first thread only
         for (int64_t tile = blockIdx.x; tile < col_tiles; tile += gridDim.x) {
             const int band = int(tile / nct);
-            if (pace) {   // bounded: a pacing hint only, giving it up costs a second read of dy, not correctness
+            // One thread watches the walk, the others wait at the role's barrier (a hardware wait that
+            // takes no issue slots from the walking warps; 128 polling threads did).  Bounded: it is a
+            // pacing hint only, giving it up costs a second read of dy from HBM, not correctness.
+            if (t == 0 && pace) {
                 uint32_t polls = 0;
                 while (*static_cast<volatile int*>(&walk_band) < band - LEAD) {   // walk_band ends at INT_MAX: no sum on that side
-                    __nanosleep(200);
+                    __nanosleep(500);
                     if (++polls > (1u << 20)) { pace = false; break; }
                 }
             }
+            role_sync<2, 128>();
             col_quant_tile<128, 2>(p, dy, band, int(tile - int64_t(band) * nct), t, cq_cmax, cq_cs, cq_cy);
         }
     }

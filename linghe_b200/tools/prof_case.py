@@ -11,6 +11,8 @@ profiler captures of a single kernel are taken from.
   group_quant                        1x128 group quantiser
   norm_fwd / norm_bwd                plain RMSNorm forward / backward
   norm_bwd_quant                     RMSNorm backward fused with the dual-axis quantisation of dy
+`--tuning key=value` (repeatable) sets a dispatch option through lh_tuning() first, e.g.
+`--tuning rmsnorm_bwd_quant_two_role_min_n=128` to capture the two-role backward kernel.
 """
 
 from __future__ import annotations
@@ -36,8 +38,15 @@ def main():
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--tuning", action="append", default=[])
     a = ap.parse_args()
     torch.cuda.set_device(0)
+    if a.tuning:
+        from linghe_b200 import _lib
+        lib = _lib.load()
+        for kv in a.tuning:
+            key, val = kv.split("=")
+            assert lib.lh_tuning(key.encode(), int(val)) >= 0, f"unknown tuning key {key}"
     from linghe_b200.quant.block import triton_blockwise_quant
     from linghe_b200.quant.group import triton_group_quant
     from linghe_b200.utils.norm import (rms_norm_backward_and_block_quant, triton_rms_norm_and_block_quant_forward,
