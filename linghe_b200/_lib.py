@@ -85,6 +85,29 @@ def load() -> ctypes.CDLL:
     return _lib
 
 
+_host = False
+
+
+def host():
+    """The C++ argument handling of the hottest wrappers (host/lh_host.cpp), or None when it was
+    not built; the callers then take the ctypes path to the same entry points."""
+    global _host
+    if _host is False:
+        load()
+        path = os.path.join(os.path.dirname(LIB_PATH), "_lh_host.so")
+        mod = None
+        if os.path.exists(path) and os.environ.get("LINGHE_B200_NO_HOST_MODULE") is None:
+            try:
+                import importlib.util
+                spec = importlib.util.spec_from_file_location("_lh_host", path)
+                mod = importlib.util.module_from_spec(spec)
+                spec.loader.exec_module(mod)
+            except Exception:  # noqa: BLE001 -- optional accelerator of the host side only
+                mod = None
+        _host = mod
+    return _host
+
+
 def last_error() -> str:
     return load().lh_last_error().decode()
 

@@ -22,6 +22,8 @@ CSRC = os.path.join(PKG, "csrc")
 LIBDIR = os.path.join(PKG, "lib")
 OBJDIR = os.path.join(PKG, "build")
 LIBNAME = "liblinghe_b200.so"
+HOSTDIR = os.path.join(PKG, "host")
+HOSTNAME = "_lh_host.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -53,6 +55,7 @@ def _digest() -> str:
     h = hashlib.sha256()
     inc = os.path.join(os.path.dirname(PKG), "include", "linghe_b200.h")
     files = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC))] + [inc]
+    files += [os.path.join(HOSTDIR, f) for f in sorted(os.listdir(HOSTDIR)) if f.endswith(".cpp")]
     for f in files:
         with open(f, "rb") as fh:
             h.update(f.encode())
@@ -93,9 +96,42 @@ def build(force: bool = False, verbose: bool = False) -> str:
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    _build_host(verbose)
     with open(stamp, "w") as fh:
         fh.write(dig)
     return lib_path()
+
+
+def host_path() -> str:
+    return os.path.join(LIBDIR, HOSTNAME)
+
+
+def _build_host(verbose: bool) -> None:
+    """The C++ argument handling of the hottest wrappers (host/lh_host.cpp): a Python extension module
+    linked against the library above.  Optional: without it the wrappers go through ctypes (the
+    same C ABI and kernels, a few microseconds more host time per call), so a failure here is
+    reported and does not fail the build."""
+    if os.path.exists(host_path()):
+        os.remove(host_path())
+    try:
+        import sysconfig
+
+        import torch
+        from torch.utils import cpp_extension as ce
+        tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", os.path.join(HOSTDIR, "lh_host.cpp"), "-o", host_path(),
+               "-I" + os.path.join(os.path.dirname(PKG), "include"), "-I/usr/local/cuda/include",
+               "-I" + sysconfig.get_paths()["include"], *["-I" + d for d in ce.include_paths()],
+               f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}", "-DTORCH_EXTENSION_NAME=_lh_host",
+               "-DTORCH_API_INCLUDE_EXTENSION_H", "-L" + tlib, "-lc10", "-lc10_cuda", "-ltorch", "-ltorch_cpu",
+               "-ltorch_python", "-L" + LIBDIR, "-llinghe_b200", "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(r.stderr[-2000:])
+        if verbose:
+            print(r.stderr)
+    except Exception as e:  # noqa: BLE001 -- optional component, see the docstring
+        print(f"linghe_b200.build: host module not built ({e}); the wrappers will use ctypes", file=sys.stderr)
 
 
 def main():

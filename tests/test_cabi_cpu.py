@@ -68,3 +68,23 @@ def test_no_cpu_fallback():
     from linghe_b200.quant.block import triton_blockwise_quant
     with pytest.raises(RuntimeError):
         triton_blockwise_quant(torch.zeros((128, 128), dtype=torch.bfloat16))
+
+
+def test_host_module_loads_and_has_no_cpu_fallback():
+    # the C++ argument handling in front of the two hottest entry points (host/lh_host.cpp)
+    import pytest
+    import torch
+    from linghe_b200.utils.norm import triton_rms_norm_and_block_quant_forward
+    from linghe_b200.utils.silu import triton_silu_and_block_quant_forward
+    B.build()
+    h = _lib.host()
+    assert h is not None, "host module was not built"
+    with pytest.raises(RuntimeError):
+        triton_rms_norm_and_block_quant_forward(torch.zeros((128, 128), dtype=torch.bfloat16),
+                                                torch.ones((128,), dtype=torch.bfloat16), output_mode=0)
+    with pytest.raises(AssertionError):     # n % 128 in the row-wise modes, as upstream asserts
+        triton_silu_and_block_quant_forward(torch.zeros((128, 200), dtype=torch.bfloat16), output_mode=0)
+    with pytest.raises(AssertionError):     # rms is an output in mode 0
+        triton_rms_norm_and_block_quant_forward(torch.zeros((128, 128), dtype=torch.bfloat16),
+                                                torch.ones((128,), dtype=torch.bfloat16), rms=torch.zeros(128),
+                                                output_mode=0)
