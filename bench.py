@@ -269,22 +269,25 @@ def run_ours(args, rank, world, device):
     h_xs = torch.empty(xs.shape, dtype=xs.dtype, pin_memory=True).copy_(xs)
     h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in (q1, s1, q2, s2)]
     h_rms = torch.empty((rows,), dtype=torch.float32, pin_memory=True)
-    NCH = 8 if rows % (8 * 128) == 0 else 1
+    NCH = 16 if rows % (16 * 128) == 0 else (8 if rows % (8 * 128) == 0 else 1)
     h_s1 = [torch.empty((HIDDEN // 128, rows // NCH), dtype=torch.float32, pin_memory=True) for _ in range(NCH)]
     h_s2 = [torch.empty((HIDDEN // 128, rows // NCH), dtype=torch.float32, pin_memory=True) for _ in range(NCH)]
     h2d = h_xn.numel() * 2 + h_xs.numel() * 2
     d2h = sum(t.numel() * t.element_size() for t in h_out) + h_rms.numel() * 4
 
     # Rows are independent, so the end-to-end path pipelines row chunks over three streams:
-    # host->device copies, kernels, device->host copies (PCIe is full duplex).
-    NCHUNK = 8 if rows % (8 * 128) == 0 else 1
+    # host->device copies, kernels, device->host copies (PCIe is full duplex).  Consecutive steps are
+    # not separated by a stream join: step k+1's first copy in may start while step k's last results
+    # are still on their way out (stream order alone keeps every buffer's writes in sequence).
+    NCHUNK = NCH
     crow = rows // NCHUNK
     s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     s_main = torch.cuda.current_stream()
 
+    s_in.wait_stream(s_main)
+    s_out.wait_stream(s_main)
+
     def e2e_step():
-        s_in.wait_stream(s_main)
-        s_out.wait_stream(s_main)
         keep = []
         for c in range(NCHUNK):
             r0, r1 = c * crow, (c + 1) * crow
@@ -310,10 +313,10 @@ def run_ours(args, rank, world, device):
                 for t_ in (a, b, cq, d, r):
                     t_.record_stream(s_out)
             keep.append((a, b, cq, d, r))
-        s_main.wait_stream(s_out)
 
     del xn, xs
     e2e_step()
+    s_main.wait_stream(s_out)
     torch.cuda.synchronize()
     barrier()
     e0 = torch.cuda.Event(enable_timing=True)
@@ -321,6 +324,7 @@ def run_ours(args, rank, world, device):
     e0.record()
     for _ in range(Ke):
         e2e_step()
+    s_main.wait_stream(s_out)     # the last results have reached the host before the closing event
     e1.record()
     torch.cuda.synchronize()
     barrier()
