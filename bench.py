@@ -258,9 +258,19 @@ def run_ours(args, rank, world, device):
         for _ in range(n_sus):
             step()
         u1.record()
+        # the split between the two kernels at the clocks the long loop settles at: the last 16 steps
+        # again with an event between the launches (outside the sustained window)
+        sev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(16)]
+        for e in sev:
+            e[0].record()
+            norm_q(xn, gamma, out=q1, scale=s1, output_mode=0)
+            e[1].record()
+            silu_q(xs, out=q2, scale=s2, output_mode=0)
+            e[2].record()
         torch.cuda.synchronize()
         sus_t1 = time.perf_counter()
         sus_ms = u0.elapsed_time(u1)
+        sus_split = (sum(e[0].elapsed_time(e[1]) for e in sev) / 16 * 1e3, sum(e[1].elapsed_time(e[2]) for e in sev) / 16 * 1e3)
     barrier()
 
     # ---- end to end through the public API with host buffers --------------------------
@@ -390,6 +400,7 @@ def run_ours(args, rank, world, device):
         sus_value = world * step_bytes * n_sus / (sus_ms * 1e-3) / 1e9
         line["sustained"] = {"gbs": round(sus_value, 1), "seconds": round(sus_ms * 1e-3, 2), "steps": n_sus,
                              "ms_per_step": round(sus_ms / n_sus, 4),
+                             "us_per_call": {"rmsnorm_quant": round(sus_split[0], 1), "swiglu_quant": round(sus_split[1], 1)},
                              "pct_of_nominal_8TBs_per_gpu": round(100 * sus_value / world / NOMINAL_HBM_GBS, 1),
                              "clocks": sampler.summary(sus_t0, sus_t1)}
     if world == 1 and not args.no_configs:
