@@ -287,6 +287,13 @@ int lh_unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_i
 int lh_fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,
                 int64_t K, int block_size, int a_s_transposed, int b_s_transposed, int out_dtype, void* stream);
 
+/* The same product with 2-D block scales: one float32 scale per block_size x block_size
+ * sub-matrix, a_s [ceil(M/block), K/block] and b_s [ceil(N/block), K/block] (what
+ * lh_block_quant writes for block_size 128).
+ * Replaces triton_bb_fp8_gemm, linghe/gemm/blockwise_fp8_gemm.py:59. */
+int lh_fp8_gemm_bb(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,
+                   int64_t K, int block_size, int out_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -144,7 +144,7 @@ int small_norm_quant(const void* x, const void* gamma, int64_t M, int64_t n, flo
 int small_norm_y(const void* x, const void* gamma, int64_t M, int64_t n, float eps, void* y, float* rms, int reuse_rms,
                  cudaStream_t stream);
 int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
-             int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream);
+             int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream, int group_2d = 0);
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
                cudaStream_t stream, int descending = 0);
@@ -417,6 +417,11 @@ int lh_fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s
                 int64_t K, int block_size, int a_s_transposed, int b_s_transposed, int out_dtype, void* stream) {
     return fp8_gemm(a, b, a_s, b_s, c, M, N, K, block_size, a_s_transposed, b_s_transposed, out_dtype,
                     static_cast<cudaStream_t>(stream));
+}
+
+int lh_fp8_gemm_bb(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,
+                   int64_t K, int block_size, int out_dtype, void* stream) {
+    return fp8_gemm(a, b, a_s, b_s, c, M, N, K, block_size, 0, 0, out_dtype, static_cast<cudaStream_t>(stream), 1);
 }
 
 int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float* rms, int dtype, int64_t M,

@@ -85,6 +85,8 @@ struct Fp8GemmParams {
     int nsb;             // scale blocks along k
     int a_s_transposed;  // 0: a_s [M, nsb]   1: a_s [nsb, M]
     int b_s_transposed;  // 0: b_s [N, nsb]   1: b_s [nsb, N]
+    int group;           // rows of a (of b) that share a scale: 1 = one scale per row and k-block, otherwise
+                         // the block size (2-D block scales: a_s [ceil(M/group), nsb], b_s [ceil(N/group), nsb])
     int out_dtype;
 };
 
@@ -181,14 +183,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int blk = i / FN, col = i - blk * FN;
             const int n = n0 + col;
             float v = 0.f;
-            if (n < p.N) v = p.b_s_transposed ? p.b_s[int64_t(blk) * p.N + n] : p.b_s[int64_t(n) * nsb + blk];
+            if (n < p.N) v = p.b_s_transposed ? p.b_s[int64_t(blk) * p.N + n] : p.b_s[int64_t(n / p.group) * nsb + blk];
             sb[i] = v;
         }
         named_bar<1, F_THREADS - 64>();
         const int quarter = warp & 3, cgrp = (warp - 2) >> 2;       // tensor-memory lane quarter, 32-column group
         const int64_t row = int64_t(m0) + quarter * 32 + lane;
         const bool row_ok = row < p.M;
-        const float* as_ptr = p.a_s + (p.a_s_transposed ? row : row * nsb);
+        const float* as_ptr = p.a_s + (p.a_s_transposed ? row : (row / p.group) * nsb);
         const int64_t as_step = p.a_s_transposed ? p.M : 1;
         float2 acc[16];
 #pragma unroll
@@ -267,8 +269,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }  // namespace
 
 // c [M,N] = blockwise-scaled a [M,K] . b [N,K]^T ; block = 128 or 64 along k, K a multiple of 128.
+// group_2d != 0: 2-D block scales (one per block x block sub-matrix of a and of b), never transposed.
 int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N, int64_t K,
-             int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream) {
+             int block, int a_s_transposed, int b_s_transposed, int out_dtype, cudaStream_t stream, int group_2d) {
     if (!a || !b || !a_s || !b_s || !c) return fail_arg("fp8_gemm: NULL pointer");
     if (block != 128 && block != 64) return fail_arg("fp8_gemm: block_size must be 128 or 64");
     if (M < 0 || N <= 0 || K <= 0 || (K % FKB)) return fail_arg("fp8_gemm: need K a positive multiple of 128 and N > 0");
@@ -285,7 +288,8 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
     Fp8GemmParams p{};
     p.a_s = a_s; p.b_s = b_s; p.c = c;
     p.M = M; p.N = int(N); p.K = int(K); p.nsb = int(nsb);
-    p.a_s_transposed = a_s_transposed; p.b_s_transposed = b_s_transposed; p.out_dtype = out_dtype;
+    p.a_s_transposed = group_2d ? 0 : a_s_transposed; p.b_s_transposed = group_2d ? 0 : b_s_transposed; p.out_dtype = out_dtype;
+    p.group = group_2d ? block : 1;
     const dim3 grid(unsigned((N + FN - 1) / FN), unsigned((M + FM - 1) / FM));
     auto go = [&](auto kern) -> int {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM);

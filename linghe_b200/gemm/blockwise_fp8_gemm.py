@@ -1,7 +1,9 @@
 """Blockwise-scaled FP8 GEMM, mirror of linghe/gemm/blockwise_fp8_gemm.py.
 
-Only the 1 x block (tile-wise, "tt") variant that consumes the activations' wire format
-is provided: `triton_tt_fp8_gemm` (linghe/gemm/blockwise_fp8_gemm.py:152)."""
+`triton_tt_fp8_gemm` (linghe/gemm/blockwise_fp8_gemm.py:152) takes one scale per 1 x block run
+along K on both operands -- the activations' wire format; `triton_bb_fp8_gemm`
+(linghe/gemm/blockwise_fp8_gemm.py:59) one scale per block x block sub-matrix, the format of
+`triton_block_quant`.  Both run the same tcgen05 kernel."""
 
 import torch
 
@@ -38,4 +40,33 @@ def triton_tt_fp8_gemm(
     t = int(bool(scales_transposed))
     _lib.call("lh_fp8_gemm", a, _lib.ptr(a), _lib.ptr(b), _lib.ptr(a_s), _lib.ptr(b_s), _lib.ptr(c), M, N, K,
               int(block_size), t, t, _OUT[out_dtype])
+    return c
+
+
+def triton_bb_fp8_gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_s: torch.Tensor,
+    b_s: torch.Tensor,
+    out_dtype=torch.bfloat16,
+    block_size=128,
+):
+    """c = dequant(a) @ dequant(b).T for e4m3 `a` [..., K], `b` [N, K] with one float32 scale per
+    block_size x block_size sub-matrix: a_s [ceil(M/block_size), K/block_size],
+    b_s [ceil(N/block_size), K/block_size] (linghe/gemm/blockwise_fp8_gemm.py:59-97).  Returns
+    c [M, N] as upstream does."""
+    assert a.is_contiguous() and b.is_contiguous()
+    assert a_s.is_contiguous() and b_s.is_contiguous()
+    assert a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn
+    assert a_s.dtype == torch.float32 and b_s.dtype == torch.float32
+    assert out_dtype in _OUT
+    K = a.size(-1)
+    M = a.numel() // K
+    N = b.size(0)
+    assert b.size(1) == K and K % block_size == 0
+    nb = K // block_size
+    assert a_s.numel() == -(-M // block_size) * nb and b_s.numel() == -(-N // block_size) * nb
+    c = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    _lib.call("lh_fp8_gemm_bb", a, _lib.ptr(a), _lib.ptr(b), _lib.ptr(a_s), _lib.ptr(b_s), _lib.ptr(c), M, N, K,
+              int(block_size), _OUT[out_dtype])
     return c

@@ -199,6 +199,23 @@ def tt_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.bfloat16, block_size: int = 
     return (a_dq @ b_dq.t()).to(out_dtype)
 
 
+def bb_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.bfloat16, block_size: int = 128):
+    """FP8 GEMM with 2-D block scales: dequantise both operands and multiply in float32.
+
+    The reference's own check for ``triton_bb_fp8_gemm`` (tests/test_blockwise_fp8_gemm.py:14-36):
+    x_dq = x_q.float().view(M/B, B, K/B, B) * x_scales[:, None, :, None], same for w,
+    y = x_dq @ w_dq.T.  a_s [ceil(M/B), K/B], b_s [ceil(N/B), K/B]; a ragged last row block
+    (which the reference's kernel masks, linghe/gemm/blockwise_fp8_gemm.py:30-31,53-55) takes the
+    scale row of its block.
+    """
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    B = block_size
+    a_dq = a_q.float() * a_s.repeat_interleave(B, dim=0)[:M].repeat_interleave(B, dim=1)
+    b_dq = b_q.float() * b_s.repeat_interleave(B, dim=0)[:N].repeat_interleave(B, dim=1)
+    return (a_dq @ b_dq.t()).to(out_dtype)
+
+
 # --------------------------------------------------------------------------- #
 # SwiGLU (dense)
 # --------------------------------------------------------------------------- #

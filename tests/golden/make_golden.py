@@ -223,7 +223,30 @@ def main():
     out["indices"] = indices.numpy().astype(np.int64)
     out["row_id_map"] = row_id_map.numpy().astype(np.int64)
     np.savez_compressed(os.path.join(HERE, "route.npz"), **out)
-    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route"):
+    # ---- FP8 GEMM with 2-D block scales: upstream computes the expected value inline in
+    # tests/test_blockwise_fp8_gemm.py:14-36 (dequantise with a_s[:, None, :, None], float32
+    # matmul); the same lines on codes and scales from upstream's torch_block_quant (B = 128) and
+    # on random scales (B = 64, as in that test).  Its own generator: the files above stay as they are.
+    out = {}
+    gbb = torch.Generator().manual_seed(20240608)
+    M, N, K = 256, 128, 512
+    xa = bf16_randn(gbb, (M, K))
+    wb = bf16_randn(gbb, (N, K), 3)
+    a_q, a_s = U.torch_block_quant(xa, B=128, round_scale=False)      # scales [M/128, K/128]
+    b_q, b_s = U.torch_block_quant(wb, B=128, round_scale=False)
+    out["a_q"], out["b_q"] = u8(a_q), u8(b_q)
+    out["a_s128"], out["b_s128"] = f32(a_s), f32(b_s)
+    a_s64 = torch.rand((M // 64, K // 64), generator=gbb)
+    b_s64 = torch.rand((N // 64, K // 64), generator=gbb)
+    out["a_s64"], out["b_s64"] = f32(a_s64), f32(b_s64)
+    for B, sa, sb in ((128, a_s, b_s), (64, a_s64, b_s64)):
+        x_dq = (a_q.float().view(M // B, B, K // B, B) * sa[:, None, :, None]).view(M, K)
+        w_dq = (b_q.float().view(N // B, B, K // B, B) * sb[:, None, :, None]).view(N, K)
+        y = x_dq @ w_dq.t()
+        out[f"y{B}_f32"] = f32(y)
+        out[f"y{B}_bf16"] = u16(y.to(torch.bfloat16))
+    np.savez_compressed(os.path.join(HERE, "fp8gemm_bb.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route", "fp8gemm_bb"):
         p = os.path.join(HERE, f + ".npz")
         print(p, os.path.getsize(p))
 

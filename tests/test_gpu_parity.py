@@ -727,6 +727,60 @@ def test_fp8_gemm(M, N, K, block, dt):
     assert err <= (1e-5 if dt == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("block", [128, 64])
+def test_golden_bb_fp8_gemm(block):
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_bb_fp8_gemm
+    G = golden("fp8gemm_bb")
+    a_q, b_q = _cuda(fp8(G["a_q"])), _cuda(fp8(G["b_q"]))
+    a_s, b_s = _cuda(torch.from_numpy(G[f"a_s{block}"])), _cuda(torch.from_numpy(G[f"b_s{block}"]))
+    y32 = triton_bb_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.float32, block_size=block)
+    assert _gemm_err(y32, torch.from_numpy(G[f"y{block}_f32"])) <= 1e-5
+    yb = triton_bb_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.bfloat16, block_size=block)
+    assert yb.dtype == torch.bfloat16
+    assert_rel_close(yb.float(), bf16(G[f"y{block}_bf16"]).float(), "y bf16", 1e-2)
+
+
+# 2-D block scales (one per block x block sub-matrix): the reference's test uses block 64 at 4096^3
+# (tests/test_blockwise_fp8_gemm.py:14-36); ragged M and N take the scale row of their block
+@pytest.mark.parametrize("M,N,K,block,dt", [(512, 384, 1024, 128, torch.bfloat16), (1024, 256, 512, 64, torch.float16),
+                                            (130, 72, 4096, 128, torch.float32), (2048, 2048, 2048, 64, torch.bfloat16),
+                                            (1000, 200, 1024, 64, torch.float32)])
+def test_bb_fp8_gemm(M, N, K, block, dt):
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_bb_fp8_gemm
+    g = torch.Generator().manual_seed(52)
+    a_q = torch.randn((M, K), generator=g).to(torch.float8_e4m3fn)
+    b_q = torch.randn((N, K), generator=g).to(torch.float8_e4m3fn)
+    a_s = torch.rand((-(-M // block), K // block), generator=g) + 0.01
+    b_s = torch.rand((-(-N // block), K // block), generator=g) + 0.01
+    ref = O.bb_fp8_gemm(a_q, b_q, a_s, b_s, torch.float32, block)
+    y = triton_bb_fp8_gemm(_cuda(a_q), _cuda(b_q), _cuda(a_s), _cuda(b_s), out_dtype=dt, block_size=block)
+    assert y.dtype == dt and tuple(y.shape) == (M, N)
+    err = _gemm_err(y, ref)
+    print(f"bb fp8 gemm {M}x{N}x{K} block {block}: max err / max |y| = {err:.2e}")
+    assert err <= (1e-5 if dt == torch.float32 else 5e-3)
+
+
+def test_bb_fp8_gemm_consumes_block_quant_outputs():
+    """x, w -> 128 x 128 block codes and scales from triton_block_quant -> GEMM, against the float32
+    product of the dequantised operands and, loosely, of the unquantised ones; and the same
+    product through the 1 x 128 entry point with the block scales repeated per row, bit for bit."""
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_bb_fp8_gemm, triton_tt_fp8_gemm
+    from linghe_b200.quant.block import triton_block_quant
+    M, N, K = 1024, 512, 2048
+    x, w = randn_bf16((M, K), 64), randn_bf16((N, K), 65)
+    xq, xs = triton_block_quant(_cuda(x))
+    wq, ws = triton_block_quant(_cuda(w))
+    y = triton_bb_fp8_gemm(xq, wq, xs, ws, out_dtype=torch.float32, block_size=128)
+    ref = O.bb_fp8_gemm(xq.cpu(), wq.cpu(), xs.cpu(), ws.cpu(), torch.float32, 128)
+    assert _gemm_err(y, ref) <= 1e-5
+    assert _gemm_err(y, x.float() @ w.float().t()) <= 5e-2           # the quantisation error itself
+    yt = triton_tt_fp8_gemm(xq, wq, xs.repeat_interleave(128, dim=0).contiguous(),
+                            ws.repeat_interleave(128, dim=0).contiguous(), out_dtype=torch.float32, block_size=128)
+    assert torch.equal(y, yt)
+    with pytest.raises(AssertionError):
+        triton_bb_fp8_gemm(xq, wq, xs[:-1].contiguous(), ws, block_size=128)
+
+
 def test_fp8_gemm_consumes_quantiser_outputs():
     """x, w -> row-wise (q, s[K/128, M]) from this package's quantisers -> GEMM; against the
     float32 product of the dequantised operands and, loosely, of the unquantised ones."""

@@ -192,6 +192,17 @@ def test_tt_fp8_gemm(block):
     assert_rel_close(yb.float(), bf16(G[f"y{block}_bf16"]).float(), "y bf16", 1e-2)
 
 
+@pytest.mark.parametrize("block", [128, 64])
+def test_bb_fp8_gemm(block):
+    G = golden("fp8gemm_bb")
+    a_q, b_q = fp8(G["a_q"]), fp8(G["b_q"])
+    a_s, b_s = torch.from_numpy(G[f"a_s{block}"]), torch.from_numpy(G[f"b_s{block}"])
+    y = O.bb_fp8_gemm(a_q, b_q, a_s, b_s, torch.float32, block)
+    assert_rel_close(y, torch.from_numpy(G[f"y{block}_f32"]), "y", 1e-5)
+    yb = O.bb_fp8_gemm(a_q, b_q, a_s, b_s, torch.bfloat16, block)
+    assert_rel_close(yb.float(), bf16(G[f"y{block}_bf16"]).float(), "y bf16", 1e-2)
+
+
 def test_row_id_map_and_unpermute():
     G = golden("route")
     rm = torch.from_numpy(G["route_map"]).bool()
