@@ -274,6 +274,26 @@ int lh_unpermute_with_mask_map(const void* grad, int dtype, const int32_t* row_i
                                int probs_dtype, int64_t tokens, int64_t experts, int64_t n, void* out,
                                void* prob_out, void* stream);
 
+/* ---- the smooth-quant recipe: one scale per row after a per-column smoothing divisor ---- */
+
+/* RMSNorm + smooth quantisation:  y = RMSNorm(x) * gamma;  ys = y / max(smooth_scale, 1e-30);
+ * scale[r] = max(max_c |ys[r,c]| / 448, 1e-30) (rounded up to a power of two when round_scale);
+ * q = e4m3(ys / scale[r]).
+ * Replaces triton_rms_norm_and_smooth_quant_forward, linghe/utils/norm.py:557.
+ * x [M,n] and gamma [n] of `dtype`, smooth_scale float32 [n], n <= 8192, n % 8 == 0.
+ * Outputs: q e4m3 [M,n], scale float32 [M]; rms (optional) float32 [M] 1/rms per row;
+ * maxs (optional, "calibrate") float32 [n] = max over rows of |y|, which needs
+ * lh_scratch_bytes("smooth_quant", M, n) bytes of scratch (none otherwise). */
+int lh_rmsnorm_smoothquant_fwd(const void* x, const void* gamma, const float* smooth_scale, int dtype, int64_t M,
+                               int64_t n, float eps, void* q, float* scale, float* rms, float* maxs, void* scratch,
+                               int64_t scratch_bytes, int round_scale, void* stream);
+
+/* SwiGLU + smooth quantisation: y = silu(x[:, :n]) * x[:, n:], then as above.
+ * Replaces triton_silu_and_smooth_quant_forward, linghe/utils/silu.py:1498.  x [M,2n]. */
+int lh_silu_smoothquant_fwd(const void* x, const float* smooth_scale, int dtype, int64_t M, int64_t n, void* q,
+                            float* scale, float* maxs, void* scratch, int64_t scratch_bytes, int round_scale,
+                            void* stream);
+
 /* ---- consumer of the wire format ------------------------------------------------- */
 
 /* Blockwise-scaled FP8 GEMM  c [M,N] = dequant(a) . dequant(b)^T.

@@ -148,6 +148,10 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
 int tile_quant(const void* x, int dtype, const void* counts, int counts_type, int E, int64_t M, int64_t N,
                void* q, float* s, void* qt, float* st, int round_scale, int mode, int scale_rowmajor,
                cudaStream_t stream, int descending = 0);
+int64_t smooth_quant_scratch(int64_t n);
+int smooth_quant_fwd(int silu, const void* x, const void* gamma, const float* smooth, int dtype, int64_t M, int64_t n,
+                     float eps, void* q, float* scale, float* rms, float* maxs, void* scratch, int64_t scratch_bytes,
+                     int round_scale, cudaStream_t stream);
 int any_col_strip(int silu, const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n,
                   void* qt, float* st, int round_scale, cudaStream_t stream);
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
@@ -266,6 +270,7 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
         return a > b ? a : b;
     }
     if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
+    if (!strcmp(what, "smooth_quant")) return smooth_quant_scratch(cols);       // calibration only
     if (!strcmp(what, "rmsnorm_bwd_static")) return 0;  // it carries its own
     if (!strcmp(what, "row_id_map")) return route_scratch_bytes(cols);          // cols = experts
     if (!strcmp(what, "rmsnorm_gemm")) return router_gemm_scratch(rows, cols);   // rows = N, cols = K
@@ -417,6 +422,20 @@ int lh_fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s
                 int64_t K, int block_size, int a_s_transposed, int b_s_transposed, int out_dtype, void* stream) {
     return fp8_gemm(a, b, a_s, b_s, c, M, N, K, block_size, a_s_transposed, b_s_transposed, out_dtype,
                     static_cast<cudaStream_t>(stream));
+}
+
+int lh_rmsnorm_smoothquant_fwd(const void* x, const void* gamma, const float* smooth_scale, int dtype, int64_t M,
+                               int64_t n, float eps, void* q, float* scale, float* rms, float* maxs, void* scratch,
+                               int64_t scratch_bytes, int round_scale, void* stream) {
+    return smooth_quant_fwd(0, x, gamma, smooth_scale, dtype, M, n, eps, q, scale, rms, maxs, scratch, scratch_bytes,
+                            round_scale, static_cast<cudaStream_t>(stream));
+}
+
+int lh_silu_smoothquant_fwd(const void* x, const float* smooth_scale, int dtype, int64_t M, int64_t n, void* q,
+                            float* scale, float* maxs, void* scratch, int64_t scratch_bytes, int round_scale,
+                            void* stream) {
+    return smooth_quant_fwd(1, x, nullptr, smooth_scale, dtype, M, n, 0.f, q, scale, nullptr, maxs, scratch, scratch_bytes,
+                            round_scale, static_cast<cudaStream_t>(stream));
 }
 
 int lh_fp8_gemm_bb(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,

@@ -1,0 +1,221 @@
+// The smooth-quant recipe of the fused producers: one scale per ROW (the whole row is one
+// quantisation group) after a per-column smoothing divisor.
+//
+//   y        = RMSNorm(x) * gamma            (lh_rmsnorm_smoothquant_fwd, linghe/utils/norm.py:557)
+//            | silu(x1) * x2                 (lh_silu_smoothquant_fwd,    linghe/utils/silu.py:1498)
+//   maxs[c]  = max over rows |y[:, c]|       (calibration, optional)
+//   ys       = y / max(smooth_scale, 1e-30)
+//   scale[r] = max(max_c |ys[r, c]| / 448, 1e-30)  [rounded up to a power of two]
+//   q        = e4m3(ys / scale[r])
+//
+// A second recipe beside the 1x128 / 128x1 block format, not on the benchmarked path: plain
+// kernels, one CTA of 256 threads walks rows, every thread owns the 8-element vectors
+// t, t + 256, ... of a row (at most four: n <= 8192), float32 math as in the block-format kernels
+// (fused variants: hardware reciprocal for the quotient, ex2 / rcp for the sigmoid).
+#include "lh_common.cuh"
+
+#include <type_traits>
+
+namespace lh {
+
+namespace {
+
+constexpr int SNT = 256;
+constexpr int SMAXV = 4;             // 4 * 256 * 8 = 8192 columns
+constexpr int kSmoothMaxCtas = 1184; // rows of the calibration scratch
+
+template <typename T>
+__device__ __forceinline__ void ld8(const T* p, float* f) {
+    if constexpr (sizeof(T) == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        const float4 b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+        f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+        Elem<T>::unpack8(*reinterpret_cast<const uint4*>(p), f);
+    }
+}
+
+// sum (SUM) or maximum of `a` over the CTA; every thread gets the result
+template <bool SUM>
+__device__ __forceinline__ float block_reduce(float a, float* red) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, a, d);
+        a = SUM ? a + o : fmaxf(a, o);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();   // red[] of the previous use has been read
+    if (lane == 0) red[warp] = a;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int w = 1; w < SNT / 32; ++w) r = SUM ? r + red[w] : fmaxf(r, red[w]);
+    return r;
+}
+
+__device__ __forceinline__ float sigmoid_fast1(float x) {
+    return rcp_approx(1.0f + ex2_approx(x * -1.4426950408889634f));
+}
+
+template <typename T, bool SILU, bool CALIB>
+__global__ void __launch_bounds__(SNT)
+smooth_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const float* __restrict__ smooth, int64_t M, int n,
+                   float eps, float inv_n, uint8_t* __restrict__ q, float* __restrict__ scale, float* __restrict__ rms_out,
+                   float* __restrict__ colmax, int round_scale) {
+    __shared__ float red[SNT / 32];
+    const int t = threadIdx.x;
+    float cm[CALIB ? SMAXV : 1][8];
+    if constexpr (CALIB) {
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cm[k][j] = 0.f;
+    }
+    const int64_t ld = SILU ? 2 * int64_t(n) : int64_t(n);
+    for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+        float v[SMAXV][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k) {
+            const int col = (k * SNT + t) * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[k][j] = 0.f;
+            if (col < n) {
+                if constexpr (SILU) {
+                    float a[8], b[8];
+                    ld8(x + row * ld + col, a);
+                    ld8(x + row * ld + n + col, b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[k][j] = (sigmoid_fast1(a[j]) * a[j]) * b[j];
+                } else {
+                    ld8(x + row * ld + col, v[k]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ss = fmaf(v[k][j], v[k][j], ss);
+                }
+            }
+        }
+        if constexpr (!SILU) {
+            const float r = rsqrt_nr(fmaf(block_reduce<true>(ss, red), inv_n, eps));
+            if (t == 0 && rms_out != nullptr) rms_out[row] = r;
+#pragma unroll
+            for (int k = 0; k < SMAXV; ++k) {
+                const int col = (k * SNT + t) * 8;
+                if (col < n) {
+                    float g[8];
+                    ld8(gamma + col, g);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[k][j] = (v[k][j] * r) * g[j];
+                }
+            }
+        }
+        float amax = 0.f;
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k) {
+            const int col = (k * SNT + t) * 8;
+            if (col < n) {
+                float s[8];
+                ld8(smooth + col, s);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if constexpr (CALIB) cm[k][j] = fmaxf(cm[k][j], fabsf(v[k][j]));
+                    v[k][j] = __fdiv_rn(v[k][j], fmaxf(s[j], kScaleFloor));
+                    amax = fmaxf(amax, fabsf(v[k][j]));
+                }
+            }
+        }
+        amax = block_reduce<false>(amax, red);
+        const float sc = scale_from_amax(amax, round_scale != 0);
+        if (t == 0) scale[row] = sc;
+        const float y = rcp_approx(sc);
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k) {
+            const int col = (k * SNT + t) * 8;
+            if (col < n) {
+                const uint32_t lo = cvt_e4m3x4(v[k][0] * y, v[k][1] * y, v[k][2] * y, v[k][3] * y);
+                const uint32_t hi = cvt_e4m3x4(v[k][4] * y, v[k][5] * y, v[k][6] * y, v[k][7] * y);
+                *reinterpret_cast<uint2*>(q + row * n + col) = make_uint2(lo, hi);
+            }
+        }
+    }
+    if constexpr (CALIB) {
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k) {
+            const int col = (k * SNT + t) * 8;
+            if (col < n) {
+                float4* dst = reinterpret_cast<float4*>(colmax + int64_t(blockIdx.x) * n + col);
+                dst[0] = make_float4(cm[k][0], cm[k][1], cm[k][2], cm[k][3]);
+                dst[1] = make_float4(cm[k][4], cm[k][5], cm[k][6], cm[k][7]);
+            }
+        }
+    }
+}
+
+// maxs[c] = max over the per-CTA rows of the calibration scratch
+__global__ void __launch_bounds__(256)
+colmax_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ maxs) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= n) return;
+    float m = 0.f;
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, partial[int64_t(p) * n + c]);
+    maxs[c] = m;
+}
+
+template <typename T, bool SILU>
+int launch_smooth(const void* x, const void* gamma, const float* smooth, int64_t M, int64_t n, float eps, void* q,
+                  float* scale, float* rms, float* maxs, float* scratch, int round_scale, cudaStream_t stream) {
+    int64_t grid = int64_t(sm_count()) * 8;
+    if (grid > kSmoothMaxCtas) grid = kSmoothMaxCtas;
+    if (grid > M) grid = M;
+    const T* xp = static_cast<const T*>(x);
+    const T* gp = static_cast<const T*>(gamma);
+    uint8_t* qp = static_cast<uint8_t*>(q);
+    const float inv_n = 1.0f / float(n);
+    if (maxs != nullptr) {
+        smooth_rows_kernel<T, SILU, true><<<unsigned(grid), SNT, 0, stream>>>(xp, gp, smooth, M, int(n), eps, inv_n, qp, scale,
+                                                                               rms, scratch, round_scale);
+        if (int rc = check_launch("smooth_rows_kernel")) return rc;
+        colmax_reduce_kernel<<<unsigned((n + 255) / 256), 256, 0, stream>>>(scratch, int(grid), int(n), maxs);
+        return check_launch("colmax_reduce_kernel");
+    }
+    smooth_rows_kernel<T, SILU, false><<<unsigned(grid), SNT, 0, stream>>>(xp, gp, smooth, M, int(n), eps, inv_n, qp, scale, rms,
+                                                                            nullptr, round_scale);
+    return check_launch("smooth_rows_kernel");
+}
+
+}  // namespace
+
+int64_t smooth_quant_scratch(int64_t n) { return int64_t(kSmoothMaxCtas) * n * 4; }
+
+// silu = 0: RMSNorm (gamma required, rms optional output); silu = 1: SwiGLU on x [M, 2n].
+// maxs != NULL: calibration, needs scratch of smooth_quant_scratch(n) bytes.
+int smooth_quant_fwd(int silu, const void* x, const void* gamma, const float* smooth, int dtype, int64_t M, int64_t n,
+                     float eps, void* q, float* scale, float* rms, float* maxs, void* scratch, int64_t scratch_bytes,
+                     int round_scale, cudaStream_t stream) {
+    const char* what = silu ? "silu_smoothquant_fwd" : "rmsnorm_smoothquant_fwd";
+    if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
+    if (M < 0 || n <= 0 || n > 8192 || (n % 8) != 0) return fail_arg("%s: need 0 < n <= 8192, n %% 8 == 0 (M=%lld n=%lld)", what, (long long)M, (long long)n);
+    if (M > 0 && (!x || !smooth || !q || !scale || (!silu && !gamma))) return fail_arg("%s: NULL pointer", what);
+    const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(smooth) | reinterpret_cast<uintptr_t>(q) |
+                         reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(scratch);
+    if (al & 15) return fail_arg("%s: pointers must be 16-byte aligned", what);
+    if (maxs != nullptr && (!scratch || scratch_bytes < smooth_quant_scratch(n)))
+        return fail_arg("%s: calibration needs %lld bytes of scratch", what, (long long)smooth_quant_scratch(n));
+    if (M == 0) {
+        if (maxs != nullptr) {
+            const cudaError_t e = cudaMemsetAsync(maxs, 0, size_t(n) * 4, stream);
+            return e == cudaSuccess ? LH_OK : int(e);
+        }
+        return LH_OK;
+    }
+    float* sp = static_cast<float*>(scratch);
+#define LH_SMOOTH(T)                                                                                               \
+    (silu ? launch_smooth<T, true>(x, gamma, smooth, M, n, eps, q, scale, rms, maxs, sp, round_scale, stream)      \
+          : launch_smooth<T, false>(x, gamma, smooth, M, n, eps, q, scale, rms, maxs, sp, round_scale, stream))
+    if (dtype == LH_F16) return LH_SMOOTH(__half);
+    if (dtype == LH_F32) return LH_SMOOTH(float);
+    return LH_SMOOTH(__nv_bfloat16);
+#undef LH_SMOOTH
+}
+
+}  // namespace lh

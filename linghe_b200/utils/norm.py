@@ -165,3 +165,46 @@ def rms_norm_backward_and_block_quant(grad_output, x, w, eps=1e-6, rms=None, rou
               _lib.dtype_code(x), M, n, float(eps), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(dy_q), _lib.ptr(dy_s),
               _lib.ptr(dyt_q), _lib.ptr(dyt_s), int(bool(round_scale)), _lib.ptr(scratch), nbytes)
     return dx, dw, dy_q, dy_s, dyt_q, dyt_s
+
+
+def triton_rms_norm_and_smooth_quant_forward(
+    x,
+    weight,
+    smooth_scale=None,
+    eps=1e-6,
+    out=None,
+    scale=None,
+    rms=None,
+    calibrate=False,
+    output_rms=False,
+    round_scale=False,
+):
+    """RMSNorm + smooth quantisation (linghe/utils/norm.py:557): y = RMSNorm(x) * weight is divided
+    by the per-column `smooth_scale` and quantised with ONE scale per row.
+
+    Returns (out e4m3 [M,N], scale f32 [M], maxs f32 [N] or None, rms f32 [M] or None): `maxs`
+    (column maxima of |y| before smoothing) only with calibrate=True, `rms` (1/rms per row) only
+    with output_rms=True or when a buffer is passed."""
+    assert x.is_contiguous() and weight.is_contiguous()
+    assert smooth_scale is not None and smooth_scale.is_contiguous()
+    M, N = x.shape
+    assert N <= 8192 and N % 8 == 0
+    device = x.device
+    if smooth_scale.dtype != torch.float32:
+        smooth_scale = smooth_scale.float()
+    if out is None:
+        out = torch.empty((M, N), device=device, dtype=E4M3)
+    if scale is None:
+        scale = torch.empty((M,), device=device, dtype=torch.float32)
+    if output_rms and rms is None:
+        rms = torch.empty((M,), dtype=torch.float32, device=device)
+    maxs = scratch = None
+    nbytes = 0
+    if calibrate:
+        maxs = torch.empty((N,), dtype=torch.float32, device=device)
+        nbytes = _lib.scratch_bytes("smooth_quant", M, N)
+        scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    _lib.call("lh_rmsnorm_smoothquant_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.ptr(smooth_scale), _lib.dtype_code(x),
+              M, N, float(eps), _lib.ptr(out), _lib.ptr(scale), _lib.ptr(rms) if output_rms else None, _lib.ptr(maxs),
+              _lib.ptr(scratch), nbytes, int(bool(round_scale)))
+    return out, scale, maxs, rms

@@ -160,3 +160,34 @@ def triton_batch_weighted_silu_and_block_quant_backward(g, x, weight, counts, sp
               _lib.ptr(dx_scale), _lib.ptr(dw), _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale),
               int(bool(round_scale)), _lib.ptr(scratch), nbytes)
     return dx, dx_scale, dw, transpose_dx, transpose_dx_scale
+
+
+def triton_silu_and_smooth_quant_forward(x, smooth_scale=None, out=None, scale=None, maxs=None, round_scale=False,
+                                         calibrate=False):
+    """SwiGLU + smooth quantisation (linghe/utils/silu.py:1498): y = silu(x1) * x2 is divided by
+    the per-column `smooth_scale` and quantised with ONE scale per row.
+
+    Returns (out e4m3 [M,n], scale f32 [M], maxs f32 [n] or None); `maxs` (column maxima of |y|
+    before smoothing) only with calibrate=True."""
+    assert x.is_contiguous()
+    assert smooth_scale is not None and smooth_scale.is_contiguous()
+    M, N = x.shape
+    n = N // 2
+    assert N % 16 == 0 and n <= 8192
+    device = x.device
+    if smooth_scale.dtype != torch.float32:
+        smooth_scale = smooth_scale.float()
+    if out is None:
+        out = torch.empty((M, n), device=device, dtype=E4M3)
+    if scale is None:
+        scale = torch.empty((M,), device=device, dtype=torch.float32)
+    scratch = None
+    nbytes = 0
+    cmax = None
+    if calibrate:
+        cmax = torch.empty((n,), dtype=torch.float32, device=device)
+        nbytes = _lib.scratch_bytes("smooth_quant", M, n)
+        scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    _lib.call("lh_silu_smoothquant_fwd", x, _lib.ptr(x), _lib.ptr(smooth_scale), _lib.dtype_code(x), M, n,
+              _lib.ptr(out), _lib.ptr(scale), _lib.ptr(cmax), _lib.ptr(scratch), nbytes, int(bool(round_scale)))
+    return out, scale, cmax

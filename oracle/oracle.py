@@ -217,6 +217,40 @@ def bb_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=torch.bfloat16, block_size: int = 
 
 
 # --------------------------------------------------------------------------- #
+# smooth-quant recipe: one scale per row after a per-column smoothing divisor
+# --------------------------------------------------------------------------- #
+def smooth_quant(x: torch.Tensor, smooth_scale: torch.Tensor, reverse: bool = False, round_scale: bool = False):
+    """``torch_smooth_quant`` (linghe/tools/util.py:127-141): column maxima of |x|, then
+    x / max(smooth, 1e-30) (x * smooth when `reverse`), one scale per row =
+    max(amax/448, 1e-30) [power of two], codes = e4m3(x_smooth / scale).
+    Returns (codes [M,N], scale [M], maxs [N])."""
+    x = x.float()
+    smooth_scale = smooth_scale.float()
+    maxs = x.abs().amax(0)
+    if reverse:
+        xs = x * smooth_scale
+    else:
+        xs = x / torch.clamp_min(smooth_scale, SCALE_FLOOR)
+    scale = torch.clamp_min(xs.abs().amax(1) / E4M3_MAX, SCALE_FLOOR)
+    if round_scale:
+        scale = _pow2_ceil(scale)
+    return (xs / scale[:, None]).to(torch.float8_e4m3fn), scale, maxs
+
+
+def rms_norm_and_smooth_quant_forward(x, weight, smooth_scale, eps: float = 1e-6, round_scale: bool = False):
+    """``torch_rms_and_smooth_quant_forward`` (tests/test_norm.py:52-67): float32 RMSNorm, then
+    smooth_quant.  Returns (codes, scale [M], maxs [N], 1/rms [M])."""
+    q, s, maxs = smooth_quant(_rms_norm_f32(x, weight, eps), smooth_scale, False, round_scale)
+    return q, s, maxs, rms_recip(x, eps)
+
+
+def silu_and_smooth_quant_forward(x, smooth_scale, round_scale: bool = False):
+    """``torch_silu_and_smooth_quant_forward`` (tests/test_silu.py:56-72): SwiGLU in float32, then
+    smooth_quant.  Returns (codes [M,n], scale [M], maxs [n])."""
+    return smooth_quant(_swiglu_f32(x), smooth_scale, False, round_scale)
+
+
+# --------------------------------------------------------------------------- #
 # SwiGLU (dense)
 # --------------------------------------------------------------------------- #
 def _swiglu_f32(x: torch.Tensor, weight: torch.Tensor | None = None) -> torch.Tensor:

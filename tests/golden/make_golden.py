@@ -246,7 +246,28 @@ def main():
         out[f"y{B}_f32"] = f32(y)
         out[f"y{B}_bf16"] = u16(y.to(torch.bfloat16))
     np.savez_compressed(os.path.join(HERE, "fp8gemm_bb.npz"), **out)
-    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route", "fp8gemm_bb"):
+    # ---- smooth-quant recipe (one scale per row after a per-column smoothing divisor): upstream's
+    # torch_rms_and_smooth_quant_forward (tests/test_norm.py:52-67) and
+    # torch_silu_and_smooth_quant_forward (tests/test_silu.py:56-72), inputs as in their tests
+    # (smooth scales 1 + 10 * rand for the norm, tests/test_norm.py:153-156; 1 + rand for SwiGLU,
+    # tests/test_silu.py:338).  Its own generator: the files above stay as they are.
+    out = {}
+    gs = torch.Generator().manual_seed(20240609)
+    x = bf16_randn(gs, (96, 512))
+    w = (1 + 0.1 * torch.randn((512,), generator=gs)).to(torch.bfloat16)
+    sm = 1 + 10 * torch.rand((512,), generator=gs)
+    out["norm_x"], out["norm_w"], out["norm_smooth"] = u16(x), u16(w), f32(sm)
+    for rs in (False, True):
+        q, sc, maxs = TN.torch_rms_and_smooth_quant_forward(x, w, smooth_scale=sm, round_scale=rs)
+        out[f"norm_r{int(rs)}_q"], out[f"norm_r{int(rs)}_s"], out[f"norm_r{int(rs)}_maxs"] = u8(q), f32(sc), f32(maxs)
+    xs = bf16_randn(gs, (80, 768))
+    sm2 = 1 + torch.rand((384,), generator=gs)
+    out["silu_x"], out["silu_smooth"] = u16(xs), f32(sm2)
+    for rs in (False, True):
+        q, sc, maxs = TS.torch_silu_and_smooth_quant_forward(xs, smooth_scale=sm2, round_scale=rs)
+        out[f"silu_r{int(rs)}_q"], out[f"silu_r{int(rs)}_s"], out[f"silu_r{int(rs)}_maxs"] = u8(q), f32(sc), f32(maxs)
+    np.savez_compressed(os.path.join(HERE, "smooth.npz"), **out)
+    for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route", "fp8gemm_bb", "smooth"):
         p = os.path.join(HERE, f + ".npz")
         print(p, os.path.getsize(p))
 

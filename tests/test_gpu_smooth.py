@@ -1,0 +1,120 @@
+"""The smooth-quant recipe (one scale per row after a per-column smoothing divisor):
+triton_rms_norm_and_smooth_quant_forward (linghe/utils/norm.py:557) and
+triton_silu_and_smooth_quant_forward (linghe/utils/silu.py:1498) against the oracle's
+restatement of upstream's torch_smooth_quant and against golden vectors made by upstream's own
+test functions.  Fused-variant tolerances: scales and calibration maxima within 1e-6 relative,
+at most 1e-3 of the codes off by one e4m3 step."""
+
+import pytest
+import torch
+
+from oracle import oracle as O
+from tests.common import (assert_codes_close, assert_scales_close, bf16, bits, fp8, golden, record)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _status_clean():
+    from linghe_b200 import _lib
+    yield
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+
+
+def check_rows(got_q, ref_q, got_s, ref_s, what, pow2):
+    """Per-row scales.  With power-of-two scales a last-bit difference in a row maximum can move a
+    scale by exactly 2x: rows whose scales agree meet the code rule, the others (at most 1e-3 of the
+    rows) must differ by a factor of two and dequantise to the same values within one step."""
+    if not pow2:
+        assert_scales_close(got_s, ref_s, what + " scale")
+        assert_codes_close(got_q, ref_q, what + " codes")
+        return
+    gs, rs = got_s.detach().float().cpu(), ref_s.detach().float().cpu()
+    same = gs == rs
+    frac = 1.0 - same.float().mean().item()
+    record(what, "pow2_scale_diff_frac", frac)
+    assert frac <= 1e-3, f"{what}: {frac:.2e} of power-of-two row scales differ"
+    if same.any():
+        assert_codes_close(got_q[same.to(got_q.device)], ref_q[same], what + " codes")
+    if (~same).any():
+        ratio = gs[~same] / rs[~same]
+        assert bool(((ratio == 2.0) | (ratio == 0.5)).all())
+        dg = got_q.detach().float().cpu()[~same] * gs[~same, None]
+        dr = ref_q.detach().float().cpu()[~same] * rs[~same, None]
+        lim = 0.13 * torch.maximum(dg.abs(), dr.abs()) + 2.0 ** -8 * torch.maximum(gs, rs)[~same, None]
+        assert bool(((dg - dr).abs() <= lim).all())
+
+
+@pytest.mark.parametrize("rs", [0, 1])
+def test_golden_smooth(rs):
+    from linghe_b200.utils.norm import triton_rms_norm_and_smooth_quant_forward
+    from linghe_b200.utils.silu import triton_silu_and_smooth_quant_forward
+    G = golden("smooth")
+    x, w, sm = bf16(G["norm_x"]).cuda(), bf16(G["norm_w"]).cuda(), torch.from_numpy(G["norm_smooth"]).cuda()
+    q, s, maxs, rms = triton_rms_norm_and_smooth_quant_forward(x, w, smooth_scale=sm, calibrate=True, output_rms=True,
+                                                               round_scale=bool(rs))
+    check_rows(q, fp8(G[f"norm_r{rs}_q"]), s, torch.from_numpy(G[f"norm_r{rs}_s"]), "golden norm smooth", bool(rs))
+    assert_scales_close(maxs, torch.from_numpy(G[f"norm_r{rs}_maxs"]), "maxs")
+    assert_scales_close(rms, O.rms_recip(x.cpu()), "rms")
+    xs, sm2 = bf16(G["silu_x"]).cuda(), torch.from_numpy(G["silu_smooth"]).cuda()
+    q, s, maxs = triton_silu_and_smooth_quant_forward(xs, smooth_scale=sm2, calibrate=True, round_scale=bool(rs))
+    check_rows(q, fp8(G[f"silu_r{rs}_q"]), s, torch.from_numpy(G[f"silu_r{rs}_s"]), "golden silu smooth", bool(rs))
+    assert_scales_close(maxs, torch.from_numpy(G[f"silu_r{rs}_maxs"]), "maxs")
+
+
+# upstream's own test shapes are (16384, 2048), (8192, 4096), (4096, 8192) (tests/test_norm.py:333-335)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,N", [(4096, 2048), (1000, 4096), (515, 8192), (64, 1536), (3, 8)])
+def test_rms_norm_and_smooth_quant(M, N, dtype):
+    from linghe_b200.utils.norm import triton_rms_norm_and_smooth_quant_forward as f
+    g = torch.Generator().manual_seed(71)
+    x = torch.randn((M, N), generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn((N,), generator=g)).to(dtype)
+    sm = 1 + 10 * torch.rand((N,), generator=g)
+    sm[::17] = 0.0           # the divisor is floored at 1e-30, as upstream's oracle does
+    x[:, ::17] = 0           # ... and the columns it hits are zero, so that the row maxima stay finite
+    for rs in (False, True):
+        rq, rsc, rmaxs, rr = O.rms_norm_and_smooth_quant_forward(x, w, sm, 1e-6, rs)
+        q, s, maxs, rms = f(x.cuda(), w.cuda(), smooth_scale=sm.cuda(), calibrate=True, output_rms=True, round_scale=rs)
+        assert q.shape == (M, N) and s.shape == (M,) and maxs.shape == (N,) and rms.shape == (M,)
+        check_rows(q, rq, s, rsc, "norm smooth", rs)
+        assert torch.allclose(maxs.cpu(), rmaxs, rtol=1e-6, atol=0)
+        assert_scales_close(rms, rr, "rms")
+    # without calibration / rms: None in their places, outputs written into the buffers passed
+    out = torch.empty((M, N), device="cuda", dtype=torch.float8_e4m3fn)
+    sc = torch.empty((M,), device="cuda")
+    r = f(x.cuda(), w.cuda(), smooth_scale=sm.cuda(), out=out, scale=sc)
+    assert r[0] is out and r[1] is sc and r[2] is None and r[3] is None
+    assert torch.equal(bits(out), bits(f(x.cuda(), w.cuda(), smooth_scale=sm.cuda())[0]))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,n", [(4096, 2048), (1000, 1408), (130, 8192), (16, 1536), (5, 8)])
+def test_silu_and_smooth_quant(M, n, dtype):
+    from linghe_b200.utils.silu import triton_silu_and_smooth_quant_forward as f
+    g = torch.Generator().manual_seed(72)
+    x = torch.randn((M, 2 * n), generator=g).to(dtype)
+    sm = 1 + torch.rand((n,), generator=g)
+    for rs in (False, True):
+        rq, rsc, rmaxs = O.silu_and_smooth_quant_forward(x, sm, rs)
+        q, s, maxs = f(x.cuda(), smooth_scale=sm.cuda(), calibrate=True, round_scale=rs)
+        assert q.shape == (M, n) and s.shape == (M,) and maxs.shape == (n,)
+        check_rows(q, rq, s, rsc, "silu smooth", rs)
+        assert torch.allclose(maxs.cpu(), rmaxs, rtol=1e-6, atol=1e-30)
+    r = f(x.cuda(), smooth_scale=sm.cuda())
+    assert r[2] is None
+
+
+def test_smooth_quant_argument_errors():
+    from linghe_b200.utils.norm import triton_rms_norm_and_smooth_quant_forward as fn
+    from linghe_b200.utils.silu import triton_silu_and_smooth_quant_forward as fs
+    x = torch.zeros((16, 16384), device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(AssertionError):
+        fn(x, torch.ones(16384, device="cuda", dtype=torch.bfloat16), smooth_scale=torch.ones(16384, device="cuda"))
+    with pytest.raises(AssertionError):
+        fs(x[:, :64].contiguous(), smooth_scale=None)
+    # empty input: nothing launched, shapes kept
+    e = torch.zeros((0, 256), device="cuda", dtype=torch.bfloat16)
+    q, s, maxs = fs(e, smooth_scale=torch.ones(128, device="cuda"), calibrate=True)
+    assert q.shape == (0, 128) and s.shape == (0,) and float(maxs.abs().max()) == 0.0

@@ -236,3 +236,19 @@ def test_row_id_map_and_unpermute():
                 ref[tok] += g[row16[tok, e]].float()
     assert torch.equal(out, ref.to(torch.bfloat16))
     assert torch.equal(rp[rm], p[row16[rm].long()]) and rp[~rm].abs().sum() == 0
+
+
+@pytest.mark.parametrize("rs", [0, 1])
+def test_smooth_quant_recipe(rs):
+    G = golden("smooth")
+    x, w, sm = bf16(G["norm_x"]), bf16(G["norm_w"]), torch.from_numpy(G["norm_smooth"])
+    q, s, maxs, r = O.rms_norm_and_smooth_quant_forward(x, w, sm, 1e-6, bool(rs))
+    assert_codes_close(q, fp8(G[f"norm_r{rs}_q"]), "norm smooth q")
+    assert_scales_close(s, torch.from_numpy(G[f"norm_r{rs}_s"]), "norm smooth scale")
+    assert_scales_close(maxs, torch.from_numpy(G[f"norm_r{rs}_maxs"]), "norm smooth maxs")
+    assert tuple(s.shape) == (x.shape[0],) and tuple(maxs.shape) == (x.shape[1],) and tuple(r.shape) == (x.shape[0],)
+    xs, sm2 = bf16(G["silu_x"]), torch.from_numpy(G["silu_smooth"])
+    q, s, maxs = O.silu_and_smooth_quant_forward(xs, sm2, bool(rs))
+    assert_bits_equal(q, fp8(G[f"silu_r{rs}_q"]), "silu smooth q")
+    assert_f32_equal(s, torch.from_numpy(G[f"silu_r{rs}_s"]), "silu smooth scale")
+    assert_f32_equal(maxs, torch.from_numpy(G[f"silu_r{rs}_maxs"]), "silu smooth maxs")
