@@ -294,6 +294,17 @@ int lh_silu_smoothquant_fwd(const void* x, const float* smooth_scale, int dtype,
                             float* scale, float* maxs, void* scratch, int64_t scratch_bytes, int round_scale,
                             void* stream);
 
+/* Per-expert weighted SwiGLU + smooth quantisation: rows grouped by expert (counts[e] rows each),
+ * y = silu(x1) * x2; ys = (y * w[row]) / max(smooth_scale[e], 1e-30) (reverse != 0: * smooth_scale[e]);
+ * one scale per row.  maxs (optional, "calibrate") float32 [E, n] = per-expert column maxima of
+ * |y| before the weight.
+ * Replaces triton_batch_weighted_silu_and_smooth_quant_forward, linghe/utils/silu.py:1821.
+ * x [R,2n], w [R] (w_dtype), smooth_scale float32 [E,n], counts as in the block-format entries;
+ * n <= 8192, n % 8 == 0, E <= 4096. */
+int lh_batch_silu_smoothquant_fwd(const void* x, const void* w, int dtype, int w_dtype, const float* smooth_scale,
+                                  const void* counts, int counts_type, int E, int64_t R, int64_t n, void* q, float* scale,
+                                  float* maxs, int round_scale, int reverse, void* stream);
+
 /* ---- consumer of the wire format ------------------------------------------------- */
 
 /* Blockwise-scaled FP8 GEMM  c [M,N] = dequant(a) . dequant(b)^T.

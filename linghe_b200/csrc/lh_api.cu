@@ -152,6 +152,9 @@ int64_t smooth_quant_scratch(int64_t n);
 int smooth_quant_fwd(int silu, const void* x, const void* gamma, const float* smooth, int dtype, int64_t M, int64_t n,
                      float eps, void* q, float* scale, float* rms, float* maxs, void* scratch, int64_t scratch_bytes,
                      int round_scale, cudaStream_t stream);
+int smooth_quant_batch_fwd(const void* x, const void* w, int dtype, int w_dtype, const float* smooth, const void* counts,
+                           int counts_type, int E, int64_t M, int64_t n, void* q, float* scale, float* emax,
+                           int round_scale, int reverse, cudaStream_t stream);
 int any_col_strip(int silu, const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n,
                   void* qt, float* st, int round_scale, cudaStream_t stream);
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
@@ -436,6 +439,13 @@ int lh_silu_smoothquant_fwd(const void* x, const float* smooth_scale, int dtype,
                             void* stream) {
     return smooth_quant_fwd(1, x, nullptr, smooth_scale, dtype, M, n, 0.f, q, scale, nullptr, maxs, scratch, scratch_bytes,
                             round_scale, static_cast<cudaStream_t>(stream));
+}
+
+int lh_batch_silu_smoothquant_fwd(const void* x, const void* w, int dtype, int w_dtype, const float* smooth_scale,
+                                  const void* counts, int counts_type, int E, int64_t R, int64_t n, void* q, float* scale,
+                                  float* maxs, int round_scale, int reverse, void* stream) {
+    return smooth_quant_batch_fwd(x, w, dtype, w_dtype, smooth_scale, counts, counts_type, E, R, n, q, scale, maxs,
+                                  round_scale, reverse, static_cast<cudaStream_t>(stream));
 }
 
 int lh_fp8_gemm_bb(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,

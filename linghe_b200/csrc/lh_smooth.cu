@@ -151,6 +151,104 @@ smooth_rows_kernel(const T* __restrict__ x, const T* __restrict__ gamma, const f
     }
 }
 
+// The per-expert form (linghe/utils/silu.py:1757-1818): rows are grouped by expert (counts[e] rows
+// each, in order), expert e has its own smoothing vector smooth[e, :], every row its own weight:
+//   y = silu(x1) * x2;  emax[e, c] = max over the expert's rows of |y|  (calibration, before the weight);
+//   ys = (y * w[row]) / max(smooth[e], 1e-30)   (reverse: * smooth[e]);  one scale per row.
+// The expert of a row comes from a binary search in the prefix sums (shared memory, warp-uniform).
+// Calibration maxima are kept in registers while the walk stays inside one expert and merged into
+// emax with atomicMax on the bit patterns (non-negative floats order like integers; the result
+// does not depend on the order of the merges).
+template <typename T, bool CALIB>
+__global__ void __launch_bounds__(SNT)
+smooth_batch_kernel(const T* __restrict__ x, const void* __restrict__ w, int w_dtype, const float* __restrict__ smooth,
+                    const void* __restrict__ counts, int counts_i64, int E, int64_t M, int n, uint8_t* __restrict__ q,
+                    float* __restrict__ scale, float* __restrict__ emax, int round_scale, int reverse) {
+    extern __shared__ int64_t seg[];   // [E + 1] prefix sums of the counts
+    __shared__ float red[SNT / 32];
+    const int t = threadIdx.x;
+    if (t == 0) {
+        int64_t acc = 0;
+        seg[0] = 0;
+        for (int e = 0; e < E; ++e) {
+            acc += counts_i64 ? reinterpret_cast<const int64_t*>(counts)[e] : int64_t(reinterpret_cast<const int32_t*>(counts)[e]);
+            seg[e + 1] = acc;
+        }
+    }
+    __syncthreads();
+    const int64_t total = seg[E] < M ? seg[E] : M;
+    float cm[CALIB ? SMAXV : 1][8];
+    int cur_e = -1;
+    auto flush = [&]() {
+        if constexpr (CALIB) {
+            if (cur_e >= 0) {
+#pragma unroll
+                for (int k = 0; k < SMAXV; ++k) {
+                    const int col = (k * SNT + t) * 8;
+                    if (col < n) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            atomicMax(reinterpret_cast<unsigned int*>(emax + int64_t(cur_e) * n + col + j), __float_as_uint(cm[k][j]));
+                    }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < SMAXV; ++k)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cm[k][j] = 0.f;
+        }
+    };
+    flush();
+    for (int64_t row = blockIdx.x; row < total; row += gridDim.x) {
+        int lo = 0, hi = E - 1;            // smallest e with seg[e + 1] > row
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (seg[mid + 1] > row) hi = mid; else lo = mid + 1;
+        }
+        if (lo != cur_e) { flush(); cur_e = lo; }
+        const float* sm = smooth + int64_t(lo) * n;
+        const float wr = w_dtype == LH_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[row])
+                         : w_dtype == LH_F16 ? __half2float(reinterpret_cast<const __half*>(w)[row])
+                                             : reinterpret_cast<const float*>(w)[row];
+        float v[SMAXV][8];
+        float amax = 0.f;
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k) {
+            const int col = (k * SNT + t) * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[k][j] = 0.f;
+            if (col < n) {
+                float a[8], b[8], s[8];
+                ld8(x + row * 2 * int64_t(n) + col, a);
+                ld8(x + row * 2 * int64_t(n) + n + col, b);
+                ld8(sm + col, s);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float y = (sigmoid_fast1(a[j]) * a[j]) * b[j];
+                    if constexpr (CALIB) cm[k][j] = fmaxf(cm[k][j], fabsf(y));
+                    const float yw = y * wr;
+                    v[k][j] = reverse ? yw * s[j] : __fdiv_rn(yw, fmaxf(s[j], kScaleFloor));
+                    amax = fmaxf(amax, fabsf(v[k][j]));
+                }
+            }
+        }
+        amax = block_reduce<false>(amax, red);
+        const float sc = scale_from_amax(amax, round_scale != 0);
+        if (t == 0) scale[row] = sc;
+        const float y = rcp_approx(sc);
+#pragma unroll
+        for (int k = 0; k < SMAXV; ++k) {
+            const int col = (k * SNT + t) * 8;
+            if (col < n) {
+                const uint32_t c0 = cvt_e4m3x4(v[k][0] * y, v[k][1] * y, v[k][2] * y, v[k][3] * y);
+                const uint32_t c1 = cvt_e4m3x4(v[k][4] * y, v[k][5] * y, v[k][6] * y, v[k][7] * y);
+                *reinterpret_cast<uint2*>(q + row * n + col) = make_uint2(c0, c1);
+            }
+        }
+    }
+    flush();
+}
+
 // maxs[c] = max over the per-CTA rows of the calibration scratch
 __global__ void __launch_bounds__(256)
 colmax_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ maxs) {
@@ -183,7 +281,55 @@ int launch_smooth(const void* x, const void* gamma, const float* smooth, int64_t
     return check_launch("smooth_rows_kernel");
 }
 
+template <typename T>
+int launch_smooth_batch(const void* x, const void* w, int w_dtype, const float* smooth, const void* counts, int counts_i64,
+                        int E, int64_t M, int64_t n, void* q, float* scale, float* emax, int round_scale, int reverse,
+                        cudaStream_t stream) {
+    // calibration merges per CTA and expert: fewer CTAs keep the atomic traffic small
+    int64_t grid = int64_t(sm_count()) * (emax != nullptr ? 2 : 8);
+    if (grid > M) grid = M;
+    const size_t smem = size_t(E + 1) * sizeof(int64_t);
+    const T* xp = static_cast<const T*>(x);
+    uint8_t* qp = static_cast<uint8_t*>(q);
+    if (emax != nullptr) {
+        const cudaError_t e = cudaMemsetAsync(emax, 0, size_t(E) * size_t(n) * 4, stream);
+        if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return int(e); }
+        smooth_batch_kernel<T, true><<<unsigned(grid), SNT, smem, stream>>>(xp, w, w_dtype, smooth, counts, counts_i64, E, M, int(n),
+                                                                             qp, scale, emax, round_scale, reverse);
+    } else {
+        smooth_batch_kernel<T, false><<<unsigned(grid), SNT, smem, stream>>>(xp, w, w_dtype, smooth, counts, counts_i64, E, M, int(n),
+                                                                              qp, scale, nullptr, round_scale, reverse);
+    }
+    return check_launch("smooth_batch_kernel");
+}
+
 }  // namespace
+
+// Per-expert SwiGLU + smooth quantisation; emax (optional) [E, n] receives the calibration maxima.
+int smooth_quant_batch_fwd(const void* x, const void* w, int dtype, int w_dtype, const float* smooth, const void* counts,
+                           int counts_type, int E, int64_t M, int64_t n, void* q, float* scale, float* emax,
+                           int round_scale, int reverse, cudaStream_t stream) {
+    const char* what = "batch_silu_smoothquant_fwd";
+    if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
+    if (w_dtype != LH_BF16 && w_dtype != LH_F16 && w_dtype != LH_F32) return fail_arg("%s: weight dtype must be bf16, f16 or f32", what);
+    if (counts_type != LH_I32 && counts_type != LH_I64) return fail_arg("%s: counts must be int32 or int64", what);
+    if (M < 0 || n <= 0 || n > 8192 || (n % 8) != 0 || E <= 0 || E > 4096)
+        return fail_arg("%s: need 0 < n <= 8192, n %% 8 == 0, 0 < E <= 4096 (M=%lld n=%lld E=%d)", what, (long long)M, (long long)n, E);
+    if (M == 0) {
+        if (emax != nullptr) {
+            const cudaError_t e = cudaMemsetAsync(emax, 0, size_t(E) * size_t(n) * 4, stream);
+            return e == cudaSuccess ? LH_OK : int(e);
+        }
+        return LH_OK;
+    }
+    if (!x || !w || !smooth || !counts || !q || !scale) return fail_arg("%s: NULL pointer", what);
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(smooth) | reinterpret_cast<uintptr_t>(q)) & 15)
+        return fail_arg("%s: pointers must be 16-byte aligned", what);
+    const int i64 = counts_type == LH_I64;
+    if (dtype == LH_F16) return launch_smooth_batch<__half>(x, w, w_dtype, smooth, counts, i64, E, M, n, q, scale, emax, round_scale, reverse, stream);
+    if (dtype == LH_F32) return launch_smooth_batch<float>(x, w, w_dtype, smooth, counts, i64, E, M, n, q, scale, emax, round_scale, reverse, stream);
+    return launch_smooth_batch<__nv_bfloat16>(x, w, w_dtype, smooth, counts, i64, E, M, n, q, scale, emax, round_scale, reverse, stream);
+}
 
 int64_t smooth_quant_scratch(int64_t n) { return int64_t(kSmoothMaxCtas) * n * 4; }
 

@@ -191,3 +191,36 @@ def triton_silu_and_smooth_quant_forward(x, smooth_scale=None, out=None, scale=N
     _lib.call("lh_silu_smoothquant_fwd", x, _lib.ptr(x), _lib.ptr(smooth_scale), _lib.dtype_code(x), M, n,
               _lib.ptr(out), _lib.ptr(scale), _lib.ptr(cmax), _lib.ptr(scratch), nbytes, int(bool(round_scale)))
     return out, scale, cmax
+
+
+def triton_batch_weighted_silu_and_smooth_quant_forward(x, weight, counts, smooth_scale=None, splits=None, out=None,
+                                                        scale=None, round_scale=False, reverse=False, calibrate=False):
+    """Per-expert weighted SwiGLU + smooth quantisation (linghe/utils/silu.py:1821): rows grouped by
+    expert (`counts[e]` rows each), expert e smoothed by `smooth_scale[e]` ([E, n]; multiplied when
+    `reverse`), one scale per row.
+
+    Returns (out e4m3 [M,n], scale f32 [M], maxs f32 [E,n] or None); `maxs` (per-expert column
+    maxima of |silu(x1) * x2|, before the row weight) with calibrate=True, zeros when M == 0."""
+    assert x.is_contiguous() and weight.is_contiguous()
+    assert smooth_scale is not None and smooth_scale.is_contiguous()
+    M, N = x.shape
+    n = N // 2
+    n_experts = counts.shape[0]
+    assert N <= 16384 and N % 16 == 0
+    assert smooth_scale.numel() == n_experts * n and weight.numel() == M
+    device = x.device
+    if smooth_scale.dtype != torch.float32:
+        smooth_scale = smooth_scale.float()
+    if out is None:
+        out = torch.empty((M, n), device=device, dtype=E4M3)
+    if scale is None:
+        scale = torch.empty((M,), device=device, dtype=torch.float32)
+    maxs = None
+    if M == 0:
+        return out, scale, torch.zeros((n_experts, n), device=device, dtype=torch.float32)
+    if calibrate:
+        maxs = torch.empty((n_experts, n), device=device, dtype=torch.float32)
+    _lib.call("lh_batch_silu_smoothquant_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x), _lib.dtype_code(weight),
+              _lib.ptr(smooth_scale), _lib.ptr(counts), _lib.itype_code(counts), n_experts, M, n, _lib.ptr(out),
+              _lib.ptr(scale), _lib.ptr(maxs), int(bool(round_scale)), int(bool(reverse)))
+    return out, scale, maxs

@@ -226,11 +226,13 @@ def smooth_quant(x: torch.Tensor, smooth_scale: torch.Tensor, reverse: bool = Fa
     Returns (codes [M,N], scale [M], maxs [N])."""
     x = x.float()
     smooth_scale = smooth_scale.float()
-    maxs = x.abs().amax(0)
+    maxs = x.abs().amax(0) if x.shape[0] > 0 else torch.zeros(x.shape[1])
     if reverse:
         xs = x * smooth_scale
     else:
         xs = x / torch.clamp_min(smooth_scale, SCALE_FLOOR)
+    if x.shape[0] == 0:
+        return xs.to(torch.float8_e4m3fn), torch.zeros(0), maxs
     scale = torch.clamp_min(xs.abs().amax(1) / E4M3_MAX, SCALE_FLOOR)
     if round_scale:
         scale = _pow2_ceil(scale)
@@ -248,6 +250,28 @@ def silu_and_smooth_quant_forward(x, smooth_scale, round_scale: bool = False):
     """``torch_silu_and_smooth_quant_forward`` (tests/test_silu.py:56-72): SwiGLU in float32, then
     smooth_quant.  Returns (codes [M,n], scale [M], maxs [n])."""
     return smooth_quant(_swiglu_f32(x), smooth_scale, False, round_scale)
+
+
+def batch_weighted_silu_and_smooth_quant_forward(x, weight, counts, smooth_scales, round_scale: bool = False,
+                                                 reverse: bool = False):
+    """``torch_batch_weighted_silu_and_smooth_quant_forward`` (tests/test_silu.py:126-160): per
+    expert, weighted SwiGLU then smooth_quant with that expert's smoothing vector.  Returns
+    (codes [R,n], scale [R], maxs [E,n]).  The calibration maxima follow the reference KERNEL
+    (linghe/utils/silu.py:1803-1809): column maxima of |silu(x1) * x2| before the row weight
+    (upstream's test helper takes them after the weight and does not compare them)."""
+    counts = [int(c) for c in (counts.tolist() if hasattr(counts, "tolist") else counts)]
+    n = x.shape[1] // 2
+    qs, scales, maxs = [], [], []
+    s = 0
+    for e, c in enumerate(counts):
+        xe = x[s:s + c]
+        y = _swiglu_f32(xe, weight.reshape(-1)[s:s + c])
+        q, sc, _ = smooth_quant(y, smooth_scales[e], reverse, round_scale)
+        qs.append(q)
+        scales.append(sc)
+        maxs.append(_swiglu_f32(xe).abs().amax(0) if c > 0 else torch.zeros(n))
+        s += c
+    return torch.cat(qs, 0), torch.cat(scales, 0), torch.stack(maxs, 0)
 
 
 # --------------------------------------------------------------------------- #

@@ -266,6 +266,19 @@ def main():
     for rs in (False, True):
         q, sc, maxs = TS.torch_silu_and_smooth_quant_forward(xs, smooth_scale=sm2, round_scale=rs)
         out[f"silu_r{int(rs)}_q"], out[f"silu_r{int(rs)}_s"], out[f"silu_r{int(rs)}_maxs"] = u8(q), f32(sc), f32(maxs)
+    # per-expert form: upstream's torch_batch_weighted_silu_and_smooth_quant_forward
+    # (tests/test_silu.py:126-160); its maxima (taken after the row weight, unlike the kernel's)
+    # are not stored
+    counts = [24, 8, 40, 16]          # upstream's helper cannot take an empty expert
+    xb = bf16_randn(gs, (sum(counts), 512))
+    wb = torch.randn((sum(counts), 1), generator=gs)
+    smb = 1 + 10 * torch.rand((len(counts), 256), generator=gs)
+    out["batch_x"], out["batch_w"], out["batch_smooth"] = u16(xb), f32(wb), f32(smb)
+    out["batch_counts"] = np.asarray(counts, dtype=np.int64)
+    for rs, rev in ((False, False), (True, False), (True, True)):
+        q, sc, _ = TS.torch_batch_weighted_silu_and_smooth_quant_forward(
+            xb, wb, torch.tensor(counts), smooth_scales=smb, round_scale=rs, reverse=rev)
+        out[f"batch_r{int(rs)}v{int(rev)}_q"], out[f"batch_r{int(rs)}v{int(rev)}_s"] = u8(q), f32(sc)
     np.savez_compressed(os.path.join(HERE, "smooth.npz"), **out)
     for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route", "fp8gemm_bb", "smooth"):
         p = os.path.join(HERE, f + ".npz")

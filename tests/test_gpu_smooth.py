@@ -118,3 +118,48 @@ def test_smooth_quant_argument_errors():
     e = torch.zeros((0, 256), device="cuda", dtype=torch.bfloat16)
     q, s, maxs = fs(e, smooth_scale=torch.ones(128, device="cuda"), calibrate=True)
     assert q.shape == (0, 128) and s.shape == (0,) and float(maxs.abs().max()) == 0.0
+
+
+# upstream's test: 32 experts with 512-1536 rows each (multiples of 16), N = 4096, weights randn,
+# smooth scales 1 + 10 * rand (tests/test_silu.py:482-527); here also empty experts, ragged counts,
+# int64 counts and the `reverse` form
+@pytest.mark.parametrize("dtype,wdt", [(torch.bfloat16, torch.float32), (torch.float16, torch.float16),
+                                       (torch.float32, torch.bfloat16)])
+@pytest.mark.parametrize("counts,n,it", [([512, 0, 1040, 16, 0, 333], 2048, torch.int32), ([7], 8, torch.int64),
+                                         ([128] * 64, 512, torch.int64), ([0, 0, 5], 1408, torch.int32)])
+def test_batch_weighted_silu_and_smooth_quant(counts, n, it, dtype, wdt):
+    from linghe_b200.utils.silu import triton_batch_weighted_silu_and_smooth_quant_forward as f
+    g = torch.Generator().manual_seed(73)
+    R, E = sum(counts), len(counts)
+    x = torch.randn((R, 2 * n), generator=g).to(dtype)
+    w = torch.randn((R, 1), generator=g).to(wdt)
+    sm = 1 + 10 * torch.rand((E, n), generator=g)
+    cd = torch.tensor(counts, dtype=it, device="cuda")
+    for rs, rev in ((False, False), (True, False), (True, True)):
+        rq, rsc, rmaxs = O.batch_weighted_silu_and_smooth_quant_forward(x, w, counts, sm, rs, rev)
+        q, s, maxs = f(x.cuda(), w.cuda(), cd, smooth_scale=sm.cuda(), splits=counts, round_scale=rs, reverse=rev,
+                       calibrate=True)
+        assert q.shape == (R, n) and s.shape == (R,) and maxs.shape == (E, n)
+        check_rows(q, rq, s, rsc, "batch smooth", rs)
+        assert torch.allclose(maxs.cpu(), rmaxs, rtol=1e-6, atol=1e-30)
+    r = f(x.cuda(), w.cuda(), cd, smooth_scale=sm.cuda())
+    assert r[2] is None
+
+
+def test_batch_smooth_quant_empty():
+    from linghe_b200.utils.silu import triton_batch_weighted_silu_and_smooth_quant_forward as f
+    x = torch.zeros((0, 512), device="cuda", dtype=torch.bfloat16)
+    w = torch.zeros((0, 1), device="cuda")
+    c = torch.zeros((4,), device="cuda", dtype=torch.int32)
+    q, s, maxs = f(x, w, c, smooth_scale=torch.ones((4, 256), device="cuda"))
+    assert q.shape == (0, 256) and s.shape == (0,) and maxs.shape == (4, 256) and float(maxs.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("rs,rev", [(0, 0), (1, 0), (1, 1)])
+def test_golden_batch_smooth(rs, rev):
+    from linghe_b200.utils.silu import triton_batch_weighted_silu_and_smooth_quant_forward as f
+    G = golden("smooth")
+    x, w, sm = bf16(G["batch_x"]).cuda(), torch.from_numpy(G["batch_w"]).cuda(), torch.from_numpy(G["batch_smooth"]).cuda()
+    counts = torch.from_numpy(G["batch_counts"]).cuda()
+    q, s, _ = f(x, w, counts, smooth_scale=sm, round_scale=bool(rs), reverse=bool(rev))
+    check_rows(q, fp8(G[f"batch_r{rs}v{rev}_q"]), s, torch.from_numpy(G[f"batch_r{rs}v{rev}_s"]), "golden batch smooth", bool(rs))

@@ -252,3 +252,14 @@ def test_smooth_quant_recipe(rs):
     assert_bits_equal(q, fp8(G[f"silu_r{rs}_q"]), "silu smooth q")
     assert_f32_equal(s, torch.from_numpy(G[f"silu_r{rs}_s"]), "silu smooth scale")
     assert_f32_equal(maxs, torch.from_numpy(G[f"silu_r{rs}_maxs"]), "silu smooth maxs")
+
+
+@pytest.mark.parametrize("rs,rev", [(0, 0), (1, 0), (1, 1)])
+def test_batch_smooth_quant_recipe(rs, rev):
+    G = golden("smooth")
+    x, w, sm = bf16(G["batch_x"]), torch.from_numpy(G["batch_w"]), torch.from_numpy(G["batch_smooth"])
+    counts = [int(c) for c in G["batch_counts"]]
+    q, s, maxs = O.batch_weighted_silu_and_smooth_quant_forward(x, w, counts, sm, bool(rs), bool(rev))
+    assert_bits_equal(q, fp8(G[f"batch_r{rs}v{rev}_q"]), "batch smooth q")
+    assert_f32_equal(s, torch.from_numpy(G[f"batch_r{rs}v{rev}_s"]), "batch smooth scale")
+    assert tuple(maxs.shape) == (len(counts), x.shape[1] // 2)
