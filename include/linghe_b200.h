@@ -294,6 +294,18 @@ int lh_silu_smoothquant_fwd(const void* x, const float* smooth_scale, int dtype,
                             float* scale, float* maxs, void* scratch, int64_t scratch_bytes, int round_scale,
                             void* stream);
 
+/* SwiGLU backward + smooth quantisation of dx = [dx1 | dx2] on both axes.
+ * Row-wise copy: dx * smooth_scale[c] (reverse != 0) or dx / max(smooth_scale[c], 1e-30), one
+ * scale per row.  Transposed copy: dx[r,c] * transpose_smooth_scale[r] (or divided), one scale
+ * per column of dx over all M rows.
+ * Replaces triton_silu_and_smooth_quant_backward, linghe/utils/silu.py:1705.
+ * g [M,n], x [M,2n] of `dtype`; smooth_scale float32 [2n], transpose_smooth_scale float32 [M];
+ * outputs dx_q e4m3 [M,2n], dx_scale [M], dxt_q e4m3 [2n,M], dxt_scale [2n]; n <= 4096, n % 8 == 0;
+ * scratch: lh_scratch_bytes("smooth_quant_bwd", M, n) bytes. */
+int lh_silu_smoothquant_bwd(const void* g, const void* x, const float* smooth_scale, const float* transpose_smooth_scale,
+                            int dtype, int64_t M, int64_t n, void* dx_q, float* dx_scale, void* dxt_q, float* dxt_scale,
+                            void* scratch, int64_t scratch_bytes, int round_scale, int reverse, void* stream);
+
 /* Per-expert weighted SwiGLU + smooth quantisation: rows grouped by expert (counts[e] rows each),
  * y = silu(x1) * x2; ys = (y * w[row]) / max(smooth_scale[e], 1e-30) (reverse != 0: * smooth_scale[e]);
  * one scale per row.  maxs (optional, "calibrate") float32 [E, n] = per-expert column maxima of

@@ -155,6 +155,10 @@ int smooth_quant_fwd(int silu, const void* x, const void* gamma, const float* sm
 int smooth_quant_batch_fwd(const void* x, const void* w, int dtype, int w_dtype, const float* smooth, const void* counts,
                            int counts_type, int E, int64_t M, int64_t n, void* q, float* scale, float* emax,
                            int round_scale, int reverse, cudaStream_t stream);
+int64_t smooth_bwd_scratch(int64_t n);
+int smooth_quant_silu_bwd(const void* g, const void* x, const float* smooth, const float* tsmooth, int dtype, int64_t M,
+                          int64_t n, void* q, float* scale, void* qt, float* tscale, void* scratch, int64_t scratch_bytes,
+                          int round_scale, int reverse, cudaStream_t stream);
 int any_col_strip(int silu, const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n,
                   void* qt, float* st, int round_scale, cudaStream_t stream);
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
@@ -274,6 +278,7 @@ int64_t lh_scratch_bytes(const char* what, int64_t rows, int64_t cols) {
     }
     if (!strcmp(what, "batch_silu_bwd")) return rows * (cols / 128) * 4;
     if (!strcmp(what, "smooth_quant")) return smooth_quant_scratch(cols);       // calibration only
+    if (!strcmp(what, "smooth_quant_bwd")) return smooth_bwd_scratch(cols);     // cols = n (half the row)
     if (!strcmp(what, "rmsnorm_bwd_static")) return 0;  // it carries its own
     if (!strcmp(what, "row_id_map")) return route_scratch_bytes(cols);          // cols = experts
     if (!strcmp(what, "rmsnorm_gemm")) return router_gemm_scratch(rows, cols);   // rows = N, cols = K
@@ -446,6 +451,13 @@ int lh_batch_silu_smoothquant_fwd(const void* x, const void* w, int dtype, int w
                                   float* maxs, int round_scale, int reverse, void* stream) {
     return smooth_quant_batch_fwd(x, w, dtype, w_dtype, smooth_scale, counts, counts_type, E, R, n, q, scale, maxs,
                                   round_scale, reverse, static_cast<cudaStream_t>(stream));
+}
+
+int lh_silu_smoothquant_bwd(const void* g, const void* x, const float* smooth_scale, const float* transpose_smooth_scale,
+                            int dtype, int64_t M, int64_t n, void* dx_q, float* dx_scale, void* dxt_q, float* dxt_scale,
+                            void* scratch, int64_t scratch_bytes, int round_scale, int reverse, void* stream) {
+    return smooth_quant_silu_bwd(g, x, smooth_scale, transpose_smooth_scale, dtype, M, n, dx_q, dx_scale, dxt_q, dxt_scale,
+                                 scratch, scratch_bytes, round_scale, reverse, static_cast<cudaStream_t>(stream));
 }
 
 int lh_fp8_gemm_bb(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,

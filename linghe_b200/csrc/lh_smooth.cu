@@ -249,6 +249,133 @@ smooth_batch_kernel(const T* __restrict__ x, const void* __restrict__ w, int w_d
     flush();
 }
 
+// ---- SwiGLU backward + smooth quantisation (linghe/utils/silu.py:1705) -----------------------
+// dx = [dx1 | dx2] with dx1 = g x2 s (1 + x1 (1 - s)), dx2 = g x1 s, s = sigmoid(x1).
+// Row-wise copy: dx * smooth[c] (reverse) or dx / max(smooth[c], 1e-30), one scale per row.
+// Transposed copy: dx[r, c] * tsmooth[r] (reverse) or / max(tsmooth[r], 1e-30), one scale per
+// COLUMN of dx over all M rows, so it takes two launches: this one also collects the column
+// maxima of the smoothed values per CTA (scratch [grid, 2n]); after their reduction to column
+// scales the second kernel recomputes dx and writes the transposed codes.  (Upstream quantises
+// 32-row groups locally and requantises the codes, linghe/utils/silu.py:1686-1754; the values here
+// are quantised once, with the final scale, as upstream's oracle does.)
+__device__ __forceinline__ void swiglu_grad8(const float* g, const float* x1, const float* x2, float* d1, float* d2) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float sg = sigmoid_fast1(x1[j]);
+        const float sgg = sg * g[j];
+        d2[j] = sgg * x1[j];
+        d1[j] = (sgg * x2[j]) * fmaf(x1[j], 1.0f - sg, 1.0f);
+    }
+}
+
+// rows: thread owns vectors t, t + 256 of each half (n <= 4096 per half: two vectors of 8 per half)
+template <typename T>
+__global__ void __launch_bounds__(SNT)
+smooth_bwd_rows_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ smooth,
+                       const float* __restrict__ tsmooth, int64_t M, int n, uint8_t* __restrict__ q,
+                       float* __restrict__ scale, float* __restrict__ colmax, int round_scale, int reverse) {
+    __shared__ float red[SNT / 32];
+    const int t = threadIdx.x;
+    constexpr int HV = SMAXV / 2;     // vectors per half and thread
+    float cm[2][HV][8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int k = 0; k < HV; ++k)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) cm[h][k][j] = 0.f;
+    for (int64_t row = blockIdx.x; row < M; row += gridDim.x) {
+        const float ts = tsmooth[row];
+        const float tmul = reverse ? ts : __frcp_rn(fmaxf(ts, kScaleFloor));
+        float v[2][HV][8];
+        float amax = 0.f;
+#pragma unroll
+        for (int k = 0; k < HV; ++k) {
+            const int col = (k * SNT + t) * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[0][k][j] = v[1][k][j] = 0.f;
+            if (col < n) {
+                float gg[8], x1[8], x2[8], s1[8], s2[8];
+                ld8(g + row * n + col, gg);
+                ld8(x + row * 2 * int64_t(n) + col, x1);
+                ld8(x + row * 2 * int64_t(n) + n + col, x2);
+                swiglu_grad8(gg, x1, x2, v[0][k], v[1][k]);
+                ld8(smooth + col, s1);
+                ld8(smooth + n + col, s2);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    cm[0][k][j] = fmaxf(cm[0][k][j], fabsf(reverse ? v[0][k][j] * tmul : __fdiv_rn(v[0][k][j], fmaxf(ts, kScaleFloor))));
+                    cm[1][k][j] = fmaxf(cm[1][k][j], fabsf(reverse ? v[1][k][j] * tmul : __fdiv_rn(v[1][k][j], fmaxf(ts, kScaleFloor))));
+                    v[0][k][j] = reverse ? v[0][k][j] * s1[j] : __fdiv_rn(v[0][k][j], fmaxf(s1[j], kScaleFloor));
+                    v[1][k][j] = reverse ? v[1][k][j] * s2[j] : __fdiv_rn(v[1][k][j], fmaxf(s2[j], kScaleFloor));
+                    amax = fmaxf(amax, fmaxf(fabsf(v[0][k][j]), fabsf(v[1][k][j])));
+                }
+            }
+        }
+        amax = block_reduce<false>(amax, red);
+        const float sc = scale_from_amax(amax, round_scale != 0);
+        if (t == 0) scale[row] = sc;
+        const float y = rcp_approx(sc);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int k = 0; k < HV; ++k) {
+                const int col = (k * SNT + t) * 8;
+                if (col < n) {
+                    const float* vv = v[h][k];
+                    *reinterpret_cast<uint2*>(q + row * 2 * int64_t(n) + h * n + col) =
+                        make_uint2(cvt_e4m3x4(vv[0] * y, vv[1] * y, vv[2] * y, vv[3] * y),
+                                   cvt_e4m3x4(vv[4] * y, vv[5] * y, vv[6] * y, vv[7] * y));
+                }
+            }
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int k = 0; k < HV; ++k) {
+            const int col = (k * SNT + t) * 8;
+            if (col < n) {
+                float4* dst = reinterpret_cast<float4*>(colmax + int64_t(blockIdx.x) * 2 * n + h * n + col);
+                dst[0] = make_float4(cm[h][k][0], cm[h][k][1], cm[h][k][2], cm[h][k][3]);
+                dst[1] = make_float4(cm[h][k][4], cm[h][k][5], cm[h][k][6], cm[h][k][7]);
+            }
+        }
+}
+
+// column scales from the per-CTA maxima: tscale[c] = max(max / 448, 1e-30) [power of two]
+__global__ void __launch_bounds__(256)
+colscale_reduce_kernel(const float* __restrict__ partial, int parts, int n2, float* __restrict__ tscale, int round_scale) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= n2) return;
+    float m = 0.f;
+    for (int p = 0; p < parts; ++p) m = fmaxf(m, partial[int64_t(p) * n2 + c]);
+    tscale[c] = scale_from_amax(m, round_scale != 0);
+}
+
+// transposed codes: CTA = 128 consecutive rows x 8 columns of each half; thread = one row
+template <typename T>
+__global__ void __launch_bounds__(128)
+smooth_bwd_cols_kernel(const T* __restrict__ g, const T* __restrict__ x, const float* __restrict__ tsmooth,
+                       const float* __restrict__ tscale, int64_t M, int n, uint8_t* __restrict__ qt, int reverse) {
+    const int64_t row = int64_t(blockIdx.x) * 128 + threadIdx.x;
+    const int col = int(blockIdx.y) * 8;
+    if (row >= M) return;
+    float gg[8], x1[8], x2[8], d1[8], d2[8];
+    ld8(g + row * n + col, gg);
+    ld8(x + row * 2 * int64_t(n) + col, x1);
+    ld8(x + row * 2 * int64_t(n) + n + col, x2);
+    swiglu_grad8(gg, x1, x2, d1, d2);
+    const float ts = tsmooth[row];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float a = reverse ? d1[j] * ts : __fdiv_rn(d1[j], fmaxf(ts, kScaleFloor));
+        const float b = reverse ? d2[j] * ts : __fdiv_rn(d2[j], fmaxf(ts, kScaleFloor));
+        const uint32_t c2 = cvt_e4m3x2(a * rcp_approx(tscale[col + j]), b * rcp_approx(tscale[n + col + j]));
+        qt[int64_t(col + j) * M + row] = uint8_t(c2);
+        qt[int64_t(n + col + j) * M + row] = uint8_t(c2 >> 8);
+    }
+}
+
 // maxs[c] = max over the per-CTA rows of the calibration scratch
 __global__ void __launch_bounds__(256)
 colmax_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ maxs) {
@@ -329,6 +456,47 @@ int smooth_quant_batch_fwd(const void* x, const void* w, int dtype, int w_dtype,
     if (dtype == LH_F16) return launch_smooth_batch<__half>(x, w, w_dtype, smooth, counts, i64, E, M, n, q, scale, emax, round_scale, reverse, stream);
     if (dtype == LH_F32) return launch_smooth_batch<float>(x, w, w_dtype, smooth, counts, i64, E, M, n, q, scale, emax, round_scale, reverse, stream);
     return launch_smooth_batch<__nv_bfloat16>(x, w, w_dtype, smooth, counts, i64, E, M, n, q, scale, emax, round_scale, reverse, stream);
+}
+
+int64_t smooth_bwd_scratch(int64_t n) { return int64_t(kSmoothMaxCtas) * 2 * n * 4; }
+
+// dx codes [M,2n] + row scales [M]; transposed codes [2n,M] + column scales [2n].  n <= 4096 per half.
+int smooth_quant_silu_bwd(const void* g, const void* x, const float* smooth, const float* tsmooth, int dtype, int64_t M,
+                          int64_t n, void* q, float* scale, void* qt, float* tscale, void* scratch, int64_t scratch_bytes,
+                          int round_scale, int reverse, cudaStream_t stream) {
+    const char* what = "silu_smoothquant_bwd";
+    if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
+    if (M < 0 || n <= 0 || n > 4096 || (n % 8) != 0) return fail_arg("%s: need 0 < n <= 4096, n %% 8 == 0 (M=%lld n=%lld)", what, (long long)M, (long long)n);
+    if (!tscale) return fail_arg("%s: NULL pointer", what);
+    if (M == 0) {   // no rows: every column maximum is zero, the scales sit on their floor
+        colscale_reduce_kernel<<<unsigned((2 * n + 255) / 256), 256, 0, stream>>>(nullptr, 0, int(2 * n), tscale, round_scale);
+        return check_launch("colscale_reduce_kernel");
+    }
+    if (!g || !x || !smooth || !tsmooth || !q || !scale || !qt || !scratch) return fail_arg("%s: NULL pointer", what);
+    if ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(smooth) |
+         reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(scratch)) & 15)
+        return fail_arg("%s: pointers must be 16-byte aligned", what);
+    if (scratch_bytes < smooth_bwd_scratch(n)) return fail_arg("%s: scratch too small (%lld < %lld)", what, (long long)scratch_bytes, (long long)smooth_bwd_scratch(n));
+    int64_t grid = int64_t(sm_count()) * 8;
+    if (grid > kSmoothMaxCtas) grid = kSmoothMaxCtas;
+    if (grid > M) grid = M;
+    float* sp = static_cast<float*>(scratch);
+    const dim3 cgrid(unsigned((M + 127) / 128), unsigned(n / 8));
+#define LH_SBWD(T)                                                                                                     \
+    do {                                                                                                               \
+        smooth_bwd_rows_kernel<T><<<unsigned(grid), SNT, 0, stream>>>(static_cast<const T*>(g), static_cast<const T*>(x), smooth, \
+            tsmooth, M, int(n), static_cast<uint8_t*>(q), scale, sp, round_scale, reverse);                            \
+        if (int rc = check_launch("smooth_bwd_rows_kernel")) return rc;                                                \
+        colscale_reduce_kernel<<<unsigned((2 * n + 255) / 256), 256, 0, stream>>>(sp, int(grid), int(2 * n), tscale, round_scale); \
+        if (int rc = check_launch("colscale_reduce_kernel")) return rc;                                                \
+        smooth_bwd_cols_kernel<T><<<cgrid, 128, 0, stream>>>(static_cast<const T*>(g), static_cast<const T*>(x), tsmooth, tscale, M, \
+            int(n), static_cast<uint8_t*>(qt), reverse);                                                               \
+    } while (0)
+    if (dtype == LH_F16) LH_SBWD(__half);
+    else if (dtype == LH_F32) LH_SBWD(float);
+    else LH_SBWD(__nv_bfloat16);
+#undef LH_SBWD
+    return check_launch("smooth_bwd_cols_kernel");
 }
 
 int64_t smooth_quant_scratch(int64_t n) { return int64_t(kSmoothMaxCtas) * n * 4; }

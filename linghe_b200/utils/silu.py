@@ -224,3 +224,38 @@ def triton_batch_weighted_silu_and_smooth_quant_forward(x, weight, counts, smoot
               _lib.ptr(smooth_scale), _lib.ptr(counts), _lib.itype_code(counts), n_experts, M, n, _lib.ptr(out),
               _lib.ptr(scale), _lib.ptr(maxs), int(bool(round_scale)), int(bool(reverse)))
     return out, scale, maxs
+
+
+def triton_silu_and_smooth_quant_backward(g, x, smooth_scale=None, transpose_smooth_scale=None, reverse=True,
+                                          round_scale=False):
+    """SwiGLU backward + smooth quantisation on both axes (linghe/utils/silu.py:1705).
+
+    dx = [dx1 | dx2] is smoothed by `smooth_scale` [2n] along the row (multiplied when `reverse`,
+    else divided) and quantised with one scale per row; the transposed copy is smoothed by
+    `transpose_smooth_scale` [M] and quantised with one scale per column of dx (over all rows).
+    Returns (dx e4m3 [M,2n], dx_scale [M], transpose_dx e4m3 [2n,M], transpose_dx_scale [2n]).
+    Upstream asserts `round_scale` (its requantisation pass needs power-of-two scales); here both
+    settings work, the values being quantised once with the final column scale."""
+    assert g.is_contiguous() and x.is_contiguous()
+    assert smooth_scale is not None and transpose_smooth_scale is not None
+    assert smooth_scale.is_contiguous() and transpose_smooth_scale.is_contiguous()
+    M, N = x.shape
+    n = N // 2
+    assert N % 16 == 0 and n <= 4096
+    assert smooth_scale.numel() == N and transpose_smooth_scale.numel() == M
+    device = x.device
+    if smooth_scale.dtype != torch.float32:
+        smooth_scale = smooth_scale.float()
+    if transpose_smooth_scale.dtype != torch.float32:
+        transpose_smooth_scale = transpose_smooth_scale.float()
+    dx = torch.empty((M, N), device=device, dtype=E4M3)
+    dx_scale = torch.empty((M,), device=device, dtype=torch.float32)
+    transpose_dx = torch.empty((N, M), device=device, dtype=E4M3)
+    transpose_dx_scale = torch.empty((N,), device=device, dtype=torch.float32)
+    nbytes = _lib.scratch_bytes("smooth_quant_bwd", M, n)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    _lib.call("lh_silu_smoothquant_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.ptr(smooth_scale),
+              _lib.ptr(transpose_smooth_scale), _lib.dtype_code(x), M, n, _lib.ptr(dx), _lib.ptr(dx_scale),
+              _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale), _lib.ptr(scratch), nbytes, int(bool(round_scale)),
+              int(bool(reverse)))
+    return dx, dx_scale, transpose_dx, transpose_dx_scale

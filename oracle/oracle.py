@@ -252,6 +252,17 @@ def silu_and_smooth_quant_forward(x, smooth_scale, round_scale: bool = False):
     return smooth_quant(_swiglu_f32(x), smooth_scale, False, round_scale)
 
 
+def silu_and_smooth_quant_backward(g, x, smooth_scale, transpose_smooth_scale, round_scale: bool = True,
+                                   reverse: bool = True):
+    """``torch_silu_and_smooth_quant_backward`` (tests/test_silu.py:87-110): dx by autograd in
+    float32, smooth_quant of dx with `smooth_scale` and of dx.T with `transpose_smooth_scale`.
+    Returns (dx codes [M,2n], dx scale [M], dx.T codes [2n,M], dx.T scale [2n])."""
+    dx, _ = weighted_silu_backward(g, x, None)
+    q, s, _ = smooth_quant(dx, smooth_scale, reverse, round_scale)
+    qt, st, _ = smooth_quant(dx.t().contiguous(), transpose_smooth_scale, reverse, round_scale)
+    return q, s, qt, st
+
+
 def batch_weighted_silu_and_smooth_quant_forward(x, weight, counts, smooth_scales, round_scale: bool = False,
                                                  reverse: bool = False):
     """``torch_batch_weighted_silu_and_smooth_quant_forward`` (tests/test_silu.py:126-160): per

@@ -279,6 +279,18 @@ def main():
         q, sc, _ = TS.torch_batch_weighted_silu_and_smooth_quant_forward(
             xb, wb, torch.tensor(counts), smooth_scales=smb, round_scale=rs, reverse=rev)
         out[f"batch_r{int(rs)}v{int(rev)}_q"], out[f"batch_r{int(rs)}v{int(rev)}_s"] = u8(q), f32(sc)
+    # backward: upstream's torch_silu_and_smooth_quant_backward (tests/test_silu.py:87-110), smooth
+    # scales 1 + rand as in tests/test_silu.py:339-342, gradients 0.1 * randn
+    gbk = (0.1 * torch.randn((64, 192), generator=gs)).to(torch.bfloat16)
+    xbk = bf16_randn(gs, (64, 384))
+    sbk = 1 + torch.rand((384,), generator=gs)
+    tsbk = 1 + torch.rand((64,), generator=gs)
+    out["bwd_g"], out["bwd_x"], out["bwd_smooth"], out["bwd_tsmooth"] = u16(gbk), u16(xbk), f32(sbk), f32(tsbk)
+    for rs, rev in ((True, True), (True, False), (False, True)):
+        q, sc, qt, sct = TS.torch_silu_and_smooth_quant_backward(gbk, xbk, smooth_scale=sbk, transpose_smooth_scale=tsbk,
+                                                                 round_scale=rs, reverse=rev)
+        tag = f"bwd_r{int(rs)}v{int(rev)}"
+        out[tag + "_q"], out[tag + "_s"], out[tag + "_qt"], out[tag + "_st"] = u8(q), f32(sc), u8(qt), f32(sct)
     np.savez_compressed(os.path.join(HERE, "smooth.npz"), **out)
     for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route", "fp8gemm_bb", "smooth"):
         p = os.path.join(HERE, f + ".npz")

@@ -163,3 +163,40 @@ def test_golden_batch_smooth(rs, rev):
     counts = torch.from_numpy(G["batch_counts"]).cuda()
     q, s, _ = f(x, w, counts, smooth_scale=sm, round_scale=bool(rs), reverse=bool(rev))
     check_rows(q, fp8(G[f"batch_r{rs}v{rev}_q"]), s, torch.from_numpy(G[f"batch_r{rs}v{rev}_s"]), "golden batch smooth", bool(rs))
+
+
+def check_cols(got_qt, ref_qt, got_st, ref_st, what, pow2):
+    """transposed copy: codes [C, M] with one scale per row of the transposed matrix"""
+    check_rows(got_qt, ref_qt, got_st, ref_st, what, pow2)
+
+
+# upstream's test: M = N = 4096, smooth scales 1 + rand, reverse=True, round_scale=True
+# (tests/test_silu.py:332-377)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("M,n", [(2048, 2048), (1000, 1408), (130, 4096), (64, 8), (4096, 512)])
+def test_silu_and_smooth_quant_backward(M, n, dtype):
+    from linghe_b200.utils.silu import triton_silu_and_smooth_quant_backward as f
+    gen = torch.Generator().manual_seed(74)
+    x = torch.randn((M, 2 * n), generator=gen).to(dtype)
+    g = (0.1 * torch.randn((M, n), generator=gen)).to(dtype)
+    sm = 1 + torch.rand((2 * n,), generator=gen)
+    tsm = 1 + torch.rand((M,), generator=gen)
+    for rs, rev in ((True, True), (True, False), (False, True)):
+        rq, rsc, rqt, rst = O.silu_and_smooth_quant_backward(g, x, sm, tsm, rs, rev)
+        q, s, qt, st = f(g.cuda(), x.cuda(), smooth_scale=sm.cuda(), transpose_smooth_scale=tsm.cuda(), reverse=rev,
+                         round_scale=rs)
+        assert q.shape == (M, 2 * n) and s.shape == (M,) and qt.shape == (2 * n, M) and st.shape == (2 * n,)
+        check_rows(q, rq, s, rsc, "smooth bwd dx", rs)
+        check_cols(qt, rqt, st, rst, "smooth bwd dxT", rs)
+
+
+@pytest.mark.parametrize("rs,rev", [(1, 1), (1, 0), (0, 1)])
+def test_golden_smooth_backward(rs, rev):
+    from linghe_b200.utils.silu import triton_silu_and_smooth_quant_backward as f
+    G = golden("smooth")
+    g, x = bf16(G["bwd_g"]).cuda(), bf16(G["bwd_x"]).cuda()
+    sm, tsm = torch.from_numpy(G["bwd_smooth"]).cuda(), torch.from_numpy(G["bwd_tsmooth"]).cuda()
+    q, s, qt, st = f(g, x, smooth_scale=sm, transpose_smooth_scale=tsm, reverse=bool(rev), round_scale=bool(rs))
+    tag = f"bwd_r{rs}v{rev}"
+    check_rows(q, fp8(G[tag + "_q"]), s, torch.from_numpy(G[tag + "_s"]), "golden smooth bwd dx", bool(rs))
+    check_cols(qt, fp8(G[tag + "_qt"]), st, torch.from_numpy(G[tag + "_st"]), "golden smooth bwd dxT", bool(rs))

@@ -263,3 +263,16 @@ def test_batch_smooth_quant_recipe(rs, rev):
     assert_bits_equal(q, fp8(G[f"batch_r{rs}v{rev}_q"]), "batch smooth q")
     assert_f32_equal(s, torch.from_numpy(G[f"batch_r{rs}v{rev}_s"]), "batch smooth scale")
     assert tuple(maxs.shape) == (len(counts), x.shape[1] // 2)
+
+
+@pytest.mark.parametrize("rs,rev", [(1, 1), (1, 0), (0, 1)])
+def test_smooth_quant_backward_recipe(rs, rev):
+    G = golden("smooth")
+    g, x = bf16(G["bwd_g"]), bf16(G["bwd_x"])
+    sm, tsm = torch.from_numpy(G["bwd_smooth"]), torch.from_numpy(G["bwd_tsmooth"])
+    q, s, qt, st = O.silu_and_smooth_quant_backward(g, x, sm, tsm, bool(rs), bool(rev))
+    tag = f"bwd_r{rs}v{rev}"
+    assert_codes_close(q, fp8(G[tag + "_q"]), "dx q")
+    assert_scales_close(s, torch.from_numpy(G[tag + "_s"]), "dx scale") if not rs else None
+    assert_codes_close(qt, fp8(G[tag + "_qt"]), "dxT q")
+    assert tuple(qt.shape) == (x.shape[1], x.shape[0]) and tuple(st.shape) == (x.shape[1],)
