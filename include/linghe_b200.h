@@ -317,6 +317,20 @@ int lh_batch_silu_smoothquant_fwd(const void* x, const void* w, int dtype, int w
                                   const void* counts, int counts_type, int E, int64_t R, int64_t n, void* q, float* scale,
                                   float* maxs, int round_scale, int reverse, void* stream);
 
+/* Backward of the above with smooth quantisation of dx = [dx1 | dx2] on both axes, per expert:
+ * dw [R] (w_dtype); row-wise copy smoothed by smooth_scale[e] ([E,2n]), one scale per row;
+ * transposed copy smoothed by transpose_smooth_scale[row] ([R]), one scale per (expert, column):
+ * dxt_scale [E,2n]; expert e's transposed codes are a [2n, pad32(counts[e])] block (zero codes in
+ * the padding) at byte offset 2n * sum_{e' < e} pad32(counts[e']) of dxt_q; padded_rows =
+ * sum_e pad32(counts[e]).  Experts without rows get the floor scale (all zero when R == 0).
+ * Replaces triton_batch_weighted_silu_and_smooth_quant_backward, linghe/utils/silu.py:2126.
+ * n <= 4096, n % 8 == 0, E <= 2048. */
+int lh_batch_silu_smoothquant_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype,
+                                  const float* smooth_scale, const float* transpose_smooth_scale, const void* counts,
+                                  int counts_type, int E, int64_t R, int64_t n, int64_t padded_rows, void* dx_q,
+                                  float* dx_scale, void* dw, void* dxt_q, float* dxt_scale, int round_scale, int reverse,
+                                  void* stream);
+
 /* ---- consumer of the wire format ------------------------------------------------- */
 
 /* Blockwise-scaled FP8 GEMM  c [M,N] = dequant(a) . dequant(b)^T.

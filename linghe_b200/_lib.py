@@ -51,6 +51,7 @@ SIGNATURES = {
     "lh_rmsnorm_smoothquant_fwd": (_i, [_p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _p, _p, _l, _i, _p]),
     "lh_silu_smoothquant_fwd": (_i, [_p, _p, _i, _l, _l, _p, _p, _p, _p, _l, _i, _p]),
     "lh_silu_smoothquant_bwd": (_i, [_p, _p, _p, _p, _i, _l, _l, _p, _p, _p, _p, _p, _l, _i, _i, _p]),
+    "lh_batch_silu_smoothquant_bwd": (_i, [_p, _p, _p, _i, _i, _p, _p, _p, _i, _i, _l, _l, _l, _p, _p, _p, _p, _p, _i, _i, _p]),
     "lh_batch_silu_smoothquant_fwd": (_i, [_p, _p, _i, _i, _p, _p, _i, _i, _l, _l, _p, _p, _p, _i, _i, _p]),
     "lh_rmsnorm_bwd": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p, _l, _p]),
     "lh_rmsnorm_bwd_static": (_i, [_p, _p, _p, _p, _i, _l, _l, _f, _p, _p, _p]),

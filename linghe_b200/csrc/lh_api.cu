@@ -159,6 +159,10 @@ int64_t smooth_bwd_scratch(int64_t n);
 int smooth_quant_silu_bwd(const void* g, const void* x, const float* smooth, const float* tsmooth, int dtype, int64_t M,
                           int64_t n, void* q, float* scale, void* qt, float* tscale, void* scratch, int64_t scratch_bytes,
                           int round_scale, int reverse, cudaStream_t stream);
+int smooth_quant_batch_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype, const float* smooth,
+                           const float* tsmooth, const void* counts, int counts_type, int E, int64_t M, int64_t n,
+                           int64_t padded_rows, void* q, float* scale, void* dw, void* qt, float* tscale,
+                           int round_scale, int reverse, cudaStream_t stream);
 int any_col_strip(int silu, const void* x, const void* gamma, const float* r, int dtype, int64_t M, int64_t n,
                   void* qt, float* st, int round_scale, cudaStream_t stream);
 int tile_gather_quant(const void* x, int dtype, const void* probs, int probs_dtype, const void* indices,
@@ -458,6 +462,16 @@ int lh_silu_smoothquant_bwd(const void* g, const void* x, const float* smooth_sc
                             void* scratch, int64_t scratch_bytes, int round_scale, int reverse, void* stream) {
     return smooth_quant_silu_bwd(g, x, smooth_scale, transpose_smooth_scale, dtype, M, n, dx_q, dx_scale, dxt_q, dxt_scale,
                                  scratch, scratch_bytes, round_scale, reverse, static_cast<cudaStream_t>(stream));
+}
+
+int lh_batch_silu_smoothquant_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype,
+                                  const float* smooth_scale, const float* transpose_smooth_scale, const void* counts,
+                                  int counts_type, int E, int64_t R, int64_t n, int64_t padded_rows, void* dx_q,
+                                  float* dx_scale, void* dw, void* dxt_q, float* dxt_scale, int round_scale, int reverse,
+                                  void* stream) {
+    return smooth_quant_batch_bwd(g, x, w, dtype, w_dtype, smooth_scale, transpose_smooth_scale, counts, counts_type, E, R, n,
+                                  padded_rows, dx_q, dx_scale, dw, dxt_q, dxt_scale, round_scale, reverse,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int lh_fp8_gemm_bb(const void* a, const void* b, const float* a_s, const float* b_s, void* c, int64_t M, int64_t N,

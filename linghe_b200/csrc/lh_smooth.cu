@@ -376,6 +376,194 @@ smooth_bwd_cols_kernel(const T* __restrict__ g, const T* __restrict__ x, const f
     }
 }
 
+// ---- per-expert weighted SwiGLU backward + smooth quantisation (linghe/utils/silu.py:2126) ----
+// Rows grouped by expert; dx1 = s g x2 w (1 + x1 (1 - s)), dx2 = s g x1 w, dw[row] = sum_j s x1 x2 g.
+// Row-wise copy: smoothed by smooth[e, :] ([E, 2n]), one scale per row.  Transposed copy, per
+// expert: dx[r, c] smoothed by tsmooth[r], one scale per (expert, column); expert e's codes are a
+// [2n, pad32(c_e)] block (rows past c_e are zero codes) at offset 2n * sum_{e' < e} pad32(c_e').
+// Same three steps as the dense form, with the column maxima merged per expert by atomicMax.
+__device__ __forceinline__ int find_seg(const int64_t* seg, int E, int64_t row) {
+    int lo = 0, hi = E - 1;            // smallest e with seg[e + 1] > row
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (seg[mid + 1] > row) hi = mid; else lo = mid + 1;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float load_scalar(const void* w, int w_dtype, int64_t i) {
+    return w_dtype == LH_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(w)[i])
+           : w_dtype == LH_F16 ? __half2float(reinterpret_cast<const __half*>(w)[i])
+                               : reinterpret_cast<const float*>(w)[i];
+}
+
+__device__ __forceinline__ void fill_prefix(int64_t* seg, const void* counts, int counts_i64, int E, int pad) {
+    int64_t acc = 0;
+    seg[0] = 0;
+    for (int e = 0; e < E; ++e) {
+        int64_t c = counts_i64 ? reinterpret_cast<const int64_t*>(counts)[e] : int64_t(reinterpret_cast<const int32_t*>(counts)[e]);
+        if (pad > 1) c = (c + pad - 1) / pad * pad;
+        acc += c;
+        seg[e + 1] = acc;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SNT)
+smooth_batch_bwd_rows_kernel(const T* __restrict__ g, const T* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                             const float* __restrict__ smooth, const float* __restrict__ tsmooth,
+                             const void* __restrict__ counts, int counts_i64, int E, int64_t M, int n,
+                             uint8_t* __restrict__ q, float* __restrict__ scale, void* __restrict__ dw,
+                             float* __restrict__ emax, int round_scale, int reverse) {
+    extern __shared__ int64_t seg[];
+    __shared__ float red[SNT / 32];
+    const int t = threadIdx.x;
+    if (t == 0) fill_prefix(seg, counts, counts_i64, E, 1);
+    __syncthreads();
+    const int64_t total = seg[E] < M ? seg[E] : M;
+    constexpr int HV = SMAXV / 2;
+    float cm[2][HV][8];
+    int cur_e = -1;
+    auto flush = [&]() {
+        if (cur_e >= 0) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int k = 0; k < HV; ++k) {
+                    const int col = (k * SNT + t) * 8;
+                    if (col < n) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            atomicMax(reinterpret_cast<unsigned int*>(emax + int64_t(cur_e) * 2 * n + h * n + col + j),
+                                      __float_as_uint(cm[h][k][j]));
+                    }
+                }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int k = 0; k < HV; ++k)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) cm[h][k][j] = 0.f;
+    };
+    flush();
+    for (int64_t row = blockIdx.x; row < total; row += gridDim.x) {
+        const int e = find_seg(seg, E, row);
+        if (e != cur_e) { flush(); cur_e = e; }
+        const float* sm = smooth + int64_t(e) * 2 * n;
+        const float wr = load_scalar(w, w_dtype, row);
+        const float ts = tsmooth[row];
+        float v[2][HV][8];
+        float amax = 0.f, dwp = 0.f;
+#pragma unroll
+        for (int k = 0; k < HV; ++k) {
+            const int col = (k * SNT + t) * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[0][k][j] = v[1][k][j] = 0.f;
+            if (col < n) {
+                float gg[8], x1[8], x2[8], s1[8], s2[8];
+                ld8(g + row * n + col, gg);
+                ld8(x + row * 2 * int64_t(n) + col, x1);
+                ld8(x + row * 2 * int64_t(n) + n + col, x2);
+                swiglu_grad8(gg, x1, x2, v[0][k], v[1][k]);
+                ld8(sm + col, s1);
+                ld8(sm + n + col, s2);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    dwp = fmaf(v[1][k][j], x2[j], dwp);          // (s g x1) x2
+                    const float d1 = v[0][k][j] * wr, d2 = v[1][k][j] * wr;
+                    cm[0][k][j] = fmaxf(cm[0][k][j], fabsf(reverse ? d1 * ts : __fdiv_rn(d1, fmaxf(ts, kScaleFloor))));
+                    cm[1][k][j] = fmaxf(cm[1][k][j], fabsf(reverse ? d2 * ts : __fdiv_rn(d2, fmaxf(ts, kScaleFloor))));
+                    v[0][k][j] = reverse ? d1 * s1[j] : __fdiv_rn(d1, fmaxf(s1[j], kScaleFloor));
+                    v[1][k][j] = reverse ? d2 * s2[j] : __fdiv_rn(d2, fmaxf(s2[j], kScaleFloor));
+                    amax = fmaxf(amax, fmaxf(fabsf(v[0][k][j]), fabsf(v[1][k][j])));
+                }
+            }
+        }
+        amax = block_reduce<false>(amax, red);
+        dwp = block_reduce<true>(dwp, red);
+        const float sc = scale_from_amax(amax, round_scale != 0);
+        if (t == 0) {
+            scale[row] = sc;
+            if (w_dtype == LH_BF16) reinterpret_cast<__nv_bfloat16*>(dw)[row] = __float2bfloat16_rn(dwp);
+            else if (w_dtype == LH_F16) reinterpret_cast<__half*>(dw)[row] = __float2half_rn(dwp);
+            else reinterpret_cast<float*>(dw)[row] = dwp;
+        }
+        const float y = rcp_approx(sc);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int k = 0; k < HV; ++k) {
+                const int col = (k * SNT + t) * 8;
+                if (col < n) {
+                    const float* vv = v[h][k];
+                    *reinterpret_cast<uint2*>(q + row * 2 * int64_t(n) + h * n + col) =
+                        make_uint2(cvt_e4m3x4(vv[0] * y, vv[1] * y, vv[2] * y, vv[3] * y),
+                                   cvt_e4m3x4(vv[4] * y, vv[5] * y, vv[6] * y, vv[7] * y));
+                }
+            }
+    }
+    flush();
+}
+
+// emax [E, 2n] (column maxima) -> column scales in place
+__global__ void __launch_bounds__(256)
+scale_from_max_kernel(float* __restrict__ m, int64_t count, int round_scale) {
+    const int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x;
+    if (i < count) m[i] = scale_from_amax(m[i], round_scale != 0);
+}
+
+// transposed codes: thread = one padded row (expert e, local row j < pad32(c_e)), 8 columns of each half
+template <typename T>
+__global__ void __launch_bounds__(128)
+smooth_batch_bwd_cols_kernel(const T* __restrict__ g, const T* __restrict__ x, const void* __restrict__ w, int w_dtype,
+                             const float* __restrict__ tsmooth, const float* __restrict__ tscale,
+                             const void* __restrict__ counts, int counts_i64, int E, int n, uint8_t* __restrict__ qt,
+                             int reverse) {
+    extern __shared__ int64_t segs[];      // [E + 1] prefix of the counts, then [E + 1] of the padded counts
+    int64_t* seg = segs;
+    int64_t* pseg = segs + E + 1;
+    if (threadIdx.x == 0) {
+        fill_prefix(seg, counts, counts_i64, E, 1);
+        fill_prefix(pseg, counts, counts_i64, E, 32);
+    }
+    __syncthreads();
+    const int64_t p = int64_t(blockIdx.x) * 128 + threadIdx.x;
+    if (p >= pseg[E]) return;
+    const int e = find_seg(pseg, E, p);
+    const int64_t j = p - pseg[e];                 // local row, may be padding
+    const int64_t ce = seg[e + 1] - seg[e], cpad = pseg[e + 1] - pseg[e];
+    const int col = int(blockIdx.y) * 8;
+    uint8_t* base = qt + 2 * int64_t(n) * pseg[e];
+    uint32_t codes[8];
+    if (j < ce) {
+        const int64_t row = seg[e] + j;
+        float gg[8], x1[8], x2[8], d1[8], d2[8];
+        ld8(g + row * n + col, gg);
+        ld8(x + row * 2 * int64_t(n) + col, x1);
+        ld8(x + row * 2 * int64_t(n) + n + col, x2);
+        swiglu_grad8(gg, x1, x2, d1, d2);
+        const float wr = load_scalar(w, w_dtype, row);
+        const float ts = tsmooth[row];
+        const float* tsc = tscale + int64_t(e) * 2 * n;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float a0 = d1[k] * wr, b0 = d2[k] * wr;
+            const float a = reverse ? a0 * ts : __fdiv_rn(a0, fmaxf(ts, kScaleFloor));
+            const float b = reverse ? b0 * ts : __fdiv_rn(b0, fmaxf(ts, kScaleFloor));
+            codes[k] = cvt_e4m3x2(a * rcp_approx(tsc[col + k]), b * rcp_approx(tsc[n + col + k]));
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) codes[k] = 0u;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        base[int64_t(col + k) * cpad + j] = uint8_t(codes[k]);
+        base[int64_t(n + col + k) * cpad + j] = uint8_t(codes[k] >> 8);
+    }
+}
+
 // maxs[c] = max over the per-CTA rows of the calibration scratch
 __global__ void __launch_bounds__(256)
 colmax_reduce_kernel(const float* __restrict__ partial, int parts, int n, float* __restrict__ maxs) {
@@ -497,6 +685,51 @@ int smooth_quant_silu_bwd(const void* g, const void* x, const float* smooth, con
     else LH_SBWD(__nv_bfloat16);
 #undef LH_SBWD
     return check_launch("smooth_bwd_cols_kernel");
+}
+
+// padded_rows = sum_e pad32(counts[e]) (the caller sized dxt_q from its host copy of the counts).
+// dxt_scale [E, 2n] doubles as the buffer of the column maxima.
+int smooth_quant_batch_bwd(const void* g, const void* x, const void* w, int dtype, int w_dtype, const float* smooth,
+                           const float* tsmooth, const void* counts, int counts_type, int E, int64_t M, int64_t n,
+                           int64_t padded_rows, void* q, float* scale, void* dw, void* qt, float* tscale,
+                           int round_scale, int reverse, cudaStream_t stream) {
+    const char* what = "batch_silu_smoothquant_bwd";
+    if (dtype != LH_BF16 && dtype != LH_F16 && dtype != LH_F32) return fail_arg("%s: dtype must be bf16, f16 or f32", what);
+    if (w_dtype != LH_BF16 && w_dtype != LH_F16 && w_dtype != LH_F32) return fail_arg("%s: weight dtype must be bf16, f16 or f32", what);
+    if (counts_type != LH_I32 && counts_type != LH_I64) return fail_arg("%s: counts must be int32 or int64", what);
+    if (M < 0 || n <= 0 || n > 4096 || (n % 8) != 0 || E <= 0 || E > 2048 || padded_rows < M)
+        return fail_arg("%s: need 0 < n <= 4096, n %% 8 == 0, 0 < E <= 2048, padded_rows >= M (M=%lld n=%lld E=%d)", what, (long long)M, (long long)n, E);
+    if (!tscale) return fail_arg("%s: NULL pointer", what);
+    {
+        const cudaError_t e = cudaMemsetAsync(tscale, 0, size_t(E) * size_t(2 * n) * 4, stream);
+        if (e != cudaSuccess) { set_error("cudaMemsetAsync: %s", cudaGetErrorString(e)); return int(e); }
+    }
+    if (M == 0) return LH_OK;     // upstream returns zero scales when there is no row at all
+    if (!g || !x || !w || !smooth || !tsmooth || !counts || !q || !scale || !dw || !qt) return fail_arg("%s: NULL pointer", what);
+    if ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(smooth) |
+         reinterpret_cast<uintptr_t>(q)) & 15)
+        return fail_arg("%s: pointers must be 16-byte aligned", what);
+    const int i64 = counts_type == LH_I64;
+    int64_t grid = int64_t(sm_count()) * 2;
+    if (grid > M) grid = M;
+    const dim3 cgrid(unsigned((padded_rows + 127) / 128), unsigned(n / 8));
+    const size_t smem1 = size_t(E + 1) * 8, smem2 = 2 * smem1;
+    const int64_t cnt = int64_t(E) * 2 * n;
+#define LH_SBB(T)                                                                                                      \
+    do {                                                                                                               \
+        smooth_batch_bwd_rows_kernel<T><<<unsigned(grid), SNT, smem1, stream>>>(static_cast<const T*>(g), static_cast<const T*>(x), \
+            w, w_dtype, smooth, tsmooth, counts, i64, E, M, int(n), static_cast<uint8_t*>(q), scale, dw, tscale, round_scale, reverse); \
+        if (int rc = check_launch("smooth_batch_bwd_rows_kernel")) return rc;                                          \
+        scale_from_max_kernel<<<unsigned((cnt + 255) / 256), 256, 0, stream>>>(tscale, cnt, round_scale);             \
+        if (int rc = check_launch("scale_from_max_kernel")) return rc;                                                 \
+        smooth_batch_bwd_cols_kernel<T><<<cgrid, 128, smem2, stream>>>(static_cast<const T*>(g), static_cast<const T*>(x), w, w_dtype, \
+            tsmooth, tscale, counts, i64, E, int(n), static_cast<uint8_t*>(qt), reverse);                              \
+    } while (0)
+    if (dtype == LH_F16) LH_SBB(__half);
+    else if (dtype == LH_F32) LH_SBB(float);
+    else LH_SBB(__nv_bfloat16);
+#undef LH_SBB
+    return check_launch("smooth_batch_bwd_cols_kernel");
 }
 
 int64_t smooth_quant_scratch(int64_t n) { return int64_t(kSmoothMaxCtas) * n * 4; }

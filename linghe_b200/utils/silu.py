@@ -259,3 +259,40 @@ def triton_silu_and_smooth_quant_backward(g, x, smooth_scale=None, transpose_smo
               _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale), _lib.ptr(scratch), nbytes, int(bool(round_scale)),
               int(bool(reverse)))
     return dx, dx_scale, transpose_dx, transpose_dx_scale
+
+
+def triton_batch_weighted_silu_and_smooth_quant_backward(g, x, weight, counts, smooth_scale=None,
+                                                         transpose_smooth_scale=None, splits=None, reverse=True,
+                                                         round_scale=False):
+    """Per-expert weighted SwiGLU backward + smooth quantisation on both axes
+    (linghe/utils/silu.py:2126).
+
+    Returns (dx e4m3 [M,2n], dx_scale f32 [M], dw like weight, transpose_dx e4m3 flat
+    [2n * sum_e pad32(splits[e])] -- expert e's [2n, pad32(c_e)] block after those before it, zero
+    codes in the padding --, transpose_dx_scale f32 [E, 2n]).  `splits` (host list of the counts)
+    sizes the flat buffer.  Upstream asserts `round_scale`; both settings work here."""
+    assert g.is_contiguous() and x.is_contiguous() and weight.is_contiguous()
+    assert smooth_scale is not None and transpose_smooth_scale is not None
+    assert smooth_scale.is_contiguous() and transpose_smooth_scale.is_contiguous()
+    assert splits is not None, "batch mode need splits to launch kernels"
+    M, N = x.shape
+    n = N // 2
+    n_expert = counts.shape[0]
+    assert N % 16 == 0 and n <= 4096
+    assert smooth_scale.numel() == n_expert * N and transpose_smooth_scale.numel() == M and weight.numel() == M
+    device = x.device
+    if smooth_scale.dtype != torch.float32:
+        smooth_scale = smooth_scale.float()
+    if transpose_smooth_scale.dtype != torch.float32:
+        transpose_smooth_scale = transpose_smooth_scale.float()
+    dx = torch.empty((M, N), device=device, dtype=E4M3)
+    dx_scale = torch.empty((M,), device=device, dtype=torch.float32)
+    dw = torch.empty_like(weight)
+    s = sum((int(c) + 31) // 32 for c in splits) * 32
+    transpose_dx = torch.empty((N * s,), device=device, dtype=E4M3)
+    transpose_dx_scale = torch.empty((n_expert, N), device=device, dtype=torch.float32)
+    _lib.call("lh_batch_silu_smoothquant_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
+              _lib.dtype_code(weight), _lib.ptr(smooth_scale), _lib.ptr(transpose_smooth_scale), _lib.ptr(counts),
+              _lib.itype_code(counts), n_expert, M, n, s, _lib.ptr(dx), _lib.ptr(dx_scale), _lib.ptr(dw),
+              _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale), int(bool(round_scale)), int(bool(reverse)))
+    return dx, dx_scale, dw, transpose_dx, transpose_dx_scale

@@ -263,6 +263,41 @@ def silu_and_smooth_quant_backward(g, x, smooth_scale, transpose_smooth_scale, r
     return q, s, qt, st
 
 
+def batch_weighted_silu_and_smooth_quant_backward(g, x, weight, counts, smooth_scales, transpose_smooth_scale,
+                                                  round_scale: bool = True, reverse: bool = False):
+    """``torch_batch_weighted_silu_and_smooth_quant_backward`` (tests/test_silu.py:202-256): dx and
+    dw by autograd in float32; per expert smooth_quant of its rows with smooth_scales[e] and of its
+    transposed block, zero-padded to a multiple of 32 rows, with its slice of
+    transpose_smooth_scale.  Returns (dx codes [R,2n], dx scale [R], dw float32 [R,1], flat
+    transposed codes, transposed scales [E, 2n]).  An expert without rows contributes no codes and
+    the floor scale."""
+    counts = [int(c) for c in (counts.tolist() if hasattr(counts, "tolist") else counts)]
+    dx, dw = weighted_silu_backward(g, x, weight)
+    N = x.shape[1]
+    qs, scales, qts, qtscales = [], [], [], []
+    s = 0
+    for e, c in enumerate(counts):
+        q, sc, _ = smooth_quant(dx[s:s + c], smooth_scales[e], reverse, round_scale)
+        qs.append(q)
+        scales.append(sc)
+        if c > 0:
+            dxt = dx[s:s + c].t().contiguous()
+            ts = transpose_smooth_scale[s:s + c].float()
+            pad = (c + 31) // 32 * 32 - c
+            if pad:
+                dxt = torch.nn.functional.pad(dxt, (0, pad, 0, 0))
+                ts = torch.nn.functional.pad(ts, (0, pad))
+            qt, tsc, _ = smooth_quant(dxt, ts, reverse, round_scale)
+            qts.append(qt.reshape(-1))
+            qtscales.append(tsc)
+        else:
+            floor = torch.full((N,), SCALE_FLOOR)
+            qtscales.append(_pow2_ceil(floor) if round_scale else floor)
+        s += c
+    qt_flat = torch.cat(qts, 0) if qts else torch.empty((0,), dtype=torch.float8_e4m3fn)
+    return torch.cat(qs, 0), torch.cat(scales, 0), dw, qt_flat, torch.stack(qtscales, 0)
+
+
 def batch_weighted_silu_and_smooth_quant_forward(x, weight, counts, smooth_scales, round_scale: bool = False,
                                                  reverse: bool = False):
     """``torch_batch_weighted_silu_and_smooth_quant_forward`` (tests/test_silu.py:126-160): per

@@ -291,6 +291,23 @@ def main():
                                                                  round_scale=rs, reverse=rev)
         tag = f"bwd_r{int(rs)}v{int(rev)}"
         out[tag + "_q"], out[tag + "_s"], out[tag + "_qt"], out[tag + "_st"] = u8(q), f32(sc), u8(qt), f32(sct)
+    # per-expert backward: upstream's torch_batch_weighted_silu_and_smooth_quant_backward
+    # (tests/test_silu.py:202-256); counts that are not multiples of 32 exercise the padding
+    bc = [24, 8, 40, 16]
+    gbb_ = (0.1 * torch.randn((sum(bc), 128), generator=gs)).to(torch.bfloat16)
+    xbb_ = bf16_randn(gs, (sum(bc), 256))
+    wbb_ = torch.randn((sum(bc), 1), generator=gs)
+    sbb_ = 1 + 10 * torch.rand((len(bc), 256), generator=gs)
+    tbb_ = 1 + 10 * torch.rand((sum(bc),), generator=gs)
+    out["bbwd_g"], out["bbwd_x"], out["bbwd_w"] = u16(gbb_), u16(xbb_), f32(wbb_)
+    out["bbwd_smooth"], out["bbwd_tsmooth"] = f32(sbb_), f32(tbb_)
+    out["bbwd_counts"] = np.asarray(bc, dtype=np.int64)
+    for rs, rev in ((True, False), (True, True), (False, False)):
+        q, sc, dw, qt, sct = TS.torch_batch_weighted_silu_and_smooth_quant_backward(
+            gbb_, xbb_, wbb_, bc, smooth_scales=sbb_, transpose_smooth_scale=tbb_, round_scale=rs, reverse=rev)
+        tag = f"bbwd_r{int(rs)}v{int(rev)}"
+        out[tag + "_q"], out[tag + "_s"], out[tag + "_qt"], out[tag + "_st"] = u8(q), f32(sc), u8(qt), f32(sct)
+        out["bbwd_dw"] = f32(dw)
     np.savez_compressed(os.path.join(HERE, "smooth.npz"), **out)
     for f in ("quant", "norm", "silu", "batch", "permute", "router", "fp8gemm", "route", "fp8gemm_bb", "smooth"):
         p = os.path.join(HERE, f + ".npz")

@@ -276,3 +276,20 @@ def test_smooth_quant_backward_recipe(rs, rev):
     assert_scales_close(s, torch.from_numpy(G[tag + "_s"]), "dx scale") if not rs else None
     assert_codes_close(qt, fp8(G[tag + "_qt"]), "dxT q")
     assert tuple(qt.shape) == (x.shape[1], x.shape[0]) and tuple(st.shape) == (x.shape[1],)
+
+
+@pytest.mark.parametrize("rs,rev", [(1, 0), (1, 1), (0, 0)])
+def test_batch_smooth_quant_backward_recipe(rs, rev):
+    G = golden("smooth")
+    g, x, w = bf16(G["bbwd_g"]), bf16(G["bbwd_x"]), torch.from_numpy(G["bbwd_w"])
+    sm, tsm = torch.from_numpy(G["bbwd_smooth"]), torch.from_numpy(G["bbwd_tsmooth"])
+    counts = [int(c) for c in G["bbwd_counts"]]
+    q, s, dw, qt, st = O.batch_weighted_silu_and_smooth_quant_backward(g, x, w, counts, sm, tsm, bool(rs), bool(rev))
+    tag = f"bbwd_r{rs}v{rev}"
+    assert_codes_close(q, fp8(G[tag + "_q"]), "dx q")
+    assert_codes_close(qt, fp8(G[tag + "_qt"]), "dxT q")
+    if not rs:
+        assert_scales_close(s, torch.from_numpy(G[tag + "_s"]), "dx scale")
+        assert_scales_close(st.reshape(-1), torch.from_numpy(G[tag + "_st"]).reshape(-1), "dxT scale")
+    assert_rel_close(dw, torch.from_numpy(G["bbwd_dw"]), "dw", 1e-5)
+    assert qt.numel() == x.shape[1] * sum((c + 31) // 32 * 32 for c in counts)
