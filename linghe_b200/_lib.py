@@ -114,6 +114,21 @@ def host():
     return _host
 
 
+_DT_CODE = {torch.float8_e4m3fn: 0, torch.float32: 1, torch.bfloat16: 2, torch.float16: 3, torch.uint8: 4,
+            torch.int32: 5, torch.int64: 6}
+
+
+def empties(ref: torch.Tensor, *specs):
+    """Uninitialised tensors on the device of `ref`, one per (shape, dtype) in `specs`.  With the
+    host module they come from ONE call into C++ (a torch.empty from Python costs about 2.4 us, which
+    for the four or five outputs of a wrapper is more than a small kernel takes)."""
+    h = host()
+    if h is not None:
+        return h.empty_many(ref, [(shape, _DT_CODE[dt]) for shape, dt in specs])
+    dev = ref.device
+    return [torch.empty(shape, device=dev, dtype=dt) for shape, dt in specs]
+
+
 def last_error() -> str:
     return load().lh_last_error().decode()
 
@@ -133,7 +148,8 @@ def itype_code(t: torch.Tensor) -> int:
 
 
 def ptr(t):
-    return None if t is None else t.data_ptr()
+    """device address of a tensor, 0 for None (a NULL pointer at the C ABI)"""
+    return 0 if t is None else t.data_ptr()
 
 
 def _check_device(idx: int):
@@ -166,7 +182,12 @@ def call(name: str, ref: torch.Tensor, *args):
         raise RuntimeError("linghe_b200 runs on CUDA tensors only (no CPU fallback)")
     fn = _fn_cache.get(name)
     if fn is None:
-        fn = _fn_cache[name] = getattr(load(), name)
+        # the generated pybind11 binding of the same C function when the host module is there
+        # (about 1 us per call), the ctypes one otherwise (about 4 us)
+        h = host()
+        fn = _fn_cache[name] = getattr(h, name, None) if h is not None else None
+        if fn is None:
+            fn = _fn_cache[name] = getattr(load(), name)
     idx = dev.index
     if idx not in _checked_devices:
         _check_device(idx)
@@ -184,7 +205,8 @@ def call(name: str, ref: torch.Tensor, *args):
 
 
 def scratch_bytes(what: str, rows: int, cols: int) -> int:
-    v = load().lh_scratch_bytes(what.encode(), rows, cols)
+    h = host()
+    v = h.lh_scratch_bytes(what, rows, cols) if h is not None else load().lh_scratch_bytes(what.encode(), rows, cols)
     if v < 0:
         raise RuntimeError(f"unknown scratch kind {what}")
     return v

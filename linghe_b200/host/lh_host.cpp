@@ -11,9 +11,12 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <cstdint>
 #include <optional>
 #include <string>
 #include <tuple>
+#include <utility>
+#include <vector>
 
 #include "linghe_b200.h"
 
@@ -127,10 +130,31 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> silu_and_block_quant_
     return {*out, *scale, tq, ts};
 }
 
+// Several uninitialised tensors on the device of `ref` from one call: specs = [(shape, code), ...]
+// with code 0 e4m3, 1 float32, 2 bfloat16, 3 float16, 4 uint8, 5 int32, 6 int64.  One
+// Python -> C++ transition instead of one per torch.empty.
+std::vector<at::Tensor> empty_many(const at::Tensor& ref, const std::vector<std::pair<std::vector<int64_t>, int>>& specs) {
+    static const at::ScalarType kinds[] = {at::kFloat8_e4m3fn, at::kFloat, at::kBFloat16, at::kHalf, at::kByte, at::kInt, at::kLong};
+    if (!ref.is_cuda()) throw std::runtime_error("linghe_b200 runs on CUDA tensors only (no CPU fallback)");
+    std::vector<at::Tensor> out;
+    out.reserve(specs.size());
+    const c10::cuda::OptionalCUDAGuard guard(ref.device());
+    for (const auto& sp : specs) {
+        if (sp.second < 0 || sp.second > 6) raise_assert("empty_many: unknown dtype code");
+        out.push_back(at::empty(sp.first, ref.options().dtype(kinds[sp.second])));
+    }
+    return out;
+}
+
+uintptr_t current_stream(int device) { return reinterpret_cast<uintptr_t>(c10::cuda::getCurrentCUDAStream(device).stream()); }
+
 }  // namespace
 
 PYBIND11_MODULE(_lh_host, m) {
     m.doc() = "C++ argument handling for the hottest linghe_b200 wrappers (allocation + C-ABI call)";
+    m.def("empty_many", &empty_many);
+    m.def("current_stream", &current_stream);
+#include "lh_host_bindings.inc"
     m.def("rms_norm_and_block_quant_forward", &rms_norm_and_block_quant_forward);
     m.def("silu_and_block_quant_forward", &silu_and_block_quant_forward);
 }

@@ -21,8 +21,7 @@ def triton_block_quant(x, block_size=128, round_scale=False):
     assert x.is_contiguous()
     assert block_size == 128, "only 128x128 blocks are implemented"
     M, N = x.size()
-    y = torch.empty((M, N), dtype=E4M3, device=x.device)
-    s = torch.empty(M // block_size, N // block_size, dtype=torch.float32, device=x.device)
+    y, s = _lib.empties(x, ((M, N), E4M3), ((M // block_size, N // block_size), torch.float32))
     _lib.call("lh_block_quant", x, _lib.ptr(x), _lib.dtype_code(x), M, N, _lib.ptr(y), _lib.ptr(s),
               int(bool(round_scale)))
     return y, s
@@ -37,11 +36,8 @@ def triton_blockwise_quant(x, round_scale=False, output_mode=2):
     uninitialised, as upstream."""
     M, N = x.shape
     assert M % 16 == 0 and x.is_contiguous()
-    device = x.device
-    x_q = torch.empty((M, N), device=device, dtype=E4M3)
-    x_scale = torch.empty((N // 128, M), device=device, dtype=torch.float32)
-    xt_q = torch.empty((N, M), device=device, dtype=E4M3)
-    xt_scale = torch.empty((_cdiv(M, 128), N), device=device, dtype=torch.float32)
+    x_q, x_scale, xt_q, xt_scale = _lib.empties(x, ((M, N), E4M3), ((N // 128, M), torch.float32), ((N, M), E4M3),
+                                               ((_cdiv(M, 128), N), torch.float32))
     _lib.call("lh_blockwise_quant", x, _lib.ptr(x), _lib.dtype_code(x), M, N, _lib.ptr(x_q),
               _lib.ptr(x_scale), _lib.ptr(xt_q), _lib.ptr(xt_scale), int(bool(round_scale)), int(output_mode))
     return x_q, x_scale, xt_q, xt_scale
@@ -54,11 +50,9 @@ def triton_batch_blockwise_quant(xs, token_count_per_expert, splits, round_scale
     M, N = xs.shape
     n_experts = token_count_per_expert.size(0)
     device = xs.device
-    x_q = torch.empty((M, N), device=device, dtype=E4M3)
-    x_scale = torch.empty((M * N // 128,), device=device, dtype=torch.float32)
-    xt_q = torch.empty((M * N,), device=device, dtype=E4M3)
-    blocks = sum(_cdiv(int(c), 128) for c in splits)
-    xt_scale = torch.empty((blocks * N,), device=device, dtype=torch.float32)
+    blocks = sum([(int(c) + 127) // 128 for c in splits])
+    x_q, x_scale, xt_q, xt_scale = _lib.empties(xs, ((M, N), E4M3), ((M * N // 128,), torch.float32), ((M * N,), E4M3),
+                                               ((blocks * N,), torch.float32))
     if M == 0:
         return x_q, x_scale, xt_q, xt_scale
     assert token_count_per_expert.is_cuda and token_count_per_expert.is_contiguous()

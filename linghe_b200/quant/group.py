@@ -15,8 +15,7 @@ def triton_group_quant(x, dtype=torch.float8_e4m3fn, group_size=128, round_scale
     assert group_size == 128 and dtype == torch.float8_e4m3fn
     assert N % group_size == 0
     assert x.is_contiguous()
-    y = torch.empty((M, N), device=x.device, dtype=dtype)
-    s = torch.empty(M, N // group_size, device=x.device, dtype=torch.float32)
+    y, s = _lib.empties(x, ((M, N), dtype), ((M, N // group_size), torch.float32))
     _lib.call("lh_group_quant", x, _lib.ptr(x), _lib.dtype_code(x), M, N, _lib.ptr(y), _lib.ptr(s),
               int(bool(round_scale)))
     return y, s

@@ -28,12 +28,13 @@ def triton_batch_block_pad_permute_with_indices(xs, token_count_per_expert, indi
     n_experts = token_count_per_expert.size(0)
     M = indices.shape[0]
     device = xs.device
-    x_q = torch.empty((M, N), device=device, dtype=E4M3)
-    x_scale = torch.empty((M, N // 128), device=device, dtype=torch.float32)
-    blocks = sum((int(c) + 127) // 128 for c in splits)
-    xt_q = torch.empty((M, N), device=device, dtype=E4M3)
-    xt_scale = torch.empty((blocks, N), device=device, dtype=torch.float32)
-    prob_output = torch.empty((M,), device=device, dtype=probs.dtype) if probs is not None else None
+    blocks = sum([(int(c) + 127) // 128 for c in splits])
+    specs = [((M, N), E4M3), ((M, N // 128), torch.float32), ((M, N), E4M3), ((blocks, N), torch.float32)]
+    if probs is not None:
+        specs.append(((M,), probs.dtype))
+    outs = _lib.empties(xs, *specs)
+    x_q, x_scale, xt_q, xt_scale = outs[:4]
+    prob_output = outs[4] if probs is not None else None
     if m == 0:
         return x_q, x_scale, xt_q, xt_scale, prob_output
     assert indices.is_contiguous() and token_count_per_expert.is_contiguous()

@@ -41,10 +41,8 @@ def triton_rms_norm_backward(grad_output, x, w, eps=1e-6, rms=None):
     assert grad_output.is_contiguous() and x.is_contiguous()
     M, n = _rows_cols(x)
     assert n <= 8192
-    dx = torch.empty_like(x)
-    dw = torch.empty((n,), dtype=torch.float32, device=x.device)
     nbytes = _lib.scratch_bytes("rmsnorm_bwd", M, n)
-    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x.device)
+    dx, dw, scratch = _lib.empties(x, (tuple(x.shape), x.dtype), ((n,), torch.float32), ((nbytes,), torch.uint8))
     _lib.call("lh_rmsnorm_bwd", x, _lib.ptr(grad_output), _lib.ptr(x), _lib.ptr(w), _lib.ptr(rms),
               _lib.dtype_code(x), M, n, float(eps), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(scratch), nbytes)
     return dx, dw
@@ -90,8 +88,8 @@ def triton_rms_norm_and_block_quant_forward(
     else:
         rms = torch.empty((M,), dtype=torch.float32, device=device)
     _lib.call("lh_rmsnorm_blockquant_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x), M, n,
-              float(eps), _lib.ptr(out) if output_mode != 1 else None,
-              _lib.ptr(scale) if output_mode != 1 else None, _lib.ptr(rms), _lib.ptr(transpose_output),
+              float(eps), _lib.ptr(out) if output_mode != 1 else 0,
+              _lib.ptr(scale) if output_mode != 1 else 0, _lib.ptr(rms), _lib.ptr(transpose_output),
               _lib.ptr(transpose_scale), int(bool(round_scale)), int(output_mode))
     if transpose_output is None:
         # mode 0 does not write the transposed pair; upstream still returns it (uninitialised), so it is
@@ -124,17 +122,13 @@ def triton_rms_norm_fp32_gemm_block_quant_forward(
     assert K2 == K
     assert M % 128 == 0 and K % 128 == 0 and N % 128 == 0
     device = x.device
-    y = torch.empty(M, K, dtype=x.dtype, device=device)
     if rms is None:
         assert output_mode == 0
         rms = torch.empty(M, dtype=torch.float32, device=device)
-    logits = torch.empty(M, N, dtype=torch.float32, device=device)
-    x_q = torch.empty((M, K), device=device, dtype=E4M3)
-    x_s = torch.empty((K // 128, M), device=device, dtype=torch.float32)
-    xt_q = torch.empty((K, M), device=device, dtype=E4M3)
-    xt_s = torch.empty((M // 128, K), device=device, dtype=torch.float32)
     nbytes = _lib.scratch_bytes("rmsnorm_gemm", N, K) if output_mode == 0 else 0
-    scratch = torch.empty((max(nbytes, 16),), dtype=torch.uint8, device=device)
+    y, logits, x_q, x_s, xt_q, xt_s, scratch = _lib.empties(
+        x, ((M, K), x.dtype), ((M, N), torch.float32), ((M, K), E4M3), ((K // 128, M), torch.float32), ((K, M), E4M3),
+        ((M // 128, K), torch.float32), ((max(nbytes, 16),), torch.uint8))
     _lib.call("lh_rmsnorm_gemm_blockquant_fwd", x, _lib.ptr(x), _lib.ptr(norm_weight), _lib.ptr(route_weight),
               _lib.dtype_code(x), M, K, N, float(eps), _lib.ptr(y), _lib.ptr(rms), _lib.ptr(logits), _lib.ptr(x_q),
               _lib.ptr(x_s), _lib.ptr(xt_q), _lib.ptr(xt_s), int(bool(round_scale)), int(output_mode),
@@ -153,14 +147,10 @@ def rms_norm_backward_and_block_quant(grad_output, x, w, eps=1e-6, rms=None, rou
     M, n = _rows_cols(x)
     assert n <= 8192 and M % 16 == 0
     device = x.device
-    dx = torch.empty_like(x)
-    dw = torch.empty((n,), dtype=torch.float32, device=device)
-    dy_q = torch.empty((M, n), device=device, dtype=E4M3)
-    dy_s = torch.empty((n // 128, M), device=device, dtype=torch.float32)
-    dyt_q = torch.empty((n, M), device=device, dtype=E4M3)
-    dyt_s = torch.empty(((M + 127) // 128, n), device=device, dtype=torch.float32)
     nbytes = _lib.scratch_bytes("rmsnorm_bwd_blockquant", M, n)
-    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
+    dx, dw, dy_q, dy_s, dyt_q, dyt_s, scratch = _lib.empties(
+        x, (tuple(x.shape), x.dtype), ((n,), torch.float32), ((M, n), E4M3), ((n // 128, M), torch.float32),
+        ((n, M), E4M3), (((M + 127) // 128, n), torch.float32), ((nbytes,), torch.uint8))
     _lib.call("lh_rmsnorm_bwd_blockquant", x, _lib.ptr(grad_output), _lib.ptr(x), _lib.ptr(w), _lib.ptr(rms),
               _lib.dtype_code(x), M, n, float(eps), _lib.ptr(dx), _lib.ptr(dw), _lib.ptr(dy_q), _lib.ptr(dy_s),
               _lib.ptr(dyt_q), _lib.ptr(dyt_s), int(bool(round_scale)), _lib.ptr(scratch), nbytes)
@@ -205,6 +195,6 @@ def triton_rms_norm_and_smooth_quant_forward(
         nbytes = _lib.scratch_bytes("smooth_quant", M, N)
         scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
     _lib.call("lh_rmsnorm_smoothquant_fwd", x, _lib.ptr(x), _lib.ptr(weight), _lib.ptr(smooth_scale), _lib.dtype_code(x),
-              M, N, float(eps), _lib.ptr(out), _lib.ptr(scale), _lib.ptr(rms) if output_rms else None, _lib.ptr(maxs),
+              M, N, float(eps), _lib.ptr(out), _lib.ptr(scale), _lib.ptr(rms) if output_rms else 0, _lib.ptr(maxs),
               _lib.ptr(scratch), nbytes, int(bool(round_scale)))
     return out, scale, maxs, rms

@@ -41,8 +41,9 @@ def triton_weighted_silu_backward(g: torch.Tensor, x: torch.Tensor, weight: Opti
     dw = None
     if weight is not None:
         assert weight.is_contiguous()
-        dw = torch.empty(weight.shape, device=x.device, dtype=weight.dtype)
-    dx = torch.empty((M, N), device=x.device, dtype=x.dtype)
+        dx, dw = _lib.empties(x, ((M, N), x.dtype), (tuple(weight.shape), weight.dtype))
+    else:
+        dx = torch.empty((M, N), device=x.device, dtype=x.dtype)
     _lib.call("lh_weighted_silu_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
               _lib.dtype_code(weight) if weight is not None else _lib.F32, M, N // 2, _lib.ptr(dx), _lib.ptr(dw))
     return dx, dw
@@ -90,11 +91,12 @@ def triton_silu_and_block_quant_backward(g, x, round_scale=False, return_bf16=Fa
     n = N // 2
     device = x.device
     assert M % 128 == 0 and N % 256 == 0
-    dx = torch.empty((M, N), device=device, dtype=E4M3)
-    dx_scale = torch.empty((N // 128, M), device=device, dtype=torch.float32)
-    transpose_dx = torch.empty((N, M), device=device, dtype=E4M3)
-    transpose_dx_scale = torch.empty((_cdiv(M, 128), N), device=device, dtype=torch.float32)
-    dx_hp = torch.empty((M, N), device=device, dtype=x.dtype) if return_bf16 else None
+    specs = [((M, N), E4M3), ((N // 128, M), torch.float32), ((N, M), E4M3), ((_cdiv(M, 128), N), torch.float32)]
+    if return_bf16:
+        specs.append(((M, N), x.dtype))
+    outs = _lib.empties(x, *specs)
+    dx, dx_scale, transpose_dx, transpose_dx_scale = outs[:4]
+    dx_hp = outs[4] if return_bf16 else None
     _lib.call("lh_silu_blockquant_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.dtype_code(x), M, n, _lib.ptr(dx),
               _lib.ptr(dx_scale), _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale), _lib.ptr(dx_hp),
               int(bool(round_scale)))
@@ -121,9 +123,8 @@ def triton_batch_weighted_silu_and_block_quant_forward(
         out = torch.empty((M, n), device=device, dtype=E4M3)
     if scale is None:
         scale = torch.empty((M, n // 128), device=device, dtype=torch.float32)
-    blocks = sum(_cdiv(int(c), 128) for c in splits)
-    transpose_output = torch.empty((M, n), device=device, dtype=E4M3)
-    transpose_scale = torch.empty((blocks, n), device=device, dtype=torch.float32)
+    blocks = sum([(int(c) + 127) // 128 for c in splits])
+    transpose_output, transpose_scale = _lib.empties(x, ((M, n), E4M3), ((blocks, n), torch.float32))
     if M == 0:
         return out, scale, transpose_output, transpose_scale
     assert counts.is_cuda and counts.is_contiguous()
@@ -144,17 +145,14 @@ def triton_batch_weighted_silu_and_block_quant_backward(g, x, weight, counts, sp
     assert g.is_contiguous() and x.is_contiguous() and weight.is_contiguous()
     assert splits is not None, "batch mode need splits to launch kernels"
     device = x.device
-    dx = torch.empty((M, N), device=device, dtype=E4M3)
-    dx_scale = torch.empty((M, N // 128), device=device, dtype=torch.float32)
-    s = sum(_cdiv(int(c), 128) for c in splits)
-    transpose_dx = torch.empty((M, N), device=device, dtype=E4M3)
-    transpose_dx_scale = torch.empty((s, N), device=device, dtype=torch.float32)
-    dw = torch.empty_like(weight)
+    s = sum([(int(c) + 127) // 128 for c in splits])
+    nbytes = M * (n // 128) * 4          # lh_scratch_bytes("batch_silu_bwd", M, n): the per-block dw partials
+    dx, dx_scale, transpose_dx, transpose_dx_scale, dw, scratch = _lib.empties(
+        x, ((M, N), E4M3), ((M, N // 128), torch.float32), ((M, N), E4M3), ((s, N), torch.float32),
+        (tuple(weight.shape), weight.dtype), ((nbytes,), torch.uint8))
     if s == 0:
         return dx, dx_scale, dw, transpose_dx, transpose_dx_scale
     assert counts.is_cuda and counts.is_contiguous()
-    nbytes = _lib.scratch_bytes("batch_silu_bwd", M, n)
-    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=device)
     _lib.call("lh_batch_silu_blockquant_bwd", x, _lib.ptr(g), _lib.ptr(x), _lib.ptr(weight), _lib.dtype_code(x),
               _lib.dtype_code(weight), _lib.ptr(counts), _lib.itype_code(counts), n_expert, M, n, _lib.ptr(dx),
               _lib.ptr(dx_scale), _lib.ptr(dw), _lib.ptr(transpose_dx), _lib.ptr(transpose_dx_scale),
