@@ -22,7 +22,7 @@ template <int SPANS, int NT, int MINB, bool WIDE, int RREG, int CREG>
 __global__ void __launch_bounds__(NT + 128, MINB)
 small_norm_bwd_duo_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
     constexpr int LEAD = 8;
-    __shared__ float wsum[2][2][NT / 32];
+    __shared__ __align__(16) float2 wsum[2][NT / 32];
     __shared__ __align__(16) float cq_cmax[8 * 128];
     __shared__ __align__(16) float cq_cs[128], cq_cy[128];
     __shared__ int walk_band;

@@ -135,9 +135,12 @@ __device__ __forceinline__ void col_quant_tile(const SmallParams& p, const uint8
 // kernel adds them in a fixed order.
 // The walk of one CTA's rows by its first NT threads.  BAR names the barrier of those threads (0 =
 // the whole CTA).  walk_band, when given, receives the band (row / 128) the walk has reached.
-template <int SPANS, int NT, bool WIDE, bool QDY, int BAR>
+// FULL: n is exactly SPANS * 16 * NT, so no thread ever has an empty span: the column tests and the
+// zero-fill of the load registers go away.  The two row sums travel as one float2 (packed adds,
+// 16-byte shared-memory reads), in the same order as two scalar reductions would take.
+template <int SPANS, int NT, bool WIDE, bool QDY, int BAR, bool FULL = false>
 __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_t* __restrict__ dy, float* __restrict__ partial,
-                                              float (*wsum)[2][NT / 32], volatile int* walk_band) {
+                                              float2 (*wsum)[NT / 32], volatile int* walk_band) {
     constexpr int SPAN = 16 * NT, NW = NT / 32;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     // gamma stays in registers for one span per thread; with two it is re-read (L1 hits) so that
@@ -152,22 +155,22 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
             return gam[i];
         } else {
             const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
-            return col < p.n ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
+            return (FULL || col < p.n) ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
         }
     };
     if constexpr (GAM_REG) {
 #pragma unroll
         for (int i = 0; i < 2 * SPANS; ++i) {
             const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
-            gam[i] = col < p.n ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
+            gam[i] = (FULL || col < p.n) ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
         }
     }
     auto fetch = [&](int64_t row) {
 #pragma unroll
         for (int i = 0; i < SPANS; ++i) {
             const int col = i * SPAN + t * 16;
-            xr[2 * i] = xr[2 * i + 1] = gr[2 * i] = gr[2 * i + 1] = make_uint4(0, 0, 0, 0);
-            if (row < p.M && col < p.n) {
+            if constexpr (!FULL) xr[2 * i] = xr[2 * i + 1] = gr[2 * i] = gr[2 * i + 1] = make_uint4(0, 0, 0, 0);
+            if (row < p.M && (FULL || col < p.n)) {   // past the last row nothing is loaded and nothing is used
                 const int64_t off = (row * p.n + col) * 2;
                 if constexpr (WIDE) {   // x, dy and dx are 32-byte aligned
                     ld_global_256(p.x + off, xr[2 * i], xr[2 * i + 1]);
@@ -200,17 +203,16 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
                 ss = fma2(x[j], x[j], ss);
             }
         }
-        float c = sc.x + sc.y, s = ss.x + ss.y;
+        float2 cs = make_float2(sc.x + sc.y, ss.x + ss.y);
 #pragma unroll
-        for (int d = 16; d >= 1; d >>= 1) {
-            c += __shfl_xor_sync(0xffffffffu, c, d);
-            s += __shfl_xor_sync(0xffffffffu, s, d);
-        }
-        if (lane == 0) { wsum[par][0][warp] = c; wsum[par][1][warp] = s; }
+        for (int d = 16; d >= 1; d >>= 1)
+            cs = add2(cs, make_float2(__shfl_xor_sync(0xffffffffu, cs.x, d), __shfl_xor_sync(0xffffffffu, cs.y, d)));
+        if (lane == 0) wsum[par][warp] = cs;
         role_sync<BAR, NT>();   // the buffer of the other parity was last read before the previous barrier
-        float ctot = 0.f, stot = 0.f;
+        float2 tot = wsum[par][0];
 #pragma unroll
-        for (int w = 0; w < NW; ++w) { ctot += wsum[par][0][w]; stot += wsum[par][1][w]; }
+        for (int w = 1; w < NW; ++w) tot = add2(tot, wsum[par][w]);
+        const float ctot = tot.x, stot = tot.y;
         const float r = p.reuse_rms ? p.rms[row] : rsqrt_nr(fmaf(stot, p.inv_n, p.eps));
         const float2 ncoef = splat2(-(r * r * r * ctot * p.inv_n));
         const float2 r2 = splat2(r);
@@ -245,7 +247,7 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
                 qs = scale_from_amax(amax, p.round_scale != 0);
                 qtiny = qs < 8.0e-28f && amax > 0.f;      // residual of the exact quotient could underflow
                 qny = -__frcp_rn(qs);
-                if ((t & 7) == 0 && col < p.n) p.s[int64_t(col >> 7) * p.M + row] = qs;
+                if ((t & 7) == 0 && (FULL || col < p.n)) p.s[int64_t(col >> 7) * p.M + row] = qs;
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -272,9 +274,9 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
                 }
             }
             if constexpr (QDY) {
-                if (col < p.n) *reinterpret_cast<uint4*>(p.q + row * p.n + col) = make_uint4(qc[0], qc[1], qc[2], qc[3]);
+                if (FULL || col < p.n) *reinterpret_cast<uint4*>(p.q + row * p.n + col) = make_uint4(qc[0], qc[1], qc[2], qc[3]);
             }
-            if (col < p.n) {
+            if (FULL || col < p.n) {
                 uint8_t* dst = p.y + (row * p.n + col) * 2;
                 if constexpr (WIDE) {
                     st_global_256(dst, make_uint4(o[0], o[1], o[2], o[3]), make_uint4(o[4], o[5], o[6], o[7]));
@@ -289,7 +291,7 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
 #pragma unroll
     for (int i = 0; i < SPANS; ++i) {
         const int col = i * SPAN + t * 16;
-        if (col < p.n) {
+        if (FULL || col < p.n) {
             float4* dst = reinterpret_cast<float4*>(partial + int64_t(blockIdx.x) * p.n + col);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
