@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(NT + 128, MINB)
 small_norm_bwd_duo_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
     constexpr int LEAD = 8;
     __shared__ __align__(16) float2 wsum[2][NT / 32];
+    __shared__ float4 gam_s[4 * SPANS * NT];
     __shared__ __align__(16) float cq_cmax[8 * 128];
     __shared__ __align__(16) float cq_cs[128], cq_cy[128];
     __shared__ int walk_band;
@@ -30,7 +31,7 @@ small_norm_bwd_duo_kernel(const __grid_constant__ SmallParams p, const uint8_t* 
     __syncthreads();
     if (threadIdx.x < NT) {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(RREG));
-        norm_bwd_walk<SPANS, NT, WIDE, true, 1>(p, dy, partial, wsum, &walk_band);
+        norm_bwd_walk<SPANS, NT, WIDE, true, 1>(p, dy, partial, wsum, &walk_band, gam_s);
     } else {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CREG));
         const int t = threadIdx.x - NT;

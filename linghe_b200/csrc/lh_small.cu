@@ -358,7 +358,8 @@ template <int SPANS, int NT, int MINB, bool WIDE, bool QDY, bool FULL = false>
 __global__ void __launch_bounds__(NT, MINB)
 small_norm_bwd_kernel(const __grid_constant__ SmallParams p, const uint8_t* __restrict__ dy, float* __restrict__ partial) {
     __shared__ __align__(16) float2 wsum[2][NT / 32];
-    norm_bwd_walk<SPANS, NT, WIDE, QDY, 0, FULL>(p, dy, partial, wsum, nullptr);
+    __shared__ float4 gam_s[4 * SPANS * NT];
+    norm_bwd_walk<SPANS, NT, WIDE, QDY, 0, FULL>(p, dy, partial, wsum, nullptr, gam_s);
 }
 
 // RMSNorm + 1x128 quantisation for long runs of wide rows: a persistent walk.  A CTA of 128

@@ -138,33 +138,35 @@ __device__ __forceinline__ void col_quant_tile(const SmallParams& p, const uint8
 // FULL: n is exactly SPANS * 16 * NT, so no thread ever has an empty span: the column tests and the
 // zero-fill of the load registers go away.  The two row sums travel as one float2 (packed adds,
 // 16-byte shared-memory reads), in the same order as two scalar reductions would take.
+// gam_s: 4 * SPANS * NT float4 of shared memory.  gamma sits there as float32 for the whole walk, laid
+// out so that a warp's 16-byte reads are 512 consecutive bytes: both passes read it with two
+// conflict-free LDS.128 per 8 elements instead of a global load and eight unpack operations (the
+// opcode counter showed 1.0 of the kernel's instructions per element and pass going into that).
 template <int SPANS, int NT, bool WIDE, bool QDY, int BAR, bool FULL = false>
 __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_t* __restrict__ dy, float* __restrict__ partial,
-                                              float2 (*wsum)[NT / 32], volatile int* walk_band) {
+                                              float2 (*wsum)[NT / 32], volatile int* walk_band, float4* gam_s) {
     constexpr int SPAN = 16 * NT, NW = NT / 32;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    // gamma stays in registers for one span per thread; with two it is re-read (L1 hits) so that
-    // three CTAs fit an SM without spills
-    constexpr bool GAM_REG = SPANS == 1;
-    uint4 xr[2 * SPANS], gr[2 * SPANS], gam[GAM_REG ? 2 * SPANS : 1];
+    uint4 xr[2 * SPANS], gr[2 * SPANS];
     float2 acc[8 * SPANS];
 #pragma unroll
     for (int i = 0; i < 8 * SPANS; ++i) acc[i] = make_float2(0.f, 0.f);
-    auto gamma_at = [&](int i) -> uint4 {     // i-th 16-byte chunk of this thread's gamma
-        if constexpr (GAM_REG) {
-            return gam[i];
-        } else {
-            const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
-            return (FULL || col < p.n) ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
-        }
-    };
-    if constexpr (GAM_REG) {
 #pragma unroll
-        for (int i = 0; i < 2 * SPANS; ++i) {
-            const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
-            gam[i] = (FULL || col < p.n) ? __ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)) : make_uint4(0, 0, 0, 0);
-        }
+    for (int i = 0; i < 2 * SPANS; ++i) {     // this thread's gamma: chunk i = 8 elements = float4 2 i and 2 i + 1
+        const int col = (i >> 1) * SPAN + t * 16 + (i & 1) * 8;
+        float2 v[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = make_float2(0.f, 0.f);
+        if (FULL || col < p.n) unpack8<__nv_bfloat16>(__ldg(reinterpret_cast<const uint4*>(p.gamma + int64_t(col) * 2)), v);
+        gam_s[(2 * i) * NT + t] = make_float4(v[0].x, v[0].y, v[1].x, v[1].y);
+        gam_s[(2 * i + 1) * NT + t] = make_float4(v[2].x, v[2].y, v[3].x, v[3].y);
     }
+    // every thread reads back only what it wrote itself: no barrier is needed
+    auto gamma_at = [&](int i, float2* w) {   // i-th 8-element chunk of this thread's gamma
+        const float4 a = gam_s[(2 * i) * NT + t], b = gam_s[(2 * i + 1) * NT + t];
+        w[0] = make_float2(a.x, a.y); w[1] = make_float2(a.z, a.w);
+        w[2] = make_float2(b.x, b.y); w[3] = make_float2(b.z, b.w);
+    };
     auto fetch = [&](int64_t row) {
 #pragma unroll
         for (int i = 0; i < SPANS; ++i) {
@@ -196,7 +198,7 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
             float2 x[4], g[4], w[4];
             unpack8<__nv_bfloat16>(xr[i], x);
             unpack8<__nv_bfloat16>(gr[i], g);
-            unpack8<__nv_bfloat16>(gamma_at(i), w);
+            gamma_at(i, w);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 sc = fma2(x[j], mul2(g[j], w[j]), sc);
@@ -254,7 +256,7 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
                 float2 x[4], g[4], w[4];
                 unpack8<__nv_bfloat16>(xc[2 * i + h], x);
                 unpack8<__nv_bfloat16>(gc[2 * i + h], g);
-                unpack8<__nv_bfloat16>(gamma_at(2 * i + h), w);
+                gamma_at(2 * i + h, w);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 d = fma2(ncoef, x[j], mul2(r2, mul2(g[j], w[j])));
