@@ -217,7 +217,10 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
         const float ctot = tot.x, stot = tot.y;
         const float r = p.reuse_rms ? p.rms[row] : rsqrt_nr(fmaf(stot, p.inv_n, p.eps));
         const float2 ncoef = splat2(-(r * r * r * ctot * p.inv_n));
-        const float2 r2 = splat2(r);
+        // QDY: dy is unpacked NEGATED in the second pass (the exact quotient wants -dy, and the sign
+        // flip is free in the widening); the dx and dgamma terms then take -r, which gives the same
+        // bits: (-r) * ((-g) * w) == r * (g * w) and ((x * (-g)) * (-r) == (x * g) * r exactly
+        const float2 r2 = splat2(QDY ? -r : r);
         // pass 2 on copies, so that the next row's loads can already land in xr / gr
         uint4 xc[2 * SPANS], gc[2 * SPANS];
 #pragma unroll
@@ -255,7 +258,12 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
             for (int h = 0; h < 2; ++h) {
                 float2 x[4], g[4], w[4];
                 unpack8<__nv_bfloat16>(xc[2 * i + h], x);
-                unpack8<__nv_bfloat16>(gc[2 * i + h], g);
+                if constexpr (QDY) {
+                    g[0] = bf16x2_to_neg_f2(gc[2 * i + h].x); g[1] = bf16x2_to_neg_f2(gc[2 * i + h].y);
+                    g[2] = bf16x2_to_neg_f2(gc[2 * i + h].z); g[3] = bf16x2_to_neg_f2(gc[2 * i + h].w);
+                } else {
+                    unpack8<__nv_bfloat16>(gc[2 * i + h], g);
+                }
                 gamma_at(2 * i + h, w);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -266,10 +274,10 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
                 if constexpr (QDY) {
                     float2 q[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) q[j] = quot_exact2(mul2(g[j], splat2(-1.f)), splat2(qs), splat2(qny));
+                    for (int j = 0; j < 4; ++j) q[j] = quot_exact2(g[j], splat2(qs), splat2(qny));   // g holds -dy
                     if (qtiny) {   // rare
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(g[j].x, qs), __fdiv_rn(g[j].y, qs));
+                        for (int j = 0; j < 4; ++j) q[j] = make_float2(__fdiv_rn(-g[j].x, qs), __fdiv_rn(-g[j].y, qs));
                     }
                     qc[2 * h] = cvt_e4m3x4(q[0].x, q[0].y, q[1].x, q[1].y);
                     qc[2 * h + 1] = cvt_e4m3x4(q[2].x, q[2].y, q[3].x, q[3].y);
