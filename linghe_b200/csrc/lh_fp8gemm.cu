@@ -9,7 +9,7 @@
 // block); the CUDA cores then fold it into float32 register accumulators with the two
 // scales.  Four partial buffers in tensor memory let the tensor cores run ahead of the fold.
 //
-// One CTA = one 128 x 128 tile of C.  warp 0: TMA producer; warp 1: MMA issuer and owner
+// One persistent CTA per SM walks 128 x 128 tiles of C.  warp 0: TMA producer; warp 1: MMA issuer and owner
 // of the tensor-memory allocation; warps 2-17: fold + store, thread = (row, 32-column group).
 #include "lh_common.cuh"
 
@@ -17,17 +17,21 @@ namespace lh {
 
 namespace {
 
-constexpr int FM = 128, FN = 128, FKB = 128;   // tile; FKB = bytes (= e4m3 elements) of k per stage
-constexpr int FSTAGES = 5;
-constexpr int F_TILE = FM * FKB;               // 16 KB
-constexpr int F_STAGE = 2 * F_TILE;
+constexpr int FM = 128, FN = 256, FKB = 128;   // tile; FKB = bytes (= e4m3 elements) of k per stage
+constexpr int FSTAGES = 4;
+constexpr int F_TILE = FM * FKB;               // a: 16 KB, then b: 32 KB
+constexpr int F_STAGE = F_TILE + FN * FKB;
 constexpr int F_BAR_OFF = FSTAGES * F_STAGE;
-constexpr int F_SB_OFF = F_BAR_OFF + 256;      // b scales of this tile, [k-block][128] float32
-constexpr int F_SB_MAX = 128;                  // scale blocks along k that fit
-constexpr int F_SMEM = 1024 + F_SB_OFF + F_SB_MAX * FN * 4;
-constexpr int FBUFS = 4;                        // partial-product buffers in tensor memory
+constexpr int F_SC_OFF = F_BAR_OFF + 256;      // scales, two chunk buffers
+constexpr int F_CH = 8;                        // scale blocks per staged chunk
+constexpr int F_SA_LD = F_CH + 1;              // a scales [row][block], odd stride: one bank per row
+constexpr int F_SC_FLOATS = FM * F_SA_LD + F_CH * FN;   // + b scales [block][column]
+constexpr int F_SMEM = 1024 + F_SC_OFF + 2 * F_SC_FLOATS * 4;
+constexpr int FBUFS = 512 / FN;                       // partial-product buffers in tensor memory
 constexpr int F_TMEM_COLS = FBUFS * FN;
-constexpr int F_FOLD_WARPS = 16;                // each folds 32 accumulator rows x 32 columns
+constexpr int F_FOLD_WARPS = 16;                // each folds 32 accumulator rows x FN/4 columns
+constexpr int F_CW = FN / 4;                    // columns per fold warp
+static_assert(F_SMEM <= 232448, "shared memory");
 constexpr int F_THREADS = 64 + 32 * F_FOLD_WARPS;
 
 enum : int { DEVERR_PART_WAIT = 5 };
@@ -67,6 +71,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
 // One lane polls; the others then observe the completed phase with one try_wait of their own.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int code, int lane) {
     bool ok = true;
@@ -74,6 +87,24 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, i
     ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
     if (ok && lane != 0) ok = mbar_try_wait(bar, parity);
     return __all_sync(0xffffffffu, ok);
+}
+
+// 4-byte asynchronous global -> shared copy (no register staging); bytes = 0 writes a zero and reads nothing
+__device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src, bool valid) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 4 : 0)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// true in one lane of the (converged) warp, the same lane every time
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred P;\n\t"
+        "elect.sync _|P, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, P;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 struct Fp8GemmParams {
@@ -97,18 +128,23 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const __grid_constant__ Fp8GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
-    uint8_t* tiles = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-    uint64_t* full = reinterpret_cast<uint64_t*>(tiles + F_BAR_OFF);   // TMA landed
+    uint8_t* tile_smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+    uint64_t* full = reinterpret_cast<uint64_t*>(tile_smem + F_BAR_OFF);   // TMA landed
     uint64_t* empty = full + FSTAGES;                                   // MMAs have read the stage
     uint64_t* part_full = empty + FSTAGES;                              // partial product complete
     uint64_t* part_empty = part_full + FBUFS;                           // partial product read out
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + FBUFS);
-    float* sb = reinterpret_cast<float*>(tiles + F_SB_OFF);
+    float* sc_all = reinterpret_cast<float*>(tile_smem + F_SC_OFF);
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-    const int m0 = blockIdx.y * FM, n0 = blockIdx.x * FN;
     const int kstages = p.K / FKB;
     const int nsb = p.nsb;
+    // Persistent: a CTA takes tiles blockIdx.x, + gridDim.x, ... (column tile fastest, so the tiles in
+    // flight share a few row blocks of a and all of b in L2).  Barriers, the tensor-memory allocation
+    // and the three roles live across tiles; the stage and partial-buffer counters simply keep
+    // counting, so the loads and MMAs of the next tile start while the fold warps still store this one.
+    const int tiles_n = (p.N + FN - 1) / FN;
+    const int64_t tiles = int64_t((p.M + FM - 1) / FM) * tiles_n;
 
     if (t == 0) {
         for (int i = 0; i < FSTAGES; ++i) {
@@ -134,125 +170,186 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tc_fence_after();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
+    // Warps 0 and 1 run their loops with all 32 lanes and elect one lane only for the instructions that
+    // issue work: the loop counters, shared-memory addresses and descriptors are then warp-uniform
+    // values, which is what the TMA and tcgen05 instructions take as operands.
     if (warp == 0) {
-        if (lane == 0) {
+        int s = 0;
+        uint32_t ph = 0;                                            // stage and its phase, over all tiles
+        bool first_pass = true, ok = true;
+        for (int64_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
             for (int ks = 0; ks < kstages; ++ks) {
-                const int s = ks % FSTAGES;
-                const uint32_t use = uint32_t(ks / FSTAGES);
-                if (ks >= FSTAGES && !mbar_wait(&empty[s], (use & 1u) ^ 1u, DEVERR_EMPTY_WAIT)) break;
-                uint8_t* st = tiles + size_t(s) * F_STAGE;
-                mbar_expect_tx(&full[s], F_STAGE);
-                tma_load_2d(st, &map_a, ks * FKB, m0, &full[s]);
-                tma_load_2d(st + F_TILE, &map_b, ks * FKB, n0, &full[s]);
+                if (!first_pass) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, DEVERR_EMPTY_WAIT));
+                    if (!ok) break;
+                }
+                if (elect_one()) {
+                    uint8_t* st = tile_smem + size_t(s) * F_STAGE;
+                    mbar_expect_tx(&full[s], F_STAGE);
+                    tma_load_2d(st, &map_a, ks * FKB, m0, &full[s]);
+                    tma_load_2d(st + F_TILE, &map_b, ks * FKB, n0, &full[s]);
+                }
+                if (++s == FSTAGES) { s = 0; ph ^= 1u; first_pass = false; }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            bool ok = true;
+        int s = 0, buf = 0;
+        uint32_t ph = 0, bph = 0;                                   // stage / partial buffer and their phases
+        bool first_bufs = true, ok = true;
+        for (int64_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             for (int ks = 0; ks < kstages && ok; ++ks) {
-                const int s = ks % FSTAGES;
-                ok = mbar_wait(&full[s], uint32_t(ks / FSTAGES) & 1u, DEVERR_FULL_WAIT);
+                ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, DEVERR_FULL_WAIT));
                 if (!ok) break;
-                const uint32_t a = smem_u32(tiles + size_t(s) * F_STAGE);
+                const uint32_t a = smem_u32(tile_smem + size_t(s) * F_STAGE);
                 const uint64_t da = umma_desc(a), db = umma_desc(a + F_TILE);
 #pragma unroll
-                for (int h = 0; h < SUB; ++h) {
-                    const int blk = ks * SUB + h;                  // scale block = partial product
-                    const int buf = blk % FBUFS;
-                    if (blk >= FBUFS) {
-                        ok = mbar_wait(&part_empty[buf], (uint32_t(blk / FBUFS) & 1u) ^ 1u, DEVERR_PART_WAIT);
+                for (int h = 0; h < SUB; ++h) {                     // scale block = partial product
+                    if (!first_bufs) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(&part_empty[buf], bph ^ 1u, DEVERR_PART_WAIT));
                         if (!ok) break;
                     }
                     tc_fence_after();
-                    constexpr int STEPS = (FKB / 32) / SUB;         // MMAs (k = 32) per scale block
+                    if (elect_one()) {
+                        constexpr int STEPS = (FKB / 32) / SUB;     // MMAs (k = 32) per scale block
 #pragma unroll
-                    for (int k4 = 0; k4 < STEPS; ++k4) {
-                        const int kk = h * STEPS + k4;              // 32 bytes = 2 descriptor units per step
-                        umma_f8(tmem + uint32_t(buf * FN), da + 2 * kk, db + 2 * kk, k4 != 0);
+                        for (int k4 = 0; k4 < STEPS; ++k4) {
+                            const int kk = h * STEPS + k4;          // 32 bytes = 2 descriptor units per step
+                            umma_f8(tmem + uint32_t(buf * FN), da + 2 * kk, db + 2 * kk, k4 != 0);
+                        }
+                        umma_commit(&part_full[buf]);       // the one commit per block: issuing costs this thread ~100 cycles
                     }
-                    if (h == SUB - 1) umma_commit(&empty[s]);
-                    umma_commit(&part_full[buf]);
+                    if (++buf == FBUFS) { buf = 0; bph ^= 1u; first_bufs = false; }
                 }
+                if (++s == FSTAGES) { s = 0; ph ^= 1u; }
             }
         }
     } else {
         // ---- fold the partial products into register accumulators, then store
-        // b scales of this tile's 128 columns -> shared memory, [scale block][column]; only these
-        // warps need them, so the loads and the MMAs start meanwhile
-        for (int i = t - 64; i < nsb * FN; i += F_THREADS - 64) {
-            const int blk = i / FN, col = i - blk * FN;
-            const int n = n0 + col;
-            float v = 0.f;
-            if (n < p.N) v = p.b_s_transposed ? p.b_s[int64_t(blk) * p.N + n] : p.b_s[int64_t(n / p.group) * nsb + blk];
-            sb[i] = v;
-        }
-        named_bar<1, F_THREADS - 64>();
         const int quarter = warp & 3, cgrp = (warp - 2) >> 2;       // tensor-memory lane quarter, 32-column group
-        const int64_t row = int64_t(m0) + quarter * 32 + lane;
-        const bool row_ok = row < p.M;
-        const float* as_ptr = p.a_s + (p.a_s_transposed ? row : (row / p.group) * nsb);
-        const int64_t as_step = p.a_s_transposed ? p.M : 1;
-        float2 acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = make_float2(0.f, 0.f);
-        // Four fold warps per scheduler: their tensor-memory loads, shared-memory reads and FMAs
-        // overlap across warps, so each warp simply loads a block's 32 columns and folds them.
-        bool ok = true;
-        const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(cgrp * 32);
-        float sa_next = row_ok ? as_ptr[0] : 0.f;
-        for (int blk = 0; blk < nsb && ok; ++blk) {
-            const int buf = blk % FBUFS;
-            const float sa = sa_next;
-            if (blk + 1 < nsb && row_ok) sa_next = as_ptr[int64_t(blk + 1) * as_step];
-            ok = mbar_wait_warp(&part_full[buf], uint32_t(blk / FBUFS) & 1u, DEVERR_PART_WAIT, lane);
-            if (!ok) break;
-            tc_fence_after();
-            uint32_t v[32];
-            tmem_ld32(tbase + uint32_t(buf * FN), v);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&part_empty[buf]);        // the tensor cores may overwrite this buffer
-            const float2 sa2 = splat2(sa);
-            const float2* sbp = reinterpret_cast<const float2*>(sb + blk * FN + cgrp * 32);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float2 pr = make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                acc[j] = fma2(mul2(pr, sbp[j]), sa2, acc[j]);
+        const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(cgrp * F_CW);
+        const int ft = t - 64;                                      // thread index among the fold warps
+        constexpr int FT = F_THREADS - 64;
+        // The scales reach shared memory in chunks of F_CH k-blocks, by asynchronous 4-byte copies
+        // issued one chunk ahead (the next chunk may be the next tile's first): a scale read straight
+        // from global memory inside the fold loop puts the load's latency into every block.
+        const int chunks = (nsb + F_CH - 1) / F_CH;
+        auto stage = [&](int64_t tile, int chunk, float* buf) {
+            const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
+            const int blk0 = chunk * F_CH;
+            float* sa_s = buf;
+            float* sb_s = buf + FM * F_SA_LD;
+#pragma unroll 2
+            for (int i = ft; i < FM * F_CH; i += FT) {
+                // consecutive threads take consecutive global addresses in either layout
+                const int r = p.a_s_transposed ? (i % FM) : (i / F_CH);
+                const int bl = p.a_s_transposed ? (i / FM) : (i % F_CH);
+                const int row = m0 + r;
+                const int blk = blk0 + bl;
+                const bool valid = row < int(p.M) && blk < nsb;
+                const float* src = p.a_s;
+                if (valid) src += p.a_s_transposed ? int64_t(blk) * p.M + row : int64_t(p.group == 1 ? row : row / p.group) * nsb + blk;
+                cp_async_f32(sa_s + r * F_SA_LD + bl, src, valid);
             }
-        }
-        if (ok && row_ok) {
-            const int c0 = n0 + cgrp * 32;
-            if (p.out_dtype == LH_F32) {
-                float* out = static_cast<float*>(p.c) + row * p.N + c0;
+#pragma unroll 2
+            for (int i = ft; i < FN * F_CH; i += FT) {
+                const int c = p.b_s_transposed ? (i % FN) : (i / F_CH);
+                const int bl = p.b_s_transposed ? (i / FN) : (i % F_CH);
+                const int n = n0 + c;
+                const int blk = blk0 + bl;
+                const bool valid = n < p.N && blk < nsb;
+                const float* src = p.b_s;
+                if (valid) src += p.b_s_transposed ? int64_t(blk) * p.N + n : int64_t(p.group == 1 ? n : n / p.group) * nsb + blk;
+                cp_async_f32(sb_s + bl * FN + c, src, valid);
+            }
+        };
+        bool ok = true;                                             // a failed wait skips the work, not the barriers
+        uint32_t gb = 0, q = 0;                                     // scale blocks and chunks so far
+        if (int64_t(blockIdx.x) < tiles) stage(blockIdx.x, 0, sc_all);
+        for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+            const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
+            const int64_t row = int64_t(m0) + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            float2 acc[F_CW / 2];
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (c0 + 2 * j < p.N) out[2 * j] = acc[j].x;
-                    if (c0 + 2 * j + 1 < p.N) out[2 * j + 1] = acc[j].y;
-                }
-            } else {
-                uint16_t* out = static_cast<uint16_t*>(p.c) + row * p.N + c0;
-                const bool vec = (p.N % 8) == 0;
+            for (int j = 0; j < F_CW / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+            // Four fold warps per scheduler: their tensor-memory loads, shared-memory reads and FMAs
+            // overlap across warps, so each warp simply loads a block's 32 columns and folds them.
+            for (int chunk = 0; chunk < chunks; ++chunk, ++q) {
+                // this chunk's copies have landed, and every warp is done with the other buffer
+                cp_async_wait_all();
+                named_bar<1, FT>();
+                const float* sc = sc_all + (q & 1u) * F_SC_FLOATS;
+                if (chunk + 1 < chunks) stage(tile, chunk + 1, sc_all + ((q + 1) & 1u) * F_SC_FLOATS);
+                else if (tile + gridDim.x < tiles) stage(tile + gridDim.x, 0, sc_all + ((q + 1) & 1u) * F_SC_FLOATS);
+                const float* sa_s = sc + (quarter * 32 + lane) * F_SA_LD;
+                const float* sb_s = sc + FM * F_SA_LD + cgrp * F_CW;
+                const int nblk = min(F_CH, nsb - chunk * F_CH);
+                for (int bl = 0; bl < nblk && ok; ++bl, ++gb) {
+                    const int buf = int(gb % FBUFS);
+                    const float sa = sa_s[bl];
+                    ok = mbar_wait_warp(&part_full[buf], (gb / FBUFS) & 1u, DEVERR_PART_WAIT, lane);
+                    if (!ok) break;
+                    // the block's MMAs are complete, so its k-stage may be refilled: one fold lane tells the producer
+                    // (a second tcgen05.commit by the MMA thread would say the same, at a higher price)
+                    if (t == 64 && (gb % SUB) == SUB - 1) mbar_arrive(&empty[(gb / SUB) % FSTAGES]);
+                    tc_fence_after();
+                    const float2 sa2 = splat2(sa);
+                    const float4* sbp = reinterpret_cast<const float4*>(sb_s + bl * FN);   // 128-bit broadcast reads
 #pragma unroll
-                for (int j8 = 0; j8 < 4; ++j8) {                 // 8 columns per step
-                    uint32_t w[4];
+                    for (int piece = 0; piece < F_CW / 16; ++piece) {       // 16 columns at a time
+                        uint32_t v[16];
+                        tmem_ld16(tbase + uint32_t(buf * FN + piece * 16), v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (piece == F_CW / 16 - 1) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&part_empty[buf]);   // the tensor cores may overwrite this buffer
+                        }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float2 a = acc[4 * j8 + j];
-                        if (p.out_dtype == LH_BF16) {
-                            w[j] = pack_bf16x2(a.x, a.y);
-                        } else {
-                            const __half2 h = __floats2half2_rn(a.x, a.y);
-                            w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                        for (int j = 0; j < 4; ++j) {
+                            const float4 sb4 = sbp[piece * 4 + j];
+                            const float2 p0 = make_float2(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
+                            const float2 p1 = make_float2(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                            acc[piece * 8 + 2 * j] = fma2(mul2(p0, make_float2(sb4.x, sb4.y)), sa2, acc[piece * 8 + 2 * j]);
+                            acc[piece * 8 + 2 * j + 1] = fma2(mul2(p1, make_float2(sb4.z, sb4.w)), sa2, acc[piece * 8 + 2 * j + 1]);
                         }
                     }
-                    const int c = c0 + 8 * j8;
-                    if (vec && c + 8 <= p.N) {
-                        *reinterpret_cast<uint4*>(out + 8 * j8) = make_uint4(w[0], w[1], w[2], w[3]);
-                    } else {
+                }
+            }
+            if (ok && row_ok) {
+                const int c0 = n0 + cgrp * F_CW;
+                if (p.out_dtype == LH_F32) {
+                    float* out = static_cast<float*>(p.c) + row * p.N + c0;
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (c + j < p.N) out[8 * j8 + j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+                    for (int j = 0; j < F_CW / 2; ++j) {
+                        if (c0 + 2 * j < p.N) out[2 * j] = acc[j].x;
+                        if (c0 + 2 * j + 1 < p.N) out[2 * j + 1] = acc[j].y;
+                    }
+                } else {
+                    uint16_t* out = static_cast<uint16_t*>(p.c) + row * p.N + c0;
+                    const bool vec = (p.N % 8) == 0;
+#pragma unroll
+                    for (int j8 = 0; j8 < F_CW / 8; ++j8) {          // 8 columns per step
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float2 a = acc[4 * j8 + j];
+                            if (p.out_dtype == LH_BF16) {
+                                w[j] = pack_bf16x2(a.x, a.y);
+                            } else {
+                                const __half2 h = __floats2half2_rn(a.x, a.y);
+                                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                        }
+                        const int c = c0 + 8 * j8;
+                        if (vec && c + 8 <= p.N) {
+                            *reinterpret_cast<uint4*>(out + 8 * j8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (c + j < p.N) out[8 * j8 + j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+                        }
                     }
                 }
             }
@@ -277,7 +374,6 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
     if (M < 0 || N <= 0 || K <= 0 || (K % FKB)) return fail_arg("fp8_gemm: need K a positive multiple of 128 and N > 0");
     if (out_dtype != LH_BF16 && out_dtype != LH_F16 && out_dtype != LH_F32) return fail_arg("fp8_gemm: bad out dtype");
     const int64_t nsb = K / block;
-    if (nsb > F_SB_MAX) return fail_arg("fp8_gemm: at most %d scale blocks along k", F_SB_MAX);
     if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15)
         return fail_arg("fp8_gemm: pointers must be 16-byte aligned");
     if (M > 0x7fffffff - FM || N > 0x7fffffff - FN) return fail_arg("fp8_gemm: size out of range");
@@ -290,7 +386,8 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
     p.M = M; p.N = int(N); p.K = int(K); p.nsb = int(nsb);
     p.a_s_transposed = group_2d ? 0 : a_s_transposed; p.b_s_transposed = group_2d ? 0 : b_s_transposed; p.out_dtype = out_dtype;
     p.group = group_2d ? block : 1;
-    const dim3 grid(unsigned((N + FN - 1) / FN), unsigned((M + FM - 1) / FM));
+    const int64_t tiles = ((N + FN - 1) / FN) * ((M + FM - 1) / FM);
+    const dim3 grid(unsigned(std::min<int64_t>(tiles, sm_count())));
     auto go = [&](auto kern) -> int {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM);
         if (e != cudaSuccess) { set_error("cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return int(e); }
