@@ -13,6 +13,8 @@
 // of the tensor-memory allocation; warps 2-17: fold + store, thread = (row, 32-column group).
 #include "lh_common.cuh"
 
+#include <type_traits>
+
 namespace lh {
 
 namespace {
@@ -32,7 +34,8 @@ constexpr int F_TMEM_COLS = FBUFS * FN;
 constexpr int F_FOLD_WARPS = 16;                // each folds 32 accumulator rows x FN/4 columns
 constexpr int F_CW = FN / 4;                    // columns per fold warp
 static_assert(F_SMEM <= 232448, "shared memory");
-constexpr int F_THREADS = 64 + 32 * F_FOLD_WARPS;
+constexpr int F_SCALE_WARP = 2 + F_FOLD_WARPS;  // warp that stages the scales
+constexpr int F_THREADS = 32 * (F_SCALE_WARP + 1);
 
 enum : int { DEVERR_PART_WAIT = 5 };
 
@@ -89,13 +92,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, i
     return __all_sync(0xffffffffu, ok);
 }
 
-// 4-byte asynchronous global -> shared copy (no register staging); bytes = 0 writes a zero and reads nothing
-__device__ __forceinline__ void cp_async_f32(float* dst_smem, const float* src, bool valid) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(valid ? 4 : 0)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 // true in one lane of the (converged) warp, the same lane every time
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
@@ -116,8 +112,8 @@ struct Fp8GemmParams {
     int nsb;             // scale blocks along k
     int a_s_transposed;  // 0: a_s [M, nsb]   1: a_s [nsb, M]
     int b_s_transposed;  // 0: b_s [N, nsb]   1: b_s [nsb, N]
-    int group;           // rows of a (of b) that share a scale: 1 = one scale per row and k-block, otherwise
-                         // the block size (2-D block scales: a_s [ceil(M/group), nsb], b_s [ceil(N/group), nsb])
+    int group_shift;     // log2 of the rows of a (of b) that share a scale: 0 = one scale per row and k-block,
+                         // otherwise log2 of the block size (2-D block scales: a_s [ceil(M/block), nsb], b_s likewise)
     int out_dtype;
 };
 
@@ -133,7 +129,9 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint64_t* empty = full + FSTAGES;                                   // MMAs have read the stage
     uint64_t* part_full = empty + FSTAGES;                              // partial product complete
     uint64_t* part_empty = part_full + FBUFS;                           // partial product read out
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(part_empty + FBUFS);
+    uint64_t* sc_full = part_empty + FBUFS;                             // a chunk of scales is in shared memory
+    uint64_t* sc_empty = sc_full + 2;                                   // the fold warps are done with it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_empty + 2);
     float* sc_all = reinterpret_cast<float*>(tile_smem + F_SC_OFF);
 
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -154,6 +152,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int i = 0; i < FBUFS; ++i) {
             mbar_init(&part_full[i], 1);
             mbar_init(&part_empty[i], F_FOLD_WARPS);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&sc_full[i], 1);
+            mbar_init(&sc_empty[i], F_FOLD_WARPS);
         }
         mbar_fence_init();
         tma_prefetch_desc(&map_a);
@@ -224,48 +226,68 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (++s == FSTAGES) { s = 0; ph ^= 1u; }
             }
         }
+    } else if (warp == F_SCALE_WARP) {
+        // ---- the scales reach shared memory in chunks of F_CH k-blocks, one chunk ahead of the fold
+        // warps (the next chunk may be the next tile's first): a scale read straight from global
+        // memory inside the fold loop would put the load's latency into every block.
+        const int chunks = (nsb + F_CH - 1) / F_CH;
+        uint32_t q = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+            const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
+            for (int chunk = 0; chunk < chunks; ++chunk, ++q) {
+                if (q >= 2) {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&sc_empty[q & 1u], ((q >> 1) & 1u) ^ 1u, DEVERR_PART_WAIT));
+                    if (!ok) break;
+                }
+                float* sa_s = sc_all + (q & 1u) * F_SC_FLOATS;
+                float* sb_s = sa_s + FM * F_SA_LD;
+                const int blk0 = chunk * F_CH;
+                // 32 loads in flight per lane; consecutive lanes take consecutive global addresses in either
+                // layout.  Element i = lane + 32 k + 1024 j of a chunk is (r, bl) = (i / F_CH, i % F_CH) in the
+                // row-major layout and (i % EXT, i / EXT) in the transposed one; with lane < 32 both split into
+                // a per-lane part and compile-time steps.
+                auto copy = [&](auto is_a_tag, auto tr_tag) {
+                    constexpr bool IS_A = decltype(is_a_tag)::value, TR = decltype(tr_tag)::value;
+                    constexpr int EXT = IS_A ? FM : FN, BATCH = 32;
+                    static_assert(F_CH == 8 && (EXT * F_CH) % (32 * BATCH) == 0, "index split below");
+                    const float* src = IS_A ? p.a_s : p.b_s;
+                    const int rows = IS_A ? int(p.M) : p.N;
+                    const int base = IS_A ? m0 : n0;
+#pragma unroll
+                    for (int j = 0; j < EXT * F_CH / (32 * BATCH); ++j) {
+                        float v[BATCH];
+#pragma unroll
+                        for (int k = 0; k < BATCH; ++k) {
+                            const int r = TR ? lane + 32 * (k % (EXT / 32)) : (lane >> 3) + 4 * k + 128 * j;
+                            const int bl = TR ? k / (EXT / 32) + (1024 / EXT) * j : (lane & 7);
+                            const int row = base + r, blk = blk0 + bl;
+                            v[k] = 0.f;
+                            if (row < rows && blk < nsb)
+                                v[k] = src[TR ? int64_t(blk) * rows + row : int64_t(row >> p.group_shift) * nsb + blk];
+                        }
+#pragma unroll
+                        for (int k = 0; k < BATCH; ++k) {
+                            const int r = TR ? lane + 32 * (k % (EXT / 32)) : (lane >> 3) + 4 * k + 128 * j;
+                            const int bl = TR ? k / (EXT / 32) + (1024 / EXT) * j : (lane & 7);
+                            if (IS_A) sa_s[r * F_SA_LD + bl] = v[k];
+                            else sb_s[bl * FN + r] = v[k];
+                        }
+                    }
+                };
+                if (p.a_s_transposed) copy(std::true_type{}, std::true_type{}); else copy(std::true_type{}, std::false_type{});
+                if (p.b_s_transposed) copy(std::false_type{}, std::true_type{}); else copy(std::false_type{}, std::false_type{});
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sc_full[q & 1u]);
+            }
+        }
     } else {
         // ---- fold the partial products into register accumulators, then store
-        const int quarter = warp & 3, cgrp = (warp - 2) >> 2;       // tensor-memory lane quarter, 32-column group
+        const int quarter = warp & 3, cgrp = (warp - 2) >> 2;       // tensor-memory lane quarter, column group
         const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(cgrp * F_CW);
-        const int ft = t - 64;                                      // thread index among the fold warps
-        constexpr int FT = F_THREADS - 64;
-        // The scales reach shared memory in chunks of F_CH k-blocks, by asynchronous 4-byte copies
-        // issued one chunk ahead (the next chunk may be the next tile's first): a scale read straight
-        // from global memory inside the fold loop puts the load's latency into every block.
         const int chunks = (nsb + F_CH - 1) / F_CH;
-        auto stage = [&](int64_t tile, int chunk, float* buf) {
-            const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
-            const int blk0 = chunk * F_CH;
-            float* sa_s = buf;
-            float* sb_s = buf + FM * F_SA_LD;
-#pragma unroll 2
-            for (int i = ft; i < FM * F_CH; i += FT) {
-                // consecutive threads take consecutive global addresses in either layout
-                const int r = p.a_s_transposed ? (i % FM) : (i / F_CH);
-                const int bl = p.a_s_transposed ? (i / FM) : (i % F_CH);
-                const int row = m0 + r;
-                const int blk = blk0 + bl;
-                const bool valid = row < int(p.M) && blk < nsb;
-                const float* src = p.a_s;
-                if (valid) src += p.a_s_transposed ? int64_t(blk) * p.M + row : int64_t(p.group == 1 ? row : row / p.group) * nsb + blk;
-                cp_async_f32(sa_s + r * F_SA_LD + bl, src, valid);
-            }
-#pragma unroll 2
-            for (int i = ft; i < FN * F_CH; i += FT) {
-                const int c = p.b_s_transposed ? (i % FN) : (i / F_CH);
-                const int bl = p.b_s_transposed ? (i / FN) : (i % F_CH);
-                const int n = n0 + c;
-                const int blk = blk0 + bl;
-                const bool valid = n < p.N && blk < nsb;
-                const float* src = p.b_s;
-                if (valid) src += p.b_s_transposed ? int64_t(blk) * p.N + n : int64_t(p.group == 1 ? n : n / p.group) * nsb + blk;
-                cp_async_f32(sb_s + bl * FN + c, src, valid);
-            }
-        };
         bool ok = true;                                             // a failed wait skips the work, not the barriers
         uint32_t gb = 0, q = 0;                                     // scale blocks and chunks so far
-        if (int64_t(blockIdx.x) < tiles) stage(blockIdx.x, 0, sc_all);
         for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
             const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
             const int64_t row = int64_t(m0) + quarter * 32 + lane;
@@ -276,12 +298,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // Four fold warps per scheduler: their tensor-memory loads, shared-memory reads and FMAs
             // overlap across warps, so each warp simply loads a block's 32 columns and folds them.
             for (int chunk = 0; chunk < chunks; ++chunk, ++q) {
-                // this chunk's copies have landed, and every warp is done with the other buffer
-                cp_async_wait_all();
-                named_bar<1, FT>();
+                if (ok) ok = mbar_wait_warp(&sc_full[q & 1u], (q >> 1) & 1u, DEVERR_PART_WAIT, lane);
                 const float* sc = sc_all + (q & 1u) * F_SC_FLOATS;
-                if (chunk + 1 < chunks) stage(tile, chunk + 1, sc_all + ((q + 1) & 1u) * F_SC_FLOATS);
-                else if (tile + gridDim.x < tiles) stage(tile + gridDim.x, 0, sc_all + ((q + 1) & 1u) * F_SC_FLOATS);
                 const float* sa_s = sc + (quarter * 32 + lane) * F_SA_LD;
                 const float* sb_s = sc + FM * F_SA_LD + cgrp * F_CW;
                 const int nblk = min(F_CH, nsb - chunk * F_CH);
@@ -316,6 +334,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         }
                     }
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sc_empty[q & 1u]);      // the scale warp may refill this buffer
             }
             if (ok && row_ok) {
                 const int c0 = n0 + cgrp * F_CW;
@@ -385,7 +405,7 @@ int fp8_gemm(const void* a, const void* b, const float* a_s, const float* b_s, v
     p.a_s = a_s; p.b_s = b_s; p.c = c;
     p.M = M; p.N = int(N); p.K = int(K); p.nsb = int(nsb);
     p.a_s_transposed = group_2d ? 0 : a_s_transposed; p.b_s_transposed = group_2d ? 0 : b_s_transposed; p.out_dtype = out_dtype;
-    p.group = group_2d ? block : 1;
+    p.group_shift = group_2d ? (block == 128 ? 7 : 6) : 0;
     const int64_t tiles = ((N + FN - 1) / FN) * ((M + FM - 1) / FM);
     const dim3 grid(unsigned(std::min<int64_t>(tiles, sm_count())));
     auto go = [&](auto kern) -> int {
