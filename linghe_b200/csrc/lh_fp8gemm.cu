@@ -341,20 +341,33 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const int c0 = n0 + cgrp * F_CW;
                 if (p.out_dtype == LH_F32) {
                     float* out = static_cast<float*>(p.c) + row * p.N + c0;
+                    const bool vec = (p.N % 8) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 31) == 0;
 #pragma unroll
-                    for (int j = 0; j < F_CW / 2; ++j) {
-                        if (c0 + 2 * j < p.N) out[2 * j] = acc[j].x;
-                        if (c0 + 2 * j + 1 < p.N) out[2 * j + 1] = acc[j].y;
+                    for (int j4 = 0; j4 < F_CW / 8; ++j4) {          // 8 columns per step
+                        const int c = c0 + 8 * j4;
+                        if (vec && c + 8 <= p.N) {
+                            const float2 a0 = acc[4 * j4], a1 = acc[4 * j4 + 1], a2 = acc[4 * j4 + 2], a3 = acc[4 * j4 + 3];
+                            st_global_256(out + 8 * j4,
+                                          make_uint4(__float_as_uint(a0.x), __float_as_uint(a0.y), __float_as_uint(a1.x), __float_as_uint(a1.y)),
+                                          make_uint4(__float_as_uint(a2.x), __float_as_uint(a2.y), __float_as_uint(a3.x), __float_as_uint(a3.y)));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                if (c + 2 * j < p.N) out[8 * j4 + 2 * j] = acc[4 * j4 + j].x;
+                                if (c + 2 * j + 1 < p.N) out[8 * j4 + 2 * j + 1] = acc[4 * j4 + j].y;
+                            }
+                        }
                     }
                 } else {
                     uint16_t* out = static_cast<uint16_t*>(p.c) + row * p.N + c0;
-                    const bool vec = (p.N % 8) == 0;
+                    // a thread owns F_CW consecutive columns of its row: 32-byte stores fill whole sectors
+                    const bool vec = (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 31) == 0;
 #pragma unroll
-                    for (int j8 = 0; j8 < F_CW / 8; ++j8) {          // 8 columns per step
-                        uint32_t w[4];
+                    for (int j16 = 0; j16 < F_CW / 16; ++j16) {      // 16 columns per step
+                        uint32_t w[8];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float2 a = acc[4 * j8 + j];
+                        for (int j = 0; j < 8; ++j) {
+                            const float2 a = acc[8 * j16 + j];
                             if (p.out_dtype == LH_BF16) {
                                 w[j] = pack_bf16x2(a.x, a.y);
                             } else {
@@ -362,13 +375,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                 w[j] = *reinterpret_cast<const uint32_t*>(&h);
                             }
                         }
-                        const int c = c0 + 8 * j8;
-                        if (vec && c + 8 <= p.N) {
-                            *reinterpret_cast<uint4*>(out + 8 * j8) = make_uint4(w[0], w[1], w[2], w[3]);
+                        const int c = c0 + 16 * j16;
+                        if (vec && c + 16 <= p.N) {
+                            st_global_256(out + 16 * j16, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
                         } else {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                if (c + j < p.N) out[8 * j8 + j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
+                            for (int j = 0; j < 16; ++j)
+                                if (c + j < p.N) out[16 * j16 + j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
                         }
                     }
                 }
