@@ -7,10 +7,19 @@
 // Each k-block's partial product is an exact e4m3 x e4m3 contraction on the tensor cores
 // (tcgen05.mma kind::f8f6f4, float32 accumulator in tensor memory, started from zero per
 // block); the CUDA cores then fold it into float32 register accumulators with the two
-// scales.  Four partial buffers in tensor memory let the tensor cores run ahead of the fold.
+// scales.  Two 128 x 256 partial buffers fill the 512 tensor-memory columns, so the tensor
+// cores work on one block while the other is folded.
 //
-// One persistent CTA per SM walks 128 x 128 tiles of C.  warp 0: TMA producer; warp 1: MMA issuer and owner
-// of the tensor-memory allocation; warps 2-17: fold + store, thread = (row, 32-column group).
+// One persistent CTA per SM walks 128 x 256 tiles of C (column tile fastest).  Roles:
+//   warp 0      TMA producer (a: 128 x 128 bytes, b: 256 x 128 bytes per k-stage, 4 stages)
+//   warp 1      MMA issuer and owner of the tensor-memory allocation: four MMAs (k = 32 each) and ONE
+//               tcgen05.commit per block -- each tcgen05 instruction costs the issuing thread about a
+//               hundred cycles, so N = 256 and a single commit halve the issue time per flop
+//   warps 2-17  fold + store, a warp = 32 accumulator rows x 64 columns, read in the 16x256b fragment layout
+//   warp 18     stages the scales of the next chunk of 8 k-blocks in shared memory
+// What bounds it: the hand-over of a partial buffer (MMA done -> fold warps read it out, four dependent
+// tensor-memory loads -> MMA thread sees it free -> issues) takes about 3000 cycles for two buffers, against
+// 512 cycles of tensor-core work per block; the probes that measured each leg are described in the design notes.
 #include "lh_common.cuh"
 
 #include <type_traits>
@@ -62,36 +71,18 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+// 16 lanes x 32 columns in the accumulator-fragment layout: register 4 i + 2 hi + lo of thread t holds
+// lane (t / 4) + 8 hi, column 8 i + 2 (t % 4) + lo, counted from the address.  A thread then owns two
+// rows and eight columns instead of one row and 32 columns, so it needs far fewer column scales.
+__device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t (&v)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
 }
-// One lane polls; the others then observe the completed phase with one try_wait of their own.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int code, int lane) {
-    bool ok = true;
-    if (lane == 0) ok = mbar_wait_inline(bar, parity, code);
-    ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
-    if (ok && lane != 0) ok = mbar_try_wait(bar, parity);
-    return __all_sync(0xffffffffu, ok);
-}
-
 // true in one lane of the (converged) warp, the same lane every time
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
@@ -183,7 +174,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
             for (int ks = 0; ks < kstages; ++ks) {
                 if (!first_pass) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&empty[s], ph ^ 1u, DEVERR_EMPTY_WAIT));
+                    ok = __all_sync(0xffffffffu, mbar_wait_inline(&empty[s], ph ^ 1u, DEVERR_EMPTY_WAIT));
                     if (!ok) break;
                 }
                 if (elect_one()) {
@@ -201,14 +192,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         bool first_bufs = true, ok = true;
         for (int64_t tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             for (int ks = 0; ks < kstages && ok; ++ks) {
-                ok = __all_sync(0xffffffffu, mbar_wait(&full[s], ph, DEVERR_FULL_WAIT));
+                ok = __all_sync(0xffffffffu, mbar_wait_inline(&full[s], ph, DEVERR_FULL_WAIT));
                 if (!ok) break;
                 const uint32_t a = smem_u32(tile_smem + size_t(s) * F_STAGE);
                 const uint64_t da = umma_desc(a), db = umma_desc(a + F_TILE);
 #pragma unroll
                 for (int h = 0; h < SUB; ++h) {                     // scale block = partial product
                     if (!first_bufs) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(&part_empty[buf], bph ^ 1u, DEVERR_PART_WAIT));
+                        ok = __all_sync(0xffffffffu, mbar_wait_inline(&part_empty[buf], bph ^ 1u, DEVERR_PART_WAIT));
                         if (!ok) break;
                     }
                     tc_fence_after();
@@ -237,7 +228,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
             for (int chunk = 0; chunk < chunks; ++chunk, ++q) {
                 if (q >= 2) {
-                    ok = __all_sync(0xffffffffu, mbar_wait(&sc_empty[q & 1u], ((q >> 1) & 1u) ^ 1u, DEVERR_PART_WAIT));
+                    ok = __all_sync(0xffffffffu, mbar_wait_inline(&sc_empty[q & 1u], ((q >> 1) & 1u) ^ 1u, DEVERR_PART_WAIT));
                     if (!ok) break;
                 }
                 float* sa_s = sc_all + (q & 1u) * F_SC_FLOATS;
@@ -284,106 +275,141 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     } else {
         // ---- fold the partial products into register accumulators, then store
         const int quarter = warp & 3, cgrp = (warp - 2) >> 2;       // tensor-memory lane quarter, column group
+        const int tq = lane >> 2, tc = lane & 3;                    // fragment coordinates of this thread
         const uint32_t tbase = tmem + (uint32_t(quarter * 32) << 16) + uint32_t(cgrp * F_CW);
         const int chunks = (nsb + F_CH - 1) / F_CH;
+        constexpr int CH = F_CW / 32;                               // 32-column pieces per warp
         bool ok = true;                                             // a failed wait skips the work, not the barriers
         uint32_t gb = 0, q = 0;                                     // scale blocks and chunks so far
         for (int64_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
             const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
-            const int64_t row = int64_t(m0) + quarter * 32 + lane;
-            const bool row_ok = row < p.M;
-            float2 acc[F_CW / 2];
+            // The warp folds 32 accumulator rows x F_CW columns.  A thread owns rows tq + 16 half + 8 hi and,
+            // per 8-column group i of each 32-column piece, the column pair 2 tc: 4 row scales and
+            // F_CW / 4 column scales per block instead of 1 and F_CW -- the shared-memory read bandwidth,
+            // which the tensor cores' operand fetches and the TMA writes also need, is what bounds the kernel.
+            float2 acc[2 * CH * 4 * 2];                             // [half][piece][i][hi]
 #pragma unroll
-            for (int j = 0; j < F_CW / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-            // Four fold warps per scheduler: their tensor-memory loads, shared-memory reads and FMAs
-            // overlap across warps, so each warp simply loads a block's 32 columns and folds them.
+            for (int j = 0; j < 2 * CH * 4 * 2; ++j) acc[j] = make_float2(0.f, 0.f);
             for (int chunk = 0; chunk < chunks; ++chunk, ++q) {
-                if (ok) ok = mbar_wait_warp(&sc_full[q & 1u], (q >> 1) & 1u, DEVERR_PART_WAIT, lane);
+                if (ok) ok = __all_sync(0xffffffffu, mbar_wait_inline(&sc_full[q & 1u], (q >> 1) & 1u, DEVERR_PART_WAIT));
                 const float* sc = sc_all + (q & 1u) * F_SC_FLOATS;
-                const float* sa_s = sc + (quarter * 32 + lane) * F_SA_LD;
-                const float* sb_s = sc + FM * F_SA_LD + cgrp * F_CW;
+                const float* sa_s = sc + (quarter * 32 + tq) * F_SA_LD;
+                const float* sb_s = sc + FM * F_SA_LD + cgrp * F_CW + 2 * tc;
                 const int nblk = min(F_CH, nsb - chunk * F_CH);
                 for (int bl = 0; bl < nblk && ok; ++bl, ++gb) {
                     const int buf = int(gb % FBUFS);
-                    const float sa = sa_s[bl];
-                    ok = mbar_wait_warp(&part_full[buf], (gb / FBUFS) & 1u, DEVERR_PART_WAIT, lane);
+                    ok = __all_sync(0xffffffffu, mbar_wait_inline(&part_full[buf], (gb / FBUFS) & 1u, DEVERR_PART_WAIT));
                     if (!ok) break;
                     // the block's MMAs are complete, so its k-stage may be refilled: one fold lane tells the producer
                     // (a second tcgen05.commit by the MMA thread would say the same, at a higher price)
                     if (t == 64 && (gb % SUB) == SUB - 1) mbar_arrive(&empty[(gb / SUB) % FSTAGES]);
                     tc_fence_after();
-                    const float2 sa2 = splat2(sa);
-                    const float4* sbp = reinterpret_cast<const float4*>(sb_s + bl * FN);   // 128-bit broadcast reads
+                    const float* sbp = sb_s + bl * FN;
 #pragma unroll
-                    for (int piece = 0; piece < F_CW / 16; ++piece) {       // 16 columns at a time
-                        uint32_t v[16];
-                        tmem_ld16(tbase + uint32_t(buf * FN + piece * 16), v);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (piece == F_CW / 16 - 1) {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&part_empty[buf]);   // the tensor cores may overwrite this buffer
-                        }
+                    for (int half = 0; half < 2; ++half) {
+                        const float2 sa2[2] = {splat2(sa_s[(16 * half) * F_SA_LD + bl]), splat2(sa_s[(16 * half + 8) * F_SA_LD + bl])};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float4 sb4 = sbp[piece * 4 + j];
-                            const float2 p0 = make_float2(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]));
-                            const float2 p1 = make_float2(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                            acc[piece * 8 + 2 * j] = fma2(mul2(p0, make_float2(sb4.x, sb4.y)), sa2, acc[piece * 8 + 2 * j]);
-                            acc[piece * 8 + 2 * j + 1] = fma2(mul2(p1, make_float2(sb4.z, sb4.w)), sa2, acc[piece * 8 + 2 * j + 1]);
+                        for (int ch = 0; ch < CH; ++ch) {
+                            uint32_t v[16];
+                            tmem_ld_frag(tbase + (uint32_t(16 * half) << 16) + uint32_t(buf * FN + 32 * ch), v);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (half == 1 && ch == CH - 1) {
+                                tc_fence_before();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&part_empty[buf]);   // the tensor cores may overwrite this buffer
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 sb2 = *reinterpret_cast<const float2*>(sbp + 32 * ch + 8 * i);
+#pragma unroll
+                                for (int hi = 0; hi < 2; ++hi) {
+                                    const float2 pr = make_float2(__uint_as_float(v[4 * i + 2 * hi]), __uint_as_float(v[4 * i + 2 * hi + 1]));
+                                    float2& a = acc[((half * CH + ch) * 4 + i) * 2 + hi];
+                                    a = fma2(mul2(pr, sb2), sa2[hi], a);
+                                }
+                            }
                         }
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&sc_empty[q & 1u]);      // the scale warp may refill this buffer
             }
-            if (ok && row_ok) {
-                const int c0 = n0 + cgrp * F_CW;
+            if (ok) {
+                const int col0 = n0 + cgrp * F_CW;                  // first column of the warp
+                const int64_t row0 = int64_t(m0) + quarter * 32 + tq;
                 if (p.out_dtype == LH_F32) {
-                    float* out = static_cast<float*>(p.c) + row * p.N + c0;
-                    const bool vec = (p.N % 8) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 31) == 0;
+                    // four lanes hold 8 consecutive columns of a row: 32 contiguous bytes
+                    const bool vec = (p.N % 2) == 0;
 #pragma unroll
-                    for (int j4 = 0; j4 < F_CW / 8; ++j4) {          // 8 columns per step
-                        const int c = c0 + 8 * j4;
-                        if (vec && c + 8 <= p.N) {
-                            const float2 a0 = acc[4 * j4], a1 = acc[4 * j4 + 1], a2 = acc[4 * j4 + 2], a3 = acc[4 * j4 + 3];
-                            st_global_256(out + 8 * j4,
-                                          make_uint4(__float_as_uint(a0.x), __float_as_uint(a0.y), __float_as_uint(a1.x), __float_as_uint(a1.y)),
-                                          make_uint4(__float_as_uint(a2.x), __float_as_uint(a2.y), __float_as_uint(a3.x), __float_as_uint(a3.y)));
-                        } else {
+                    for (int half = 0; half < 2; ++half)
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                if (c + 2 * j < p.N) out[8 * j4 + 2 * j] = acc[4 * j4 + j].x;
-                                if (c + 2 * j + 1 < p.N) out[8 * j4 + 2 * j + 1] = acc[4 * j4 + j].y;
-                            }
+                        for (int hi = 0; hi < 2; ++hi) {
+                            const int64_t row = row0 + 16 * half + 8 * hi;
+                            if (row >= p.M) continue;
+                            float* out = static_cast<float*>(p.c) + row * p.N;
+#pragma unroll
+                            for (int ch = 0; ch < CH; ++ch)
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float2 a = acc[((half * CH + ch) * 4 + i) * 2 + hi];
+                                    const int c = col0 + 32 * ch + 8 * i + 2 * tc;
+                                    if (vec && c + 2 <= p.N) {
+                                        *reinterpret_cast<float2*>(out + c) = a;
+                                    } else {
+                                        if (c < p.N) out[c] = a.x;
+                                        if (c + 1 < p.N) out[c + 1] = a.y;
+                                    }
+                                }
                         }
-                    }
                 } else {
-                    uint16_t* out = static_cast<uint16_t*>(p.c) + row * p.N + c0;
-                    // a thread owns F_CW consecutive columns of its row: 32-byte stores fill whole sectors
-                    const bool vec = (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(p.c) & 31) == 0;
+                    // 16-bit output: the four lanes of a row exchange their words (a 4 x 4 transpose over the
+                    // 8-column groups) so that each lane stores 16 contiguous bytes, four lanes 64
+                    const bool vec = (p.N % 8) == 0;
 #pragma unroll
-                    for (int j16 = 0; j16 < F_CW / 16; ++j16) {      // 16 columns per step
-                        uint32_t w[8];
+                    for (int half = 0; half < 2; ++half)
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            const float2 a = acc[8 * j16 + j];
-                            if (p.out_dtype == LH_BF16) {
-                                w[j] = pack_bf16x2(a.x, a.y);
-                            } else {
-                                const __half2 h = __floats2half2_rn(a.x, a.y);
-                                w[j] = *reinterpret_cast<const uint32_t*>(&h);
+                        for (int hi = 0; hi < 2; ++hi) {
+                            const int64_t row = row0 + 16 * half + 8 * hi;
+                            uint16_t* out = static_cast<uint16_t*>(p.c) + row * p.N;
+#pragma unroll
+                            for (int ch = 0; ch < CH; ++ch) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float2 a = acc[((half * CH + ch) * 4 + i) * 2 + hi];
+                                    if (p.out_dtype == LH_BF16) {
+                                        w[i] = pack_bf16x2(a.x, a.y);
+                                    } else {
+                                        const __half2 h = __floats2half2_rn(a.x, a.y);
+                                        w[i] = *reinterpret_cast<const uint32_t*>(&h);
+                                    }
+                                }
+                                const int cbase = col0 + 32 * ch;
+                                if (vec && cbase + 32 <= p.N) {      // warp-uniform: every lane takes part in the shuffles
+                                    // w[i] of lane tc  ->  w[tc'] of lane i
+                                    {
+                                        const bool odd = (tc & 1) != 0;
+                                        const uint32_t x0 = odd ? w[0] : w[1], x1 = odd ? w[2] : w[3];
+                                        const uint32_t y0 = __shfl_xor_sync(0xffffffffu, x0, 1), y1 = __shfl_xor_sync(0xffffffffu, x1, 1);
+                                        if (odd) { w[0] = y0; w[2] = y1; } else { w[1] = y0; w[3] = y1; }
+                                    }
+                                    {
+                                        const bool up = (tc & 2) != 0;
+                                        const uint32_t x0 = up ? w[0] : w[2], x1 = up ? w[1] : w[3];
+                                        const uint32_t y0 = __shfl_xor_sync(0xffffffffu, x0, 2), y1 = __shfl_xor_sync(0xffffffffu, x1, 2);
+                                        if (up) { w[0] = y0; w[1] = y1; } else { w[2] = y0; w[3] = y1; }
+                                    }
+                                    if (row < p.M) *reinterpret_cast<uint4*>(out + cbase + 8 * tc) = make_uint4(w[0], w[1], w[2], w[3]);
+                                } else if (row < p.M) {
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        const int c = cbase + 8 * i + 2 * tc;
+                                        if (c < p.N) out[c] = uint16_t(w[i]);
+                                        if (c + 1 < p.N) out[c + 1] = uint16_t(w[i] >> 16);
+                                    }
+                                }
                             }
                         }
-                        const int c = c0 + 16 * j16;
-                        if (vec && c + 16 <= p.N) {
-                            st_global_256(out + 16 * j16, make_uint4(w[0], w[1], w[2], w[3]), make_uint4(w[4], w[5], w[6], w[7]));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; ++j)
-                                if (c + j < p.N) out[16 * j16 + j] = uint16_t(w[j >> 1] >> (16 * (j & 1)));
-                        }
-                    }
                 }
             }
         }
