@@ -7,19 +7,23 @@
 // Each k-block's partial product is an exact e4m3 x e4m3 contraction on the tensor cores
 // (tcgen05.mma kind::f8f6f4, float32 accumulator in tensor memory, started from zero per
 // block); the CUDA cores then fold it into float32 register accumulators with the two
-// scales.  Two 128 x 256 partial buffers fill the 512 tensor-memory columns, so the tensor
-// cores work on one block while the other is folded.
+// scales.  Four 128 x 128 partial buffers fill the 512 tensor-memory columns, so the tensor
+// cores run up to four blocks ahead of the fold.
 //
-// One persistent CTA per SM walks 128 x 256 tiles of C (column tile fastest).  Roles:
-//   warp 0      TMA producer (a: 128 x 128 bytes, b: 256 x 128 bytes per k-stage, 4 stages)
+// One persistent CTA per SM walks 128 x 128 tiles of C (column tile fastest).  Roles:
+//   warp 0      TMA producer (a and b: 128 rows x 128 bytes each per k-stage, 6 stages)
 //   warp 1      MMA issuer and owner of the tensor-memory allocation: four MMAs (k = 32 each) and ONE
 //               tcgen05.commit per block -- each tcgen05 instruction costs the issuing thread about a
-//               hundred cycles, so N = 256 and a single commit halve the issue time per flop
-//   warps 2-17  fold + store, a warp = 32 accumulator rows x 64 columns, read in the 16x256b fragment layout
+//               hundred cycles; the k-stage is handed back to the producer by a fold lane instead
+//   warps 2-17  fold + store, a warp = 32 accumulator rows x 32 columns, read in the 16x256b fragment
+//               layout (4 row scales + 8 column scales per thread and block instead of 1 + 32)
 //   warp 18     stages the scales of the next chunk of 8 k-blocks in shared memory
-// What bounds it: the hand-over of a partial buffer (MMA done -> fold warps read it out, four dependent
-// tensor-memory loads -> MMA thread sees it free -> issues) takes about 3000 cycles for two buffers, against
-// 512 cycles of tensor-core work per block; the probes that measured each leg are described in the design notes.
+// Waits are inline mbarrier polls by every lane of a role (a shuffle-and-vote around one polling lane,
+// or a call into a shared wait routine, adds its latency to every hand-over of a buffer).
+// The tile width is a compile-time constant (FN): 256 halves the MMA instructions per flop and cuts the
+// L2 -> shared-memory traffic by a quarter, but leaves two partial buffers and 64 accumulator registers
+// per fold thread; measured level with 128 at 8192^3 and behind it at 4096^3, where 512 tiles on 148 SMs
+// quantise badly.  At 128 the kernel moves 32 KB per block and SM through L2, about 9.5 TB/s in all.
 #include "lh_common.cuh"
 
 #include <type_traits>
@@ -28,9 +32,9 @@ namespace lh {
 
 namespace {
 
-constexpr int FM = 128, FN = 256, FKB = 128;   // tile; FKB = bytes (= e4m3 elements) of k per stage
-constexpr int FSTAGES = 4;
-constexpr int F_TILE = FM * FKB;               // a: 16 KB, then b: 32 KB
+constexpr int FM = 128, FN = 128, FKB = 128;   // tile; FKB = bytes (= e4m3 elements) of k per stage
+constexpr int FSTAGES = 6;
+constexpr int F_TILE = FM * FKB;               // a: 16 KB, then b: FN x 128 bytes
 constexpr int F_STAGE = F_TILE + FN * FKB;
 constexpr int F_BAR_OFF = FSTAGES * F_STAGE;
 constexpr int F_SC_OFF = F_BAR_OFF + 256;      // scales, two chunk buffers
@@ -305,25 +309,30 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (t == 64 && (gb % SUB) == SUB - 1) mbar_arrive(&empty[(gb / SUB) % FSTAGES]);
                     tc_fence_after();
                     const float* sbp = sb_s + bl * FN;
+                    // all of the warp's 32 x F_CW partial in flight at once, one wait: the hand-over of the buffer
+                    // back to the tensor cores is on the critical path, the registers are there (acc is F_CW floats)
+                    uint32_t v[2 * CH][16];
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+#pragma unroll
+                        for (int ch = 0; ch < CH; ++ch)
+                            tmem_ld_frag(tbase + (uint32_t(16 * half) << 16) + uint32_t(buf * FN + 32 * ch), v[half * CH + ch]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&part_empty[buf]);   // the tensor cores may overwrite this buffer
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         const float2 sa2[2] = {splat2(sa_s[(16 * half) * F_SA_LD + bl]), splat2(sa_s[(16 * half + 8) * F_SA_LD + bl])};
 #pragma unroll
                         for (int ch = 0; ch < CH; ++ch) {
-                            uint32_t v[16];
-                            tmem_ld_frag(tbase + (uint32_t(16 * half) << 16) + uint32_t(buf * FN + 32 * ch), v);
-                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            if (half == 1 && ch == CH - 1) {
-                                tc_fence_before();
-                                __syncwarp();
-                                if (lane == 0) mbar_arrive(&part_empty[buf]);   // the tensor cores may overwrite this buffer
-                            }
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
                                 const float2 sb2 = *reinterpret_cast<const float2*>(sbp + 32 * ch + 8 * i);
 #pragma unroll
                                 for (int hi = 0; hi < 2; ++hi) {
-                                    const float2 pr = make_float2(__uint_as_float(v[4 * i + 2 * hi]), __uint_as_float(v[4 * i + 2 * hi + 1]));
+                                    const uint32_t* vv = v[half * CH + ch];
+                                    const float2 pr = make_float2(__uint_as_float(vv[4 * i + 2 * hi]), __uint_as_float(vv[4 * i + 2 * hi + 1]));
                                     float2& a = acc[((half * CH + ch) * 4 + i) * 2 + hi];
                                     a = fma2(mul2(pr, sb2), sa2[hi], a);
                                 }

@@ -11,6 +11,7 @@ profiler captures of a single kernel are taken from.
   group_quant                        1x128 group quantiser
   norm_fwd / norm_bwd                plain RMSNorm forward / backward
   norm_bwd_quant                     RMSNorm backward fused with the dual-axis quantisation of dy
+  fp8_gemm                           blockwise-scaled FP8 GEMM, [rows, k] x [cols, k]^T with 1 x 128 scales (`--k`)
 `--tuning key=value` (repeatable) sets a dispatch option through lh_tuning() first, e.g.
 `--tuning rmsnorm_bwd_quant_two_role_min_n=128` to capture the two-role backward kernel.
 """
@@ -38,6 +39,7 @@ def main():
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--k", type=int, default=4096, help="contraction length of the fp8_gemm case")
     ap.add_argument("--tuning", action="append", default=[])
     a = ap.parse_args()
     torch.cuda.set_device(0)
@@ -79,6 +81,14 @@ def main():
         x, dy = bf16_randn((M, n), 1), bf16_randn((M, n), 2, 0.01)
         fn = (lambda: triton_rms_norm_backward(dy, x, gam)) if c == "norm_bwd" else \
              (lambda: rms_norm_backward_and_block_quant(dy, x, gam))
+    elif c == "fp8_gemm":
+        from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+        g = torch.Generator(device="cuda").manual_seed(5)
+        qa = torch.randn((M, a.k), device="cuda", generator=g).to(torch.float8_e4m3fn)
+        qb = torch.randn((n, a.k), device="cuda", generator=g).to(torch.float8_e4m3fn)
+        sa = torch.rand((M, a.k // 128), device="cuda", generator=g) + 0.1
+        sb = torch.rand((n, a.k // 128), device="cuda", generator=g) + 0.1
+        fn = lambda: triton_tt_fp8_gemm(qa, qb, sa, sb)
     else:
         raise SystemExit(f"unknown case {c}")
     keep = None
