@@ -336,7 +336,7 @@ int lh_batch_silu_smoothquant_bwd(const void* g, const void* x, const void* w, i
 /* Blockwise-scaled FP8 GEMM  c [M,N] = dequant(a) . dequant(b)^T.
  * Replaces triton_tt_fp8_gemm, linghe/gemm/blockwise_fp8_gemm.py:152.
  * a [M,K], b [N,K] e4m3 codes; one float32 scale per 1 x block_size run of k (block_size
- * 128 or 64; K a multiple of 128, at most 128 scale blocks).  Scales as the reference
+ * 128 or 64; K a multiple of 128, any number of scale blocks).  Scales as the reference
  * stores them, a_s [M, K/block] and b_s [N, K/block], or -- *_transposed != 0 -- as the
  * quantisers of this library write them, [K/block, M] and [K/block, N], so that
  * (q, s) of lh_blockwise_quant / lh_rmsnorm_blockquant_fwd feed it unchanged.

@@ -715,7 +715,8 @@ def test_golden_fp8_gemm(block):
                                             # widths the vector epilogues do not take (N % 8, odd N), a partial last
                                             # chunk of scales (10 k-blocks), several ragged tiles per persistent CTA
                                             (300, 100, 1280, 128, torch.bfloat16), (257, 77, 384, 128, torch.float32),
-                                            (5000, 3000, 768, 128, torch.bfloat16), (3000, 1500, 1024, 64, torch.float16)])
+                                            (5000, 3000, 768, 128, torch.bfloat16), (3000, 1500, 1024, 64, torch.float16),
+                                            (128, 256, 32768, 128, torch.float32)])     # 256 k-blocks: 32 chunks of scales
 def test_fp8_gemm(M, N, K, block, dt):
     from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
     g = torch.Generator().manual_seed(51)
