@@ -732,6 +732,30 @@ def test_fp8_gemm(M, N, K, block, dt):
     assert err <= (1e-5 if dt == torch.float32 else 5e-3)
 
 
+@pytest.mark.parametrize("dt,code", [(torch.bfloat16, 0), (torch.float32, 2)])
+def test_fp8_gemm_output_at_16_byte_offset(dt, code):
+    # through the C ABI with an output pointer that is 16- but not 32-byte aligned: the 32-byte
+    # store path must step aside, the result must not change
+    from linghe_b200 import _lib
+    from linghe_b200.gemm.blockwise_fp8_gemm import triton_tt_fp8_gemm
+    M, N, K = 256, 384, 512
+    g = torch.Generator().manual_seed(57)
+    a_q = _cuda(torch.randn((M, K), generator=g).to(torch.float8_e4m3fn))
+    b_q = _cuda(torch.randn((N, K), generator=g).to(torch.float8_e4m3fn))
+    a_s = _cuda(torch.rand((M, K // 128), generator=g) + 0.01)
+    b_s = _cuda(torch.rand((N, K // 128), generator=g) + 0.01)
+    want = triton_tt_fp8_gemm(a_q, b_q, a_s, b_s, out_dtype=dt)
+    shift = 16 // want.element_size()
+    flat = torch.zeros(M * N + shift, dtype=dt, device="cuda")
+    out = flat[shift:]
+    assert out.data_ptr() % 32 == 16
+    _lib.call("lh_fp8_gemm", a_q, _lib.ptr(a_q), _lib.ptr(b_q), _lib.ptr(a_s), _lib.ptr(b_s), out.data_ptr(), M, N, K,
+              128, 0, 0, code)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(M, N), want)
+    assert float(flat[:shift].abs().max()) == 0.0
+
+
 @pytest.mark.parametrize("block", [128, 64])
 def test_golden_bb_fp8_gemm(block):
     from linghe_b200.gemm.blockwise_fp8_gemm import triton_bb_fp8_gemm
