@@ -289,8 +289,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const int m0 = int(tile / tiles_n) * FM, n0 = int(tile % tiles_n) * FN;
             // The warp folds 32 accumulator rows x F_CW columns.  A thread owns rows tq + 16 half + 8 hi and,
             // per 8-column group i of each 32-column piece, the column pair 2 tc: 4 row scales and
-            // F_CW / 4 column scales per block instead of 1 and F_CW -- the shared-memory read bandwidth,
-            // which the tensor cores' operand fetches and the TMA writes also need, is what bounds the kernel.
+            // F_CW / 4 column scales per block instead of 1 and F_CW, a third of the shared-memory loads
+            // (the same data pipe feeds the tensor cores' operand reads and takes the TMA writes).
             float2 acc[2 * CH * 4 * 2];                             // [half][piece][i][hi]
 #pragma unroll
             for (int j = 0; j < 2 * CH * 4 * 2; ++j) acc[j] = make_float2(0.f, 0.f);
