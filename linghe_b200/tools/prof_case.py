@@ -7,7 +7,7 @@ profiler captures of a single kernel are taken from.
   norm_rows / norm_col / norm_both   RMSNorm + blockwise quant, output_mode 0 / 1 / 2
   swiglu_rows / swiglu_both          SwiGLU + blockwise quant, output_mode 0 / 2
   swiglu_bwd                         SwiGLU backward + dual quant (+ bf16 dx)
-  quant_rows / quant_both            pure blockwise quantiser, output_mode 0 / 2
+  quant_rows / quant_col / quant_both  pure blockwise quantiser, output_mode 0 / 1 / 2
   group_quant                        1x128 group quantiser
   norm_fwd / norm_bwd                plain RMSNorm forward / backward
   norm_bwd_quant                     RMSNorm backward fused with the dual-axis quantisation of dy
@@ -68,9 +68,9 @@ def main():
     elif c == "swiglu_bwd":
         x, g = bf16_randn((M, 2 * n), 1), bf16_randn((M, n), 2, 0.01)
         fn = lambda: triton_silu_and_block_quant_backward(g, x, return_bf16=True)
-    elif c in ("quant_rows", "quant_both"):
+    elif c in ("quant_rows", "quant_col", "quant_both"):
         x = bf16_randn((M, n), 2, 0.01)
-        fn = lambda: triton_blockwise_quant(x, output_mode=0 if c == "quant_rows" else 2)
+        fn = lambda: triton_blockwise_quant(x, output_mode={"quant_rows": 0, "quant_col": 1, "quant_both": 2}[c])
     elif c == "group_quant":
         x = bf16_randn((M, n), 2)
         fn = lambda: triton_group_quant(x)
