@@ -195,7 +195,7 @@ int lh_rmsnorm_bwd(const void* dy, const void* x, const void* gamma, const float
  *     reads), but two calls whose kernels overlap on the GPU -- different streams, or
  *     different host threads on different streams -- race on it: serialise them.
  * Arguments as lh_rmsnorm_bwd without the scratch pair.  dx and dgamma agree with
- * lh_rmsnorm_bwd to within float32 summation order: for n <= 2048 on a 148-SM device both
+ * lh_rmsnorm_bwd to within float32 summation order: for n < 1536 on a 148-SM device both
  * run the same kernel on the same grid and the results are bit-identical; for wider rows
  * lh_rmsnorm_bwd takes a different kernel, so the last bits of dgamma (and, through the
  * row sums, of a few dx values) may differ. */

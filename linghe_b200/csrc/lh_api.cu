@@ -22,6 +22,7 @@ static int g_band_kernel = 1;
 static int g_band_bwd = 0;
 static int g_second_descends = 1;   // second launch of a two-launch path walks the row bands last to first
 static int g_bwd_two_role_min_n = 1 << 30;
+extern int g_bwd_stream_min_n;   // lh_rows.cu
 static bool use_band_kernel(int64_t n) { return g_band_kernel == 2 || (g_band_kernel == 1 && n < 6144); }
 
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int code) {
@@ -250,6 +251,7 @@ int lh_device_status(int* status) {
 int lh_tuning(const char* key, int value) {
     if (key && !strcmp(key, "rmsnorm_both_single_pass")) { const int old = g_band_kernel; g_band_kernel = value; return old; }
     if (key && !strcmp(key, "rmsnorm_bwd_quant_single_pass")) { const int old = g_band_bwd; g_band_bwd = value; return old; }
+    if (key && !strcmp(key, "rmsnorm_bwd_stream_min_n")) { const int old = g_bwd_stream_min_n; g_bwd_stream_min_n = value; return old; }
     if (key && !strcmp(key, "rmsnorm_bwd_quant_two_role_min_n")) { const int old = g_bwd_two_role_min_n; g_bwd_two_role_min_n = value; return old; }
     if (key && !strcmp(key, "second_launch_descends")) { const int old = g_second_descends; g_second_descends = value; return old; }
     if (key && !strcmp(key, "band_cluster")) { const int old = g_band_cluster; g_band_cluster = value; return old; }

@@ -743,6 +743,10 @@ int rows_norm_y(const void* x, const void* gamma, int dtype, int64_t M, int64_t 
 
 int64_t rows_norm_bwd_scratch(int64_t n) { return int64_t(kMaxRowCtas) * n * 4; }
 
+// narrowest row that takes the streaming register kernel instead of the TMA ring (lh_tuning "rmsnorm_bwd_stream_min_n"):
+// streaming / ring at 65536 rows: 1024 columns 107.5 / 83.3 us, 1536 119.5 / 133.3, 2048 135.1 / 160.3
+int g_bwd_stream_min_n = 1536;
+
 // dy_q / dy_s (optional): where the streaming kernel runs it also writes the row-wise 1x128 codes
 // and scales ([n/128, M]) of dy and sets *dy_rows_done = 1; with dy_qt / dy_st as well (and M a
 // multiple of 16) also the transposed 128x1 copy, *dy_rows_done = 2.  Otherwise they are left
@@ -767,12 +771,11 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     p.rms = const_cast<float*>(rms); p.reuse_rms = rms != nullptr; p.eps = eps; p.M = M; p.n = int(n);
     p.hp = static_cast<uint8_t*>(dx); p.partial = static_cast<float*>(scratch);
     int grid = 0;
-    // Rows wider than 2048 take the streaming register kernel (77 vs 83 us at 16384 x 4096, 279 vs
-    // 301 us at 65536 x 4096, 354 vs 370 us at 32768 x 8192), narrower ones the TMA ring (159 vs
-    // 174 us at 65536 x 2048).
+    // Rows of 1536 columns and more take the streaming register kernel (67.7 vs 83 us at 16384 x 4096,
+    // 268.8 vs 301 us at 65536 x 4096, 254.6 vs 370 us at 32768 x 8192), narrower ones the TMA ring.
     const bool qdy = dy_q != nullptr && dy_s != nullptr && aligned16(dy_q) && dy_rows_done != nullptr;
     const bool colq = qdy && dy_qt != nullptr && dy_st != nullptr && aligned16(dy_qt) && (M % 16) == 0 && n >= two_role_min_n;
-    if (n > 2048 || colq) {
+    if (n >= g_bwd_stream_min_n || colq) {
         int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, qdy ? dy_q : nullptr,
                                 dy_s, round_scale, stream, colq ? dy_qt : nullptr, dy_st);
         bool cols_done = colq;
