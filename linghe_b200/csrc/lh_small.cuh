@@ -230,9 +230,12 @@ __device__ __forceinline__ void norm_bwd_walk(const SmallParams& p, const uint8_
         for (int i = 0; i < 2 * SPANS; ++i) { xc[i] = xr[i]; gc[i] = gr[i]; }
         fetch(row + gridDim.x);
         if constexpr (L2PF) {
-            // the row after next: pulled into L2 now, so that its register loads (issued one row from now)
-            // find it there; a thread covers 32 bytes per span, every fourth thread asks for the 128-byte line
-            const int64_t prow = row + 2 * int64_t(gridDim.x);
+            // a row two or three ahead: pulled into L2 now, so that its register loads find it there; a thread covers 32 bytes per span, every fourth thread asks for the 128-byte line
+            // distance in rows of this CTA: 3 measured best for one span per thread and for 256 threads (65536 x 2048:
+            // 123 vs 135 us at distance 2; 32768 x 8192: 234 vs 255 us), 2 for two spans of 128 threads (16384 x 4096:
+            // 67.7 vs 70.1 us at distance 3)
+            constexpr int AHEAD = (SPANS == 2 && NT == 128) ? 2 : 3;
+            const int64_t prow = row + AHEAD * int64_t(gridDim.x);
             if (prow < p.M && (t & 3) == 0) {
 #pragma unroll
                 for (int i = 0; i < SPANS; ++i) {
