@@ -775,7 +775,9 @@ int rows_norm_bwd(const void* dy, const void* x, const void* gamma, const float*
     // 268.8 vs 301 us at 65536 x 4096, 254.6 vs 370 us at 32768 x 8192), narrower ones the TMA ring.
     const bool qdy = dy_q != nullptr && dy_s != nullptr && aligned16(dy_q) && dy_rows_done != nullptr;
     const bool colq = qdy && dy_qt != nullptr && dy_st != nullptr && aligned16(dy_qt) && (M % 16) == 0 && n >= two_role_min_n;
-    if (n >= g_bwd_stream_min_n || colq) {
+    // the fused call (row codes of dy wanted) keeps the ring up to 2048 columns: there the streaming kernel runs
+    // without the prefetch and the two paths measure level (65536 x 1536: 237.7 vs 218.2 us for the ring)
+    if ((qdy ? n > 2048 : n >= g_bwd_stream_min_n) || colq) {
         int rc = small_norm_bwd(dy, x, gamma, rms, M, n, eps, dx, p.partial, kMaxRowCtas, &grid, qdy ? dy_q : nullptr,
                                 dy_s, round_scale, stream, colq ? dy_qt : nullptr, dy_st);
         bool cols_done = colq;
