@@ -90,7 +90,9 @@ int lh_selftest_wait_timeout(int polls, void* stream);
  *                                transposed copy tile by tile beside the walk (default: never)
  *   "second_launch_descends"     1 (default) = the second launch of a two-launch path walks the row
  *                                bands last to first, starting with what the first left in L2
- *   "band_cluster"               cluster size of the single-pass kernels: 0 = chosen per shape, else 1 / 2 / 4 / 8 */
+ *   "band_cluster"               cluster size of the single-pass kernels: 0 = chosen per shape, else 1 / 2 / 4 / 8
+ *   "rmsnorm_bwd_stream_min_n"   lh_rmsnorm_bwd: rows at least this wide take the streaming register kernel,
+ *                                narrower ones the TMA ring (default 1536) */
 int lh_tuning(const char* key, int value);
 
 /* Scratch bytes needed by the entry point named `what` ("rmsnorm_bwd",
