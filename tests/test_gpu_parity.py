@@ -240,8 +240,8 @@ def test_rms_block_quant_modes(M, n):
     check_fused(qt, rqt, st, rst, "pow2 col", True)
 
 
-# n > 2048 takes the streaming backward kernel (two spans per thread; 2304 and 5120 leave the
-# second span partly empty), narrower rows the ring kernel
+# n >= 1536 takes the streaming backward kernel (one span per thread up to 2048 columns, two above;
+# 2304 and 5120 leave the second span partly empty), narrower rows the ring kernel
 @pytest.mark.parametrize("M,n", [(1000, 1536), (512, 2048), (4096, 4096), (130, 8192), (96, 256), (778, 2304),
                                  (2000, 5120)])
 def test_rms_fwd_bwd(M, n):
@@ -264,6 +264,28 @@ def test_rms_fwd_bwd(M, n):
     # 3-D input as the facade passes it
     dx3, dw3 = triton_rms_norm_backward(dyd.view(2, M // 2, n), xd.view(2, M // 2, n), gd)
     assert dx3.shape == (2, M // 2, n) and torch.equal(dx3.view(M, n), dx)
+
+
+# the two backward kernels at the same width (the crossover is a tuning value): both against the oracle,
+# dx of the two identical up to the last bf16 bit of a few elements (different summation order of the row sums)
+@pytest.mark.parametrize("M,n", [(1000, 1536), (777, 2048), (640, 1024), (2000, 1792)])
+def test_rms_bwd_ring_and_streaming_kernels(M, n):
+    from linghe_b200.utils.norm import triton_rms_norm_backward
+    x = randn_bf16((M, n), 21)
+    g = (1 + 0.1 * torch.randn(n, generator=torch.Generator().manual_seed(22))).to(torch.bfloat16)
+    dy = randn_bf16((M, n), 23, 1, 0.01)
+    xd, gd, dyd = _cuda(x), _cuda(g), _cuda(dy)
+    rdx, rdw = O.rms_norm_backward(x, g, dy)
+    got = {}
+    for name, min_n in (("streaming", 1), ("ring", 1 << 30)):
+        with tuning("rmsnorm_bwd_stream_min_n", min_n):
+            dx, dw = triton_rms_norm_backward(dyd, xd, gd)
+            torch.cuda.synchronize()
+        assert_rel_close(dx, rdx, f"dx {name}", 1e-2)
+        assert_rel_close(dw, rdw, f"dgamma {name}", 1e-3, 1e-5)
+        got[name] = (dx, dw)
+    differ = (got["ring"][0] != got["streaming"][0]).float().mean().item()
+    assert differ < 1e-2, f"{differ:.2e} of dx differs between the two kernels"
 
 
 def test_golden_rms_fwd_bwd():
